@@ -1,0 +1,171 @@
+// Shared device/host helpers of the rasterizer kernels (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "adop/adop_math.h"
+#include "adop/adop_raster.h"
+
+namespace adop {
+
+constexpr int kBlock = 256;  // threads per block of the point kernels (one point per thread and iteration)
+
+// thread-local text of the last CUDA error, returned by adop_last_error()
+char* last_error_buffer();
+adop_status record_cuda_error(cudaError_t e, const char* what);
+
+#define ADOP_CUDA_TRY(expr)                                                     \
+    do {                                                                        \
+        cudaError_t _e = (expr);                                                \
+        if (_e != cudaSuccess) return ::adop::record_cuda_error(_e, #expr);     \
+    } while (0)
+
+// Everything a kernel needs to know about the pyramid of ONE view: sizes and the view's slice of every
+// per-layer tensor (pointers already advanced to batch entry b).
+struct LayerTable
+{
+    int L;
+    int w[kMaxLayers], h[kMaxLayers];
+    unsigned rec_off[kMaxLayers + 1];  // first accumulator record (= pixel) of each layer; [L] = total
+    float* depth[kMaxLayers];
+    float* weight[kMaxLayers];
+    float* color[kMaxLayers];   // [C,h,w] of this view
+    float* mask[kMaxLayers];    // may be null
+    const float* grad[kMaxLayers];  // upstream gradient [C,h,w] of this view (backward only)
+};
+
+struct PointStreams
+{
+    const float4* position;
+    const int32_t* normal;  // may be null
+    const int32_t* index;   // may be null (identity)
+    int n;
+};
+
+// the handful of RenderParams fields the kernels read (Settings.h:16-52)
+struct KernelParams
+{
+    float depth_accept_plus_one;  // formed once in float like PointRenderer.cu:380
+    float dropout;
+    uint32_t dropout_seed;
+    float drop_out_radius_threshold;
+    float dist_cutoff;
+    float K_gradient_factor, distortion_gradient_factor;
+    float mask_background_value;
+    int drop_out_points_by_radius;
+    int check_normal;
+    int ghost_gradients;
+    int test_backward_mode;
+    int batch_slot;               // b: index of the view inside the batch (drop-out stream id)
+    const uint8_t* dropout_mask;  // already advanced to view b, or null
+};
+
+inline KernelParams make_kernel_params(const adop_render_params* rp, const uint8_t* dropout_mask, int n_points, int b)
+{
+    KernelParams k;
+    k.depth_accept_plus_one = rp->depth_accept + 1.0f;
+    k.dropout = rp->dropout;
+    k.dropout_seed = rp->dropout_seed;
+    k.drop_out_radius_threshold = rp->drop_out_radius_threshold;
+    k.dist_cutoff = rp->dist_cutoff;
+    k.K_gradient_factor = rp->K_gradient_factor;
+    k.distortion_gradient_factor = rp->distortion_gradient_factor;
+    k.mask_background_value = rp->output_background_mask_value;
+    k.drop_out_points_by_radius = rp->drop_out_points_by_radius;
+    k.check_normal = rp->check_normal;
+    k.ghost_gradients = rp->ghost_gradients;
+    k.test_backward_mode = rp->test_backward_mode;
+    k.batch_slot = b;
+    k.dropout_mask = dropout_mask ? dropout_mask + (size_t)b * n_points : nullptr;
+    return k;
+}
+
+// floats per accumulator record: C colour sums, the weight, padded to whole 16-byte vectors so that one
+// splat is one or two vector atomics into a single 32-byte sector (for C <= 7)
+__host__ __device__ inline int record_floats(int C) { return ((C + 1) + 3) & ~3; }
+
+inline void fill_layer_dims(int w, int h, int L, LayerTable* lt)
+{
+    lt->L = L;
+    unsigned off = 0;
+    for (int l = 0; l < kMaxLayers; ++l)
+    {
+        if (l < L)
+        {
+            lt->w[l] = w; lt->h[l] = h;
+            lt->rec_off[l] = off;
+            off += (unsigned)w * (unsigned)h;
+            w /= 2; h /= 2;  // PointRenderer.cu:1015-1016
+        }
+        else
+        {
+            lt->w[l] = 0; lt->h[l] = 0; lt->rec_off[l] = off;
+        }
+        lt->depth[l] = lt->weight[l] = lt->color[l] = lt->mask[l] = nullptr;
+        lt->grad[l] = nullptr;
+    }
+    lt->rec_off[kMaxLayers] = off;
+    for (int l = L; l <= kMaxLayers; ++l) lt->rec_off[l] = off;
+}
+
+// Where one view's camera comes from: rows of the pose / intrinsics tensors (device memory, they are
+// trainable parameters) plus the ReducedImageInfo fields. Kernels gather it into shared memory once per block.
+struct CamSource
+{
+    const double* poses;
+    const float* intrinsics;
+    int intrinsics_cols;
+    int image_index, camera_index, camera_model;
+    float crop[5];
+    int w0;
+};
+inline CamSource make_cam_source(const adop_scene* s, const adop_view* v)
+{
+    CamSource c;
+    c.poses = s->poses; c.intrinsics = s->intrinsics; c.intrinsics_cols = s->intrinsics_cols;
+    c.image_index = v->image_index; c.camera_index = v->camera_index; c.camera_model = v->camera_model;
+    for (int i = 0; i < 5; ++i) c.crop[i] = v->crop[i];
+    c.w0 = v->w;
+    return c;
+}
+
+adop_status validate_common(const adop_scene* s, const adop_view* views, int B, const adop_render_params* rp, int L);
+int sm_count();
+
+#if defined(__CUDACC__)
+struct FetchedPoint { V3 p; V3 n; float r; bool has_normal; };
+
+// DevicePointCloud::GetPoint (NeuralPointCloudCuda.h:82-103): one 128-bit load of xyz + radius
+__device__ __forceinline__ FetchedPoint fetch_point(const PointStreams& s, int i)
+{
+    FetchedPoint f;
+    float4 q = __ldg(s.position + i);
+    f.p.x = q.x; f.p.y = q.y; f.p.z = q.z; f.r = q.w;
+    f.has_normal = s.normal != nullptr;
+    if (f.has_normal) f.n = unpack_normal_10bit(__ldg(s.normal + i));
+    else { f.n.x = 0.f; f.n.y = 0.f; f.n.z = 0.f; }
+    return f;
+}
+// every thread of the block must call this (it synchronises)
+__device__ __forceinline__ void load_cam_shared(ViewCam* sh, const CamSource& src)
+{
+    if (threadIdx.x == 0)
+        *sh = load_view_cam(src.poses, src.intrinsics, src.intrinsics_cols, src.image_index, src.camera_index,
+                            src.camera_model, src.crop, src.w0);
+    __syncthreads();
+}
+__device__ __forceinline__ bool point_dropped(const KernelParams& kp, int i)
+{
+    if (kp.dropout_mask) return kp.dropout_mask[i] == 1;
+    return dropout_decision(kp.dropout, kp.dropout_seed, (uint32_t)kp.batch_slot, (uint32_t)i);
+}
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+#endif
+
+}  // namespace adop

@@ -1,0 +1,449 @@
+// Backward pass of the one-pixel point rasterizer for sm_100a.
+// Stands in for BlendPointCloudBackward and its kernels (darglein/ADOP src/lib/rendering/PointRenderer.cu:
+// CombineAndFillBackward :851-900, RenderBackward :396-724, NormalizeGradient :1534-1547) and the gradient
+// of the environment-map composite (RenderModule.cpp:121-125, grid_sample backward).
+//
+// Differences in how the same sums are formed (results agree within float-ordering tolerance):
+//  * one thread owns one point of one view: its descriptor gradient is summed over the layers in registers
+//    and leaves as C atomics per point, not C per (point, layer);
+//  * the point gradient and its counter leave as ONE 16-byte vector atomic (x, y, z, count);
+//  * pose and intrinsics gradients, which the reference adds with 7 + 14 same-address atomics per splat,
+//    are reduced warp -> block in shared memory and leave as one atomic per component and block.
+#include "common.cuh"
+
+namespace adop {
+
+// ------------------------------------------------------------------------------------------------------
+// K4: gradient of the background colour (sum of the upstream gradient over uncovered pixels) and, with the
+// fused composite, of the environment map (bilinear scatter).
+template <int C>
+__global__ void __launch_bounds__(kBlock) k_background_backward(LayerTable lt, CamSource cs, KernelParams kp,
+                                                                 float* __restrict__ grad_background,
+                                                                 float* __restrict__ grad_env, int env_h, int env_w)
+{
+    __shared__ ViewCam cam;
+    __shared__ float s_bg[C];
+    load_cam_shared(&cam, cs);
+    if (threadIdx.x < C) s_bg[threadIdx.x] = 0.f;
+    __syncthreads();
+    const unsigned total = lt.rec_off[kMaxLayers];
+    float g[C];
+#pragma unroll
+    for (int c = 0; c < C; ++c) g[c] = 0.f;
+    for (unsigned r = blockIdx.x * blockDim.x + threadIdx.x; r < total; r += gridDim.x * blockDim.x)
+    {
+        int l = 0;
+#pragma unroll
+        for (int k = 1; k < kMaxLayers; ++k)
+            if (k < lt.L && r >= lt.rec_off[k]) l = k;
+        const unsigned pix = r - lt.rec_off[l];
+        if (__ldg(lt.weight[l] + pix) != 0.f) continue;
+        const int w = lt.w[l], h = lt.h[l];
+        const size_t plane = (size_t)w * h;
+        float gl[C];
+#pragma unroll
+        for (int c = 0; c < C; ++c) { gl[c] = __ldg(lt.grad[l] + c * plane + pix); g[c] += gl[c]; }
+        if (grad_env)
+        {
+            int gy = pix / w, gx = pix - gy * w;
+            Intr5 crop_l = scale_intr(cam.crop, __int_as_float((127 - l) << 23));
+            V2 uv = env_uv_for_pixel(gx, gy, cam.V, cam.K, cam.dist, crop_l);
+            BilinearTap tp = bilinear_taps(uv, env_w, env_h);
+            const float om = 1.0f - kp.mask_background_value;
+            const float w00 = (1.0f - tp.wx) * (1.0f - tp.wy), w01 = tp.wx * (1.0f - tp.wy);
+            const float w10 = (1.0f - tp.wx) * tp.wy, w11 = tp.wx * tp.wy;
+#pragma unroll
+            for (int c = 0; c < C; ++c)
+            {
+                float* e = grad_env + (size_t)c * env_h * env_w;
+                float ge = om * gl[c];
+                atomicAdd(e + (size_t)tp.y0 * env_w + tp.x0, ge * w00);
+                atomicAdd(e + (size_t)tp.y0 * env_w + tp.x1, ge * w01);
+                atomicAdd(e + (size_t)tp.y1 * env_w + tp.x0, ge * w10);
+                atomicAdd(e + (size_t)tp.y1 * env_w + tp.x1, ge * w11);
+            }
+        }
+    }
+    if (grad_background)
+    {
+#pragma unroll
+        for (int c = 0; c < C; ++c)
+        {
+            float v = warp_sum(g[c]);
+            if ((threadIdx.x & 31) == 0 && v != 0.f) atomicAdd(&s_bg[c], v);
+        }
+        __syncthreads();
+        if (threadIdx.x < C && s_bg[threadIdx.x] != 0.f) atomicAdd(grad_background + threadIdx.x, s_bg[threadIdx.x]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// K5: per-point backward.
+struct BackwardTargets
+{
+    const float* texture;
+    int num_texels;
+    const float* background;
+    float* grad_texture;
+    float4* grad_points;
+    double* grad_pose;        // row of this view's image, 6 doubles
+    float* count_pose;        // element of this view's image
+    float* grad_intrinsics;   // row of this view's camera
+    float* count_intrinsics;  // element of this view's camera
+};
+
+template <int C, int MODEL>
+__global__ void __launch_bounds__(kBlock) k_splat_backward(PointStreams pts, CamSource cs, KernelParams kp, LayerTable lt,
+                                                            BackwardTargets bt)
+{
+    constexpr int NI = MODEL == kPinholeDistortion ? 13 : 5;
+    __shared__ ViewCam cam;
+    __shared__ double s_pose[6];
+    __shared__ float s_intr[NI];
+    __shared__ float s_cnt[2];
+    __shared__ int s_any;
+    load_cam_shared(&cam, cs);
+    if (threadIdx.x < 6) s_pose[threadIdx.x] = 0.0;
+    if (threadIdx.x < NI) s_intr[threadIdx.x] = 0.f;
+    if (threadIdx.x < 2) s_cnt[threadIdx.x] = 0.f;
+    if (threadIdx.x == 0) s_any = 0;
+    __syncthreads();
+
+    const bool want_geo = bt.grad_points || bt.grad_pose || bt.grad_intrinsics;
+    float a_pose[6], a_intr[NI], a_cnt = 0.f;
+#pragma unroll
+    for (int k = 0; k < 6; ++k) a_pose[k] = 0.f;
+#pragma unroll
+    for (int k = 0; k < NI; ++k) a_intr[k] = 0.f;
+
+    const int stride = gridDim.x * blockDim.x;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < pts.n; i += stride)
+    {
+        const bool drop_out = point_dropped(kp, i);
+        FetchedPoint f = fetch_point(pts, i);
+        RasterPoint q;
+        if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, kp.check_normal != 0, kp.dist_cutoff, &q)) continue;
+        float x = q.x, y = q.y, rad = q.radius_px, scale = 1.f;
+        const bool point_grad = want_geo && ((kp.ghost_gradients && drop_out) || (!kp.ghost_gradients && !drop_out));
+        int ti = -1;
+        float T_p[C], dg[C];
+        bool have_t = false, have_dg = false;
+        float gp[3] = {0.f, 0.f, 0.f};
+        float np = 0.f;
+#pragma unroll
+        for (int c = 0; c < C; ++c) dg[c] = 0.f;
+
+#pragma unroll 1
+        for (int l = 0; l < lt.L; ++l, scale *= 0.5f, rad *= 0.5f, x *= 0.5f, y *= 0.5f)
+        {
+            if (kp.drop_out_points_by_radius && rad < kp.drop_out_radius_threshold) continue;
+            const int px = round_half_even(x), py = round_half_even(y);
+            const int w = lt.w[l], h = lt.h[l];
+            if (px < 0 || py < 0 || px >= w || py >= h) continue;
+            const size_t plane = (size_t)w * h;
+            const size_t pix = (size_t)py * w + px;
+            const float* __restrict__ D = lt.depth[l];
+            const float* __restrict__ W = lt.weight[l];
+            const float* __restrict__ I = lt.color[l];
+            const float* __restrict__ G = lt.grad[l];
+            if (q.z > __ldg(D + pix) * kp.depth_accept_plus_one) break;
+            const float wgt = __ldg(W + pix);
+            if (!drop_out)
+            {
+                if (wgt == 0.f) continue;
+                if (bt.grad_texture)
+                {
+                    const float iw = 1.f / wgt;
+#pragma unroll
+                    for (int c = 0; c < C; ++c) dg[c] += iw * __ldg(G + c * plane + pix);
+                    have_dg = true;
+                }
+            }
+            int edge = min(min(px, py), min(w - 1 - px, h - 1 - py));
+            if (!(point_grad && edge > 2)) continue;
+
+            if (!have_t)
+            {
+                ti = pts.index ? __ldg(pts.index + i) : i;
+#pragma unroll
+                for (int c = 0; c < C; ++c) T_p[c] = __ldg(bt.texture + (size_t)c * bt.num_texels + ti);
+                have_t = true;
+            }
+            const size_t nb[4] = {pix - 1, pix + 1, pix - (size_t)w, pix + (size_t)w};
+            float Wn[4], Dn[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) Wn[k] = __ldg(W + nb[k]);
+            if (kp.test_backward_mode == 4)
+            {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) Dn[k] = __ldg(D + nb[k]);
+            }
+            float dRx = 0.f, dRy = 0.f;
+#pragma unroll
+            for (int c = 0; c < C; ++c)
+            {
+                const float bgc = __ldg(bt.background + c);
+                float dR[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                {
+                    float I_x = Wn[k] > 0.f ? __ldg(I + c * plane + nb[k]) : bgc;
+                    float G_x = __ldg(G + c * plane + nb[k]);
+                    float dI;
+                    if (kp.test_backward_mode == 4)
+                    {
+                        if (Wn[k] == 0.f || q.z * kp.depth_accept_plus_one < Dn[k]) dI = T_p[c] - I_x;
+                        else if (q.z > Dn[k] * kp.depth_accept_plus_one) dI = 0.f;
+                        else dI = (Wn[k] / (Wn[k] + 1.f) * I_x + 1.f / (Wn[k] + 1.f) * T_p[c] - I_x);
+                    }
+                    else
+                        dI = T_p[c] - I_x;
+                    dR[k] = dI * G_x;
+                }
+                dRx += 0.5f * (-dR[0] + dR[1]);
+                dRy += 0.5f * (-dR[2] + dR[3]);
+            }
+            V2 g; g.x = dRx / (float)C; g.y = dRy / (float)C;
+            Intr5 crop_l = scale_intr(cam.crop, scale);
+            if (MODEL == kPinholeDistortion)
+            {
+                GradPinhole o;
+                if (!project_pinhole_backward(f.p, f.n, f.has_normal, g, cam.V, cam.K, crop_l, cam.dist, kp.check_normal != 0,
+                                              kp.dist_cutoff, &o))
+                    continue;
+                gp[0] += o.g_point[0]; gp[1] += o.g_point[1]; gp[2] += o.g_point[2]; np += 1.f;
+#pragma unroll
+                for (int k = 0; k < 6; ++k) a_pose[k] += o.g_pose[k];
+                // damping of PointRenderer.cu:647-678
+                const float kf = kp.K_gradient_factor, df = kp.distortion_gradient_factor;
+                a_intr[0] += kf * o.g_k[0]; a_intr[1] += kf * o.g_k[1]; a_intr[2] += kf * o.g_k[2]; a_intr[3] += kf * o.g_k[3];
+                a_intr[5] += df * o.g_dis[0]; a_intr[6] += df * o.g_dis[1];
+                a_intr[7] += df * (o.g_dis[2] * 0.25f);
+                a_intr[8] += df * (o.g_dis[3] * 0.1f); a_intr[9] += df * (o.g_dis[4] * 0.1f); a_intr[10] += df * (o.g_dis[5] * 0.1f);
+                a_intr[11] += df * (o.g_dis[6] * 0.1f); a_intr[12] += df * (o.g_dis[7] * 0.1f);
+            }
+            else
+            {
+                GradOcam o;
+                if (!project_ocam_backward(f.p, f.n, f.has_normal, g, cam.V, crop_l, cam.ocam, kp.check_normal != 0,
+                                           kp.dist_cutoff, &o))
+                    continue;
+                gp[0] += o.g_point[0]; gp[1] += o.g_point[1]; gp[2] += o.g_point[2]; np += 1.f;
+#pragma unroll
+                for (int k = 0; k < 6; ++k) a_pose[k] += o.g_pose[k];
+#pragma unroll
+                for (int k = 0; k < 5; ++k) a_intr[k] += o.g_affine[k];
+            }
+            a_cnt += 1.f;
+        }
+
+        if (have_dg)
+        {
+            if (ti < 0) ti = pts.index ? __ldg(pts.index + i) : i;
+#pragma unroll
+            for (int c = 0; c < C; ++c) atomicAdd(bt.grad_texture + (size_t)c * bt.num_texels + ti, dg[c]);
+        }
+        if (np > 0.f && bt.grad_points) atomicAdd(bt.grad_points + i, make_float4(gp[0], gp[1], gp[2], np));
+    }
+
+    // block reduction of the per-view pose / intrinsics sums
+    if (!(bt.grad_pose || bt.grad_intrinsics)) return;
+    const unsigned any = __ballot_sync(0xffffffffu, a_cnt > 0.f);
+    if (any)
+    {
+        const bool lane0 = (threadIdx.x & 31) == 0;
+        if (bt.grad_pose)
+        {
+#pragma unroll
+            for (int k = 0; k < 6; ++k)
+            {
+                float v = warp_sum(a_pose[k]);
+                if (lane0) atomicAdd(&s_pose[k], (double)v);
+            }
+        }
+        if (bt.grad_intrinsics)
+        {
+#pragma unroll
+            for (int k = 0; k < NI; ++k)
+            {
+                float v = warp_sum(a_intr[k]);
+                if (lane0) atomicAdd(&s_intr[k], v);
+            }
+        }
+        float c = warp_sum(a_cnt);
+        if (lane0) { atomicAdd(&s_cnt[0], c); s_any = 1; }
+    }
+    __syncthreads();
+    if (!s_any) return;
+    if (bt.grad_pose)
+    {
+        if (threadIdx.x < 6) atomicAdd(bt.grad_pose + threadIdx.x, s_pose[threadIdx.x]);
+        if (threadIdx.x == 6) atomicAdd(bt.count_pose, s_cnt[0]);
+    }
+    if (bt.grad_intrinsics)
+    {
+        if (threadIdx.x >= 32 && threadIdx.x < 32 + NI) atomicAdd(bt.grad_intrinsics + (threadIdx.x - 32), s_intr[threadIdx.x - 32]);
+        // the reference counts 1/1024 per pinhole contribution and 1 per OCam contribution (:680-681, :718)
+        if (threadIdx.x == 64) atomicAdd(bt.count_intrinsics, MODEL == kPinholeDistortion ? s_cnt[0] * (1.f / 1024.f) : s_cnt[0]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// NormalizeGradient, PointRenderer.cu:1534-1547
+__global__ void k_normalize_points(float4* g, int n)
+{
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float4 v = g[i];
+    if (v.w > 0.f) { v.x = v.x / v.w; v.y = v.y / v.w; v.z = v.z / v.w; }
+    v.w = 0.f;
+    g[i] = v;
+}
+__global__ void k_normalize_pose(double* g, const float* cnt, int n)
+{
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n * 6) return;
+    float c = cnt[i / 6];
+    if (c > 0.f) g[i] = g[i] / (double)c;
+}
+__global__ void k_normalize_intrinsics(float* g, const float* cnt, int n, int cols)
+{
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n * cols) return;
+    float c = cnt[i / cols];
+    if (c > 0.f) g[i] = g[i] / c;
+}
+
+// ------------------------------------------------------------------------------------------------------
+template <int C>
+static adop_status launch_view_backward(const PointStreams& pts, const CamSource& cam, const KernelParams& kp, const LayerTable& lt,
+                                        const BackwardTargets& bt, float* grad_background, float* grad_env, int env_h, int env_w,
+                                        cudaStream_t st, int grid_points, int model)
+{
+    if (grad_background || grad_env)
+    {
+        unsigned total = lt.rec_off[kMaxLayers];
+        int grid_px = (int)((total + kBlock - 1) / kBlock);
+        int cap = sm_count() * 8;
+        if (grid_px > cap) grid_px = cap;
+        k_background_backward<C><<<grid_px, kBlock, 0, st>>>(lt, cam, kp, grad_background, grad_env, env_h, env_w);
+    }
+    if (model == kPinholeDistortion)
+        k_splat_backward<C, kPinholeDistortion><<<grid_points, kBlock, 0, st>>>(pts, cam, kp, lt, bt);
+    else
+        k_splat_backward<C, kOcam><<<grid_points, kBlock, 0, st>>>(pts, cam, kp, lt, bt);
+    ADOP_CUDA_TRY(cudaGetLastError());
+    return ADOP_OK;
+}
+
+}  // namespace adop
+
+using namespace adop;
+
+extern "C" adop_status adop_raster_normalize_gradients(float* grad_points, int32_t num_points, double* grad_pose,
+                                                       const float* count_pose, int32_t num_images, float* grad_intrinsics,
+                                                       const float* count_intrinsics, int32_t num_cameras,
+                                                       int32_t intrinsics_cols, void* stream)
+{
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (grad_pose)
+    {
+        if (!count_pose || num_images <= 0) return ADOP_ERR_INVALID_ARGUMENT;
+        int n = num_images * 6;
+        k_normalize_pose<<<(n + 127) / 128, 128, 0, st>>>(grad_pose, count_pose, num_images);
+    }
+    if (grad_points && num_points > 0)
+        k_normalize_points<<<(num_points + 255) / 256, 256, 0, st>>>(reinterpret_cast<float4*>(grad_points), num_points);
+    if (grad_intrinsics)
+    {
+        if (!count_intrinsics || num_cameras <= 0 || intrinsics_cols <= 0) return ADOP_ERR_INVALID_ARGUMENT;
+        int n = num_cameras * intrinsics_cols;
+        k_normalize_intrinsics<<<(n + 127) / 128, 128, 0, st>>>(grad_intrinsics, count_intrinsics, num_cameras, intrinsics_cols);
+    }
+    ADOP_CUDA_TRY(cudaGetLastError());
+    return ADOP_OK;
+}
+
+extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view* views, int32_t B,
+                                            const adop_render_params* rp, int32_t L, adop_backward_io* io, void* stream)
+{
+    adop_status vs = validate_common(s, views, B, rp, L);
+    if (vs != ADOP_OK) return vs;
+    if (!io) return ADOP_ERR_INVALID_ARGUMENT;
+    const int C = s->channels, N = s->num_points, T = s->num_texels, cols = s->intrinsics_cols;
+    for (int l = 0; l < L; ++l)
+        if (!io->layers[l].color || !io->layers[l].depth || !io->layers[l].weight || !io->grad_color[l])
+            return ADOP_ERR_INVALID_ARGUMENT;
+    if ((io->grad_pose && !io->count_pose) || (io->grad_intrinsics && !io->count_intrinsics)) return ADOP_ERR_INVALID_ARGUMENT;
+    if (reinterpret_cast<uintptr_t>(io->grad_points) & 15) return ADOP_ERR_INVALID_ARGUMENT;
+    const bool env = rp->composite_environment_map && s->env_map && io->grad_env_map;
+    if (env)
+        for (int b = 0; b < B; ++b)
+            if (views[b].camera_model != ADOP_CAMERA_PINHOLE_DISTORTION) return ADOP_ERR_UNSUPPORTED;
+
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!io->accumulate)
+    {
+        if (io->grad_texture) ADOP_CUDA_TRY(cudaMemsetAsync(io->grad_texture, 0, sizeof(float) * (size_t)C * T, st));
+        if (io->grad_background) ADOP_CUDA_TRY(cudaMemsetAsync(io->grad_background, 0, sizeof(float) * C, st));
+        if (io->grad_points) ADOP_CUDA_TRY(cudaMemsetAsync(io->grad_points, 0, sizeof(float) * (size_t)N * 4, st));
+        if (io->grad_pose) ADOP_CUDA_TRY(cudaMemsetAsync(io->grad_pose, 0, sizeof(double) * (size_t)s->num_images * 6, st));
+        if (io->count_pose) ADOP_CUDA_TRY(cudaMemsetAsync(io->count_pose, 0, sizeof(float) * s->num_images, st));
+        if (io->grad_intrinsics) ADOP_CUDA_TRY(cudaMemsetAsync(io->grad_intrinsics, 0, sizeof(float) * (size_t)s->num_cameras * cols, st));
+        if (io->count_intrinsics) ADOP_CUDA_TRY(cudaMemsetAsync(io->count_intrinsics, 0, sizeof(float) * s->num_cameras, st));
+        if (io->grad_env_map && s->env_h > 0 && s->env_w > 0)
+            ADOP_CUDA_TRY(cudaMemsetAsync(io->grad_env_map, 0, sizeof(float) * (size_t)C * s->env_h * s->env_w, st));
+    }
+
+    LayerTable base;
+    fill_layer_dims(views[0].w, views[0].h, L, &base);
+    PointStreams pts;
+    pts.position = reinterpret_cast<const float4*>(s->position);
+    pts.normal = s->normal;
+    pts.index = s->index;
+    pts.n = N;
+    const int sms = sm_count();
+    int grid_points = (N + kBlock - 1) / kBlock;
+    if (grid_points > sms * 8) grid_points = sms * 8;
+    if (grid_points < 1) grid_points = 1;
+
+    for (int b = 0; b < B; ++b)
+    {
+        LayerTable lt = base;
+        for (int l = 0; l < L; ++l)
+        {
+            size_t plane = (size_t)base.w[l] * base.h[l];
+            lt.depth[l] = io->layers[l].depth + (size_t)b * plane;
+            lt.weight[l] = io->layers[l].weight + (size_t)b * plane;
+            lt.color[l] = io->layers[l].color + (size_t)b * C * plane;
+            lt.grad[l] = io->grad_color[l] + (size_t)b * C * plane;
+        }
+        KernelParams kp = make_kernel_params(rp, io->dropout_mask, N, b);
+        CamSource cam = make_cam_source(s, &views[b]);
+        BackwardTargets bt;
+        bt.texture = s->texture;
+        bt.num_texels = T;
+        bt.background = s->background;
+        bt.grad_texture = io->grad_texture;
+        bt.grad_points = reinterpret_cast<float4*>(io->grad_points);
+        bt.grad_pose = io->grad_pose ? io->grad_pose + (size_t)views[b].image_index * 6 : nullptr;
+        bt.count_pose = io->grad_pose ? io->count_pose + views[b].image_index : nullptr;
+        bt.grad_intrinsics = io->grad_intrinsics ? io->grad_intrinsics + (size_t)views[b].camera_index * cols : nullptr;
+        bt.count_intrinsics = io->grad_intrinsics ? io->count_intrinsics + views[b].camera_index : nullptr;
+        float* ge = env ? io->grad_env_map : nullptr;
+        adop_status r;
+        switch (C)
+        {
+            case 3: r = launch_view_backward<3>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, st, grid_points, views[b].camera_model); break;
+            case 4: r = launch_view_backward<4>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, st, grid_points, views[b].camera_model); break;
+            case 8: r = launch_view_backward<8>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, st, grid_points, views[b].camera_model); break;
+            case 16: r = launch_view_backward<16>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, st, grid_points, views[b].camera_model); break;
+            default: return ADOP_ERR_UNSUPPORTED;
+        }
+        if (r != ADOP_OK) return r;
+    }
+    if (io->normalize)
+        return adop_raster_normalize_gradients(io->grad_points, N, io->grad_pose, io->count_pose, s->num_images,
+                                               io->grad_intrinsics, io->count_intrinsics, s->num_cameras, cols, stream);
+    return ADOP_OK;
+}

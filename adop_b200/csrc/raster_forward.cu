@@ -1,0 +1,312 @@
+// Forward pass of the one-pixel point rasterizer for sm_100a: depth prepass, fuzzy-depth blend, resolve.
+// Stands in for BlendPointCloudForward and its kernels (darglein/ADOP src/lib/rendering/PointRenderer.cu:
+// DepthPrepassMulti :203-301, RenderForwardMulti :303-393, CombineAndFill :726-754, CreateMask :828-847)
+// plus the environment-map composite of RenderModule.cpp:106-127 / EnvironmentMap.cu:62-156.
+//
+// Layout choices (none of these kernels is a dense contraction, so no tensor cores):
+//  * points stream as one 128-bit load per thread; normals / indices are separate 4-byte streams;
+//  * descriptor sums go to a pixel-interleaved accumulator record (C sums + weight, padded to 16-byte
+//    vectors) so that one splat is one vector atomic plus one scalar atomic into the same 32-byte sector,
+//    instead of C+1 atomics into C+1 planes;
+//  * the resolve kernel turns records into the NCHW tensors of the operator's interface in a single pass
+//    (normalise, background, environment map, mask, weight plane) and clears the records it read, so the
+//    one accumulator, small enough to stay in the 126 MB L2, is reused by every view of the batch.
+#include "common.cuh"
+
+namespace adop {
+
+// ------------------------------------------------------------------------------------------------------
+__global__ void k_fill(float* __restrict__ dst, size_t n, float v)
+{
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t n4 = n / 4;
+    float4 v4 = make_float4(v, v, v, v);
+    for (size_t k = i; k < n4; k += stride) reinterpret_cast<float4*>(dst)[k] = v4;
+    for (size_t k = n4 * 4 + i; k < n; k += stride) dst[k] = v;
+}
+
+// ------------------------------------------------------------------------------------------------------
+// K1: depth prepass. One thread per point and iteration; per layer an early-z read and, if the point could
+// be the closest, an atomicMin on the float's bit pattern (valid because z > 0).
+template <int L>
+__global__ void __launch_bounds__(kBlock) k_depth_prepass(PointStreams pts, CamSource cs, KernelParams kp, LayerTable lt)
+{
+    __shared__ ViewCam cam;
+    load_cam_shared(&cam, cs);
+    const int stride = gridDim.x * blockDim.x;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < pts.n; i += stride)
+    {
+        FetchedPoint f = fetch_point(pts, i);
+        RasterPoint q;
+        if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, kp.check_normal != 0, kp.dist_cutoff, &q)) continue;
+        float x = q.x, y = q.y, rad = q.radius_px;
+        const int zi = __float_as_int(q.z);
+#pragma unroll
+        for (int l = 0; l < L; ++l, rad *= 0.5f, x *= 0.5f, y *= 0.5f)
+        {
+            if (kp.drop_out_points_by_radius && rad < kp.drop_out_radius_threshold) break;
+            int px = round_half_even(x), py = round_half_even(y);
+            if (px < 0 || py < 0 || px >= lt.w[l] || py >= lt.h[l]) continue;
+            int* dst = reinterpret_cast<int*>(lt.depth[l]) + (size_t)py * lt.w[l] + px;
+            // early z (PointRenderer.cu:275-279): a stale value only costs an extra atomic
+            if (zi >= __ldcg(dst)) continue;
+            atomicMin(dst, zi);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// K2: fuzzy-depth blend into the interleaved accumulator.
+template <int C>
+__device__ __forceinline__ void splat_record(float* rec, const float* t)
+{
+    constexpr int full = C / 4;
+    constexpr int rem = C % 4;
+#pragma unroll
+    for (int v = 0; v < full; ++v)
+        atomicAdd(reinterpret_cast<float4*>(rec) + v, make_float4(t[4 * v], t[4 * v + 1], t[4 * v + 2], t[4 * v + 3]));
+    if (rem == 0)
+    {
+        atomicAdd(rec + C, 1.0f);
+    }
+    else
+    {
+        float a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int k = 0; k < rem; ++k) a[k] = t[4 * full + k];
+        a[rem] = 1.0f;
+        atomicAdd(reinterpret_cast<float4*>(rec) + full, make_float4(a[0], a[1], a[2], a[3]));
+    }
+}
+
+template <int L, int C>
+__global__ void __launch_bounds__(kBlock) k_blend(PointStreams pts, const float* __restrict__ texture, int num_texels,
+                                                   CamSource cs, KernelParams kp, LayerTable lt, float* __restrict__ accum)
+{
+    __shared__ ViewCam cam;
+    load_cam_shared(&cam, cs);
+    constexpr int RS = ((C + 1) + 3) & ~3;
+    const int stride = gridDim.x * blockDim.x;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < pts.n; i += stride)
+    {
+        if (point_dropped(kp, i)) continue;
+        FetchedPoint f = fetch_point(pts, i);
+        RasterPoint q;
+        if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, kp.check_normal != 0, kp.dist_cutoff, &q)) continue;
+        float x = q.x, y = q.y, rad = q.radius_px;
+        bool have_t = false;
+        float t[C];
+#pragma unroll
+        for (int l = 0; l < L; ++l, rad *= 0.5f, x *= 0.5f, y *= 0.5f)
+        {
+            if (kp.drop_out_points_by_radius && rad < kp.drop_out_radius_threshold) break;
+            int px = round_half_even(x), py = round_half_even(y);
+            if (px < 0 || py < 0 || px >= lt.w[l] || py >= lt.h[l]) continue;
+            size_t pix = (size_t)py * lt.w[l] + px;
+            float image_depth = __ldg(lt.depth[l] + pix);
+            if (q.z > image_depth * kp.depth_accept_plus_one) continue;
+            if (!have_t)
+            {
+                int ti = pts.index ? __ldg(pts.index + i) : i;
+#pragma unroll
+                for (int c = 0; c < C; ++c) t[c] = __ldg(texture + (size_t)c * num_texels + ti);
+                have_t = true;
+            }
+            splat_record<C>(accum + ((size_t)lt.rec_off[l] + pix) * RS, t);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// K3: resolve. One thread per pyramid pixel of the view (all layers in one launch).
+template <int C>
+__global__ void __launch_bounds__(kBlock) k_resolve(LayerTable lt, CamSource cs, KernelParams kp, float* __restrict__ accum,
+                                                     const float* __restrict__ background, const float* __restrict__ env,
+                                                     int env_h, int env_w)
+{
+    __shared__ ViewCam cam;
+    load_cam_shared(&cam, cs);
+    constexpr int RS = ((C + 1) + 3) & ~3;
+    const unsigned total = lt.rec_off[kMaxLayers];
+    for (unsigned r = blockIdx.x * blockDim.x + threadIdx.x; r < total; r += gridDim.x * blockDim.x)
+    {
+        int l = 0;
+#pragma unroll
+        for (int k = 1; k < kMaxLayers; ++k)
+            if (k < lt.L && r >= lt.rec_off[k]) l = k;
+        const unsigned pix = r - lt.rec_off[l];
+        const int w = lt.w[l], h = lt.h[l];
+        const size_t plane = (size_t)w * h;
+        float4* rec = reinterpret_cast<float4*>(accum + (size_t)r * RS);
+        float v[RS];
+#pragma unroll
+        for (int k = 0; k < RS / 4; ++k)
+        {
+            float4 a = __ldcg(rec + k);
+            v[4 * k] = a.x; v[4 * k + 1] = a.y; v[4 * k + 2] = a.z; v[4 * k + 3] = a.w;
+        }
+        const float cou = v[C];
+        float* color = lt.color[l] + pix;
+        lt.weight[l][pix] = cou;
+        const float m = cou == 0.f ? kp.mask_background_value : 1.f;
+        if (lt.mask[l]) lt.mask[l][pix] = m;
+        if (cou == 0.f)
+        {
+            if (env)
+            {
+                int gy = pix / w, gx = pix - gy * w;
+                Intr5 crop_l = scale_intr(cam.crop, __int_as_float((127 - l) << 23));  // 0.5^l
+                V2 uv = env_uv_for_pixel(gx, gy, cam.V, cam.K, cam.dist, crop_l);
+                BilinearTap tp = bilinear_taps(uv, env_w, env_h);
+                const float one_minus_m = 1.0f - m;
+#pragma unroll
+                for (int c = 0; c < C; ++c)
+                {
+                    const float* e = env + (size_t)c * env_h * env_w;
+                    float e00 = __ldg(e + (size_t)tp.y0 * env_w + tp.x0), e01 = __ldg(e + (size_t)tp.y0 * env_w + tp.x1);
+                    float e10 = __ldg(e + (size_t)tp.y1 * env_w + tp.x0), e11 = __ldg(e + (size_t)tp.y1 * env_w + tp.x1);
+                    float top = e00 + (e01 - e00) * tp.wx;
+                    float bot = e10 + (e11 - e10) * tp.wx;
+                    float ev = top + (bot - top) * tp.wy;
+                    color[c * plane] = __ldg(background + c) + one_minus_m * ev;
+                }
+            }
+            else
+            {
+#pragma unroll
+                for (int c = 0; c < C; ++c) color[c * plane] = __ldg(background + c);
+            }
+        }
+        else
+        {
+#pragma unroll
+            for (int c = 0; c < C; ++c) color[c * plane] = v[c] / cou;
+            // leave the record clean for the next view
+#pragma unroll
+            for (int k = 0; k < RS / 4; ++k) rec[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+template <int L, int C>
+static adop_status launch_view_forward(const PointStreams& pts, const adop_scene* s, const CamSource& cam, const KernelParams& kp,
+                                       const LayerTable& lt, float* accum, bool env, cudaStream_t st, int grid_points)
+{
+    k_depth_prepass<L><<<grid_points, kBlock, 0, st>>>(pts, cam, kp, lt);
+    k_blend<L, C><<<grid_points, kBlock, 0, st>>>(pts, s->texture, s->num_texels, cam, kp, lt, accum);
+    unsigned total = lt.rec_off[kMaxLayers];
+    int grid_px = (int)((total + kBlock - 1) / kBlock);
+    k_resolve<C><<<grid_px, kBlock, 0, st>>>(lt, cam, kp, accum, s->background, env ? s->env_map : nullptr, s->env_h, s->env_w);
+    ADOP_CUDA_TRY(cudaGetLastError());
+    return ADOP_OK;
+}
+
+template <int C>
+static adop_status dispatch_layers_forward(int L, const PointStreams& pts, const adop_scene* s, const CamSource& cam,
+                                           const KernelParams& kp, const LayerTable& lt, float* accum, bool env,
+                                           cudaStream_t st, int grid_points)
+{
+    switch (L)
+    {
+        case 1: return launch_view_forward<1, C>(pts, s, cam, kp, lt, accum, env, st, grid_points);
+        case 2: return launch_view_forward<2, C>(pts, s, cam, kp, lt, accum, env, st, grid_points);
+        case 3: return launch_view_forward<3, C>(pts, s, cam, kp, lt, accum, env, st, grid_points);
+        case 4: return launch_view_forward<4, C>(pts, s, cam, kp, lt, accum, env, st, grid_points);
+        case 5: return launch_view_forward<5, C>(pts, s, cam, kp, lt, accum, env, st, grid_points);
+        case 6: return launch_view_forward<6, C>(pts, s, cam, kp, lt, accum, env, st, grid_points);
+        case 7: return launch_view_forward<7, C>(pts, s, cam, kp, lt, accum, env, st, grid_points);
+        case 8: return launch_view_forward<8, C>(pts, s, cam, kp, lt, accum, env, st, grid_points);
+    }
+    return ADOP_ERR_INVALID_ARGUMENT;
+}
+
+}  // namespace adop
+
+using namespace adop;
+
+extern "C" size_t adop_raster_workspace_bytes(int32_t w, int32_t h, int32_t layers, int32_t channels)
+{
+    if (w <= 0 || h <= 0 || layers <= 0 || layers > ADOP_MAX_LAYERS || channels <= 0) return 0;
+    LayerTable lt;
+    fill_layer_dims(w, h, layers, &lt);
+    size_t bytes = (size_t)lt.rec_off[kMaxLayers] * record_floats(channels) * sizeof(float);
+    return bytes + 256;
+}
+
+extern "C" adop_status adop_raster_forward(const adop_scene* s, const adop_view* views, int32_t B,
+                                           const adop_render_params* rp, int32_t L, adop_forward_io* io, void* stream)
+{
+    adop_status vs = validate_common(s, views, B, rp, L);
+    if (vs != ADOP_OK) return vs;
+    if (!io || !io->workspace) return ADOP_ERR_INVALID_ARGUMENT;
+    const int C = s->channels, N = s->num_points;
+    const int w0 = views[0].w, h0 = views[0].h;
+    if (io->workspace_bytes < adop_raster_workspace_bytes(w0, h0, L, C)) return ADOP_ERR_WORKSPACE_TOO_SMALL;
+    if ((reinterpret_cast<uintptr_t>(io->workspace) & 15) || (reinterpret_cast<uintptr_t>(s->position) & 15))
+        return ADOP_ERR_INVALID_ARGUMENT;
+    const bool env = rp->composite_environment_map && s->env_map;
+    for (int l = 0; l < L; ++l)
+    {
+        if (!io->layers[l].color || !io->layers[l].depth || !io->layers[l].weight) return ADOP_ERR_INVALID_ARGUMENT;
+        if (rp->output_background_mask && !io->layers[l].mask) return ADOP_ERR_INVALID_ARGUMENT;
+    }
+    if (env)
+        for (int b = 0; b < B; ++b)
+            if (views[b].camera_model != ADOP_CAMERA_PINHOLE_DISTORTION) return ADOP_ERR_UNSUPPORTED;  // EnvironmentMap.cu:129
+
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    LayerTable base;
+    fill_layer_dims(w0, h0, L, &base);
+    float* accum = static_cast<float*>(io->workspace);
+    const size_t accum_bytes = (size_t)base.rec_off[kMaxLayers] * record_floats(C) * sizeof(float);
+    ADOP_CUDA_TRY(cudaMemsetAsync(accum, 0, accum_bytes, st));
+    const int sms = sm_count();
+    // depth.fill_(100000), PointRenderer.cu:1045 (weights and colours are written by the resolve kernel)
+    for (int l = 0; l < L; ++l)
+    {
+        size_t n = (size_t)B * base.w[l] * base.h[l];
+        if (n == 0) continue;
+        int grid = (int)((n / 4 + kBlock - 1) / kBlock) + 1;
+        if (grid > sms * 16) grid = sms * 16;
+        k_fill<<<grid, kBlock, 0, st>>>(io->layers[l].depth, n, kDepthInit);
+    }
+    ADOP_CUDA_TRY(cudaGetLastError());
+
+    PointStreams pts;
+    pts.position = reinterpret_cast<const float4*>(s->position);
+    pts.normal = s->normal;
+    pts.index = s->index;
+    pts.n = N;
+    int grid_points = (N + kBlock - 1) / kBlock;
+    if (grid_points > sms * 8) grid_points = sms * 8;  // 8 resident blocks of 256 threads per SM, grid-stride
+    if (grid_points < 1) grid_points = 1;
+
+    // the pose and intrinsics tensors live on the device; the per-view camera is gathered there
+    for (int b = 0; b < B; ++b)
+    {
+        LayerTable lt = base;
+        for (int l = 0; l < L; ++l)
+        {
+            size_t plane = (size_t)base.w[l] * base.h[l];
+            lt.depth[l] = io->layers[l].depth + (size_t)b * plane;
+            lt.weight[l] = io->layers[l].weight + (size_t)b * plane;
+            lt.color[l] = io->layers[l].color + (size_t)b * C * plane;
+            lt.mask[l] = (rp->output_background_mask && io->layers[l].mask) ? io->layers[l].mask + (size_t)b * plane : nullptr;
+        }
+        KernelParams kp = make_kernel_params(rp, io->dropout_mask, N, b);
+        CamSource cam = make_cam_source(s, &views[b]);
+        adop_status r;
+        switch (C)
+        {
+            case 3: r = dispatch_layers_forward<3>(L, pts, s, cam, kp, lt, accum, env, st, grid_points); break;
+            case 4: r = dispatch_layers_forward<4>(L, pts, s, cam, kp, lt, accum, env, st, grid_points); break;
+            case 8: r = dispatch_layers_forward<8>(L, pts, s, cam, kp, lt, accum, env, st, grid_points); break;
+            case 16: r = dispatch_layers_forward<16>(L, pts, s, cam, kp, lt, accum, env, st, grid_points); break;
+            default: return ADOP_ERR_UNSUPPORTED;
+        }
+        if (r != ADOP_OK) return r;
+    }
+    return ADOP_OK;
+}

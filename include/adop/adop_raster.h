@@ -1,0 +1,224 @@
+/* adop_raster.h — C ABI of the B200 one-pixel point rasterizer (libadop_raster.so).
+ *
+ * Plain pointers and sizes only. Unless a function says "host", every pointer inside the structs is a
+ * DEVICE pointer owned by the caller; the library allocates nothing and writes results in place.
+ * Each entry point names the reference interface (darglein/ADOP, path:line) that it stands in for.
+ * All functions return an adop_status; none aborts, traps or throws.
+ */
+#ifndef ADOP_RASTER_H
+#define ADOP_RASTER_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ADOP_MAX_LAYERS 8
+#define ADOP_MAX_CHANNELS 32
+#define ADOP_MAX_OCAM_POLY 16
+
+typedef enum adop_status
+{
+    ADOP_OK                      = 0,
+    ADOP_ERR_INVALID_ARGUMENT    = 1,
+    ADOP_ERR_UNSUPPORTED         = 2,
+    ADOP_ERR_CUDA                = 3,
+    ADOP_ERR_WORKSPACE_TOO_SMALL = 4,
+    ADOP_ERR_SIZE_LIMIT          = 5
+} adop_status;
+
+/* camera models: CameraModel in src/lib/data/SceneData.h:27-31 */
+#define ADOP_CAMERA_PINHOLE_DISTORTION 0
+#define ADOP_CAMERA_OCAM 1
+
+/* One image of the batch: ReducedImageInfo, src/lib/data/SceneData.h:37-47.
+ * crop = the 5 coefficients fx fy cx cy s of crop_transform. */
+typedef struct adop_view
+{
+    int32_t w, h;
+    int32_t image_index;
+    int32_t camera_index;
+    int32_t camera_model;
+    float crop[5];
+} adop_view;
+
+/* The compute-relevant fields of RenderParams, src/lib/data/Settings.h:16-52 (same names, same defaults
+ * through adop_render_params_default). Added: dropout_seed (the reference draws a [B,N] Bernoulli tensor,
+ * PointRenderer.cu:1081-1088; here the decision is a hash of (seed, batch slot, point)). */
+typedef struct adop_render_params
+{
+    int32_t test_backward_mode;
+    int32_t check_normal;
+    float dropout;
+    uint32_t dropout_seed;
+    float depth_accept;
+    int32_t ghost_gradients;
+    float drop_out_radius_threshold;
+    int32_t drop_out_points_by_radius;
+    float distortion_gradient_factor;
+    float K_gradient_factor;
+    float dist_cutoff;
+    int32_t output_background_mask;
+    float output_background_mask_value;
+    /* fused extras, off by default so that the plain operator stays a drop-in */
+    int32_t composite_environment_map; /* out = img + (1 - mask) * env, RenderModule.cpp:106-127 */
+} adop_render_params;
+
+/* The tensors the operator reads from the scene modules (PointRenderer.cu:1146-1155, RenderInfo.cpp:25-30):
+ *   position   [N,4] f32  xyz + drop-out radius            (NeuralPointCloudCuda.h:34)
+ *   normal     [N]   i32  10-bit packed, may be NULL       (NeuralPointCloudCuda.h:36)
+ *   index      [N]   i32  descriptor column, NULL=identity (NeuralPointCloudCuda.h:41)
+ *   texture    [C,T] f32  descriptors                      (NeuralTexture.h:62)
+ *   background [C]   f32                                    (NeuralTexture.h:65)
+ *   poses      [I,8] f64  world->camera, quaternion xyzw + translation + pad (NeuralStructure.cpp:13-27)
+ *   intrinsics [K,cols] f32: pinhole cols=13 (fx fy cx cy s k1..k6 p1 p2), OCam cols=5+m (c d e cx cy a0..)
+ *   env_map    [C,eh,ew] f32, may be NULL                  (EnvironmentMap.h:28) */
+typedef struct adop_scene
+{
+    int32_t num_points;
+    int32_t num_texels;
+    int32_t channels;
+    int32_t num_images;
+    int32_t num_cameras;
+    int32_t intrinsics_cols;
+    int32_t env_h, env_w;
+    const float* position;
+    const int32_t* normal;
+    const int32_t* index;
+    const float* texture;
+    const float* background;
+    const double* poses;
+    const float* intrinsics;
+    const float* env_map;
+} adop_scene;
+
+/* Per pyramid layer l (size w>>l, h>>l by integer halving, PointRenderer.cu:1015-1016), batch-major:
+ *   color  [B,C,h_l,w_l]  output image (PointRenderer.cu:1057)
+ *   depth  [B,1,h_l,w_l]  closest depth, 100000 where empty (PointRenderer.cu:1004,1045)
+ *   weight [B,1,h_l,w_l]  number of blended points (PointRenderer.cu:1006)
+ *   mask   [B,1,h_l,w_l]  1 where covered else output_background_mask_value; NULL unless requested */
+typedef struct adop_layer_buffers
+{
+    float* color;
+    float* depth;
+    float* weight;
+    float* mask;
+} adop_layer_buffers;
+
+typedef struct adop_forward_io
+{
+    adop_layer_buffers layers[ADOP_MAX_LAYERS];
+    const uint8_t* dropout_mask; /* optional [B,N]: 1 = dropped; NULL = hash of dropout_seed */
+    void* workspace;
+    size_t workspace_bytes;
+} adop_forward_io;
+
+/* Gradients (outputs) follow the reference's order {texture, background, points, pose tangents, intrinsics}
+ * (PointRenderer.cu:1641-1643). NULL = not requested.
+ *   grad_texture    [C,T] f32
+ *   grad_background [C]   f32
+ *   grad_points     [N,4] f32  xyz = gradient, w = number of contributions until normalised, then 0
+ *   grad_pose       [I,6] f64, count_pose [I] f32
+ *   grad_intrinsics [K,cols] f32, count_intrinsics [K] f32
+ *   grad_env_map    [C,eh,ew] f32 (only with composite_environment_map)
+ * accumulate = 0: the library zeroes the gradient buffers first (the reference allocates zeros,
+ * PointRenderer.cu:924-948). normalize = 1: divide by the counts as PointRenderer.cu:1609-1637 does;
+ * 0 leaves sums and counts so that several ranks can add them up first (adop_raster_normalize_gradients). */
+typedef struct adop_backward_io
+{
+    adop_layer_buffers layers[ADOP_MAX_LAYERS]; /* saved forward results (color, depth, weight) */
+    const float* grad_color[ADOP_MAX_LAYERS];   /* upstream gradient, [B,C,h_l,w_l] */
+    const uint8_t* dropout_mask;
+    float* grad_texture;
+    float* grad_background;
+    float* grad_points;
+    double* grad_pose;
+    float* count_pose;
+    float* grad_intrinsics;
+    float* count_intrinsics;
+    float* grad_env_map;
+    int32_t accumulate;
+    int32_t normalize;
+    void* workspace;
+    size_t workspace_bytes;
+} adop_backward_io;
+
+const char* adop_status_string(adop_status s);
+/* text of the last CUDA error seen by this thread's calls ("" if none) */
+const char* adop_last_error(void);
+
+/* RenderParams defaults, Settings.h:22-52 */
+void adop_render_params_default(adop_render_params* p);
+
+/* Bytes of scratch that forward/backward need for views of w x h with `layers` layers and `channels`
+ * descriptor channels. Replaces the size-keyed PointRendererCache (PointRenderer.h:96-157). */
+size_t adop_raster_workspace_bytes(int32_t w, int32_t h, int32_t layers, int32_t channels);
+
+/* BlendPointCloudForward, src/lib/rendering/PointRenderer.cu:1389-1531: depth prepass, fuzzy-depth blend,
+ * combine-and-fill, mask, and (optionally) the environment-map composite of RenderModule.cpp:106-127.
+ * `views` is a HOST array of B entries. stream is a cudaStream_t (NULL = default stream). */
+adop_status adop_raster_forward(const adop_scene* scene, const adop_view* views, int32_t num_views,
+                                const adop_render_params* params, int32_t num_layers, adop_forward_io* io,
+                                void* stream);
+
+/* BlendPointCloudBackward, src/lib/rendering/PointRenderer.cu:1549-1644. */
+adop_status adop_raster_backward(const adop_scene* scene, const adop_view* views, int32_t num_views,
+                                 const adop_render_params* params, int32_t num_layers, adop_backward_io* io,
+                                 void* stream);
+
+/* NormalizeGradient calls of PointRenderer.cu:1609-1637, as a separate step for callers that sum the
+ * un-normalised gradients of several GPUs first. NULL pointers are skipped. */
+adop_status adop_raster_normalize_gradients(float* grad_points, int32_t num_points, double* grad_pose,
+                                            const float* count_pose, int32_t num_images, float* grad_intrinsics,
+                                            const float* count_intrinsics, int32_t num_cameras,
+                                            int32_t intrinsics_cols, void* stream);
+
+/* ApplyTangentToPose, src/lib/rendering/PointRenderer.cu:1646-1665: pose <- exp(tangent) * pose, tangent <- 0.
+ * tangent [n,6] f64, pose [n,8] f64. */
+adop_status adop_apply_tangent(double* tangent, double* pose, int32_t n, void* stream);
+
+/* Photometric tonemapper, NeuralCameraImpl::forward, src/lib/models/NeuralCamera.cpp:258-335, with
+ * VignetteNetImpl::forward (:22-42) and CameraResponseNetImpl::forward (:87-135) fused into one pass.
+ *   x, out        [B,3,H,W] f32
+ *   frame_index   [B] i32  row of exposure / white_balance per image
+ *   exposure      [n] f32 or NULL          (exposures_values [n,1,1,1])
+ *   white_balance [n,3] f32 or NULL        (white_balance_values [n,3,1,1])
+ *   vignette      3 polynomial coefficients then the centre (2), f32[5], or NULL
+ *   uv            [B,2,H,W] f32 or NULL = 2*(col/(W-1), row/(H-1))-1 (Dataset.cpp:12-34)
+ *   response      [3,K] f32 or NULL (then clamp to [0,1])
+ *   leak          leaky-clamp slope used while training (0 = hard clamp) */
+typedef struct adop_tonemap_params
+{
+    int32_t batch, height, width;
+    int32_t response_bins;
+    int32_t vignette_image_w, vignette_image_h; /* aspect = w / h of VignetteNet's image_size */
+    float leak;
+    const int32_t* frame_index;
+    const float* exposure;
+    const float* white_balance;
+    const float* vignette;
+    const float* uv;
+    const float* response;
+} adop_tonemap_params;
+
+typedef struct adop_tonemap_grads
+{
+    float* grad_x;             /* [B,3,H,W] */
+    float* grad_exposure;      /* [n] */
+    float* grad_white_balance; /* [n,3] */
+    float* grad_vignette;      /* [5] */
+    float* grad_response;      /* [3,K] */
+    int32_t num_frames;        /* n, for zeroing */
+    int32_t accumulate;
+} adop_tonemap_grads;
+
+adop_status adop_tonemap_forward(const adop_tonemap_params* p, const float* x, float* out, void* stream);
+adop_status adop_tonemap_backward(const adop_tonemap_params* p, const float* x, const float* grad_out,
+                                  adop_tonemap_grads* g, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ADOP_RASTER_H */

@@ -1,0 +1,241 @@
+"""GPU parity of the rasterizer against the CPU checker, through the C ABI.
+
+Bar: depth and weight buffers bit-exact (integer-like data); colours and gradients within 1e-4 relative (float atomics
+add in a different order on the GPU), scaled by the magnitude of the tensor where values cancel.
+"""
+import numpy as np
+import pytest
+import torch
+
+from adop_b200 import capi, synth
+from adop_b200.raster import PointRasterizer, Scene
+
+pytestmark = pytest.mark.gpu
+
+RTOL = 1e-4
+
+
+def to_scene(arrays, dev="cuda:0"):
+    return Scene(**{k: (torch.from_numpy(v).to(dev) if v is not None else None) for k, v in arrays.items()})
+
+
+def close(a, b, rtol=RTOL, name=""):
+    a = a.detach().cpu().numpy() if isinstance(a, torch.Tensor) else a
+    scale = max(float(np.abs(b).max()), 1e-12)
+    err = float(np.abs(a.astype(np.float64) - b.astype(np.float64)).max())
+    assert err <= rtol * scale, f"{name}: max err {err:.3e} vs scale {scale:.3e}"
+
+
+def run_both(oracle, cfg, want_env=False, dropout_mask=None, **bw):
+    arrays, views, params, L = cfg["arrays"], cfg["views"], cfg["params"], cfg["num_layers"]
+    grads = synth.upstream_gradients(cfg["meta"], batch=len(views))
+    ref = oracle.forward(arrays, views, params, L, dropout_mask=dropout_mask)
+    ref_b = oracle.backward(arrays, views, params, L, ref, grads, want_env=want_env, dropout_mask=dropout_mask, **bw)
+    scene = to_scene(arrays)
+    r = PointRasterizer("cuda:0")
+    dm = torch.from_numpy(dropout_mask).cuda() if dropout_mask is not None else None
+    fwd = r.forward(scene, views, params, L, dropout_mask=dm)
+    bwd = r.backward(scene, params, fwd, [torch.from_numpy(g).cuda() for g in grads], want_env=want_env,
+                     dropout_mask=dm, **bw)
+    torch.cuda.synchronize()
+    return ref, ref_b, fwd, bwd
+
+
+def check_forward(ref, fwd, L, masks=False):
+    for l in range(L):
+        d = fwd.depths[l].cpu().numpy()
+        assert np.array_equal(d.view(np.uint32), ref["depths"][l].view(np.uint32)), f"depth layer {l} not bit-exact"
+        assert np.array_equal(fwd.weights[l].cpu().numpy(), ref["weights"][l]), f"weight layer {l}"
+        close(fwd.colors[l], ref["colors"][l], name=f"colour layer {l}")
+        if masks:
+            assert np.array_equal(fwd.masks[l].cpu().numpy(), ref["masks"][l])
+
+
+def check_backward(ref_b, bwd):
+    for k in ("texture", "background", "points", "pose", "intrinsics", "env_map"):
+        if ref_b.get(k) is None:
+            assert bwd.get(k) is None
+            continue
+        close(bwd[k], ref_b[k], name=f"grad {k}")
+    for k in ("count_pose", "count_intrinsics"):
+        if ref_b.get(k) is not None:
+            close(bwd[k], ref_b[k], rtol=1e-6, name=k)
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_c1_small_cloud(oracle, cuda_lib, seed):
+    cfg = synth.make_config("c1", n_points=1 << 17, size=(256, 256), seed=seed)
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg)
+    check_forward(ref, fwd, cfg["num_layers"])
+    check_backward(ref_b, bwd)
+    assert ref["weights"][0].sum() > 1000
+
+
+def test_c1_full_size(oracle, cuda_lib):
+    cfg = synth.make_config("c1")
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg)
+    check_forward(ref, fwd, 4)
+    check_backward(ref_b, bwd)
+
+
+def test_c2_distortion_env_map_pose_grads(oracle, cuda_lib):
+    cfg = synth.make_config("c2", n_points=400_000, n_views=3, size=(480, 270))
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg, want_env=True)
+    check_forward(ref, fwd, 4, masks=True)
+    check_backward(ref_b, bwd)
+    assert np.abs(ref_b["pose"]).max() > 0 and np.abs(ref_b["env_map"]).max() > 0
+
+
+def test_c3_ocam(oracle, cuda_lib):
+    cfg = synth.make_config("c3", n_points=500_000, size=(480, 270))
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg)
+    check_forward(ref, fwd, 4)
+    check_backward(ref_b, bwd)
+    assert ref["weights"][0].sum() > 1000
+
+
+def test_c5_eight_channels_six_layers(oracle, cuda_lib):
+    cfg = synth.make_config("c5", n_points=300_000, n_views=2, size=(384, 216))
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg, want_env=True)
+    check_forward(ref, fwd, 6, masks=True)
+    check_backward(ref_b, bwd)
+
+
+@pytest.mark.parametrize("channels", [3, 16])
+def test_other_channel_counts(oracle, cuda_lib, channels):
+    cfg = synth.make_config("c1", n_points=50_000, size=(96, 64), channels=channels, layers=3)
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg)
+    check_forward(ref, fwd, 3)
+    check_backward(ref_b, bwd)
+
+
+def test_odd_sizes_and_ragged_point_count(oracle, cuda_lib):
+    # 135 -> 67 -> 33 by integer halving; N not a multiple of 32
+    cfg = synth.make_config("c1", n_points=10_007, size=(135, 77), layers=3)
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg)
+    check_forward(ref, fwd, 3)
+    check_backward(ref_b, bwd)
+
+
+@pytest.mark.parametrize("ghost", [0, 1])
+def test_dropout_hash_and_ghost_gradients(oracle, cuda_lib, ghost):
+    cfg = synth.make_config("c1", n_points=80_000, size=(128, 128))
+    cfg["params"].dropout = 0.25
+    cfg["params"].dropout_seed = 7
+    cfg["params"].ghost_gradients = ghost
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg)
+    check_forward(ref, fwd, 4)
+    check_backward(ref_b, bwd)
+    assert np.abs(ref_b["points"]).max() > 0
+
+
+def test_dropout_mask_all_and_none(oracle, cuda_lib):
+    cfg = synth.make_config("c1", n_points=20_000, size=(64, 64))
+    n = cfg["meta"]["n_points"]
+    for value in (0, 1):
+        mask = np.full((1, n), value, np.uint8)
+        ref, ref_b, fwd, bwd = run_both(oracle, cfg, dropout_mask=mask)
+        check_forward(ref, fwd, 4)
+        check_backward(ref_b, bwd)
+        if value == 1:  # everything dropped: depth still written (dropped points occlude), nothing blended
+            assert ref["weights"][0].sum() == 0 and (ref["depths"][0] < 100000).any()
+
+
+def test_normals_radius_dropout_and_index(oracle, cuda_lib):
+    cfg = synth.make_config("c1", n_points=60_000, size=(128, 96))
+    rng = np.random.default_rng(3)
+    n = cfg["meta"]["n_points"]
+    nrm = rng.normal(size=(n, 3))
+    nrm /= np.linalg.norm(nrm, axis=1, keepdims=True)
+    q = np.round((nrm + 1) * 0.5 * 1023).astype(np.uint32)
+    cfg["arrays"]["normal"] = (q[:, 0] | (q[:, 1] << 10) | (q[:, 2] << 20)).astype(np.int32)
+    cfg["arrays"]["index"] = rng.permutation(n).astype(np.int32)
+    cfg["arrays"]["position"][:, 3] = rng.uniform(0.001, 0.02, n).astype(np.float32)
+    cfg["params"].check_normal = 1
+    cfg["params"].drop_out_points_by_radius = 1
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg)
+    check_forward(ref, fwd, 4)
+    check_backward(ref_b, bwd)
+    assert 0 < ref["weights"][0].sum() < n
+
+
+def test_backward_mode_4(oracle, cuda_lib):
+    cfg = synth.make_config("c1", n_points=40_000, size=(96, 96))
+    cfg["params"].test_backward_mode = 4
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg)
+    check_backward(ref_b, bwd)
+
+
+def test_no_visible_points_and_empty_cloud(oracle, cuda_lib):
+    cfg = synth.make_config("c1", n_points=1000, size=(64, 64))
+    cfg["arrays"]["position"][:, 2] = -5.0  # everything behind the camera
+    cfg["arrays"]["background"][:] = [0.1, 0.2, 0.3, 0.4]
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg)
+    check_forward(ref, fwd, 4)
+    assert float(fwd.weights[0].sum()) == 0
+    assert torch.allclose(fwd.colors[0][0, :, 5, 5].cpu(), torch.tensor([0.1, 0.2, 0.3, 0.4]))
+    close(bwd["background"], ref_b["background"], name="background gradient")
+
+
+def test_unnormalized_then_normalize_matches(oracle, cuda_lib):
+    cfg = synth.make_config("c1", n_points=50_000, size=(128, 128))
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg, normalize=False)
+    check_backward(ref_b, bwd)
+    r = PointRasterizer("cuda:0")
+    r.normalize_gradients(bwd)
+    ref_n = oracle.backward(cfg["arrays"], cfg["views"], cfg["params"], 4, ref,
+                            synth.upstream_gradients(cfg["meta"], batch=1))
+    check_backward(ref_n, bwd)
+
+
+def test_descriptor_gradient_is_exact_adjoint(cuda_lib):
+    """The op is linear in the descriptors: <G, forward(T)> == <backward(G), T> when the background is 0."""
+    cfg = synth.make_config("c1", n_points=100_000, size=(128, 128))
+    scene = to_scene(cfg["arrays"])
+    r = PointRasterizer("cuda:0")
+    fwd = r.forward(scene, cfg["views"], cfg["params"], 4)
+    grads = [torch.from_numpy(g).cuda() for g in synth.upstream_gradients(cfg["meta"], batch=1)]
+    bwd = r.backward(scene, cfg["params"], fwd, grads, want_points=False, want_pose=False, want_intrinsics=False)
+    lhs = sum(float((g.double() * c.double()).sum()) for g, c in zip(grads, fwd.colors))
+    rhs = float((bwd["texture"].double() * scene.texture.double()).sum())
+    assert abs(lhs - rhs) <= 1e-4 * max(abs(lhs), 1.0)
+
+
+def test_point_order_invariance(cuda_lib):
+    cfg = synth.make_config("c1", n_points=60_000, size=(128, 128))
+    scene = to_scene(cfg["arrays"])
+    r = PointRasterizer("cuda:0")
+    a = r.forward(scene, cfg["views"], cfg["params"], 4)
+    perm = torch.randperm(scene.position.shape[0], device="cuda")
+    scene2 = Scene(scene.position[perm].contiguous(), scene.texture[:, perm].contiguous(), scene.background,
+                   scene.poses, scene.intrinsics)
+    r2 = PointRasterizer("cuda:0")
+    b = r2.forward(scene2, cfg["views"], cfg["params"], 4)
+    for l in range(4):
+        assert torch.equal(a.depths[l], b.depths[l]) and torch.equal(a.weights[l], b.weights[l])
+        assert torch.allclose(a.colors[l], b.colors[l], rtol=1e-4, atol=1e-5)
+
+
+def test_workspace_is_clean_across_calls(cuda_lib):
+    cfg = synth.make_config("c2", n_points=100_000, n_views=2, size=(320, 180))
+    scene = to_scene(cfg["arrays"])
+    r = PointRasterizer("cuda:0")
+    a = r.forward(scene, cfg["views"], cfg["params"], 4)
+    first = [c.clone() for c in a.colors]
+    b = r.forward(scene, cfg["views"], cfg["params"], 4, out=a)
+    for x, y in zip(first, b.colors):
+        assert torch.allclose(x, y, rtol=1e-4, atol=1e-5)
+
+
+def test_argument_errors(cuda_lib):
+    cfg = synth.make_config("c1", n_points=1000, size=(64, 64))
+    scene = to_scene(cfg["arrays"])
+    r = PointRasterizer("cuda:0")
+    bad = [dict(cfg["views"][0], image_index=5)]
+    with pytest.raises(capi.AdopError, match="invalid argument"):
+        r.forward(scene, bad, cfg["params"], 4)
+    with pytest.raises(capi.AdopError, match="invalid argument"):
+        r.forward(scene, cfg["views"], cfg["params"], 9)
+    with pytest.raises(capi.AdopError):
+        r.forward(Scene(**{k: (v.cpu() if v is not None else None) for k, v in scene.tensors().items()}),
+                  cfg["views"], cfg["params"], 4)
