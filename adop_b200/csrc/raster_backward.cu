@@ -8,28 +8,39 @@
 //    and leaves as C atomics per point, not C per (point, layer);
 //  * the point gradient and its counter leave as ONE 16-byte vector atomic (x, y, z, count);
 //  * pose and intrinsics gradients, which the reference adds with 7 + 14 same-address atomics per splat,
-//    are reduced warp -> block in shared memory and leave as one atomic per component and block.
+//    are reduced warp -> block in shared memory and leave as one atomic per component and block;
+//  * the ghost-gradient stencil reads, per neighbour pixel, C values of the forward image and C of the upstream
+//    gradient. From NCHW planes that is 2C scattered 4-byte reads in 2C different sectors; a preparation pass
+//    (fused with the background / environment-map gradient) first interleaves both into one record per pixel
+//    [I_0..I_C-1, G_0..G_C-1], so a neighbour costs one or two 32-byte sectors.
 #include "common.cuh"
 
 namespace adop {
 
 // ------------------------------------------------------------------------------------------------------
-// K4: gradient of the background colour (sum of the upstream gradient over uncovered pixels) and, with the
-// fused composite, of the environment map (bilinear scatter).
+// K4: preparation pass over the pyramid pixels of one view.
+//  * writes the interleaved record [I_0..I_C-1 | G_0..G_C-1] (I = the forward image before the environment-map
+//    composite: the background colour where nothing was blended, PointRenderer.cu:1523);
+//  * sums the gradient of the background colour over uncovered pixels (CombineAndFillBackward, :851-900);
+//  * with the fused composite, scatters the environment-map gradient (bilinear, 4 taps).
+__host__ __device__ inline int backward_record_floats(int C) { return (2 * C + 3) & ~3; }
+
 template <int C>
-__global__ void __launch_bounds__(kBlock) k_background_backward(LayerTable lt, CamSource cs, KernelParams kp,
-                                                                 float* __restrict__ grad_background,
-                                                                 float* __restrict__ grad_env, int env_h, int env_w)
+__global__ void __launch_bounds__(kBlock) k_prepare_backward(LayerTable lt, CamSource cs, KernelParams kp,
+                                                              const float* __restrict__ background, float* __restrict__ records,
+                                                              float* __restrict__ grad_background,
+                                                              float* __restrict__ grad_env, int env_h, int env_w)
 {
+    constexpr int RB = (2 * C + 3) & ~3;
     __shared__ ViewCam cam;
     __shared__ float s_bg[C];
     load_cam_shared(&cam, cs);
     if (threadIdx.x < C) s_bg[threadIdx.x] = 0.f;
     __syncthreads();
     const unsigned total = lt.rec_off[kMaxLayers];
-    float g[C];
+    float g[C], bgc[C];
 #pragma unroll
-    for (int c = 0; c < C; ++c) g[c] = 0.f;
+    for (int c = 0; c < C; ++c) { g[c] = 0.f; bgc[c] = __ldg(background + c); }
     for (unsigned r = blockIdx.x * blockDim.x + threadIdx.x; r < total; r += gridDim.x * blockDim.x)
     {
         int l = 0;
@@ -37,12 +48,24 @@ __global__ void __launch_bounds__(kBlock) k_background_backward(LayerTable lt, C
         for (int k = 1; k < kMaxLayers; ++k)
             if (k < lt.L && r >= lt.rec_off[k]) l = k;
         const unsigned pix = r - lt.rec_off[l];
-        if (__ldg(lt.weight[l] + pix) != 0.f) continue;
         const int w = lt.w[l], h = lt.h[l];
         const size_t plane = (size_t)w * h;
-        float gl[C];
+        const bool covered = __ldg(lt.weight[l] + pix) != 0.f;
+        float rec[RB];
 #pragma unroll
-        for (int c = 0; c < C; ++c) { gl[c] = __ldg(lt.grad[l] + c * plane + pix); g[c] += gl[c]; }
+        for (int c = 0; c < C; ++c)
+        {
+            rec[C + c] = __ldcs(lt.grad[l] + c * plane + pix);
+            rec[c] = covered ? __ldg(lt.color[l] + c * plane + pix) : bgc[c];
+        }
+#pragma unroll
+        for (int k = 2 * C; k < RB; ++k) rec[k] = 0.f;
+        float4* dst = reinterpret_cast<float4*>(records + (size_t)r * RB);
+#pragma unroll
+        for (int k = 0; k < RB / 4; ++k) dst[k] = make_float4(rec[4 * k], rec[4 * k + 1], rec[4 * k + 2], rec[4 * k + 3]);
+        if (covered) continue;
+#pragma unroll
+        for (int c = 0; c < C; ++c) g[c] += rec[C + c];
         if (grad_env)
         {
             int gy = pix / w, gx = pix - gy * w;
@@ -56,7 +79,7 @@ __global__ void __launch_bounds__(kBlock) k_background_backward(LayerTable lt, C
             for (int c = 0; c < C; ++c)
             {
                 float* e = grad_env + (size_t)c * env_h * env_w;
-                float ge = om * gl[c];
+                float ge = om * rec[C + c];
                 atomicAdd(e + (size_t)tp.y0 * env_w + tp.x0, ge * w00);
                 atomicAdd(e + (size_t)tp.y0 * env_w + tp.x1, ge * w01);
                 atomicAdd(e + (size_t)tp.y1 * env_w + tp.x0, ge * w10);
@@ -90,13 +113,28 @@ struct BackwardTargets
     float* count_pose;        // element of this view's image
     float* grad_intrinsics;   // row of this view's camera
     float* count_intrinsics;  // element of this view's camera
+    const float* records;     // interleaved [I | G] per pyramid pixel, written by k_prepare_backward
 };
+
+template <int C>
+__device__ __forceinline__ void load_record(const float* records, size_t r, float* out)
+{
+    constexpr int RB = (2 * C + 3) & ~3;
+    const float4* src = reinterpret_cast<const float4*>(records + r * RB);
+#pragma unroll
+    for (int k = 0; k < RB / 4; ++k)
+    {
+        float4 a = __ldg(src + k);
+        out[4 * k] = a.x; out[4 * k + 1] = a.y; out[4 * k + 2] = a.z; out[4 * k + 3] = a.w;
+    }
+}
 
 template <int C, int MODEL>
 __global__ void __launch_bounds__(kBlock) k_splat_backward(PointStreams pts, CamSource cs, KernelParams kp, LayerTable lt,
                                                             BackwardTargets bt)
 {
     constexpr int NI = MODEL == kPinholeDistortion ? 13 : 5;
+    constexpr int RB = (2 * C + 3) & ~3;
     __shared__ ViewCam cam;
     __shared__ double s_pose[6];
     __shared__ float s_intr[NI];
@@ -140,22 +178,22 @@ __global__ void __launch_bounds__(kBlock) k_splat_backward(PointStreams pts, Cam
             const int px = round_half_even(x), py = round_half_even(y);
             const int w = lt.w[l], h = lt.h[l];
             if (px < 0 || py < 0 || px >= w || py >= h) continue;
-            const size_t plane = (size_t)w * h;
             const size_t pix = (size_t)py * w + px;
             const float* __restrict__ D = lt.depth[l];
             const float* __restrict__ W = lt.weight[l];
-            const float* __restrict__ I = lt.color[l];
-            const float* __restrict__ G = lt.grad[l];
             if (q.z > __ldg(D + pix) * kp.depth_accept_plus_one) break;
             const float wgt = __ldg(W + pix);
+            const size_t rbase = (size_t)lt.rec_off[l] + pix;
             if (!drop_out)
             {
                 if (wgt == 0.f) continue;
                 if (bt.grad_texture)
                 {
+                    float rc[RB];
+                    load_record<C>(bt.records, rbase, rc);
                     const float iw = 1.f / wgt;
 #pragma unroll
-                    for (int c = 0; c < C; ++c) dg[c] += iw * __ldg(G + c * plane + pix);
+                    for (int c = 0; c < C; ++c) dg[c] += iw * rc[C + c];
                     have_dg = true;
                 }
             }
@@ -170,39 +208,36 @@ __global__ void __launch_bounds__(kBlock) k_splat_backward(PointStreams pts, Cam
                 have_t = true;
             }
             const size_t nb[4] = {pix - 1, pix + 1, pix - (size_t)w, pix + (size_t)w};
-            float Wn[4], Dn[4];
+            float dR[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) Wn[k] = __ldg(W + nb[k]);
-            if (kp.test_backward_mode == 4)
+            for (int k = 0; k < 4; ++k)
             {
-#pragma unroll
-                for (int k = 0; k < 4; ++k) Dn[k] = __ldg(D + nb[k]);
-            }
-            float dRx = 0.f, dRy = 0.f;
-#pragma unroll
-            for (int c = 0; c < C; ++c)
-            {
-                const float bgc = __ldg(bt.background + c);
-                float dR[4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k)
+                float rn[RB];
+                load_record<C>(bt.records, (size_t)lt.rec_off[l] + nb[k], rn);
+                float acc = 0.f;
+                if (kp.test_backward_mode == 4)  // PointRenderer.cu:543-566
                 {
-                    float I_x = Wn[k] > 0.f ? __ldg(I + c * plane + nb[k]) : bgc;
-                    float G_x = __ldg(G + c * plane + nb[k]);
-                    float dI;
-                    if (kp.test_backward_mode == 4)
+                    const float W_x = __ldg(W + nb[k]), D_x = __ldg(D + nb[k]);
+#pragma unroll
+                    for (int c = 0; c < C; ++c)
                     {
-                        if (Wn[k] == 0.f || q.z * kp.depth_accept_plus_one < Dn[k]) dI = T_p[c] - I_x;
-                        else if (q.z > Dn[k] * kp.depth_accept_plus_one) dI = 0.f;
-                        else dI = (Wn[k] / (Wn[k] + 1.f) * I_x + 1.f / (Wn[k] + 1.f) * T_p[c] - I_x);
+                        float dI;
+                        if (W_x == 0.f || q.z * kp.depth_accept_plus_one < D_x) dI = T_p[c] - rn[c];
+                        else if (q.z > D_x * kp.depth_accept_plus_one) dI = 0.f;
+                        else dI = (W_x / (W_x + 1.f) * rn[c] + 1.f / (W_x + 1.f) * T_p[c] - rn[c]);
+                        acc += dI * rn[C + c];
                     }
-                    else
-                        dI = T_p[c] - I_x;
-                    dR[k] = dI * G_x;
                 }
-                dRx += 0.5f * (-dR[0] + dR[1]);
-                dRy += 0.5f * (-dR[2] + dR[3]);
+                else
+                {
+#pragma unroll
+                    for (int c = 0; c < C; ++c) acc += (T_p[c] - rn[c]) * rn[C + c];
+                }
+                dR[k] = acc;
             }
+            // central differences (PointRenderer.cu:601-608); the per-channel halves are summed here per direction
+            const float dRx = 0.5f * (-dR[0] + dR[1]);
+            const float dRy = 0.5f * (-dR[2] + dR[3]);
             V2 g; g.x = dRx / (float)C; g.y = dRy / (float)C;
             Intr5 crop_l = scale_intr(cam.crop, scale);
             if (MODEL == kPinholeDistortion)
@@ -320,13 +355,13 @@ static adop_status launch_view_backward(const PointStreams& pts, const CamSource
                                         const BackwardTargets& bt, float* grad_background, float* grad_env, int env_h, int env_w,
                                         cudaStream_t st, int grid_points, int model)
 {
-    if (grad_background || grad_env)
     {
         unsigned total = lt.rec_off[kMaxLayers];
         int grid_px = (int)((total + kBlock - 1) / kBlock);
         int cap = sm_count() * 8;
         if (grid_px > cap) grid_px = cap;
-        k_background_backward<C><<<grid_px, kBlock, 0, st>>>(lt, cam, kp, grad_background, grad_env, env_h, env_w);
+        k_prepare_backward<C><<<grid_px, kBlock, 0, st>>>(lt, cam, kp, bt.background, const_cast<float*>(bt.records),
+                                                           grad_background, grad_env, env_h, env_w);
     }
     if (model == kPinholeDistortion)
         k_splat_backward<C, kPinholeDistortion><<<grid_points, kBlock, 0, st>>>(pts, cam, kp, lt, bt);
@@ -376,6 +411,8 @@ extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view
             return ADOP_ERR_INVALID_ARGUMENT;
     if ((io->grad_pose && !io->count_pose) || (io->grad_intrinsics && !io->count_intrinsics)) return ADOP_ERR_INVALID_ARGUMENT;
     if (reinterpret_cast<uintptr_t>(io->grad_points) & 15) return ADOP_ERR_INVALID_ARGUMENT;
+    if (!io->workspace || (reinterpret_cast<uintptr_t>(io->workspace) & 15)) return ADOP_ERR_INVALID_ARGUMENT;
+    if (io->workspace_bytes < adop_raster_workspace_bytes(views[0].w, views[0].h, L, C)) return ADOP_ERR_WORKSPACE_TOO_SMALL;
     const bool env = rp->composite_environment_map && s->env_map && io->grad_env_map;
     if (env)
         for (int b = 0; b < B; ++b)
@@ -430,6 +467,7 @@ extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view
         bt.count_pose = io->grad_pose ? io->count_pose + views[b].image_index : nullptr;
         bt.grad_intrinsics = io->grad_intrinsics ? io->grad_intrinsics + (size_t)views[b].camera_index * cols : nullptr;
         bt.count_intrinsics = io->grad_intrinsics ? io->count_intrinsics + views[b].camera_index : nullptr;
+        bt.records = static_cast<const float*>(io->workspace);
         float* ge = env ? io->grad_env_map : nullptr;
         adop_status r;
         switch (C)

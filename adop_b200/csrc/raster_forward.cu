@@ -231,7 +231,9 @@ extern "C" size_t adop_raster_workspace_bytes(int32_t w, int32_t h, int32_t laye
     if (w <= 0 || h <= 0 || layers <= 0 || layers > ADOP_MAX_LAYERS || channels <= 0) return 0;
     LayerTable lt;
     fill_layer_dims(w, h, layers, &lt);
-    size_t bytes = (size_t)lt.rec_off[kMaxLayers] * record_floats(channels) * sizeof(float);
+    // forward: accumulator records (C sums + weight); backward: interleaved [image | gradient] records
+    int fwd = record_floats(channels), bwd = (2 * channels + 3) & ~3;
+    size_t bytes = (size_t)lt.rec_off[kMaxLayers] * (fwd > bwd ? fwd : bwd) * sizeof(float);
     return bytes + 256;
 }
 

@@ -185,6 +185,9 @@ class PointRasterizer:
             io.grad_env_map = p("env_map")
             io.accumulate = 0
             io.normalize = 1 if normalize else 0
+            ws = self._workspace(va[0].w, va[0].h, L, sc.channels)
+            io.workspace = ws.data_ptr()
+            io.workspace_bytes = ws.numel()
             stream = torch.cuda.current_stream(self.device).cuda_stream
             st = self.lib.adop_raster_backward(C.byref(sc), va, B, C.byref(params), L, C.byref(io), C.c_void_p(stream))
             capi.check(st, "adop_raster_backward")
