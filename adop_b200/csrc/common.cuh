@@ -134,6 +134,19 @@ adop_status validate_common(const adop_scene* s, const adop_view* views, int B, 
 int sm_count();
 
 #if defined(__CUDACC__)
+// Grid of a persistent grid-stride kernel: exactly the blocks that are resident at once (occupancy x SMs),
+// so there is no partial second wave, capped by the work available.
+template <class Kernel>
+inline int resident_grid(Kernel kernel, long long work_items)
+{
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kBlock, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
+    long long need = (work_items + kBlock - 1) / kBlock;
+    long long g = (long long)per_sm * sm_count();
+    if (g > need) g = need;
+    return g < 1 ? 1 : (int)g;
+}
+
 struct FetchedPoint { V3 p; V3 n; float r; bool has_normal; };
 
 // DevicePointCloud::GetPoint (NeuralPointCloudCuda.h:82-103): one 128-bit load of xyz + radius

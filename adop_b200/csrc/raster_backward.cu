@@ -160,7 +160,8 @@ __global__ void __launch_bounds__(kBlock) k_splat_backward(PointStreams pts, Cam
         const bool drop_out = point_dropped(kp, i);
         FetchedPoint f = fetch_point(pts, i);
         RasterPoint q;
-        if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, kp.check_normal != 0, kp.dist_cutoff, &q)) continue;
+        if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, kp.check_normal != 0, kp.dist_cutoff, &q,
+                                kp.drop_out_points_by_radius != 0)) continue;
         float x = q.x, y = q.y, rad = q.radius_px, scale = 1.f;
         const bool point_grad = want_geo && ((kp.ghost_gradients && drop_out) || (!kp.ghost_gradients && !drop_out));
         int ti = -1;
@@ -175,9 +176,9 @@ __global__ void __launch_bounds__(kBlock) k_splat_backward(PointStreams pts, Cam
         for (int l = 0; l < lt.L; ++l, scale *= 0.5f, rad *= 0.5f, x *= 0.5f, y *= 0.5f)
         {
             if (kp.drop_out_points_by_radius && rad < kp.drop_out_radius_threshold) continue;
-            const int px = round_half_even(x), py = round_half_even(y);
+            const int px = round_half_even_bounded(x), py = round_half_even_bounded(y);
             const int w = lt.w[l], h = lt.h[l];
-            if (px < 0 || py < 0 || px >= w || py >= h) continue;
+            if ((unsigned)px >= (unsigned)w || (unsigned)py >= (unsigned)h) continue;
             const size_t pix = (size_t)py * w + px;
             const float* __restrict__ D = lt.depth[l];
             const float* __restrict__ W = lt.weight[l];
@@ -355,18 +356,26 @@ static adop_status launch_view_backward(const PointStreams& pts, const CamSource
                                         const BackwardTargets& bt, float* grad_background, float* grad_env, int env_h, int env_w,
                                         cudaStream_t st, int grid_points, int model)
 {
+    (void)grid_points;
+    const int need = (pts.n + kBlock - 1) / kBlock;
     {
+        static const int cap = resident_grid(k_prepare_backward<C>, 1ll << 40);
         unsigned total = lt.rec_off[kMaxLayers];
         int grid_px = (int)((total + kBlock - 1) / kBlock);
-        int cap = sm_count() * 8;
         if (grid_px > cap) grid_px = cap;
         k_prepare_backward<C><<<grid_px, kBlock, 0, st>>>(lt, cam, kp, bt.background, const_cast<float*>(bt.records),
                                                            grad_background, grad_env, env_h, env_w);
     }
     if (model == kPinholeDistortion)
-        k_splat_backward<C, kPinholeDistortion><<<grid_points, kBlock, 0, st>>>(pts, cam, kp, lt, bt);
+    {
+        static const int g = resident_grid(k_splat_backward<C, kPinholeDistortion>, 1ll << 40);
+        k_splat_backward<C, kPinholeDistortion><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(pts, cam, kp, lt, bt);
+    }
     else
-        k_splat_backward<C, kOcam><<<grid_points, kBlock, 0, st>>>(pts, cam, kp, lt, bt);
+    {
+        static const int g = resident_grid(k_splat_backward<C, kOcam>, 1ll << 40);
+        k_splat_backward<C, kOcam><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(pts, cam, kp, lt, bt);
+    }
     ADOP_CUDA_TRY(cudaGetLastError());
     return ADOP_OK;
 }

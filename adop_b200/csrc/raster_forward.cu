@@ -39,15 +39,16 @@ __global__ void __launch_bounds__(kBlock) k_depth_prepass(PointStreams pts, CamS
     {
         FetchedPoint f = fetch_point(pts, i);
         RasterPoint q;
-        if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, kp.check_normal != 0, kp.dist_cutoff, &q)) continue;
+        if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, kp.check_normal != 0, kp.dist_cutoff, &q,
+                                kp.drop_out_points_by_radius != 0)) continue;
         float x = q.x, y = q.y, rad = q.radius_px;
         const int zi = __float_as_int(q.z);
 #pragma unroll
         for (int l = 0; l < L; ++l, rad *= 0.5f, x *= 0.5f, y *= 0.5f)
         {
             if (kp.drop_out_points_by_radius && rad < kp.drop_out_radius_threshold) break;
-            int px = round_half_even(x), py = round_half_even(y);
-            if (px < 0 || py < 0 || px >= lt.w[l] || py >= lt.h[l]) continue;
+            int px = round_half_even_bounded(x), py = round_half_even_bounded(y);
+            if ((unsigned)px >= (unsigned)lt.w[l] || (unsigned)py >= (unsigned)lt.h[l]) continue;
             int* dst = reinterpret_cast<int*>(lt.depth[l]) + (size_t)py * lt.w[l] + px;
             // early z (PointRenderer.cu:275-279): a stale value only costs an extra atomic
             if (zi >= __ldcg(dst)) continue;
@@ -93,7 +94,8 @@ __global__ void __launch_bounds__(kBlock) k_blend(PointStreams pts, const float*
         if (point_dropped(kp, i)) continue;
         FetchedPoint f = fetch_point(pts, i);
         RasterPoint q;
-        if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, kp.check_normal != 0, kp.dist_cutoff, &q)) continue;
+        if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, kp.check_normal != 0, kp.dist_cutoff, &q,
+                                kp.drop_out_points_by_radius != 0)) continue;
         float x = q.x, y = q.y, rad = q.radius_px;
         bool have_t = false;
         float t[C];
@@ -101,8 +103,8 @@ __global__ void __launch_bounds__(kBlock) k_blend(PointStreams pts, const float*
         for (int l = 0; l < L; ++l, rad *= 0.5f, x *= 0.5f, y *= 0.5f)
         {
             if (kp.drop_out_points_by_radius && rad < kp.drop_out_radius_threshold) break;
-            int px = round_half_even(x), py = round_half_even(y);
-            if (px < 0 || py < 0 || px >= lt.w[l] || py >= lt.h[l]) continue;
+            int px = round_half_even_bounded(x), py = round_half_even_bounded(y);
+            if ((unsigned)px >= (unsigned)lt.w[l] || (unsigned)py >= (unsigned)lt.h[l]) continue;
             size_t pix = (size_t)py * lt.w[l] + px;
             float image_depth = __ldg(lt.depth[l] + pix);
             if (q.z > image_depth * kp.depth_accept_plus_one) continue;
@@ -194,10 +196,16 @@ template <int L, int C>
 static adop_status launch_view_forward(const PointStreams& pts, const adop_scene* s, const CamSource& cam, const KernelParams& kp,
                                        const LayerTable& lt, float* accum, bool env, cudaStream_t st, int grid_points)
 {
-    k_depth_prepass<L><<<grid_points, kBlock, 0, st>>>(pts, cam, kp, lt);
-    k_blend<L, C><<<grid_points, kBlock, 0, st>>>(pts, s->texture, s->num_texels, cam, kp, lt, accum);
+    (void)grid_points;
+    static const int g_depth = resident_grid(k_depth_prepass<L>, 1ll << 40);
+    static const int g_blend = resident_grid(k_blend<L, C>, 1ll << 40);
+    static const int g_resolve = resident_grid(k_resolve<C>, 1ll << 40);
+    const int need = (pts.n + kBlock - 1) / kBlock;
+    k_depth_prepass<L><<<need < g_depth ? (need < 1 ? 1 : need) : g_depth, kBlock, 0, st>>>(pts, cam, kp, lt);
+    k_blend<L, C><<<need < g_blend ? (need < 1 ? 1 : need) : g_blend, kBlock, 0, st>>>(pts, s->texture, s->num_texels, cam, kp, lt, accum);
     unsigned total = lt.rec_off[kMaxLayers];
     int grid_px = (int)((total + kBlock - 1) / kBlock);
+    if (grid_px > g_resolve) grid_px = g_resolve;
     k_resolve<C><<<grid_px, kBlock, 0, st>>>(lt, cam, kp, accum, s->background, env ? s->env_map : nullptr, s->env_h, s->env_w);
     ADOP_CUDA_TRY(cudaGetLastError());
     return ADOP_OK;

@@ -1,10 +1,13 @@
 // adop_math.h — the arithmetic specification of the one-pixel point rasterizer.
 //
 // Every function here compiles both for the host (g++) and for the device (nvcc) and is written so that
-// both produce the same bits: single operations per statement where order matters, no fast-math, IEEE
-// division and square root, own polynomial atan/atan2/acos instead of the two different libm versions.
-// Build rules that the bit-equality relies on:  g++ -ffp-contract=off   /   nvcc -fmad=false
-// (-prec-div=true and -prec-sqrt=true are nvcc defaults).
+// both produce the same bits: a fixed operation order, fused multiply-adds only where fmaf() is written out
+// (correctly rounded on both sides), no fast-math, IEEE division and square root, own polynomial
+// atan/atan2/acos instead of the two different libm versions.
+// Build rules that the bit-equality relies on:  g++ -ffp-contract=off (-mfma makes fmaf one instruction)
+// and nvcc -fmad=false (-prec-div=true and -prec-sqrt=true are nvcc defaults).
+// The point kernels are instruction-issue bound as much as memory bound, so the forward projection is
+// written for a short instruction stream: Horner forms in fmaf, one reciprocal instead of several divisions.
 //
 // The reference (darglein/ADOP) takes all of this arithmetic from the saiga library, whose source is not
 // part of the reference tree; each function states the reference call site whose contract it restates and
@@ -52,6 +55,15 @@ ADOP_HD int round_half_even(float x)
     return (int)lrintf(x);  // default rounding mode = to nearest even
 #endif
 }
+// the same for |x| < 1e9 (what project_for_raster guarantees for image positions): no clamp needed
+ADOP_HD int round_half_even_bounded(float x)
+{
+#if defined(__CUDA_ARCH__)
+    return __float2int_rn(x);
+#else
+    return (int)lrintf(x);  // default rounding mode = to nearest even
+#endif
+}
 
 // Counter-based hash for the per-(view,point) Bernoulli drop-out decision. The reference draws
 // bernoulli_() into a [B,N] float tensor (PointRenderer.cu:1081-1088); a hash needs no memory.
@@ -81,12 +93,12 @@ ADOP_HD float atan_core(float x)  // |x| <= tan(pi/8)
 {
     float z = x * x;
     float p = -0.06065608f;
-    p = p * z + 0.10588396f;
-    p = p * z + -0.14242722f;
-    p = p * z + 0.19998422f;
-    p = p * z + -0.33333313f;
+    p = fmaf(p, z, 0.10588396f);
+    p = fmaf(p, z, -0.14242722f);
+    p = fmaf(p, z, 0.19998422f);
+    p = fmaf(p, z, -0.33333313f);
     float x3 = z * x;
-    return x + x3 * p;
+    return fmaf(x3, p, x);
 }
 ADOP_HD float atan_unit(float t)  // 0 <= t <= 1
 {
@@ -143,17 +155,17 @@ struct V2 { float x, y; };
 // formula of Eigen's quaternion-vector product that Sophus' SO3 * point resolves to.
 ADOP_HD V3 rotate_q(float qx, float qy, float qz, float qw, V3 v)
 {
-    float ux = qy * v.z - qz * v.y;
-    float uy = qz * v.x - qx * v.z;
-    float uz = qx * v.y - qy * v.x;
+    float ux = fmaf(qy, v.z, -(qz * v.y));
+    float uy = fmaf(qz, v.x, -(qx * v.z));
+    float uz = fmaf(qx, v.y, -(qy * v.x));
     ux = ux + ux; uy = uy + uy; uz = uz + uz;
-    float cx = qy * uz - qz * uy;
-    float cy = qz * ux - qx * uz;
-    float cz = qx * uy - qy * ux;
+    float cx = fmaf(qy, uz, -(qz * uy));
+    float cy = fmaf(qz, ux, -(qx * uz));
+    float cz = fmaf(qx, uy, -(qy * ux));
     V3 o;
-    o.x = (v.x + qw * ux) + cx;
-    o.y = (v.y + qw * uy) + cy;
-    o.z = (v.z + qw * uz) + cz;
+    o.x = fmaf(qw, ux, v.x) + cx;
+    o.y = fmaf(qw, uy, v.y) + cy;
+    o.z = fmaf(qw, uz, v.z) + cz;
     return o;
 }
 ADOP_HD V3 rotate(const Pose32& P, V3 v)     { return rotate_q(P.qx, P.qy, P.qz, P.qw, v); }
@@ -193,8 +205,8 @@ ADOP_HD Intr5 load_intr5(const float* p) { Intr5 K; K.fx = p[0]; K.fy = p[1]; K.
 ADOP_HD V2 normalized_to_image(const Intr5& K, V2 p)
 {
     V2 o;
-    o.x = (K.fx * p.x + K.s * p.y) + K.cx;
-    o.y = K.fy * p.y + K.cy;
+    o.x = fmaf(K.fx, p.x, fmaf(K.s, p.y, K.cx));
+    o.y = fmaf(K.fy, p.y, K.cy);
     return o;
 }
 ADOP_HD V2 image_to_normalized(const Intr5& K, V2 ip)  // unproject2 (EnvironmentMap.cu:82)
@@ -229,20 +241,19 @@ ADOP_HD V2 distort(V2 m, const Dist8& d, float cutoff, bool* rejected, float* J_
     float x2 = x * x, y2 = y * y;
     float r2 = x2 + y2;
     float xy2 = (x + x) * y;
-    float r4 = r2 * r2;
-    float r6 = r4 * r2;
-    float num = ((1.0f + d.k1 * r2) + d.k2 * r4) + d.k3 * r6;
-    float den = ((1.0f + d.k4 * r2) + d.k5 * r4) + d.k6 * r6;
-    float iden = 1.0f / den;
+    float num = fmaf(fmaf(fmaf(d.k3, r2, d.k2), r2, d.k1), r2, 1.0f);
+    float den = fmaf(fmaf(fmaf(d.k6, r2, d.k5), r2, d.k4), r2, 1.0f);
+    float iden = den == 1.0f ? 1.0f : 1.0f / den;  // same bits either way; skips the division for k4 = k5 = k6 = 0
     float rad = num * iden;
-    float tx = d.p1 * xy2 + d.p2 * (r2 + (x2 + x2));
-    float ty = d.p1 * (r2 + (y2 + y2)) + d.p2 * xy2;
+    float tx = fmaf(d.p1, xy2, d.p2 * fmaf(2.0f, x2, r2));
+    float ty = fmaf(d.p2, xy2, d.p1 * fmaf(2.0f, y2, r2));
     V2 o;
-    o.x = x * rad + tx;
-    o.y = y * rad + ty;
+    o.x = fmaf(x, rad, tx);
+    o.y = fmaf(y, rad, ty);
     *rejected = r2 > cutoff * cutoff;
     if (J_p)
     {
+        float r4 = r2 * r2;
         float dnum = (d.k1 + 2.0f * d.k2 * r2) + 3.0f * d.k3 * r4;
         float dden = (d.k4 + 2.0f * d.k5 * r2) + 3.0f * d.k6 * r4;
         float drad_dr2 = (dnum * den - num * dden) * (iden * iden);
@@ -255,6 +266,8 @@ ADOP_HD V2 distort(V2 m, const Dist8& d, float cutoff, bool* rejected, float* J_
     }
     if (J_d)
     {
+        float r4 = r2 * r2;
+        float r6 = r4 * r2;
         float a1 = r2 * iden, a2 = r4 * iden, a3 = r6 * iden;
         float nb = -(num * (iden * iden));
         float b1 = nb * r2, b2 = nb * r4, b3 = nb * r6;
@@ -277,13 +290,11 @@ ADOP_HD V2 undistort_simple(V2 dpt, const Dist8& d)
         float x2 = x * x, y2 = y * y;
         float r2 = x2 + y2;
         float xy2 = (x + x) * y;
-        float r4 = r2 * r2;
-        float r6 = r4 * r2;
-        float num = ((1.0f + d.k1 * r2) + d.k2 * r4) + d.k3 * r6;
-        float den = ((1.0f + d.k4 * r2) + d.k5 * r4) + d.k6 * r6;
+        float num = fmaf(fmaf(fmaf(d.k3, r2, d.k2), r2, d.k1), r2, 1.0f);
+        float den = fmaf(fmaf(fmaf(d.k6, r2, d.k5), r2, d.k4), r2, 1.0f);
         float irad = den / num;
-        float tx = d.p1 * xy2 + d.p2 * (r2 + (x2 + x2));
-        float ty = d.p1 * (r2 + (y2 + y2)) + d.p2 * xy2;
+        float tx = fmaf(d.p1, xy2, d.p2 * fmaf(2.0f, x2, r2));
+        float ty = fmaf(d.p2, xy2, d.p1 * fmaf(2.0f, y2, r2));
         m.x = (dpt.x - tx) * irad;
         m.y = (dpt.y - ty) * irad;
     }
@@ -307,15 +318,20 @@ ADOP_HD Projected project_pinhole(V3 p, V3 n, bool has_normal, const Pose32& V, 
     Projected r;
     r.view = transform_point(V, p);
     float z = fmaxf(r.view.z, 0.f);
+    r.z = 0.f;
+    r.ip.x = 0.f; r.ip.y = 0.f;
+    if (!(z > 0.f)) return r;  // behind the camera: the reference carries z = 0 to its skip at PointRenderer.cu:254
     if (check_normal && has_normal)
     {
         V3 vn = rotate(V, n);
-        float dt = (r.view.x * vn.x + r.view.y * vn.y) + r.view.z * vn.z;
-        if (dt > 0.f) z = 0.f;
+        float dt = fmaf(r.view.z, vn.z, fmaf(r.view.y, vn.y, r.view.x * vn.x));
+        if (dt > 0.f) return r;
     }
+    // DivideByZ (PointRendererHelper.h:70) as one reciprocal and two products
+    float iz = 1.0f / r.view.z;
     V2 m;
-    m.x = r.view.x / r.view.z;
-    m.y = r.view.y / r.view.z;
+    m.x = r.view.x * iz;
+    m.y = r.view.y * iz;
     bool rejected;
     V2 dp = distort(m, dist, dist_cutoff, &rejected, nullptr, nullptr);
     if (rejected) z = 0.f;
@@ -337,7 +353,7 @@ struct Ocam
 };
 ADOP_HD V2 ocam_project(V3 v, const Ocam& o, float cutoff, float* depth, float* J_p /*2x3*/, float* J_aff /*2x5*/)
 {
-    float l2 = v.x * v.x + v.y * v.y;
+    float l2 = fmaf(v.x, v.x, v.y * v.y);
     float l = fmaxf(sqrtf(l2), 1.0e-12f);
     float il = 1.0f / l;
     float t = -v.z * il;
@@ -345,15 +361,15 @@ ADOP_HD V2 ocam_project(V3 v, const Ocam& o, float cutoff, float* depth, float* 
     float rho = 0.f, drho = 0.f;
     for (int i = o.npoly - 1; i >= 0; --i)
     {
-        drho = drho * theta + rho;
-        rho = rho * theta + o.poly[i];
+        if (J_p) drho = fmaf(drho, theta, rho);
+        rho = fmaf(rho, theta, o.poly[i]);
     }
     float s = rho * il;
     float xp = v.x * s, yp = v.y * s;
     V2 ip;
-    ip.x = (o.c * xp + o.d * yp) + o.cx;
-    ip.y = (o.e * xp + yp) + o.cy;
-    float nrm = sqrtf(l2 + v.z * v.z);
+    ip.x = fmaf(o.c, xp, fmaf(o.d, yp, o.cx));
+    ip.y = fmaf(o.e, xp, yp + o.cy);
+    float nrm = sqrtf(fmaf(v.z, v.z, l2));
     *depth = (t > cutoff) ? 0.f : nrm;
     if (J_p)
     {
@@ -392,7 +408,7 @@ ADOP_HD Projected project_ocam(V3 p, V3 n, bool has_normal, const Pose32& V, con
     if (check_normal && has_normal)
     {
         V3 vn = rotate(V, n);
-        float dt = (r.view.x * vn.x + r.view.y * vn.y) + r.view.z * vn.z;
+        float dt = fmaf(r.view.z, vn.z, fmaf(r.view.y, vn.y, r.view.x * vn.x));
         if (dt > 0.f) z = 0.f;
     }
     r.z = z;
@@ -451,7 +467,7 @@ struct RasterPoint
 
 // false = the point does not take part in this view (z == 0 in the reference, PointRenderer.cu:254)
 ADOP_HD bool project_for_raster(const ViewCam& c, V3 p, float drop_out_radius, V3 n, bool has_normal,
-                                bool check_normal, float dist_cutoff, RasterPoint* out)
+                                bool check_normal, float dist_cutoff, RasterPoint* out, bool want_radius = true)
 {
     Projected pr;
     float focal;
@@ -467,8 +483,12 @@ ADOP_HD bool project_for_raster(const ViewCam& c, V3 p, float drop_out_radius, V
     }
     if (!(pr.z > 0.f)) return false;
     V2 ip = normalized_to_image(c.crop, pr.ip);
+    // positions that are not finite or absurdly far off can not land in any layer; rejecting them here keeps the
+    // per-layer rounding free of range checks
+    if (!(fabsf(ip.x) < 1.0e9f) || !(fabsf(ip.y) < 1.0e9f)) return false;
     out->x = ip.x; out->y = ip.y; out->z = pr.z;
-    out->radius_px = focal * drop_out_radius / pr.z;
+    // only the radius drop-out rule reads it (PointRenderer.cu:261-264); skipping it saves a division
+    out->radius_px = want_radius ? focal * drop_out_radius / pr.z : 0.f;
     return true;
 }
 
@@ -498,11 +518,11 @@ ADOP_HD bool project_pinhole_backward(V3 p, V3 n, bool has_normal, V2 g, const P
     if (check_normal && has_normal)
     {
         V3 vn = rotate(V, n);
-        float dt = (view.x * vn.x + view.y * vn.y) + view.z * vn.z;
+        float dt = fmaf(view.z, vn.z, fmaf(view.y, vn.y, view.x * vn.x));
         if (dt > 0.f) return false;
     }
     float iz = 1.0f / view.z;
-    V2 m; m.x = view.x / view.z; m.y = view.y / view.z;
+    V2 m; m.x = view.x * iz; m.y = view.y * iz;
     float Jp[4], Jd[16];
     bool rejected;
     V2 dp = distort(m, dist, dist_cutoff, &rejected, Jp, Jd);
@@ -535,7 +555,7 @@ ADOP_HD bool project_ocam_backward(V3 p, V3 n, bool has_normal, V2 g, const Pose
     if (check_normal && has_normal)
     {
         V3 vn = rotate(V, n);
-        float dt = (view.x * vn.x + view.y * vn.y) + view.z * vn.z;
+        float dt = fmaf(view.z, vn.z, fmaf(view.y, vn.y, view.x * vn.x));
         if (dt > 0.f) return false;
     }
     float Jp[6], Ja[10], z;

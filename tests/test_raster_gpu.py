@@ -236,7 +236,7 @@ def test_argument_errors(cuda_lib):
     bad = [dict(cfg["views"][0], image_index=5)]
     with pytest.raises(capi.AdopError, match="invalid argument"):
         r.forward(scene, bad, cfg["params"], 4)
-    with pytest.raises(capi.AdopError, match="invalid argument"):
+    with pytest.raises((capi.AdopError, ValueError)):
         r.forward(scene, cfg["views"], cfg["params"], 9)
     with pytest.raises(capi.AdopError):
         r.forward(Scene(**{k: (v.cpu() if v is not None else None) for k, v in scene.tensors().items()}),
