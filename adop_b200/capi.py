@@ -73,11 +73,15 @@ class AdopTonemapGrads(C.Structure):
                 ("accumulate", C.c_int32)]
 
 
+class AdopKernelTime(C.Structure):
+    _fields_ = [("name", C.c_char * 48), ("launches", C.c_int32), ("total_ms", C.c_float)]
+
+
 # every symbol include/adop/adop_raster.h declares
 EXPORTED_SYMBOLS = [
     "adop_status_string", "adop_last_error", "adop_render_params_default", "adop_raster_workspace_bytes",
     "adop_raster_forward", "adop_raster_backward", "adop_raster_normalize_gradients", "adop_apply_tangent",
-    "adop_tonemap_forward", "adop_tonemap_backward",
+    "adop_tonemap_forward", "adop_tonemap_backward", "adop_profile_enable", "adop_profile_collect",
 ]
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
@@ -115,6 +119,10 @@ def load_library():
     lib.adop_tonemap_forward.argtypes = [C.POINTER(AdopTonemapParams), C.c_void_p, C.c_void_p, C.c_void_p]
     lib.adop_tonemap_backward.argtypes = [C.POINTER(AdopTonemapParams), C.c_void_p, C.c_void_p,
                                           C.POINTER(AdopTonemapGrads), C.c_void_p]
+    lib.adop_profile_enable.argtypes = [C.c_int32]
+    lib.adop_profile_enable.restype = C.c_int
+    lib.adop_profile_collect.argtypes = [C.POINTER(AdopKernelTime), C.c_int32]
+    lib.adop_profile_collect.restype = C.c_int32
     for name in ("adop_raster_forward", "adop_raster_backward", "adop_raster_normalize_gradients",
                  "adop_apply_tangent", "adop_tonemap_forward", "adop_tonemap_backward"):
         getattr(lib, name).restype = C.c_int
@@ -127,6 +135,21 @@ def check(status, what):
         lib = load_library()
         raise AdopError(f"{what}: {lib.adop_status_string(status).decode()} ({status}) "
                         f"{lib.adop_last_error().decode()}")
+
+
+def profile_enable(on=True):
+    """Bracket every kernel launch of the library with CUDA events (the CudaTimerSystem scopes of the reference)."""
+    load_library().adop_profile_enable(1 if on else 0)
+
+
+def profile_collect():
+    """-> {kernel name: (launches, total ms)}; synchronises the recorded events and resets the collection."""
+    lib = load_library()
+    buf = (AdopKernelTime * 64)()
+    n = lib.adop_profile_collect(buf, 64)
+    if n < 0:
+        raise AdopError("adop_profile_collect: CUDA error while reading events")
+    return {buf[i].name.decode(): (buf[i].launches, buf[i].total_ms) for i in range(min(n, 64))}
 
 
 def default_render_params():

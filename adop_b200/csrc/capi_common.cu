@@ -1,6 +1,10 @@
 // Status strings, defaults, argument validation: the parts of the C ABI that launch nothing.
 #include <string.h>
 
+#include <map>
+#include <string>
+#include <vector>
+
 #include "common.cuh"
 
 namespace adop {
@@ -15,6 +19,47 @@ adop_status record_cuda_error(cudaError_t e, const char* what)
 {
     snprintf(last_error_buffer(), 512, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
     return ADOP_ERR_CUDA;
+}
+
+namespace {
+struct ProfileMark { const char* name; cudaEvent_t begin, end; };
+struct ProfileState
+{
+    bool on = false;
+    std::vector<ProfileMark> marks;
+    std::vector<cudaEvent_t> pool;
+};
+ProfileState& profile_state()
+{
+    static thread_local ProfileState st;
+    return st;
+}
+cudaEvent_t profile_event(ProfileState& ps)
+{
+    if (!ps.pool.empty()) { cudaEvent_t e = ps.pool.back(); ps.pool.pop_back(); return e; }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+}
+}  // namespace
+
+bool profile_on() { return profile_state().on; }
+
+void profile_mark(const char* name, cudaStream_t st, bool begin)
+{
+    ProfileState& ps = profile_state();
+    if (begin)
+    {
+        ProfileMark m{name, profile_event(ps), nullptr};
+        if (m.begin) cudaEventRecord(m.begin, st);
+        ps.marks.push_back(m);
+    }
+    else if (!ps.marks.empty())
+    {
+        ProfileMark& m = ps.marks.back();
+        m.end = profile_event(ps);
+        if (m.end) cudaEventRecord(m.end, st);
+    }
 }
 
 int sm_count()
@@ -83,6 +128,49 @@ extern "C" const char* adop_status_string(adop_status s)
         case ADOP_ERR_SIZE_LIMIT: return "size beyond the supported maximum";
     }
     return "unknown status";
+}
+
+extern "C" adop_status adop_profile_enable(int32_t on)
+{
+    adop::profile_state().on = on != 0;
+    return ADOP_OK;
+}
+
+extern "C" int32_t adop_profile_collect(adop_kernel_time* out, int32_t max_entries)
+{
+    auto& ps = adop::profile_state();
+    std::map<std::string, std::pair<int, float>> acc;
+    std::vector<std::string> order;
+    bool failed = false;
+    for (auto& m : ps.marks)
+    {
+        float ms = 0.f;
+        if (m.begin && m.end && cudaEventSynchronize(m.end) == cudaSuccess && cudaEventElapsedTime(&ms, m.begin, m.end) == cudaSuccess)
+        {
+            auto it = acc.find(m.name);
+            if (it == acc.end()) { acc[m.name] = {1, ms}; order.push_back(m.name); }
+            else { it->second.first += 1; it->second.second += ms; }
+        }
+        else
+            failed = true;
+        if (m.begin) ps.pool.push_back(m.begin);
+        if (m.end) ps.pool.push_back(m.end);
+    }
+    ps.marks.clear();
+    if (failed) return -1;
+    int n = 0;
+    for (auto& name : order)
+    {
+        if (out && n < max_entries)
+        {
+            memset(&out[n], 0, sizeof(out[n]));
+            strncpy(out[n].name, name.c_str(), sizeof(out[n].name) - 1);
+            out[n].launches = acc[name].first;
+            out[n].total_ms = acc[name].second;
+        }
+        ++n;
+    }
+    return n;
 }
 
 extern "C" const char* adop_last_error(void) { return adop::last_error_buffer(); }

@@ -21,6 +21,16 @@ adop_status record_cuda_error(cudaError_t e, const char* what);
         if (_e != cudaSuccess) return ::adop::record_cuda_error(_e, #expr);     \
     } while (0)
 
+// Optional per-kernel timing (adop_profile_enable): records an event before and after the launch expression.
+bool profile_on();
+void profile_mark(const char* name, cudaStream_t st, bool begin);
+#define ADOP_LAUNCH(name, st, launch_expr)                          \
+    do {                                                            \
+        if (::adop::profile_on()) ::adop::profile_mark(name, st, true);  \
+        launch_expr;                                                \
+        if (::adop::profile_on()) ::adop::profile_mark(name, st, false); \
+    } while (0)
+
 // Everything a kernel needs to know about the pyramid of ONE view: sizes and the view's slice of every
 // per-layer tensor (pointers already advanced to batch entry b).
 struct LayerTable

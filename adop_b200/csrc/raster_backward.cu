@@ -363,18 +363,21 @@ static adop_status launch_view_backward(const PointStreams& pts, const CamSource
         unsigned total = lt.rec_off[kMaxLayers];
         int grid_px = (int)((total + kBlock - 1) / kBlock);
         if (grid_px > cap) grid_px = cap;
-        k_prepare_backward<C><<<grid_px, kBlock, 0, st>>>(lt, cam, kp, bt.background, const_cast<float*>(bt.records),
-                                                           grad_background, grad_env, env_h, env_w);
+        ADOP_LAUNCH("k_prepare_backward", st, (k_prepare_backward<C><<<grid_px, kBlock, 0, st>>>(
+                                                  lt, cam, kp, bt.background, const_cast<float*>(bt.records), grad_background,
+                                                  grad_env, env_h, env_w)));
     }
     if (model == kPinholeDistortion)
     {
         static const int g = resident_grid(k_splat_backward<C, kPinholeDistortion>, 1ll << 40);
-        k_splat_backward<C, kPinholeDistortion><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(pts, cam, kp, lt, bt);
+        ADOP_LAUNCH("k_splat_backward", st, (k_splat_backward<C, kPinholeDistortion><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(
+                                                pts, cam, kp, lt, bt)));
     }
     else
     {
         static const int g = resident_grid(k_splat_backward<C, kOcam>, 1ll << 40);
-        k_splat_backward<C, kOcam><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(pts, cam, kp, lt, bt);
+        ADOP_LAUNCH("k_splat_backward", st, (k_splat_backward<C, kOcam><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(
+                                                pts, cam, kp, lt, bt)));
     }
     ADOP_CUDA_TRY(cudaGetLastError());
     return ADOP_OK;
@@ -394,15 +397,15 @@ extern "C" adop_status adop_raster_normalize_gradients(float* grad_points, int32
     {
         if (!count_pose || num_images <= 0) return ADOP_ERR_INVALID_ARGUMENT;
         int n = num_images * 6;
-        k_normalize_pose<<<(n + 127) / 128, 128, 0, st>>>(grad_pose, count_pose, num_images);
+        ADOP_LAUNCH("k_normalize", st, (k_normalize_pose<<<(n + 127) / 128, 128, 0, st>>>(grad_pose, count_pose, num_images)));
     }
     if (grad_points && num_points > 0)
-        k_normalize_points<<<(num_points + 255) / 256, 256, 0, st>>>(reinterpret_cast<float4*>(grad_points), num_points);
+        ADOP_LAUNCH("k_normalize", st, (k_normalize_points<<<(num_points + 255) / 256, 256, 0, st>>>(reinterpret_cast<float4*>(grad_points), num_points)));
     if (grad_intrinsics)
     {
         if (!count_intrinsics || num_cameras <= 0 || intrinsics_cols <= 0) return ADOP_ERR_INVALID_ARGUMENT;
         int n = num_cameras * intrinsics_cols;
-        k_normalize_intrinsics<<<(n + 127) / 128, 128, 0, st>>>(grad_intrinsics, count_intrinsics, num_cameras, intrinsics_cols);
+        ADOP_LAUNCH("k_normalize", st, (k_normalize_intrinsics<<<(n + 127) / 128, 128, 0, st>>>(grad_intrinsics, count_intrinsics, num_cameras, intrinsics_cols)));
     }
     ADOP_CUDA_TRY(cudaGetLastError());
     return ADOP_OK;

@@ -201,12 +201,15 @@ static adop_status launch_view_forward(const PointStreams& pts, const adop_scene
     static const int g_blend = resident_grid(k_blend<L, C>, 1ll << 40);
     static const int g_resolve = resident_grid(k_resolve<C>, 1ll << 40);
     const int need = (pts.n + kBlock - 1) / kBlock;
-    k_depth_prepass<L><<<need < g_depth ? (need < 1 ? 1 : need) : g_depth, kBlock, 0, st>>>(pts, cam, kp, lt);
-    k_blend<L, C><<<need < g_blend ? (need < 1 ? 1 : need) : g_blend, kBlock, 0, st>>>(pts, s->texture, s->num_texels, cam, kp, lt, accum);
+    ADOP_LAUNCH("k_depth_prepass", st,
+                (k_depth_prepass<L><<<need < g_depth ? (need < 1 ? 1 : need) : g_depth, kBlock, 0, st>>>(pts, cam, kp, lt)));
+    ADOP_LAUNCH("k_blend", st, (k_blend<L, C><<<need < g_blend ? (need < 1 ? 1 : need) : g_blend, kBlock, 0, st>>>(
+                                   pts, s->texture, s->num_texels, cam, kp, lt, accum)));
     unsigned total = lt.rec_off[kMaxLayers];
     int grid_px = (int)((total + kBlock - 1) / kBlock);
     if (grid_px > g_resolve) grid_px = g_resolve;
-    k_resolve<C><<<grid_px, kBlock, 0, st>>>(lt, cam, kp, accum, s->background, env ? s->env_map : nullptr, s->env_h, s->env_w);
+    ADOP_LAUNCH("k_resolve", st, (k_resolve<C><<<grid_px, kBlock, 0, st>>>(lt, cam, kp, accum, s->background,
+                                                                          env ? s->env_map : nullptr, s->env_h, s->env_w)));
     ADOP_CUDA_TRY(cudaGetLastError());
     return ADOP_OK;
 }
@@ -280,7 +283,7 @@ extern "C" adop_status adop_raster_forward(const adop_scene* s, const adop_view*
         if (n == 0) continue;
         int grid = (int)((n / 4 + kBlock - 1) / kBlock) + 1;
         if (grid > sms * 16) grid = sms * 16;
-        k_fill<<<grid, kBlock, 0, st>>>(io->layers[l].depth, n, kDepthInit);
+        ADOP_LAUNCH("k_fill", st, (k_fill<<<grid, kBlock, 0, st>>>(io->layers[l].depth, n, kDepthInit)));
     }
     ADOP_CUDA_TRY(cudaGetLastError());
 

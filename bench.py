@@ -1,0 +1,352 @@
+"""Benchmark of the point-rasterizer hot path: forward + backward of the training-scene workload.
+
+    python bench.py --gpus 1 --steps 20 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
+    python bench.py --impl reference ...      # the CPU restatement of the reference kernels on the host cores
+
+A step = one forward + backward of the rasterizer over one batch of views of the synthetic training scene
+(10 M points on 64 random spheres / plane patches, 16 views per GPU at 1920x1080 on a radius-4 orbit, pinhole with
+k1=-0.1 k2=0.02, 4-layer pyramid, 4 descriptor channels, 1024x512 environment map, pose / intrinsics / point gradients
+on). Metric: points rasterized per second forward+backward = points x views / time, in Gpts/s, summed over all GPUs.
+Multi-GPU: views are sharded over ranks (weak scaling: 16 views per GPU), the scene is replicated, and the descriptor
+and point gradients are reduce-scattered with NCCL before normalisation.
+Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "points rasterized/sec fwd+bwd at 1080p"
+UNIT = "Gpts/s"
+WORKLOAD = "c2: 10M points x 16 views/GPU, 1920x1080, L=4, C=4, pinhole k1=-0.1 k2=0.02, env 1024x512, fwd+bwd with pose grads"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--points", type=int, default=10_000_000)
+    ap.add_argument("--views", type=int, default=16, help="views per GPU")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def algorithmic_bytes(N, C, P, U_views, normals=False, point_grads=True, env_hw=None):
+    """Bytes that one step has to move at the least. Per view: forward N*2*(16+n) + U*(4+4C) + P*(4C+8), backward
+    N*(16+n) + U*(4+4C) + P*(8C+8); per step + 4CN for the descriptor gradient, + 20N with point gradients, + the
+    environment map read once forward and its gradient written once backward."""
+    n = 4 if normals else 0
+    fwd = sum(N * 2 * (16 + n) + U * (4 + 4 * C) + P * (4 * C + 8) for U in U_views)
+    bwd = sum(N * (16 + n) + U * (4 + 4 * C) + P * (8 * C + 8) for U in U_views)
+    step = 4 * C * N + (20 * N if point_grads else 0)
+    if env_hw:
+        step += 2 * 4 * C * env_hw[0] * env_hw[1]
+    per_view_bwd = [N * (16 + n) + U * (4 + 4 * C) + P * (8 * C + 8) for U in U_views]
+    return fwd, bwd, step, per_view_bwd
+
+
+def cpu_reference_arm(args, rank, world):
+    """--impl reference: the reference has no CPU rasterizer and its CUDA code cannot be built without the saiga library,
+    so this arm times the CPU restatement of the reference kernels (oracle/) with all host threads."""
+    if rank != 0:
+        return
+    import numpy as np
+    from adop_b200 import synth
+    from tests.oracle_lib import Oracle
+    ora = Oracle()
+    cores = ora.lib.adop_oracle_max_threads()
+    cfg = synth.make_config("c2", n_points=args.points, n_views=1)
+    arrays = cfg["arrays"]
+    stride = 4  # bounded sample: every 4th point of the Morton-sorted cloud, one view, full image size
+    arrays["position"] = np.ascontiguousarray(arrays["position"][::stride])
+    arrays["texture"] = np.ascontiguousarray(arrays["texture"][:, ::stride])
+    n = arrays["position"].shape[0]
+    grads = synth.upstream_gradients(cfg["meta"], batch=1)
+    times = []
+    for it in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        fwd = ora.forward(arrays, cfg["views"], cfg["params"], cfg["num_layers"], threads=cores)
+        ora.backward(arrays, cfg["views"], cfg["params"], cfg["num_layers"], fwd, grads, want_env=True, threads=cores)
+        dt = time.perf_counter() - t0
+        if it >= args.warmup:
+            times.append(dt)
+    total = sum(times)
+    value = n * len(times) / total / 1e9
+    sample = f"1 view, every {stride}th point of the cloud ({n} points), full 1080p pyramid, fwd+bwd per step"
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference kernels; the reference's own CUDA "
+                       "renderer needs the saiga library, which is not in its tree"},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        cpu_reference_arm(args, rank, world)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from adop_b200 import capi, synth
+    from adop_b200 import dist as adist
+    from adop_b200.raster import PointRasterizer, Scene
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path in the product)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    capi.load_library()
+
+    # ---- workload: the scene is replicated, every rank gets its own views on the orbit -------------------------------
+    V = args.views
+    cfg = synth.make_config("c2", n_points=args.points, n_views=V * world)
+    arrays, params, L = cfg["arrays"], cfg["params"], cfg["num_layers"]
+    my_ids = adist.shard_views(list(range(V * world)), rank, world)
+    views = capi.make_views([cfg["views"][i] for i in my_ids])
+    N, C = cfg["meta"]["n_points"], cfg["meta"]["channels"]
+    w, h = cfg["meta"]["w"], cfg["meta"]["h"]
+    P = sum(a * b for a, b in capi.layer_sizes(w, h, L))
+    scene = Scene(**{k: (torch.from_numpy(v).to(dev) if v is not None else None) for k, v in arrays.items()})
+    ras = PointRasterizer(dev)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234 + rank)
+    grads_dev = [torch.randn((V, C, hh, ww), device=dev, generator=gen) for ww, hh in capi.layer_sizes(w, h, L)]
+    grads_host = [g.cpu().pin_memory() for g in grads_dev]
+    normalize_local = world == 1
+
+    fwd = ras.forward(scene, views, params, L)
+    bwd = ras.backward(scene, params, fwd, grads_dev, want_env=True, normalize=normalize_local)
+    torch.cuda.synchronize()
+
+    def step():
+        ras.forward(scene, views, params, L, out=fwd)
+        ras.backward(scene, params, fwd, grads_dev, want_env=True, normalize=normalize_local, out=bwd)
+        if world > 1:
+            ex = adist.exchange_gradients(bwd)
+            # normalise the owned shard of the point gradients (sum / count), PointRenderer.cu:1620-1627
+            if adist.points_shard_is_aligned(N, world):
+                shard = ex["points_shard"]
+                ras.normalize_gradients({"points": shard.view(-1, 4), "pose": None, "intrinsics": None})
+            ras.normalize_gradients({"points": None, "pose": ex["pose"], "count_pose": ex["count_pose"],
+                                     "intrinsics": ex["intrinsics"], "count_intrinsics": ex["count_intrinsics"]})
+
+    kernels_per_step = L + 3 * V + 2 * V + 3  # depth fills, (prepass, blend, resolve) and (prepare, splat) per view, normalise
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-timed region (inputs resident in HBM) ---------------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    value = N * V * world * args.steps / (ms_total * 1e-3) / 1e9
+
+    # ---- end-to-end through the public API with host buffers ---------------------------------------------------------
+    # per step: host->device copy of the step's upstream gradient pyramid from pinned memory (it overlaps the forward
+    # pass on a copy stream), forward, backward, device->host read of the pose / intrinsics / background gradients.
+    copy_stream = torch.cuda.Stream(device=dev)
+    staged = [torch.empty_like(g) for g in grads_dev]
+    small_host = {k: torch.empty_like(bwd[k], device="cpu").pin_memory() for k in ("pose", "intrinsics", "background")}
+    h2d_bytes = sum(g.numel() * 4 for g in grads_host) + len(views) * 40
+    d2h_bytes = sum(v.numel() * v.element_size() for v in small_host.values())
+
+    def step_e2e():
+        main_stream = torch.cuda.current_stream(dev)
+        copy_stream.wait_stream(main_stream)
+        with torch.cuda.stream(copy_stream):
+            for s, hsrc in zip(staged, grads_host):
+                s.copy_(hsrc, non_blocking=True)
+        ras.forward(scene, views, params, L, out=fwd)
+        main_stream.wait_stream(copy_stream)
+        ras.backward(scene, params, fwd, staged, want_env=True, normalize=normalize_local, out=bwd)
+        if world > 1:
+            adist.exchange_gradients(bwd)
+        for k, hdst in small_host.items():
+            hdst.copy_(bwd[k], non_blocking=True)
+        main_stream.synchronize()
+
+    for _ in range(3):
+        step_e2e()
+    barrier()
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(args.steps):
+        step_e2e()
+    e1.record()
+    barrier()
+    ms_e2e = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms_e2e, op=dist.ReduceOp.MAX)
+    e2e_value = N * V * world * args.steps / (float(ms_e2e.item()) * 1e-3) / 1e9
+
+    # ---- per-kernel times (CUDA events around every launch, on the launching stream) and the roofline -----------------
+    capi.profile_enable(True)
+    for _ in range(max(1, min(args.steps, 5))):
+        ras.forward(scene, views, params, L, out=fwd)
+        ras.backward(scene, params, fwd, grads_dev, want_env=True, normalize=normalize_local, out=bwd)
+    torch.cuda.synchronize()
+    ktimes = capi.profile_collect()
+    capi.profile_enable(False)
+    ras.forward(scene, views, params, L, out=fwd)
+    torch.cuda.synchronize()
+    # U_v: points with at least one accepted layer, per view. Until the library reports it, the number of points accepted
+    # on the finest layer stands in for it (a lower bound, so `achieved` is a lower bound too).
+    U_views = [float(fwd.weights[0][b].sum().item()) for b in range(V)]
+    fwd_b, bwd_b, step_b, per_view_bwd = algorithmic_bytes(N, C, P, U_views, env_hw=arrays["env_map"].shape[1:])
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except (OSError, ValueError):
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_kind = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+    dom = max(ktimes.items(), key=lambda kv: kv[1][1])
+    dom_name, (dom_launches, dom_ms) = dom
+    dom_bytes = {"k_splat_backward": sum(per_view_bwd) / V}.get(dom_name, (fwd_b + bwd_b + step_b) / V)
+    achieved = dom_bytes / (dom_ms / dom_launches * 1e-3) / 1e9
+    step_ms = ms_total / args.steps
+    step_achieved = (fwd_b + bwd_b + step_b) / (step_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                "algorithmic_bytes_per_launch": dom_bytes, "avg_launch_ms": dom_ms / dom_launches,
+                "step": {"algorithmic_bytes": fwd_b + bwd_b + step_b, "achieved": step_achieved, "frac": step_achieved / peak},
+                "kernel_ms_per_step": {k: v[1] / max(1, min(args.steps, 5)) for k, v in ktimes.items()}}
+
+    # ---- CPU baseline (rank 0, N = 1): the CPU restatement on a bounded sample ------------------------------------------
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from tests.oracle_lib import Oracle
+        ora = Oracle()
+        cores = ora.lib.adop_oracle_max_threads()
+        stride = 4
+        sub = dict(arrays)
+        sub["position"] = np.ascontiguousarray(arrays["position"][::stride])
+        sub["texture"] = np.ascontiguousarray(arrays["texture"][:, ::stride])
+        one_view = [cfg["views"][0]]
+        g1 = [g[:1].contiguous().numpy() for g in grads_host]
+        reps, t_cpu = 0, 0.0
+        while t_cpu < 10.0 and reps < 8:
+            t0 = time.perf_counter()
+            f = ora.forward(sub, one_view, params, L, threads=cores)
+            ora.backward(sub, one_view, params, L, f, g1, want_env=True, threads=cores)
+            t_cpu += time.perf_counter() - t0
+            reps += 1
+        n_sub = sub["position"].shape[0]
+        cpu_baseline = {"value": n_sub * reps / t_cpu / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
+                        "sample": f"{reps} x (1 view, every {stride}th point = {n_sub} points, full 1080p pyramid, fwd+bwd)"}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+                "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic",
+                "config": {"workload": WORKLOAD, "points": N, "views_per_gpu": V, "image": [w, h], "layers": L, "channels": C,
+                           "l2": "inputs exceed L2: 160 MB of points and ~100 MB of image state per view stream per pass",
+                           "parallelism": f"view-sharded x{world}, gradients reduce-scattered" if world > 1 else "single GPU",
+                           "point_order": "Morton-sorted once (untimed), as the reference's scene preprocessing does"},
+                "fwd_ms_per_view": ktimes_ms(ktimes, ("k_fill", "k_depth_prepass", "k_blend", "k_resolve"), V, args),
+                "bwd_ms_per_view": ktimes_ms(ktimes, ("k_prepare_backward", "k_splat_backward", "k_normalize"), V, args),
+                "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
+                "gpu_launches": kernels_per_step * args.steps,
+                "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def ktimes_ms(ktimes, names, V, args):
+    reps = max(1, min(args.steps, 5))
+    return sum(ktimes[k][1] for k in names if k in ktimes) / reps / V
+
+
+if __name__ == "__main__":
+    main()

@@ -214,6 +214,21 @@ typedef struct adop_tonemap_grads
     int32_t accumulate;
 } adop_tonemap_grads;
 
+/* Per-kernel device timing, the role of the CudaTimerSystem scopes threaded through the reference
+ * (NeuralRenderInfo::timer_system, src/lib/rendering/PointRenderer.h:32; scopes at PointRenderer.cu:1414-1447,
+ * 1594-1610). While enabled, every kernel launch of this library is bracketed by CUDA events on its stream.
+ * adop_profile_collect synchronises those events, adds the times up per kernel name, writes up to max_entries
+ * records, forgets what it collected and returns the number of distinct kernels (or -1 on a CUDA error).
+ * Per host thread; off by default. */
+typedef struct adop_kernel_time
+{
+    char name[48];
+    int32_t launches;
+    float total_ms;
+} adop_kernel_time;
+adop_status adop_profile_enable(int32_t on);
+int32_t adop_profile_collect(adop_kernel_time* out, int32_t max_entries);
+
 adop_status adop_tonemap_forward(const adop_tonemap_params* p, const float* x, float* out, void* stream);
 adop_status adop_tonemap_backward(const adop_tonemap_params* p, const float* x, const float* grad_out,
                                   adop_tonemap_grads* g, void* stream);

@@ -280,6 +280,8 @@ int adop_oracle_backward(const adop_scene* s, const adop_view* views, int B, con
             const size_t plane = (size_t)w * h;
             Intr5 crop_l = scale_intr(cam.crop, ldexpf(1.0f, -l));
             const bool env = rp->composite_environment_map && s->env_map && io->grad_env_map;
+            std::vector<double> bg_rows((size_t)h * C, 0.0);  // per-row partial sums keep the scalar order fixed
+#pragma omp parallel for schedule(static) if (par)
             for (int y = 0; y < h; ++y)
                 for (int x = 0; x < w; ++x)
                 {
@@ -294,17 +296,36 @@ int adop_oracle_backward(const adop_scene* s, const adop_view* views, int B, con
                     for (int c = 0; c < C; ++c)
                     {
                         float g = io->grad_color[l][((size_t)b * C + c) * plane + pix];
-                        if (io->grad_background) io->grad_background[c] += g;
+                        bg_rows[(size_t)y * C + c] += g;
                         if (env)
                         {
                             float ge = (1.0f - rp->output_background_mask_value) * g;
                             float* e = io->grad_env_map + (size_t)c * s->env_h * s->env_w;
-                            e[(size_t)tp.y0 * s->env_w + tp.x0] += ge * (1.0f - tp.wx) * (1.0f - tp.wy);
-                            e[(size_t)tp.y0 * s->env_w + tp.x1] += ge * tp.wx * (1.0f - tp.wy);
-                            e[(size_t)tp.y1 * s->env_w + tp.x0] += ge * (1.0f - tp.wx) * tp.wy;
-                            e[(size_t)tp.y1 * s->env_w + tp.x1] += ge * tp.wx * tp.wy;
+                            float v00 = ge * (1.0f - tp.wx) * (1.0f - tp.wy), v01 = ge * tp.wx * (1.0f - tp.wy);
+                            float v10 = ge * (1.0f - tp.wx) * tp.wy, v11 = ge * tp.wx * tp.wy;
+                            if (par)
+                            {
+                                atomic_add_float(e + (size_t)tp.y0 * s->env_w + tp.x0, v00);
+                                atomic_add_float(e + (size_t)tp.y0 * s->env_w + tp.x1, v01);
+                                atomic_add_float(e + (size_t)tp.y1 * s->env_w + tp.x0, v10);
+                                atomic_add_float(e + (size_t)tp.y1 * s->env_w + tp.x1, v11);
+                            }
+                            else
+                            {
+                                e[(size_t)tp.y0 * s->env_w + tp.x0] += v00;
+                                e[(size_t)tp.y0 * s->env_w + tp.x1] += v01;
+                                e[(size_t)tp.y1 * s->env_w + tp.x0] += v10;
+                                e[(size_t)tp.y1 * s->env_w + tp.x1] += v11;
+                            }
                         }
                     }
+                }
+            if (io->grad_background)
+                for (int c = 0; c < C; ++c)
+                {
+                    double acc = 0.0;
+                    for (int y = 0; y < h; ++y) acc += bg_rows[(size_t)y * C + c];
+                    io->grad_background[c] += (float)acc;
                 }
         }
 
@@ -449,6 +470,7 @@ int adop_oracle_backward(const adop_scene* s, const adop_view* views, int B, con
                 if (c > 0) for (int k = 0; k < 6; ++k) io->grad_pose[(size_t)i * 6 + k] /= (double)c;
             }
         if (io->grad_points)
+#pragma omp parallel for schedule(static) if (par)
             for (int i = 0; i < N; ++i)
             {
                 float* gp = io->grad_points + (size_t)i * 4;

@@ -1,0 +1,77 @@
+"""World-size-2 gloo test of the view-sharded gradient exchange (host logic only, no GPU).
+
+Each rank computes un-normalised gradients of its own views with the CPU checker, the exchange sums and shards them, the
+shards are normalised, and the result must equal the single-process gradient over all views."""
+import os
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from adop_b200 import synth
+from adop_b200 import dist as adist
+
+
+def _normalize_points(flat):
+    p = flat.reshape(-1, 4).copy()
+    c = p[:, 3:4]
+    p[:, :3] = np.where(c > 0, p[:, :3] / np.maximum(c, 1e-30), p[:, :3])
+    p[:, 3] = 0
+    return p
+
+
+def _worker(rank, world, port, result_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from tests.oracle_lib import Oracle
+    ora = Oracle()
+    cfg = synth.make_config("c2", n_points=20000, n_views=4, size=(96, 54))
+    grads_up = synth.upstream_gradients(cfg["meta"])
+    mine = adist.shard_views(list(range(4)), rank, world)
+    views = [cfg["views"][i] for i in mine]
+    g_mine = [np.ascontiguousarray(g[mine]) for g in grads_up]
+    fwd = ora.forward(cfg["arrays"], views, cfg["params"], 4)
+    bwd = ora.backward(cfg["arrays"], views, cfg["params"], 4, fwd, g_mine, want_env=True, normalize=False)
+    t = {k: (torch.from_numpy(v) if v is not None else None) for k, v in bwd.items()}
+    ex = adist.exchange_gradients(t)
+    np.save(os.path.join(result_dir, f"tex_{rank}.npy"), ex["texture_shard"].numpy())
+    np.save(os.path.join(result_dir, f"pts_{rank}.npy"), ex["points_shard"].numpy())
+    if rank == 0:
+        np.save(os.path.join(result_dir, "pose.npy"), ex["pose"].numpy())
+        np.save(os.path.join(result_dir, "count_pose.npy"), ex["count_pose"].numpy())
+        np.save(os.path.join(result_dir, "intr.npy"), ex["intrinsics"].numpy())
+        np.save(os.path.join(result_dir, "count_intr.npy"), ex["count_intrinsics"].numpy())
+        np.save(os.path.join(result_dir, "bg.npy"), ex["background"].numpy())
+        np.save(os.path.join(result_dir, "env.npy"), ex["env_map"].numpy())
+    dist.destroy_process_group()
+
+
+def test_view_sharded_gradient_exchange_world_size_2(oracle, tmp_path):
+    world = 2
+    port = 29500 + (os.getpid() % 2000)
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    cfg = synth.make_config("c2", n_points=20000, n_views=4, size=(96, 54))
+    grads_up = synth.upstream_gradients(cfg["meta"])
+    fwd = oracle.forward(cfg["arrays"], cfg["views"], cfg["params"], 4)
+    ref = oracle.backward(cfg["arrays"], cfg["views"], cfg["params"], 4, fwd, grads_up, want_env=True, normalize=True)
+    tex = np.concatenate([np.load(tmp_path / f"tex_{r}.npy") for r in range(world)])
+    assert np.allclose(tex.reshape(ref["texture"].shape), ref["texture"], rtol=1e-5, atol=1e-6)
+    pts = np.concatenate([np.load(tmp_path / f"pts_{r}.npy") for r in range(world)])
+    assert adist.points_shard_is_aligned(20000, world)
+    assert np.allclose(_normalize_points(pts), ref["points"], rtol=1e-5, atol=1e-6)
+    pose, cp = np.load(tmp_path / "pose.npy"), np.load(tmp_path / "count_pose.npy")
+    assert np.allclose(pose / np.maximum(cp, 1)[:, None], ref["pose"], rtol=1e-9, atol=1e-12)
+    intr, ci = np.load(tmp_path / "intr.npy"), np.load(tmp_path / "count_intr.npy")
+    assert np.allclose(intr / ci[:, None], ref["intrinsics"], rtol=1e-4, atol=1e-5)
+    assert np.allclose(np.load(tmp_path / "bg.npy"), ref["background"], rtol=1e-4, atol=1e-4)
+    assert np.allclose(np.load(tmp_path / "env.npy"), ref["env_map"], rtol=1e-4, atol=1e-5)
+
+
+def test_shard_helpers():
+    assert adist.shard_views(list(range(10)), 0, 4) == [0, 1, 2]
+    assert adist.shard_views(list(range(10)), 3, 4) == [8, 9]
+    assert sum(len(adist.shard_views(list(range(10)), r, 4)) for r in range(4)) == 10
+    assert adist.shard_range(10, 3, 4) == (9, 10)
+    assert adist.shard_range(8, 1, 4) == (2, 4)
