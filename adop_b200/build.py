@@ -9,7 +9,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG_DIR)
 CSRC = os.path.join(PKG_DIR, "csrc")
-SOURCES = ["capi_common.cu", "raster_forward.cu", "raster_backward.cu", "pose_tonemap.cu"]
+SOURCES = ["capi_common.cu", "raster_forward.cu", "raster_forward_static.cu", "raster_backward.cu", "pose_tonemap.cu"]
 LIB = os.path.join(PKG_DIR, "libadop_raster.so")
 
 # -fmad=false: the arithmetic header promises the same bits on host and device

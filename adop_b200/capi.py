@@ -82,6 +82,7 @@ EXPORTED_SYMBOLS = [
     "adop_status_string", "adop_last_error", "adop_render_params_default", "adop_raster_workspace_bytes",
     "adop_raster_forward", "adop_raster_backward", "adop_raster_normalize_gradients", "adop_apply_tangent",
     "adop_tonemap_forward", "adop_tonemap_backward", "adop_profile_enable", "adop_profile_collect",
+    "adop_raster_static_scratch_bytes", "adop_raster_forward_static",
 ]
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
@@ -111,6 +112,10 @@ def load_library():
     lib.adop_raster_workspace_bytes.argtypes = [C.c_int32] * 4
     lib.adop_raster_forward.argtypes = [C.POINTER(AdopScene), C.POINTER(AdopView), C.c_int32,
                                         C.POINTER(AdopRenderParams), C.c_int32, C.POINTER(AdopForwardIO), C.c_void_p]
+    lib.adop_raster_forward_static.argtypes = lib.adop_raster_forward.argtypes
+    lib.adop_raster_forward_static.restype = C.c_int
+    lib.adop_raster_static_scratch_bytes.argtypes = []
+    lib.adop_raster_static_scratch_bytes.restype = C.c_size_t
     lib.adop_raster_backward.argtypes = [C.POINTER(AdopScene), C.POINTER(AdopView), C.c_int32,
                                          C.POINTER(AdopRenderParams), C.c_int32, C.POINTER(AdopBackwardIO), C.c_void_p]
     lib.adop_raster_normalize_gradients.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32,

@@ -163,6 +163,26 @@ adop_status adop_raster_forward(const adop_scene* scene, const adop_view* views,
                                 const adop_render_params* params, int32_t num_layers, adop_forward_io* io,
                                 void* stream);
 
+/* The forward pass without a caller-owned workspace. No counterpart in the reference (which allocates through
+ * libtorch whenever it likes): this entry point exists for hosts that may not allocate device memory at the time
+ * they render - a callback running while the allocator is locked, a plugin that only ever receives input and
+ * output buffers from its host application, a process with a memory budget fixed at start-up. io->workspace and
+ * io->workspace_bytes are ignored; the scratch is a built-in device array of adop_raster_static_scratch_bytes()
+ * bytes (32 MiB) that every GPU which loads this library keeps until the process exits. Inputs and outputs are
+ * still the caller's.
+ *   - Limit: adop_raster_workspace_bytes(w, h, layers, channels) must not exceed that size (e.g. 1024 x 576 with
+ *     4 layers and 4 channels fits); larger views return ADOP_ERR_SIZE_LIMIT and adop_last_error() names both sizes.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current). Make that first call outside any stream capture.
+ *   - The function itself calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - All calls on a device share the one array. Each call clears what it needs before use, so earlier contents do
+ *     not leak into results, but two calls whose kernels overlap on the GPU (different streams, different threads)
+ *     race on it: run them one after the other. */
+size_t adop_raster_static_scratch_bytes(void);
+adop_status adop_raster_forward_static(const adop_scene* scene, const adop_view* views, int32_t num_views,
+                                       const adop_render_params* params, int32_t num_layers, adop_forward_io* io,
+                                       void* stream);
+
 /* BlendPointCloudBackward, src/lib/rendering/PointRenderer.cu:1549-1644. */
 adop_status adop_raster_backward(const adop_scene* scene, const adop_view* views, int32_t num_views,
                                  const adop_render_params* params, int32_t num_layers, adop_backward_io* io,
