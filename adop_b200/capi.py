@@ -48,7 +48,7 @@ class AdopLayerBuffers(C.Structure):
 
 class AdopForwardIO(C.Structure):
     _fields_ = [("layers", AdopLayerBuffers * MAX_LAYERS), ("dropout_mask", C.c_void_p),
-                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("visible_list", C.c_void_p)]
 
 
 class AdopBackwardIO(C.Structure):
@@ -57,7 +57,7 @@ class AdopBackwardIO(C.Structure):
                 ("grad_points", C.c_void_p), ("grad_pose", C.c_void_p), ("count_pose", C.c_void_p),
                 ("grad_intrinsics", C.c_void_p), ("count_intrinsics", C.c_void_p), ("grad_env_map", C.c_void_p),
                 ("accumulate", C.c_int32), ("normalize", C.c_int32),
-                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("visible_list", C.c_void_p)]
 
 
 class AdopTonemapParams(C.Structure):
@@ -82,7 +82,7 @@ EXPORTED_SYMBOLS = [
     "adop_status_string", "adop_last_error", "adop_render_params_default", "adop_raster_workspace_bytes",
     "adop_raster_forward", "adop_raster_backward", "adop_raster_normalize_gradients", "adop_apply_tangent",
     "adop_tonemap_forward", "adop_tonemap_backward", "adop_profile_enable", "adop_profile_collect",
-    "adop_raster_static_scratch_bytes", "adop_raster_forward_static",
+    "adop_raster_static_scratch_bytes", "adop_raster_forward_static", "adop_raster_visible_list_ints",
 ]
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
@@ -116,6 +116,8 @@ def load_library():
     lib.adop_raster_forward_static.restype = C.c_int
     lib.adop_raster_static_scratch_bytes.argtypes = []
     lib.adop_raster_static_scratch_bytes.restype = C.c_size_t
+    lib.adop_raster_visible_list_ints.argtypes = [C.c_int32]
+    lib.adop_raster_visible_list_ints.restype = C.c_size_t
     lib.adop_raster_backward.argtypes = [C.POINTER(AdopScene), C.POINTER(AdopView), C.c_int32,
                                          C.POINTER(AdopRenderParams), C.c_int32, C.POINTER(AdopBackwardIO), C.c_void_p]
     lib.adop_raster_normalize_gradients.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32,

@@ -140,6 +140,35 @@ inline CamSource make_cam_source(const adop_scene* s, const adop_view* v)
     return c;
 }
 
+// Compact list of the points of one view that passed the fuzzy depth test on at least one layer, written by the blend
+// kernel and consumed by the backward kernel (the role of the reference's saved [B,N] drop-out tensor: per-view state
+// carried from forward to backward, PointRenderer.cu:1524). Layout per view, in int32:
+//   [0, kVisibleSegments)            number of entries of each segment (one segment per block of the blend launch)
+//   [kVisibleSegments + 0 / + 1]     segments in use / entries per segment (`seg_cap`), written by the blend kernel
+//   [kVisibleHeaderInts, ...)        segments of `seg_cap` entries each (point ids, unordered)
+constexpr int kVisibleSegments = 2048;
+constexpr int kVisibleHeaderInts = kVisibleSegments + 8;
+inline size_t visible_list_ints(int num_points) { return (size_t)kVisibleHeaderInts + (size_t)num_points + (size_t)kVisibleSegments * kBlock; }
+struct VisibleList
+{
+    int* header;   // null = no list
+    int* entries;
+    int segments;  // blocks of the blend launch
+    int seg_cap;   // entries per segment
+};
+inline VisibleList make_visible_list(int32_t* base, int num_points, int view, int segments)
+{
+    VisibleList v;
+    if (!base) { v.header = nullptr; v.entries = nullptr; v.segments = 0; v.seg_cap = 0; return v; }
+    int* p = base + (size_t)view * visible_list_ints(num_points);
+    v.header = p;
+    v.entries = p + kVisibleHeaderInts;
+    v.segments = segments;
+    long long iters = ((long long)(num_points + kBlock - 1) / kBlock + segments - 1) / segments;
+    v.seg_cap = (int)(iters * kBlock);
+    return v;
+}
+
 adop_status validate_common(const adop_scene* s, const adop_view* views, int B, const adop_render_params* rp, int L);
 int sm_count();
 

@@ -129,13 +129,50 @@ __device__ __forceinline__ void load_record(const float* records, size_t r, floa
     }
 }
 
-template <int C, int MODEL>
+// Inclusive prefix sums of the visible list's segment counts, in shared memory (every thread of the block takes part).
+__device__ __forceinline__ int scan_segments(const int* __restrict__ header, int* s_prefix, int* s_warp)
+{
+    constexpr int PER = kVisibleSegments / kBlock;
+    int local[PER];
+    int sum = 0;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) { sum += __ldg(header + threadIdx.x * PER + j); local[j] = sum; }
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1)
+    {
+        int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if ((threadIdx.x & 31) >= o) incl += v;
+    }
+    if ((threadIdx.x & 31) == 31) s_warp[threadIdx.x >> 5] = incl;
+    __syncthreads();
+    int woff = 0;
+    for (int k = 0; k < (int)(threadIdx.x >> 5); ++k) woff += s_warp[k];
+    const int excl = woff + incl - sum;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) s_prefix[threadIdx.x * PER + j] = excl + local[j];
+    __syncthreads();
+    return s_prefix[kVisibleSegments - 1];
+}
+
+// LISTED: the kernel walks the view's visible list (dense warps of points that passed the depth test in the forward
+// pass) instead of all points.
+template <int C, int MODEL, bool LISTED>
 __global__ void __launch_bounds__(kBlock) k_splat_backward(PointStreams pts, CamSource cs, KernelParams kp, LayerTable lt,
-                                                            BackwardTargets bt)
+                                                            BackwardTargets bt, VisibleList vl)
 {
     constexpr int NI = MODEL == kPinholeDistortion ? 13 : 5;
     constexpr int RB = (2 * C + 3) & ~3;
     __shared__ ViewCam cam;
+    __shared__ int s_prefix[LISTED ? kVisibleSegments : 1];
+    __shared__ int s_warp[kBlock / 32];
+    int work = pts.n, n_segments = 0, seg_cap = 0;
+    if (LISTED)
+    {
+        work = scan_segments(vl.header, s_prefix, s_warp);
+        n_segments = __ldg(vl.header + kVisibleSegments);
+        seg_cap = __ldg(vl.header + kVisibleSegments + 1);
+    }
     __shared__ double s_pose[6];
     __shared__ float s_intr[NI];
     __shared__ float s_cnt[2];
@@ -155,8 +192,21 @@ __global__ void __launch_bounds__(kBlock) k_splat_backward(PointStreams pts, Cam
     for (int k = 0; k < NI; ++k) a_intr[k] = 0.f;
 
     const int stride = gridDim.x * blockDim.x;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < pts.n; i += stride)
+    for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < work; t += stride)
     {
+        int i = t;
+        if (LISTED)
+        {
+            // segment k = first with prefix[k] > t
+            int lo = 0, hi = n_segments - 1;
+            while (lo < hi)
+            {
+                int mid = (lo + hi) >> 1;
+                if (s_prefix[mid] > t) hi = mid; else lo = mid + 1;
+            }
+            const int before = lo ? s_prefix[lo - 1] : 0;
+            i = __ldg(vl.entries + (size_t)lo * seg_cap + (t - before));
+        }
         const bool drop_out = point_dropped(kp, i);
         FetchedPoint f = fetch_point(pts, i);
         RasterPoint q;
@@ -354,9 +404,8 @@ __global__ void k_normalize_intrinsics(float* g, const float* cnt, int n, int co
 template <int C>
 static adop_status launch_view_backward(const PointStreams& pts, const CamSource& cam, const KernelParams& kp, const LayerTable& lt,
                                         const BackwardTargets& bt, float* grad_background, float* grad_env, int env_h, int env_w,
-                                        cudaStream_t st, int grid_points, int model)
+                                        cudaStream_t st, const VisibleList& vl, int model)
 {
-    (void)grid_points;
     const int need = (pts.n + kBlock - 1) / kBlock;
     {
         static const int cap = resident_grid(k_prepare_backward<C>, 1ll << 40);
@@ -367,17 +416,32 @@ static adop_status launch_view_backward(const PointStreams& pts, const CamSource
                                                   lt, cam, kp, bt.background, const_cast<float*>(bt.records), grad_background,
                                                   grad_env, env_h, env_w)));
     }
-    if (model == kPinholeDistortion)
+    if (vl.header)
     {
-        static const int g = resident_grid(k_splat_backward<C, kPinholeDistortion>, 1ll << 40);
-        ADOP_LAUNCH("k_splat_backward", st, (k_splat_backward<C, kPinholeDistortion><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(
-                                                pts, cam, kp, lt, bt)));
+        if (model == kPinholeDistortion)
+        {
+            static const int g = resident_grid(k_splat_backward<C, kPinholeDistortion, true>, 1ll << 40);
+            ADOP_LAUNCH("k_splat_backward", st, (k_splat_backward<C, kPinholeDistortion, true><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(
+                                                    pts, cam, kp, lt, bt, vl)));
+        }
+        else
+        {
+            static const int g = resident_grid(k_splat_backward<C, kOcam, true>, 1ll << 40);
+            ADOP_LAUNCH("k_splat_backward", st, (k_splat_backward<C, kOcam, true><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(
+                                                    pts, cam, kp, lt, bt, vl)));
+        }
+    }
+    else if (model == kPinholeDistortion)
+    {
+        static const int g = resident_grid(k_splat_backward<C, kPinholeDistortion, false>, 1ll << 40);
+        ADOP_LAUNCH("k_splat_backward_all", st, (k_splat_backward<C, kPinholeDistortion, false><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(
+                                                    pts, cam, kp, lt, bt, vl)));
     }
     else
     {
-        static const int g = resident_grid(k_splat_backward<C, kOcam>, 1ll << 40);
-        ADOP_LAUNCH("k_splat_backward", st, (k_splat_backward<C, kOcam><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(
-                                                pts, cam, kp, lt, bt)));
+        static const int g = resident_grid(k_splat_backward<C, kOcam, false>, 1ll << 40);
+        ADOP_LAUNCH("k_splat_backward_all", st, (k_splat_backward<C, kOcam, false><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(
+                                                    pts, cam, kp, lt, bt, vl)));
     }
     ADOP_CUDA_TRY(cudaGetLastError());
     return ADOP_OK;
@@ -451,11 +515,6 @@ extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view
     pts.normal = s->normal;
     pts.index = s->index;
     pts.n = N;
-    const int sms = sm_count();
-    int grid_points = (N + kBlock - 1) / kBlock;
-    if (grid_points > sms * 8) grid_points = sms * 8;
-    if (grid_points < 1) grid_points = 1;
-
     for (int b = 0; b < B; ++b)
     {
         LayerTable lt = base;
@@ -481,13 +540,15 @@ extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view
         bt.count_intrinsics = io->grad_intrinsics ? io->count_intrinsics + views[b].camera_index : nullptr;
         bt.records = static_cast<const float*>(io->workspace);
         float* ge = env ? io->grad_env_map : nullptr;
+        // the list's geometry (segments in use, entries per segment) sits in its header, written by the forward pass
+        VisibleList vl = make_visible_list(const_cast<int32_t*>(io->visible_list), N, b, 1);
         adop_status r;
         switch (C)
         {
-            case 3: r = launch_view_backward<3>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, st, grid_points, views[b].camera_model); break;
-            case 4: r = launch_view_backward<4>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, st, grid_points, views[b].camera_model); break;
-            case 8: r = launch_view_backward<8>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, st, grid_points, views[b].camera_model); break;
-            case 16: r = launch_view_backward<16>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, st, grid_points, views[b].camera_model); break;
+            case 3: r = launch_view_backward<3>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, st, vl, views[b].camera_model); break;
+            case 4: r = launch_view_backward<4>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, st, vl, views[b].camera_model); break;
+            case 8: r = launch_view_backward<8>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, st, vl, views[b].camera_model); break;
+            case 16: r = launch_view_backward<16>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, st, vl, views[b].camera_model); break;
             default: return ADOP_ERR_UNSUPPORTED;
         }
         if (r != ADOP_OK) return r;

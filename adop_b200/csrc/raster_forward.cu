@@ -81,23 +81,35 @@ __device__ __forceinline__ void splat_record(float* rec, const float* t)
     }
 }
 
-template <int L, int C>
+// With EMIT the kernel also appends every point that passed the test on some layer to this block's segment of the
+// view's visible list (shared-memory counter, no global atomics); in ghost-gradient mode dropped points are tested too
+// (they blend nothing but the backward pass needs them, PointRenderer.cu:487-488).
+template <int L, int C, bool EMIT>
 __global__ void __launch_bounds__(kBlock) k_blend(PointStreams pts, const float* __restrict__ texture, int num_texels,
-                                                   CamSource cs, KernelParams kp, LayerTable lt, float* __restrict__ accum)
+                                                   CamSource cs, KernelParams kp, LayerTable lt, float* __restrict__ accum,
+                                                   VisibleList vl)
 {
     __shared__ ViewCam cam;
+    __shared__ int s_count;
     load_cam_shared(&cam, cs);
+    if (EMIT)
+    {
+        if (threadIdx.x == 0) s_count = 0;
+        __syncthreads();
+    }
     constexpr int RS = ((C + 1) + 3) & ~3;
     const int stride = gridDim.x * blockDim.x;
+    int* seg = EMIT ? vl.entries + (size_t)blockIdx.x * vl.seg_cap : nullptr;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < pts.n; i += stride)
     {
-        if (point_dropped(kp, i)) continue;
+        const bool dropped = point_dropped(kp, i);
+        if (dropped && !(EMIT && kp.ghost_gradients)) continue;
         FetchedPoint f = fetch_point(pts, i);
         RasterPoint q;
         if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, kp.check_normal != 0, kp.dist_cutoff, &q,
                                 kp.drop_out_points_by_radius != 0)) continue;
         float x = q.x, y = q.y, rad = q.radius_px;
-        bool have_t = false;
+        bool have_t = false, passed = false;
         float t[C];
 #pragma unroll
         for (int l = 0; l < L; ++l, rad *= 0.5f, x *= 0.5f, y *= 0.5f)
@@ -108,6 +120,8 @@ __global__ void __launch_bounds__(kBlock) k_blend(PointStreams pts, const float*
             size_t pix = (size_t)py * lt.w[l] + px;
             float image_depth = __ldg(lt.depth[l] + pix);
             if (q.z > image_depth * kp.depth_accept_plus_one) continue;
+            passed = true;
+            if (dropped) break;  // listed for the backward pass; blends nothing
             if (!have_t)
             {
                 int ti = pts.index ? __ldg(pts.index + i) : i;
@@ -116,6 +130,16 @@ __global__ void __launch_bounds__(kBlock) k_blend(PointStreams pts, const float*
                 have_t = true;
             }
             splat_record<C>(accum + ((size_t)lt.rec_off[l] + pix) * RS, t);
+        }
+        if (EMIT && passed) seg[atomicAdd(&s_count, 1)] = i;
+    }
+    if (EMIT)
+    {
+        __syncthreads();
+        if (threadIdx.x == 0)
+        {
+            vl.header[blockIdx.x] = s_count;
+            if (blockIdx.x == 0) { vl.header[kVisibleSegments] = vl.segments; vl.header[kVisibleSegments + 1] = vl.seg_cap; }
         }
     }
 }
@@ -194,17 +218,25 @@ __global__ void __launch_bounds__(kBlock) k_resolve(LayerTable lt, CamSource cs,
 // ------------------------------------------------------------------------------------------------------
 template <int L, int C>
 static adop_status launch_view_forward(const PointStreams& pts, const adop_scene* s, const CamSource& cam, const KernelParams& kp,
-                                       const LayerTable& lt, float* accum, bool env, cudaStream_t st, int grid_points)
+                                       const LayerTable& lt, float* accum, bool env, cudaStream_t st, int32_t* list_base, int view)
 {
-    (void)grid_points;
     static const int g_depth = resident_grid(k_depth_prepass<L>, 1ll << 40);
-    static const int g_blend = resident_grid(k_blend<L, C>, 1ll << 40);
+    static const int g_blend_plain = resident_grid(k_blend<L, C, false>, 1ll << 40);
+    static const int g_blend_emit = resident_grid(k_blend<L, C, true>, 1ll << 40);
+    const int g_blend = list_base ? (g_blend_emit < kVisibleSegments ? g_blend_emit : kVisibleSegments) : g_blend_plain;
     static const int g_resolve = resident_grid(k_resolve<C>, 1ll << 40);
     const int need = (pts.n + kBlock - 1) / kBlock;
     ADOP_LAUNCH("k_depth_prepass", st,
                 (k_depth_prepass<L><<<need < g_depth ? (need < 1 ? 1 : need) : g_depth, kBlock, 0, st>>>(pts, cam, kp, lt)));
-    ADOP_LAUNCH("k_blend", st, (k_blend<L, C><<<need < g_blend ? (need < 1 ? 1 : need) : g_blend, kBlock, 0, st>>>(
-                                   pts, s->texture, s->num_texels, cam, kp, lt, accum)));
+    const int grid_blend = need < g_blend ? (need < 1 ? 1 : need) : g_blend;
+    VisibleList vl = make_visible_list(list_base, pts.n, view, grid_blend);
+    if (list_base)
+    {
+        ADOP_CUDA_TRY(cudaMemsetAsync(vl.header, 0, sizeof(int) * kVisibleHeaderInts, st));
+        ADOP_LAUNCH("k_blend", st, (k_blend<L, C, true><<<grid_blend, kBlock, 0, st>>>(pts, s->texture, s->num_texels, cam, kp, lt, accum, vl)));
+    }
+    else
+        ADOP_LAUNCH("k_blend", st, (k_blend<L, C, false><<<grid_blend, kBlock, 0, st>>>(pts, s->texture, s->num_texels, cam, kp, lt, accum, vl)));
     unsigned total = lt.rec_off[kMaxLayers];
     int grid_px = (int)((total + kBlock - 1) / kBlock);
     if (grid_px > g_resolve) grid_px = g_resolve;
@@ -217,18 +249,18 @@ static adop_status launch_view_forward(const PointStreams& pts, const adop_scene
 template <int C>
 static adop_status dispatch_layers_forward(int L, const PointStreams& pts, const adop_scene* s, const CamSource& cam,
                                            const KernelParams& kp, const LayerTable& lt, float* accum, bool env,
-                                           cudaStream_t st, int grid_points)
+                                           cudaStream_t st, int32_t* list_base, int view)
 {
     switch (L)
     {
-        case 1: return launch_view_forward<1, C>(pts, s, cam, kp, lt, accum, env, st, grid_points);
-        case 2: return launch_view_forward<2, C>(pts, s, cam, kp, lt, accum, env, st, grid_points);
-        case 3: return launch_view_forward<3, C>(pts, s, cam, kp, lt, accum, env, st, grid_points);
-        case 4: return launch_view_forward<4, C>(pts, s, cam, kp, lt, accum, env, st, grid_points);
-        case 5: return launch_view_forward<5, C>(pts, s, cam, kp, lt, accum, env, st, grid_points);
-        case 6: return launch_view_forward<6, C>(pts, s, cam, kp, lt, accum, env, st, grid_points);
-        case 7: return launch_view_forward<7, C>(pts, s, cam, kp, lt, accum, env, st, grid_points);
-        case 8: return launch_view_forward<8, C>(pts, s, cam, kp, lt, accum, env, st, grid_points);
+        case 1: return launch_view_forward<1, C>(pts, s, cam, kp, lt, accum, env, st, list_base, view);
+        case 2: return launch_view_forward<2, C>(pts, s, cam, kp, lt, accum, env, st, list_base, view);
+        case 3: return launch_view_forward<3, C>(pts, s, cam, kp, lt, accum, env, st, list_base, view);
+        case 4: return launch_view_forward<4, C>(pts, s, cam, kp, lt, accum, env, st, list_base, view);
+        case 5: return launch_view_forward<5, C>(pts, s, cam, kp, lt, accum, env, st, list_base, view);
+        case 6: return launch_view_forward<6, C>(pts, s, cam, kp, lt, accum, env, st, list_base, view);
+        case 7: return launch_view_forward<7, C>(pts, s, cam, kp, lt, accum, env, st, list_base, view);
+        case 8: return launch_view_forward<8, C>(pts, s, cam, kp, lt, accum, env, st, list_base, view);
     }
     return ADOP_ERR_INVALID_ARGUMENT;
 }
@@ -246,6 +278,11 @@ extern "C" size_t adop_raster_workspace_bytes(int32_t w, int32_t h, int32_t laye
     int fwd = record_floats(channels), bwd = (2 * channels + 3) & ~3;
     size_t bytes = (size_t)lt.rec_off[kMaxLayers] * (fwd > bwd ? fwd : bwd) * sizeof(float);
     return bytes + 256;
+}
+
+extern "C" size_t adop_raster_visible_list_ints(int32_t num_points)
+{
+    return num_points < 0 ? 0 : visible_list_ints(num_points);
 }
 
 extern "C" adop_status adop_raster_forward(const adop_scene* s, const adop_view* views, int32_t B,
@@ -292,10 +329,6 @@ extern "C" adop_status adop_raster_forward(const adop_scene* s, const adop_view*
     pts.normal = s->normal;
     pts.index = s->index;
     pts.n = N;
-    int grid_points = (N + kBlock - 1) / kBlock;
-    if (grid_points > sms * 8) grid_points = sms * 8;  // 8 resident blocks of 256 threads per SM, grid-stride
-    if (grid_points < 1) grid_points = 1;
-
     // the pose and intrinsics tensors live on the device; the per-view camera is gathered there
     for (int b = 0; b < B; ++b)
     {
@@ -313,10 +346,10 @@ extern "C" adop_status adop_raster_forward(const adop_scene* s, const adop_view*
         adop_status r;
         switch (C)
         {
-            case 3: r = dispatch_layers_forward<3>(L, pts, s, cam, kp, lt, accum, env, st, grid_points); break;
-            case 4: r = dispatch_layers_forward<4>(L, pts, s, cam, kp, lt, accum, env, st, grid_points); break;
-            case 8: r = dispatch_layers_forward<8>(L, pts, s, cam, kp, lt, accum, env, st, grid_points); break;
-            case 16: r = dispatch_layers_forward<16>(L, pts, s, cam, kp, lt, accum, env, st, grid_points); break;
+            case 3: r = dispatch_layers_forward<3>(L, pts, s, cam, kp, lt, accum, env, st, io->visible_list, b); break;
+            case 4: r = dispatch_layers_forward<4>(L, pts, s, cam, kp, lt, accum, env, st, io->visible_list, b); break;
+            case 8: r = dispatch_layers_forward<8>(L, pts, s, cam, kp, lt, accum, env, st, io->visible_list, b); break;
+            case 16: r = dispatch_layers_forward<16>(L, pts, s, cam, kp, lt, accum, env, st, io->visible_list, b); break;
             default: return ADOP_ERR_UNSUPPORTED;
         }
         if (r != ADOP_OK) return r;

@@ -81,9 +81,19 @@ def _tptr(t):
 
 
 class ForwardResult:
-    def __init__(self, colors, masks, depths, weights, views, num_layers):
+    """Outputs of the forward pass plus what the backward pass needs again (the reference's saved variables,
+    PointRenderer.cu:1514-1527): depth, weight and colour per layer, and the per-view list of points that passed the
+    depth test (in place of the saved [B,N] drop-out tensor)."""
+
+    def __init__(self, colors, masks, depths, weights, views, num_layers, visible=None):
         self.colors, self.masks, self.depths, self.weights = colors, masks, depths, weights
         self.views, self.num_layers = views, num_layers
+        self.visible = visible
+
+    def visible_counts(self):
+        """Points per view that passed the depth test on at least one layer (needs `visible`)."""
+        n_seg = 2048
+        return self.visible[:, :n_seg].sum(dim=1)
 
 
 class PointRasterizer:
@@ -102,7 +112,7 @@ class PointRasterizer:
             self._ws = torch.empty(need, dtype=torch.uint8, device=self.device)
         return self._ws
 
-    def forward(self, scene, views, params, num_layers, dropout_mask=None, out=None):
+    def forward(self, scene, views, params, num_layers, dropout_mask=None, out=None, record_visible=True):
         """BlendPointCloudForward (PointRenderer.cu:1389-1531). `views`: list of dicts or an AdopView array.
 
         Returns a ForwardResult; result.colors + result.masks is the reference's return list.
@@ -121,7 +131,11 @@ class PointRasterizer:
                 depths = [torch.empty((B, 1, hh, ww), **f32) for ww, hh in sizes]
                 weights = [torch.empty((B, 1, hh, ww), **f32) for ww, hh in sizes]
                 masks = [torch.empty((B, 1, hh, ww), **f32) for ww, hh in sizes] if params.output_background_mask else []
-                out = ForwardResult(colors, masks, depths, weights, va, num_layers)
+                visible = None
+                if record_visible:
+                    ints = self.lib.adop_raster_visible_list_ints(sc.num_points)
+                    visible = torch.empty((B, ints), dtype=torch.int32, device=self.device)
+                out = ForwardResult(colors, masks, depths, weights, va, num_layers, visible)
             else:
                 out.views = va
             io = capi.AdopForwardIO()
@@ -133,6 +147,7 @@ class PointRasterizer:
             io.dropout_mask = _tptr(dropout_mask) if dropout_mask is not None else None
             io.workspace = ws.data_ptr()
             io.workspace_bytes = ws.numel()
+            io.visible_list = out.visible.data_ptr() if out.visible is not None else None
             stream = torch.cuda.current_stream(self.device).cuda_stream
             st = self.lib.adop_raster_forward(C.byref(sc), va, B, C.byref(params), num_layers, C.byref(io),
                                               C.c_void_p(stream))
@@ -188,6 +203,7 @@ class PointRasterizer:
             ws = self._workspace(va[0].w, va[0].h, L, sc.channels)
             io.workspace = ws.data_ptr()
             io.workspace_bytes = ws.numel()
+            io.visible_list = fwd.visible.data_ptr() if fwd.visible is not None else None
             stream = torch.cuda.current_stream(self.device).cuda_stream
             st = self.lib.adop_raster_backward(C.byref(sc), va, B, C.byref(params), L, C.byref(io), C.c_void_p(stream))
             capi.check(st, "adop_raster_backward")

@@ -279,9 +279,8 @@ def main():
     capi.profile_enable(False)
     ras.forward(scene, views, params, L, out=fwd)
     torch.cuda.synchronize()
-    # U_v: points with at least one accepted layer, per view. Until the library reports it, the number of points accepted
-    # on the finest layer stands in for it (a lower bound, so `achieved` is a lower bound too).
-    U_views = [float(fwd.weights[0][b].sum().item()) for b in range(V)]
+    # U_v: points of the view with at least one accepted layer = length of the visible list the forward pass recorded
+    U_views = [float(c) for c in fwd.visible_counts().tolist()]
     fwd_b, bwd_b, step_b, per_view_bwd = algorithmic_bytes(N, C, P, U_views, env_hw=arrays["env_map"].shape[1:])
     peaks = {}
     try:

@@ -113,6 +113,10 @@ typedef struct adop_forward_io
     const uint8_t* dropout_mask; /* optional [B,N]: 1 = dropped; NULL = hash of dropout_seed */
     void* workspace;
     size_t workspace_bytes;
+    /* optional, [B, adop_raster_visible_list_ints(N)] i32: the forward pass records which points of each view passed
+     * the depth test, so that the backward pass visits only those. It takes the place of the [B,N] drop-out tensor
+     * the reference saves for backward (PointRenderer.cu:1524). NULL = not recorded. */
+    int32_t* visible_list;
 } adop_forward_io;
 
 /* Gradients (outputs) follow the reference's order {texture, background, points, pose tangents, intrinsics}
@@ -143,6 +147,9 @@ typedef struct adop_backward_io
     int32_t normalize;
     void* workspace;
     size_t workspace_bytes;
+    /* optional: the list the forward call of the same views, scene and parameters filled (see adop_forward_io).
+     * NULL = the backward pass walks all points again, as the reference does. */
+    const int32_t* visible_list;
 } adop_backward_io;
 
 const char* adop_status_string(adop_status s);
@@ -155,6 +162,9 @@ void adop_render_params_default(adop_render_params* p);
 /* Bytes of scratch that forward/backward need for views of w x h with `layers` layers and `channels`
  * descriptor channels. Replaces the size-keyed PointRendererCache (PointRenderer.h:96-157). */
 size_t adop_raster_workspace_bytes(int32_t w, int32_t h, int32_t layers, int32_t channels);
+
+/* int32 elements per view of adop_forward_io.visible_list for a cloud of num_points points. */
+size_t adop_raster_visible_list_ints(int32_t num_points);
 
 /* BlendPointCloudForward, src/lib/rendering/PointRenderer.cu:1389-1531: depth prepass, fuzzy-depth blend,
  * combine-and-fill, mask, and (optionally) the environment-map composite of RenderModule.cpp:106-127.

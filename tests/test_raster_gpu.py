@@ -26,7 +26,7 @@ def close(a, b, rtol=RTOL, name=""):
     assert err <= rtol * scale, f"{name}: max err {err:.3e} vs scale {scale:.3e}"
 
 
-def run_both(oracle, cfg, want_env=False, dropout_mask=None, **bw):
+def run_both(oracle, cfg, want_env=False, dropout_mask=None, record_visible=True, **bw):
     arrays, views, params, L = cfg["arrays"], cfg["views"], cfg["params"], cfg["num_layers"]
     grads = synth.upstream_gradients(cfg["meta"], batch=len(views))
     ref = oracle.forward(arrays, views, params, L, dropout_mask=dropout_mask)
@@ -34,7 +34,7 @@ def run_both(oracle, cfg, want_env=False, dropout_mask=None, **bw):
     scene = to_scene(arrays)
     r = PointRasterizer("cuda:0")
     dm = torch.from_numpy(dropout_mask).cuda() if dropout_mask is not None else None
-    fwd = r.forward(scene, views, params, L, dropout_mask=dm)
+    fwd = r.forward(scene, views, params, L, dropout_mask=dm, record_visible=record_visible)
     bwd = r.backward(scene, params, fwd, [torch.from_numpy(g).cuda() for g in grads], want_env=want_env,
                      dropout_mask=dm, **bw)
     torch.cuda.synchronize()
@@ -78,17 +78,25 @@ def test_c1_full_size(oracle, cuda_lib):
     check_backward(ref_b, bwd)
 
 
-def test_c2_distortion_env_map_pose_grads(oracle, cuda_lib):
+@pytest.mark.parametrize("listed", [True, False])
+def test_c2_distortion_env_map_pose_grads(oracle, cuda_lib, listed):
+    """listed: the backward pass walks the visible list the forward pass recorded; else it walks all points."""
     cfg = synth.make_config("c2", n_points=400_000, n_views=3, size=(480, 270))
-    ref, ref_b, fwd, bwd = run_both(oracle, cfg, want_env=True)
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg, want_env=True, record_visible=listed)
+    if listed:
+        # the list holds exactly the points with at least one accepted layer
+        proj_ok = [int((ref["weights"][0][b] > 0).sum()) for b in range(3)]
+        counts = fwd.visible_counts().cpu().numpy()
+        assert all(c >= p for c, p in zip(counts, proj_ok)) and counts.max() < 400_000
     check_forward(ref, fwd, 4, masks=True)
     check_backward(ref_b, bwd)
     assert np.abs(ref_b["pose"]).max() > 0 and np.abs(ref_b["env_map"]).max() > 0
 
 
-def test_c3_ocam(oracle, cuda_lib):
+@pytest.mark.parametrize("listed", [True, False])
+def test_c3_ocam(oracle, cuda_lib, listed):
     cfg = synth.make_config("c3", n_points=500_000, size=(480, 270))
-    ref, ref_b, fwd, bwd = run_both(oracle, cfg)
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg, record_visible=listed)
     check_forward(ref, fwd, 4)
     check_backward(ref_b, bwd)
     assert ref["weights"][0].sum() > 1000
@@ -117,13 +125,14 @@ def test_odd_sizes_and_ragged_point_count(oracle, cuda_lib):
     check_backward(ref_b, bwd)
 
 
+@pytest.mark.parametrize("listed", [True, False])
 @pytest.mark.parametrize("ghost", [0, 1])
-def test_dropout_hash_and_ghost_gradients(oracle, cuda_lib, ghost):
+def test_dropout_hash_and_ghost_gradients(oracle, cuda_lib, ghost, listed):
     cfg = synth.make_config("c1", n_points=80_000, size=(128, 128))
     cfg["params"].dropout = 0.25
     cfg["params"].dropout_seed = 7
     cfg["params"].ghost_gradients = ghost
-    ref, ref_b, fwd, bwd = run_both(oracle, cfg)
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg, record_visible=listed)
     check_forward(ref, fwd, 4)
     check_backward(ref_b, bwd)
     assert np.abs(ref_b["points"]).max() > 0
