@@ -39,7 +39,7 @@ class AdopScene(C.Structure):
                 ("env_h", C.c_int32), ("env_w", C.c_int32),
                 ("position", C.c_void_p), ("normal", C.c_void_p), ("index", C.c_void_p), ("texture", C.c_void_p),
                 ("background", C.c_void_p), ("poses", C.c_void_p), ("intrinsics", C.c_void_p),
-                ("env_map", C.c_void_p)]
+                ("env_map", C.c_void_p), ("texture_interleaved", C.c_void_p)]
 
 
 class AdopLayerBuffers(C.Structure):
@@ -57,7 +57,8 @@ class AdopBackwardIO(C.Structure):
                 ("grad_points", C.c_void_p), ("grad_pose", C.c_void_p), ("count_pose", C.c_void_p),
                 ("grad_intrinsics", C.c_void_p), ("count_intrinsics", C.c_void_p), ("grad_env_map", C.c_void_p),
                 ("accumulate", C.c_int32), ("normalize", C.c_int32),
-                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("visible_list", C.c_void_p)]
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("visible_list", C.c_void_p),
+                ("grad_texture_interleaved", C.c_void_p)]
 
 
 class AdopTonemapParams(C.Structure):
@@ -83,6 +84,7 @@ EXPORTED_SYMBOLS = [
     "adop_raster_forward", "adop_raster_backward", "adop_raster_normalize_gradients", "adop_apply_tangent",
     "adop_tonemap_forward", "adop_tonemap_backward", "adop_profile_enable", "adop_profile_collect",
     "adop_raster_static_scratch_bytes", "adop_raster_forward_static", "adop_raster_visible_list_ints",
+    "adop_texture_interleave", "adop_texture_deinterleave",
 ]
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
@@ -116,6 +118,10 @@ def load_library():
     lib.adop_raster_forward_static.restype = C.c_int
     lib.adop_raster_static_scratch_bytes.argtypes = []
     lib.adop_raster_static_scratch_bytes.restype = C.c_size_t
+    lib.adop_texture_interleave.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
+    lib.adop_texture_interleave.restype = C.c_int
+    lib.adop_texture_deinterleave.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
+    lib.adop_texture_deinterleave.restype = C.c_int
     lib.adop_raster_visible_list_ints.argtypes = [C.c_int32]
     lib.adop_raster_visible_list_ints.restype = C.c_size_t
     lib.adop_raster_backward.argtypes = [C.POINTER(AdopScene), C.POINTER(AdopView), C.c_int32,

@@ -82,6 +82,7 @@ adop_status validate_common(const adop_scene* s, const adop_view* views, int B, 
 {
     if (!s || !views || !rp) return ADOP_ERR_INVALID_ARGUMENT;
     if (B <= 0 || L <= 0 || L > ADOP_MAX_LAYERS) return ADOP_ERR_INVALID_ARGUMENT;
+    if (s->num_points > 0x7F000000) return ADOP_ERR_SIZE_LIMIT;  // grid-stride loops index points with 32-bit ints
     if (s->num_points < 0 || s->channels <= 0 || s->channels > ADOP_MAX_CHANNELS) return ADOP_ERR_INVALID_ARGUMENT;
     if (s->num_texels <= 0 || s->num_images <= 0 || s->num_cameras <= 0) return ADOP_ERR_INVALID_ARGUMENT;
     if (!s->position || !s->texture || !s->background || !s->poses || !s->intrinsics) return ADOP_ERR_INVALID_ARGUMENT;

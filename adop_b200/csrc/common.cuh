@@ -119,33 +119,45 @@ inline void fill_layer_dims(int w, int h, int L, LayerTable* lt)
     for (int l = L; l <= kMaxLayers; ++l) lt->rec_off[l] = off;
 }
 
-// Where one view's camera comes from: rows of the pose / intrinsics tensors (device memory, they are
-// trainable parameters) plus the ReducedImageInfo fields. Kernels gather it into shared memory once per block.
-struct CamSource
+// One view's camera is gathered from rows of the pose / intrinsics tensors (device memory: they are trainable
+// parameters) plus the ReducedImageInfo fields of the view. A small kernel does that for a chunk of views and leaves the
+// ViewCam records at the head of the workspace; the point kernels read their view's record through a pointer. (Measured
+// on the depth prepass: camera as a by-value kernel argument 72 us, through this pointer 82 us, in shared memory 90 us, in
+// an indexed __constant__ array 100 us; by-value needs the numbers on the host, which would cost a device-to-host sync.)
+constexpr int kCamChunk = 64;                      // views per chunk
+constexpr size_t kCamRegionBytes = 16384;          // head of the workspace, >= kCamChunk * sizeof(ViewCam)
+struct CamChunkSource
 {
     const double* poses;
     const float* intrinsics;
     int intrinsics_cols;
-    int image_index, camera_index, camera_model;
-    float crop[5];
-    int w0;
+    int n;
+    struct View { int image_index, camera_index, camera_model, w0; float crop[5]; } v[kCamChunk];
 };
-inline CamSource make_cam_source(const adop_scene* s, const adop_view* v)
+static_assert(sizeof(ViewCam) * kCamChunk <= kCamRegionBytes, "camera region too small");
+inline void fill_cam_chunk(CamChunkSource* c, const adop_scene* s, const adop_view* views, int n)
 {
-    CamSource c;
-    c.poses = s->poses; c.intrinsics = s->intrinsics; c.intrinsics_cols = s->intrinsics_cols;
-    c.image_index = v->image_index; c.camera_index = v->camera_index; c.camera_model = v->camera_model;
-    for (int i = 0; i < 5; ++i) c.crop[i] = v->crop[i];
-    c.w0 = v->w;
-    return c;
+    c->poses = s->poses; c->intrinsics = s->intrinsics; c->intrinsics_cols = s->intrinsics_cols; c->n = n;
+    for (int k = 0; k < n; ++k)
+    {
+        c->v[k].image_index = views[k].image_index; c->v[k].camera_index = views[k].camera_index;
+        c->v[k].camera_model = views[k].camera_model; c->v[k].w0 = views[k].w;
+        for (int i = 0; i < 5; ++i) c->v[k].crop[i] = views[k].crop[i];
+    }
 }
 
-// Compact list of the points of one view that passed the fuzzy depth test on at least one layer, written by the blend
-// kernel and consumed by the backward kernel (the role of the reference's saved [B,N] drop-out tensor: per-view state
-// carried from forward to backward, PointRenderer.cu:1524). Layout per view, in int32:
+// Splat list of one view: every (point, layer) pair that the backward pass has to visit - the point passed the fuzzy
+// depth test on that layer and on every finer layer it landed in (the backward pass stops at the first failure,
+// PointRenderer.cu:462). Written by the blend kernel, consumed by the backward kernel; it takes the role of the
+// reference's saved [B,N] drop-out tensor as the per-view state carried from forward to backward (:1524).
+// Layout per view, in int32:
 //   [0, kVisibleSegments)            number of entries of each segment (one segment per block of the blend launch)
 //   [kVisibleSegments + 0 / + 1]     segments in use / entries per segment (`seg_cap`), written by the blend kernel
-//   [kVisibleHeaderInts, ...)        segments of `seg_cap` entries each (point ids, unordered)
+//   [kVisibleSegments + 2]           overflow flag: a segment ran out of room, the list is incomplete and not used
+//   [kVisibleHeaderInts, ...)        segments of `seg_cap` entries each: point id | layer << 28, unordered
+constexpr unsigned kSplatPointMask = 0x0FFFFFFFu;
+constexpr int kSplatLayerShift = 28;
+constexpr int kSplatMaxPoints = 1 << 28;  // larger clouds are rendered without a list
 constexpr int kVisibleSegments = 2048;
 constexpr int kVisibleHeaderInts = kVisibleSegments + 8;
 inline size_t visible_list_ints(int num_points) { return (size_t)kVisibleHeaderInts + (size_t)num_points + (size_t)kVisibleSegments * kBlock; }
@@ -189,23 +201,79 @@ inline int resident_grid(Kernel kernel, long long work_items)
 struct FetchedPoint { V3 p; V3 n; float r; bool has_normal; };
 
 // DevicePointCloud::GetPoint (NeuralPointCloudCuda.h:82-103): one 128-bit load of xyz + radius
-__device__ __forceinline__ FetchedPoint fetch_point(const PointStreams& s, int i)
+__device__ __forceinline__ FetchedPoint fetch_point(const PointStreams& s, int i, float4 q)
 {
     FetchedPoint f;
-    float4 q = __ldg(s.position + i);
     f.p.x = q.x; f.p.y = q.y; f.p.z = q.z; f.r = q.w;
     f.has_normal = s.normal != nullptr;
     if (f.has_normal) f.n = unpack_normal_10bit(__ldg(s.normal + i));
     else { f.n.x = 0.f; f.n.y = 0.f; f.n.z = 0.f; }
     return f;
 }
-// every thread of the block must call this (it synchronises)
-__device__ __forceinline__ void load_cam_shared(ViewCam* sh, const CamSource& src)
+__device__ __forceinline__ FetchedPoint fetch_point(const PointStreams& s, int i) { return fetch_point(s, i, __ldg(s.position + i)); }
+static __global__ void k_build_cams(CamChunkSource src, ViewCam* __restrict__ out)
 {
-    if (threadIdx.x == 0)
-        *sh = load_view_cam(src.poses, src.intrinsics, src.intrinsics_cols, src.image_index, src.camera_index,
-                            src.camera_model, src.crop, src.w0);
-    __syncthreads();
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= src.n) return;
+    out[k] = load_view_cam(src.poses, src.intrinsics, src.intrinsics_cols, src.v[k].image_index, src.v[k].camera_index,
+                           src.v[k].camera_model, src.v[k].crop, src.v[k].w0);
+}
+// A point's descriptor: from the interleaved [T,C] copy when the caller provides one (one or two 16-byte loads), else
+// from the C planes of the [C,T] tensor.
+template <int C>
+__device__ __forceinline__ void load_descriptor(const float* __restrict__ planar, const float* __restrict__ interleaved,
+                                                int num_texels, int ti, float* t)
+{
+    if (interleaved)
+    {
+        const float* src = interleaved + (size_t)ti * C;
+        if (C % 4 == 0)
+        {
+#pragma unroll
+            for (int k = 0; k < C / 4; ++k)
+            {
+                float4 a = __ldg(reinterpret_cast<const float4*>(src) + k);
+                t[4 * k] = a.x; t[4 * k + 1] = a.y; t[4 * k + 2] = a.z; t[4 * k + 3] = a.w;
+            }
+        }
+        else
+        {
+#pragma unroll
+            for (int c = 0; c < C; ++c) t[c] = __ldg(src + c);
+        }
+    }
+    else
+    {
+#pragma unroll
+        for (int c = 0; c < C; ++c) t[c] = __ldg(planar + (size_t)c * num_texels + ti);
+    }
+}
+// Add a descriptor gradient: one vector atomic per 4 channels into the interleaved scratch, else C scalar atomics
+// into the planes.
+template <int C>
+__device__ __forceinline__ void add_descriptor_gradient(float* __restrict__ planar, float* __restrict__ interleaved,
+                                                        int num_texels, int ti, const float* g)
+{
+    if (interleaved)
+    {
+        float* dst = interleaved + (size_t)ti * C;
+        if (C % 4 == 0)
+        {
+#pragma unroll
+            for (int k = 0; k < C / 4; ++k)
+                atomicAdd(reinterpret_cast<float4*>(dst) + k, make_float4(g[4 * k], g[4 * k + 1], g[4 * k + 2], g[4 * k + 3]));
+        }
+        else
+        {
+#pragma unroll
+            for (int c = 0; c < C; ++c) atomicAdd(dst + c, g[c]);
+        }
+    }
+    else
+    {
+#pragma unroll
+        for (int c = 0; c < C; ++c) atomicAdd(planar + (size_t)c * num_texels + ti, g[c]);
+    }
 }
 __device__ __forceinline__ bool point_dropped(const KernelParams& kp, int i)
 {

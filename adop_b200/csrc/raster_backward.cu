@@ -4,8 +4,9 @@
 // of the environment-map composite (RenderModule.cpp:121-125, grid_sample backward).
 //
 // Differences in how the same sums are formed (results agree within float-ordering tolerance):
-//  * one thread owns one point of one view: its descriptor gradient is summed over the layers in registers
-//    and leaves as C atomics per point, not C per (point, layer);
+//  * the forward pass records which (point, layer) splats the backward pass will visit; the backward kernel then runs
+//    one thread per recorded splat in dense warps instead of one thread per point of the cloud (a fallback kernel
+//    with the reference's structure handles calls without such a list);
 //  * the point gradient and its counter leave as ONE 16-byte vector atomic (x, y, z, count);
 //  * pose and intrinsics gradients, which the reference adds with 7 + 14 same-address atomics per splat,
 //    are reduced warp -> block in shared memory and leave as one atomic per component and block;
@@ -26,15 +27,14 @@ namespace adop {
 __host__ __device__ inline int backward_record_floats(int C) { return (2 * C + 3) & ~3; }
 
 template <int C>
-__global__ void __launch_bounds__(kBlock) k_prepare_backward(LayerTable lt, CamSource cs, KernelParams kp,
+__global__ void __launch_bounds__(kBlock) k_prepare_backward(LayerTable lt, const ViewCam* __restrict__ camp, KernelParams kp,
                                                               const float* __restrict__ background, float* __restrict__ records,
                                                               float* __restrict__ grad_background,
                                                               float* __restrict__ grad_env, int env_h, int env_w)
 {
     constexpr int RB = (2 * C + 3) & ~3;
-    __shared__ ViewCam cam;
+    const ViewCam& cam = *camp;
     __shared__ float s_bg[C];
-    load_cam_shared(&cam, cs);
     if (threadIdx.x < C) s_bg[threadIdx.x] = 0.f;
     __syncthreads();
     const unsigned total = lt.rec_off[kMaxLayers];
@@ -101,13 +101,15 @@ __global__ void __launch_bounds__(kBlock) k_prepare_backward(LayerTable lt, CamS
 }
 
 // ------------------------------------------------------------------------------------------------------
-// K5: per-point backward.
+// K5: gradients of the splats.
 struct BackwardTargets
 {
     const float* texture;
+    const float* texture_interleaved;  // optional [T,C]
     int num_texels;
     const float* background;
     float* grad_texture;
+    float* grad_texture_interleaved;   // optional [T,C]; when set the descriptor gradient goes there
     float4* grad_points;
     double* grad_pose;        // row of this view's image, 6 doubles
     float* count_pose;        // element of this view's image
@@ -129,84 +131,181 @@ __device__ __forceinline__ void load_record(const float* records, size_t r, floa
     }
 }
 
-// Inclusive prefix sums of the visible list's segment counts, in shared memory (every thread of the block takes part).
-__device__ __forceinline__ int scan_segments(const int* __restrict__ header, int* s_prefix, int* s_warp)
+// per-thread partial sums of the view's pose / intrinsics gradient
+template <int MODEL>
+struct GeoAccum
 {
-    constexpr int PER = kVisibleSegments / kBlock;
-    int local[PER];
-    int sum = 0;
-#pragma unroll
-    for (int j = 0; j < PER; ++j) { sum += __ldg(header + threadIdx.x * PER + j); local[j] = sum; }
-    int incl = sum;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1)
+    static constexpr int NI = MODEL == kPinholeDistortion ? 13 : 5;
+    float pose[6];
+    float intr[NI];
+    float cnt;
+    __device__ __forceinline__ void clear()
     {
-        int v = __shfl_up_sync(0xffffffffu, incl, o);
-        if ((threadIdx.x & 31) >= o) incl += v;
-    }
-    if ((threadIdx.x & 31) == 31) s_warp[threadIdx.x >> 5] = incl;
-    __syncthreads();
-    int woff = 0;
-    for (int k = 0; k < (int)(threadIdx.x >> 5); ++k) woff += s_warp[k];
-    const int excl = woff + incl - sum;
 #pragma unroll
-    for (int j = 0; j < PER; ++j) s_prefix[threadIdx.x * PER + j] = excl + local[j];
-    __syncthreads();
-    return s_prefix[kVisibleSegments - 1];
+        for (int k = 0; k < 6; ++k) pose[k] = 0.f;
+#pragma unroll
+        for (int k = 0; k < NI; ++k) intr[k] = 0.f;
+        cnt = 0.f;
+    }
+};
+
+// The ghost-geometry image gradient of one splat (PointRenderer.cu:522-611): central differences over the four
+// neighbours of (T_p - I_x) * G_x, averaged over the channels. rn[k] = record of neighbour k (left, right, up, down).
+template <int C>
+__device__ __forceinline__ V2 stencil_gradient(const KernelParams& kp, const float* T_p, const float (*rn)[(2 * C + 3) & ~3],
+                                               float z, const float* __restrict__ W, const float* __restrict__ D, const size_t* nb)
+{
+    float dR[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+    {
+        float acc = 0.f;
+        if (kp.test_backward_mode == 4)  // PointRenderer.cu:543-566
+        {
+            const float W_x = __ldg(W + nb[k]), D_x = __ldg(D + nb[k]);
+#pragma unroll
+            for (int c = 0; c < C; ++c)
+            {
+                float dI;
+                if (W_x == 0.f || z * kp.depth_accept_plus_one < D_x) dI = T_p[c] - rn[k][c];
+                else if (z > D_x * kp.depth_accept_plus_one) dI = 0.f;
+                else dI = (W_x / (W_x + 1.f) * rn[k][c] + 1.f / (W_x + 1.f) * T_p[c] - rn[k][c]);
+                acc += dI * rn[k][C + c];
+            }
+        }
+        else
+        {
+#pragma unroll
+            for (int c = 0; c < C; ++c) acc += (T_p[c] - rn[k][c]) * rn[k][C + c];
+        }
+        dR[k] = acc;
+    }
+    V2 g;
+    g.x = 0.5f * (-dR[0] + dR[1]) / (float)C;
+    g.y = 0.5f * (-dR[2] + dR[3]) / (float)C;
+    return g;
 }
 
-// LISTED: the kernel walks the view's visible list (dense warps of points that passed the depth test in the forward
-// pass) instead of all points.
-template <int C, int MODEL, bool LISTED>
-__global__ void __launch_bounds__(kBlock) k_splat_backward(PointStreams pts, CamSource cs, KernelParams kp, LayerTable lt,
-                                                            BackwardTargets bt, VisibleList vl)
+// Chain the image gradient through the projection (PointRenderer.cu:613-720) and add to the partial sums.
+// Returns false when the chain rejects the point; gp = (x, y, z, count) partial sum of the point gradient.
+template <int MODEL>
+__device__ __forceinline__ bool chain_gradient(const ViewCam& cam, const KernelParams& kp, const FetchedPoint& f, V2 g,
+                                               float scale, float* gp, GeoAccum<MODEL>& acc)
 {
-    constexpr int NI = MODEL == kPinholeDistortion ? 13 : 5;
-    constexpr int RB = (2 * C + 3) & ~3;
-    __shared__ ViewCam cam;
-    __shared__ int s_prefix[LISTED ? kVisibleSegments : 1];
-    __shared__ int s_warp[kBlock / 32];
-    int work = pts.n, n_segments = 0, seg_cap = 0;
-    if (LISTED)
+    Intr5 crop_l = scale_intr(cam.crop, scale);
+    if (MODEL == kPinholeDistortion)
     {
-        work = scan_segments(vl.header, s_prefix, s_warp);
-        n_segments = __ldg(vl.header + kVisibleSegments);
-        seg_cap = __ldg(vl.header + kVisibleSegments + 1);
+        GradPinhole o;
+        if (!project_pinhole_backward(f.p, f.n, f.has_normal, g, cam.V, cam.K, crop_l, cam.dist, kp.check_normal != 0,
+                                      kp.dist_cutoff, &o))
+            return false;
+        gp[0] += o.g_point[0]; gp[1] += o.g_point[1]; gp[2] += o.g_point[2]; gp[3] += 1.f;
+#pragma unroll
+        for (int k = 0; k < 6; ++k) acc.pose[k] += o.g_pose[k];
+        // damping of PointRenderer.cu:647-678 (skew gets no gradient)
+        const float kf = kp.K_gradient_factor, df = kp.distortion_gradient_factor;
+        acc.intr[0] += kf * o.g_k[0]; acc.intr[1] += kf * o.g_k[1]; acc.intr[2] += kf * o.g_k[2]; acc.intr[3] += kf * o.g_k[3];
+        acc.intr[5] += df * o.g_dis[0]; acc.intr[6] += df * o.g_dis[1];
+        acc.intr[7] += df * (o.g_dis[2] * 0.25f);
+        acc.intr[8] += df * (o.g_dis[3] * 0.1f); acc.intr[9] += df * (o.g_dis[4] * 0.1f); acc.intr[10] += df * (o.g_dis[5] * 0.1f);
+        acc.intr[11] += df * (o.g_dis[6] * 0.1f); acc.intr[12] += df * (o.g_dis[7] * 0.1f);
     }
-    __shared__ double s_pose[6];
-    __shared__ float s_intr[NI];
-    __shared__ float s_cnt[2];
-    __shared__ int s_any;
-    load_cam_shared(&cam, cs);
-    if (threadIdx.x < 6) s_pose[threadIdx.x] = 0.0;
-    if (threadIdx.x < NI) s_intr[threadIdx.x] = 0.f;
-    if (threadIdx.x < 2) s_cnt[threadIdx.x] = 0.f;
-    if (threadIdx.x == 0) s_any = 0;
-    __syncthreads();
-
-    const bool want_geo = bt.grad_points || bt.grad_pose || bt.grad_intrinsics;
-    float a_pose[6], a_intr[NI], a_cnt = 0.f;
-#pragma unroll
-    for (int k = 0; k < 6; ++k) a_pose[k] = 0.f;
-#pragma unroll
-    for (int k = 0; k < NI; ++k) a_intr[k] = 0.f;
-
-    const int stride = gridDim.x * blockDim.x;
-    for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < work; t += stride)
+    else
     {
-        int i = t;
-        if (LISTED)
+        GradOcam o;
+        if (!project_ocam_backward(f.p, f.n, f.has_normal, g, cam.V, crop_l, cam.ocam, kp.check_normal != 0, kp.dist_cutoff, &o))
+            return false;
+        gp[0] += o.g_point[0]; gp[1] += o.g_point[1]; gp[2] += o.g_point[2]; gp[3] += 1.f;
+#pragma unroll
+        for (int k = 0; k < 6; ++k) acc.pose[k] += o.g_pose[k];
+#pragma unroll
+        for (int k = 0; k < 5; ++k) acc.intr[k] += o.g_affine[k];
+    }
+    acc.cnt += 1.f;
+    return true;
+}
+
+// Block reduction of the per-view pose / intrinsics sums: warp shuffle, shared memory (double for the pose, which the
+// reference accumulates in double, :1113), then one global atomic per component and block.
+template <int MODEL>
+struct GeoShared
+{
+    double pose[6];
+    float intr[GeoAccum<MODEL>::NI];
+    float cnt;
+    int any;
+};
+template <int MODEL>
+__device__ __forceinline__ void geo_shared_init(GeoShared<MODEL>* s)
+{
+    if (threadIdx.x < 6) s->pose[threadIdx.x] = 0.0;
+    if (threadIdx.x < GeoAccum<MODEL>::NI) s->intr[threadIdx.x] = 0.f;
+    if (threadIdx.x == 0) { s->cnt = 0.f; s->any = 0; }
+}
+// every thread of the block must call this
+template <int MODEL>
+__device__ __forceinline__ void geo_block_reduce(GeoShared<MODEL>* s, const GeoAccum<MODEL>& acc, const BackwardTargets& bt)
+{
+    constexpr int NI = GeoAccum<MODEL>::NI;
+    if (!(bt.grad_pose || bt.grad_intrinsics)) return;
+    const unsigned any = __ballot_sync(0xffffffffu, acc.cnt > 0.f);
+    if (any)
+    {
+        const bool lane0 = (threadIdx.x & 31) == 0;
+        if (bt.grad_pose)
         {
-            // segment k = first with prefix[k] > t
-            int lo = 0, hi = n_segments - 1;
-            while (lo < hi)
+#pragma unroll
+            for (int k = 0; k < 6; ++k)
             {
-                int mid = (lo + hi) >> 1;
-                if (s_prefix[mid] > t) hi = mid; else lo = mid + 1;
+                float v = warp_sum(acc.pose[k]);
+                if (lane0) atomicAdd(&s->pose[k], (double)v);
             }
-            const int before = lo ? s_prefix[lo - 1] : 0;
-            i = __ldg(vl.entries + (size_t)lo * seg_cap + (t - before));
         }
+        if (bt.grad_intrinsics)
+        {
+#pragma unroll
+            for (int k = 0; k < NI; ++k)
+            {
+                float v = warp_sum(acc.intr[k]);
+                if (lane0) atomicAdd(&s->intr[k], v);
+            }
+        }
+        float c = warp_sum(acc.cnt);
+        if (lane0) { atomicAdd(&s->cnt, c); s->any = 1; }
+    }
+    __syncthreads();
+    if (!s->any) return;
+    if (bt.grad_pose)
+    {
+        if (threadIdx.x < 6) atomicAdd(bt.grad_pose + threadIdx.x, s->pose[threadIdx.x]);
+        if (threadIdx.x == 6) atomicAdd(bt.count_pose, s->cnt);
+    }
+    if (bt.grad_intrinsics)
+    {
+        if (threadIdx.x >= 32 && threadIdx.x < 32 + NI) atomicAdd(bt.grad_intrinsics + (threadIdx.x - 32), s->intr[threadIdx.x - 32]);
+        // the reference counts 1/1024 per pinhole contribution and 1 per OCam contribution (:680-681, :718)
+        if (threadIdx.x == 64) atomicAdd(bt.count_intrinsics, MODEL == kPinholeDistortion ? s->cnt * (1.f / 1024.f) : s->cnt);
+    }
+}
+
+// K5 (all points): the reference's structure, one thread per point walking its layers (RenderBackward, :396-724). Used
+// when the forward pass recorded no splat list (or the list overflowed).
+template <int C, int MODEL>
+__global__ void __launch_bounds__(kBlock) k_splat_backward_all(PointStreams pts, const ViewCam* __restrict__ camp, KernelParams kp, LayerTable lt,
+                                                                BackwardTargets bt, const int* __restrict__ run_if_nonzero)
+{
+    constexpr int RB = (2 * C + 3) & ~3;
+    if (run_if_nonzero && __ldg(run_if_nonzero) == 0) return;
+    const ViewCam& cam = *camp;
+    __shared__ GeoShared<MODEL> s_geo;
+    geo_shared_init(&s_geo);
+    __syncthreads();
+    const bool want_geo = bt.grad_points || bt.grad_pose || bt.grad_intrinsics;
+    GeoAccum<MODEL> acc;
+    acc.clear();
+    const int stride = gridDim.x * blockDim.x;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < pts.n; i += stride)
+    {
         const bool drop_out = point_dropped(kp, i);
         FetchedPoint f = fetch_point(pts, i);
         RasterPoint q;
@@ -217,11 +316,9 @@ __global__ void __launch_bounds__(kBlock) k_splat_backward(PointStreams pts, Cam
         int ti = -1;
         float T_p[C], dg[C];
         bool have_t = false, have_dg = false;
-        float gp[3] = {0.f, 0.f, 0.f};
-        float np = 0.f;
+        float gp[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int c = 0; c < C; ++c) dg[c] = 0.f;
-
 #pragma unroll 1
         for (int l = 0; l < lt.L; ++l, scale *= 0.5f, rad *= 0.5f, x *= 0.5f, y *= 0.5f)
         {
@@ -248,130 +345,145 @@ __global__ void __launch_bounds__(kBlock) k_splat_backward(PointStreams pts, Cam
                     have_dg = true;
                 }
             }
-            int edge = min(min(px, py), min(w - 1 - px, h - 1 - py));
+            const int edge = min(min(px, py), min(w - 1 - px, h - 1 - py));
             if (!(point_grad && edge > 2)) continue;
-
             if (!have_t)
             {
                 ti = pts.index ? __ldg(pts.index + i) : i;
-#pragma unroll
-                for (int c = 0; c < C; ++c) T_p[c] = __ldg(bt.texture + (size_t)c * bt.num_texels + ti);
+                load_descriptor<C>(bt.texture, bt.texture_interleaved, bt.num_texels, ti, T_p);
                 have_t = true;
             }
             const size_t nb[4] = {pix - 1, pix + 1, pix - (size_t)w, pix + (size_t)w};
-            float dR[4];
+            float rn[4][RB];
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-            {
-                float rn[RB];
-                load_record<C>(bt.records, (size_t)lt.rec_off[l] + nb[k], rn);
-                float acc = 0.f;
-                if (kp.test_backward_mode == 4)  // PointRenderer.cu:543-566
-                {
-                    const float W_x = __ldg(W + nb[k]), D_x = __ldg(D + nb[k]);
-#pragma unroll
-                    for (int c = 0; c < C; ++c)
-                    {
-                        float dI;
-                        if (W_x == 0.f || q.z * kp.depth_accept_plus_one < D_x) dI = T_p[c] - rn[c];
-                        else if (q.z > D_x * kp.depth_accept_plus_one) dI = 0.f;
-                        else dI = (W_x / (W_x + 1.f) * rn[c] + 1.f / (W_x + 1.f) * T_p[c] - rn[c]);
-                        acc += dI * rn[C + c];
-                    }
-                }
-                else
-                {
-#pragma unroll
-                    for (int c = 0; c < C; ++c) acc += (T_p[c] - rn[c]) * rn[C + c];
-                }
-                dR[k] = acc;
-            }
-            // central differences (PointRenderer.cu:601-608); the per-channel halves are summed here per direction
-            const float dRx = 0.5f * (-dR[0] + dR[1]);
-            const float dRy = 0.5f * (-dR[2] + dR[3]);
-            V2 g; g.x = dRx / (float)C; g.y = dRy / (float)C;
-            Intr5 crop_l = scale_intr(cam.crop, scale);
-            if (MODEL == kPinholeDistortion)
-            {
-                GradPinhole o;
-                if (!project_pinhole_backward(f.p, f.n, f.has_normal, g, cam.V, cam.K, crop_l, cam.dist, kp.check_normal != 0,
-                                              kp.dist_cutoff, &o))
-                    continue;
-                gp[0] += o.g_point[0]; gp[1] += o.g_point[1]; gp[2] += o.g_point[2]; np += 1.f;
-#pragma unroll
-                for (int k = 0; k < 6; ++k) a_pose[k] += o.g_pose[k];
-                // damping of PointRenderer.cu:647-678
-                const float kf = kp.K_gradient_factor, df = kp.distortion_gradient_factor;
-                a_intr[0] += kf * o.g_k[0]; a_intr[1] += kf * o.g_k[1]; a_intr[2] += kf * o.g_k[2]; a_intr[3] += kf * o.g_k[3];
-                a_intr[5] += df * o.g_dis[0]; a_intr[6] += df * o.g_dis[1];
-                a_intr[7] += df * (o.g_dis[2] * 0.25f);
-                a_intr[8] += df * (o.g_dis[3] * 0.1f); a_intr[9] += df * (o.g_dis[4] * 0.1f); a_intr[10] += df * (o.g_dis[5] * 0.1f);
-                a_intr[11] += df * (o.g_dis[6] * 0.1f); a_intr[12] += df * (o.g_dis[7] * 0.1f);
-            }
-            else
-            {
-                GradOcam o;
-                if (!project_ocam_backward(f.p, f.n, f.has_normal, g, cam.V, crop_l, cam.ocam, kp.check_normal != 0,
-                                           kp.dist_cutoff, &o))
-                    continue;
-                gp[0] += o.g_point[0]; gp[1] += o.g_point[1]; gp[2] += o.g_point[2]; np += 1.f;
-#pragma unroll
-                for (int k = 0; k < 6; ++k) a_pose[k] += o.g_pose[k];
-#pragma unroll
-                for (int k = 0; k < 5; ++k) a_intr[k] += o.g_affine[k];
-            }
-            a_cnt += 1.f;
+            for (int k = 0; k < 4; ++k) load_record<C>(bt.records, (size_t)lt.rec_off[l] + nb[k], rn[k]);
+            V2 g = stencil_gradient<C>(kp, T_p, rn, q.z, W, D, nb);
+            chain_gradient<MODEL>(cam, kp, f, g, scale, gp, acc);
         }
-
         if (have_dg)
         {
             if (ti < 0) ti = pts.index ? __ldg(pts.index + i) : i;
-#pragma unroll
-            for (int c = 0; c < C; ++c) atomicAdd(bt.grad_texture + (size_t)c * bt.num_texels + ti, dg[c]);
+            add_descriptor_gradient<C>(bt.grad_texture, bt.grad_texture_interleaved, bt.num_texels, ti, dg);
         }
-        if (np > 0.f && bt.grad_points) atomicAdd(bt.grad_points + i, make_float4(gp[0], gp[1], gp[2], np));
+        if (gp[3] > 0.f && bt.grad_points) atomicAdd(bt.grad_points + i, make_float4(gp[0], gp[1], gp[2], gp[3]));
     }
+    geo_block_reduce<MODEL>(&s_geo, acc, bt);
+}
 
-    // block reduction of the per-view pose / intrinsics sums
-    if (!(bt.grad_pose || bt.grad_intrinsics)) return;
-    const unsigned any = __ballot_sync(0xffffffffu, a_cnt > 0.f);
-    if (any)
+// Inclusive prefix sums of the splat list's segment counts, in shared memory (every thread of the block takes part).
+__device__ __forceinline__ int scan_segments(const int* __restrict__ header, int* s_prefix, int* s_warp)
+{
+    constexpr int PER = kVisibleSegments / kBlock;
+    int local[PER];
+    int sum = 0;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) { sum += __ldg(header + threadIdx.x * PER + j); local[j] = sum; }
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1)
     {
-        const bool lane0 = (threadIdx.x & 31) == 0;
-        if (bt.grad_pose)
-        {
-#pragma unroll
-            for (int k = 0; k < 6; ++k)
-            {
-                float v = warp_sum(a_pose[k]);
-                if (lane0) atomicAdd(&s_pose[k], (double)v);
-            }
-        }
-        if (bt.grad_intrinsics)
-        {
-#pragma unroll
-            for (int k = 0; k < NI; ++k)
-            {
-                float v = warp_sum(a_intr[k]);
-                if (lane0) atomicAdd(&s_intr[k], v);
-            }
-        }
-        float c = warp_sum(a_cnt);
-        if (lane0) { atomicAdd(&s_cnt[0], c); s_any = 1; }
+        int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if ((threadIdx.x & 31) >= o) incl += v;
     }
+    if ((threadIdx.x & 31) == 31) s_warp[threadIdx.x >> 5] = incl;
     __syncthreads();
-    if (!s_any) return;
-    if (bt.grad_pose)
+    int woff = 0;
+    for (int k = 0; k < (int)(threadIdx.x >> 5); ++k) woff += s_warp[k];
+    const int excl = woff + incl - sum;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) s_prefix[threadIdx.x * PER + j] = excl + local[j];
+    __syncthreads();
+    return s_prefix[kVisibleSegments - 1];
+}
+
+// K5 (splat list): one thread per (point, layer) pair that the backward pass has to visit, as recorded by the blend
+// kernel. Dense warps, no layer loop, no depth test (the forward pass already applied it, including the stop at a point's
+// first failure), and everything a splat needs is requested at once: weight, the pixel's record, the four neighbours.
+template <int C, int MODEL>
+__global__ void __launch_bounds__(kBlock) k_splat_backward_list(PointStreams pts, const ViewCam* __restrict__ camp, KernelParams kp, LayerTable lt,
+                                                                 BackwardTargets bt, VisibleList vl)
+{
+    constexpr int RB = (2 * C + 3) & ~3;
+    if (__ldg(vl.header + kVisibleSegments + 2) != 0) return;  // the list overflowed: k_splat_backward_all takes over
+    const ViewCam& cam = *camp;
+    __shared__ GeoShared<MODEL> s_geo;
+    __shared__ int s_prefix[kVisibleSegments];
+    __shared__ int s_warp[kBlock / 32];
+    geo_shared_init(&s_geo);
+    const int work = scan_segments(vl.header, s_prefix, s_warp);
+    const int n_segments = __ldg(vl.header + kVisibleSegments);
+    const int seg_cap = __ldg(vl.header + kVisibleSegments + 1);
+    const bool want_geo = bt.grad_points || bt.grad_pose || bt.grad_intrinsics;
+    GeoAccum<MODEL> acc;
+    acc.clear();
+    const int stride = gridDim.x * blockDim.x;
+    // t -> list entry: segment by binary search over the prefix sums
+    auto entry_of = [&](int t) -> unsigned
     {
-        if (threadIdx.x < 6) atomicAdd(bt.grad_pose + threadIdx.x, s_pose[threadIdx.x]);
-        if (threadIdx.x == 6) atomicAdd(bt.count_pose, s_cnt[0]);
-    }
-    if (bt.grad_intrinsics)
+        int lo = 0, hi = n_segments - 1;
+        while (lo < hi)
+        {
+            int mid = (lo + hi) >> 1;
+            if (s_prefix[mid] > t) hi = mid; else lo = mid + 1;
+        }
+        const int before = lo ? s_prefix[lo - 1] : 0;
+        return (unsigned)__ldg(vl.entries + (size_t)lo * seg_cap + (t - before));
+    };
+    int t = blockIdx.x * blockDim.x + threadIdx.x;
+    unsigned e_next = 0;
+    float4 p_next = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (t < work) { e_next = entry_of(t); p_next = __ldg(pts.position + (e_next & kSplatPointMask)); }
+    for (; t < work; t += stride)
     {
-        if (threadIdx.x >= 32 && threadIdx.x < 32 + NI) atomicAdd(bt.grad_intrinsics + (threadIdx.x - 32), s_intr[threadIdx.x - 32]);
-        // the reference counts 1/1024 per pinhole contribution and 1 per OCam contribution (:680-681, :718)
-        if (threadIdx.x == 64) atomicAdd(bt.count_intrinsics, MODEL == kPinholeDistortion ? s_cnt[0] * (1.f / 1024.f) : s_cnt[0]);
+        // the next entry and its position are requested before this one is processed
+        const unsigned e = e_next;
+        const float4 p_cur = p_next;
+        if (stride < work - t) { e_next = entry_of(t + stride); p_next = __ldg(pts.position + (e_next & kSplatPointMask)); }
+        const int i = (int)(e & kSplatPointMask);
+        const int l = (int)(e >> kSplatLayerShift);
+        const bool drop_out = point_dropped(kp, i);
+        const bool point_grad = want_geo && ((kp.ghost_gradients && drop_out) || (!kp.ghost_gradients && !drop_out));
+        FetchedPoint f = fetch_point(pts, i, p_cur);
+        RasterPoint q;
+        if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, kp.check_normal != 0, kp.dist_cutoff, &q, false)) continue;
+        const float scale = __int_as_float((127 - l) << 23);  // 0.5^l, the same value l halvings give
+        const int px = round_half_even_bounded(q.x * scale), py = round_half_even_bounded(q.y * scale);
+        const int w = lt.w[l], h = lt.h[l];
+        if ((unsigned)px >= (unsigned)w || (unsigned)py >= (unsigned)h) continue;  // cannot happen for a recorded splat
+        const size_t pix = (size_t)py * w + px;
+        const float* __restrict__ W = lt.weight[l];
+        const float* __restrict__ D = lt.depth[l];
+        const size_t rbase = (size_t)lt.rec_off[l] + pix;
+        const int edge = min(min(px, py), min(w - 1 - px, h - 1 - py));
+        const bool stencil = point_grad && edge > 2;
+        const size_t nb[4] = {pix - 1, pix + 1, pix - (size_t)w, pix + (size_t)w};
+        const int ti = pts.index ? __ldg(pts.index + i) : i;
+        const float wgt = __ldg(W + pix);
+        float rc[RB], rn[4][RB], T_p[C];
+        const bool want_dg = !drop_out && bt.grad_texture;
+        if (want_dg) load_record<C>(bt.records, rbase, rc);
+        if (stencil)
+        {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) load_record<C>(bt.records, (size_t)lt.rec_off[l] + nb[k], rn[k]);
+            load_descriptor<C>(bt.texture, bt.texture_interleaved, bt.num_texels, ti, T_p);
+        }
+        if (!drop_out && wgt == 0.f) continue;  // :473
+        if (want_dg)
+        {
+            const float iw = 1.f / wgt;
+            float dg[C];
+#pragma unroll
+            for (int c = 0; c < C; ++c) dg[c] = iw * rc[C + c];
+            add_descriptor_gradient<C>(bt.grad_texture, bt.grad_texture_interleaved, bt.num_texels, ti, dg);
+        }
+        if (!stencil) continue;
+        V2 g = stencil_gradient<C>(kp, T_p, rn, q.z, W, D, nb);
+        float gp[4] = {0.f, 0.f, 0.f, 0.f};
+        if (chain_gradient<MODEL>(cam, kp, f, g, scale, gp, acc) && bt.grad_points)
+            atomicAdd(bt.grad_points + i, make_float4(gp[0], gp[1], gp[2], gp[3]));
     }
+    geo_block_reduce<MODEL>(&s_geo, acc, bt);
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -402,7 +514,7 @@ __global__ void k_normalize_intrinsics(float* g, const float* cnt, int n, int co
 
 // ------------------------------------------------------------------------------------------------------
 template <int C>
-static adop_status launch_view_backward(const PointStreams& pts, const CamSource& cam, const KernelParams& kp, const LayerTable& lt,
+static adop_status launch_view_backward(const PointStreams& pts, const ViewCam* cam, const KernelParams& kp, const LayerTable& lt,
                                         const BackwardTargets& bt, float* grad_background, float* grad_env, int env_h, int env_w,
                                         cudaStream_t st, const VisibleList& vl, int model)
 {
@@ -416,32 +528,30 @@ static adop_status launch_view_backward(const PointStreams& pts, const CamSource
                                                   lt, cam, kp, bt.background, const_cast<float*>(bt.records), grad_background,
                                                   grad_env, env_h, env_w)));
     }
-    if (vl.header)
+    // With a splat list the dense kernel runs; the all-points kernel is launched behind it and returns at once unless
+    // the list's overflow flag is set (decided on the device, no host round trip).
+    const int* flag = vl.header ? vl.header + kVisibleSegments + 2 : nullptr;
+    if (model == kPinholeDistortion)
     {
-        if (model == kPinholeDistortion)
+        if (vl.header)
         {
-            static const int g = resident_grid(k_splat_backward<C, kPinholeDistortion, true>, 1ll << 40);
-            ADOP_LAUNCH("k_splat_backward", st, (k_splat_backward<C, kPinholeDistortion, true><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(
-                                                    pts, cam, kp, lt, bt, vl)));
+            static const int g = resident_grid(k_splat_backward_list<C, kPinholeDistortion>, 1ll << 40);
+            ADOP_LAUNCH("k_splat_backward_list", st, (k_splat_backward_list<C, kPinholeDistortion><<<g, kBlock, 0, st>>>(pts, cam, kp, lt, bt, vl)));
         }
-        else
-        {
-            static const int g = resident_grid(k_splat_backward<C, kOcam, true>, 1ll << 40);
-            ADOP_LAUNCH("k_splat_backward", st, (k_splat_backward<C, kOcam, true><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(
-                                                    pts, cam, kp, lt, bt, vl)));
-        }
-    }
-    else if (model == kPinholeDistortion)
-    {
-        static const int g = resident_grid(k_splat_backward<C, kPinholeDistortion, false>, 1ll << 40);
-        ADOP_LAUNCH("k_splat_backward_all", st, (k_splat_backward<C, kPinholeDistortion, false><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(
-                                                    pts, cam, kp, lt, bt, vl)));
+        static const int g = resident_grid(k_splat_backward_all<C, kPinholeDistortion>, 1ll << 40);
+        ADOP_LAUNCH("k_splat_backward_all", st, (k_splat_backward_all<C, kPinholeDistortion><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(
+                                                    pts, cam, kp, lt, bt, flag)));
     }
     else
     {
-        static const int g = resident_grid(k_splat_backward<C, kOcam, false>, 1ll << 40);
-        ADOP_LAUNCH("k_splat_backward_all", st, (k_splat_backward<C, kOcam, false><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(
-                                                    pts, cam, kp, lt, bt, vl)));
+        if (vl.header)
+        {
+            static const int g = resident_grid(k_splat_backward_list<C, kOcam>, 1ll << 40);
+            ADOP_LAUNCH("k_splat_backward_list", st, (k_splat_backward_list<C, kOcam><<<g, kBlock, 0, st>>>(pts, cam, kp, lt, bt, vl)));
+        }
+        static const int g = resident_grid(k_splat_backward_all<C, kOcam>, 1ll << 40);
+        ADOP_LAUNCH("k_splat_backward_all", st, (k_splat_backward_all<C, kOcam><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(
+                                                    pts, cam, kp, lt, bt, flag)));
     }
     ADOP_CUDA_TRY(cudaGetLastError());
     return ADOP_OK;
@@ -497,7 +607,8 @@ extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (!io->accumulate)
     {
-        if (io->grad_texture) ADOP_CUDA_TRY(cudaMemsetAsync(io->grad_texture, 0, sizeof(float) * (size_t)C * T, st));
+        if (io->grad_texture && !io->grad_texture_interleaved)
+            ADOP_CUDA_TRY(cudaMemsetAsync(io->grad_texture, 0, sizeof(float) * (size_t)C * T, st));
         if (io->grad_background) ADOP_CUDA_TRY(cudaMemsetAsync(io->grad_background, 0, sizeof(float) * C, st));
         if (io->grad_points) ADOP_CUDA_TRY(cudaMemsetAsync(io->grad_points, 0, sizeof(float) * (size_t)N * 4, st));
         if (io->grad_pose) ADOP_CUDA_TRY(cudaMemsetAsync(io->grad_pose, 0, sizeof(double) * (size_t)s->num_images * 6, st));
@@ -508,8 +619,11 @@ extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view
             ADOP_CUDA_TRY(cudaMemsetAsync(io->grad_env_map, 0, sizeof(float) * (size_t)C * s->env_h * s->env_w, st));
     }
 
+    if (io->grad_texture && io->grad_texture_interleaved)
+        ADOP_CUDA_TRY(cudaMemsetAsync(io->grad_texture_interleaved, 0, sizeof(float) * (size_t)C * T, st));
     LayerTable base;
     fill_layer_dims(views[0].w, views[0].h, L, &base);
+    ViewCam* cams = static_cast<ViewCam*>(io->workspace);
     PointStreams pts;
     pts.position = reinterpret_cast<const float4*>(s->position);
     pts.normal = s->normal;
@@ -527,9 +641,17 @@ extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view
             lt.grad[l] = io->grad_color[l] + (size_t)b * C * plane;
         }
         KernelParams kp = make_kernel_params(rp, io->dropout_mask, N, b);
-        CamSource cam = make_cam_source(s, &views[b]);
+        if (b % kCamChunk == 0)
+        {
+            CamChunkSource src;
+            fill_cam_chunk(&src, s, views + b, B - b < kCamChunk ? B - b : kCamChunk);
+            ADOP_LAUNCH("k_build_cams", st, (k_build_cams<<<1, kCamChunk, 0, st>>>(src, cams)));
+        }
+        const ViewCam* cam = cams + (b % kCamChunk);
         BackwardTargets bt;
         bt.texture = s->texture;
+        bt.texture_interleaved = s->texture_interleaved;
+        bt.grad_texture_interleaved = io->grad_texture ? io->grad_texture_interleaved : nullptr;
         bt.num_texels = T;
         bt.background = s->background;
         bt.grad_texture = io->grad_texture;
@@ -538,7 +660,7 @@ extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view
         bt.count_pose = io->grad_pose ? io->count_pose + views[b].image_index : nullptr;
         bt.grad_intrinsics = io->grad_intrinsics ? io->grad_intrinsics + (size_t)views[b].camera_index * cols : nullptr;
         bt.count_intrinsics = io->grad_intrinsics ? io->count_intrinsics + views[b].camera_index : nullptr;
-        bt.records = static_cast<const float*>(io->workspace);
+        bt.records = reinterpret_cast<const float*>(static_cast<const char*>(io->workspace) + kCamRegionBytes);
         float* ge = env ? io->grad_env_map : nullptr;
         // the list's geometry (segments in use, entries per segment) sits in its header, written by the forward pass
         VisibleList vl = make_visible_list(const_cast<int32_t*>(io->visible_list), N, b, 1);
@@ -552,6 +674,11 @@ extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view
             default: return ADOP_ERR_UNSUPPORTED;
         }
         if (r != ADOP_OK) return r;
+    }
+    if (io->grad_texture && io->grad_texture_interleaved)
+    {
+        adop_status ds = adop_texture_deinterleave(io->grad_texture_interleaved, io->grad_texture, C, T, io->accumulate ? 1 : 0, stream);
+        if (ds != ADOP_OK) return ds;
     }
     if (io->normalize)
         return adop_raster_normalize_gradients(io->grad_points, N, io->grad_pose, io->count_pose, s->num_images,

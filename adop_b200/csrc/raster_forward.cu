@@ -11,6 +11,8 @@
 //  * the resolve kernel turns records into the NCHW tensors of the operator's interface in a single pass
 //    (normalise, background, environment map, mask, weight plane) and clears the records it read, so the
 //    one accumulator, small enough to stay in the 126 MB L2, is reused by every view of the batch.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace adop {
@@ -26,33 +28,55 @@ __global__ void k_fill(float* __restrict__ dst, size_t n, float v)
     for (size_t k = n4 * 4 + i; k < n; k += stride) dst[k] = v;
 }
 
-// ------------------------------------------------------------------------------------------------------
-// K1: depth prepass. One thread per point and iteration; per layer an early-z read and, if the point could
-// be the closest, an atomicMin on the float's bit pattern (valid because z > 0).
-template <int L>
-__global__ void __launch_bounds__(kBlock) k_depth_prepass(PointStreams pts, CamSource cs, KernelParams kp, LayerTable lt)
+// [C,T] planes <-> [T,C] interleaved descriptors (one texel per thread; plane accesses are coalesced, interleaved
+// accesses are contiguous vectors)
+__global__ void k_texture_interleave(const float* __restrict__ in, float* __restrict__ out, int C, int T)
 {
-    __shared__ ViewCam cam;
-    load_cam_shared(&cam, cs);
+    for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < T; t += gridDim.x * blockDim.x)
+        for (int c = 0; c < C; ++c) out[(size_t)t * C + c] = __ldcs(in + (size_t)c * T + t);
+}
+__global__ void k_texture_deinterleave(const float* __restrict__ in, float* __restrict__ out, int C, int T, int accumulate)
+{
+    for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < T; t += gridDim.x * blockDim.x)
+        for (int c = 0; c < C; ++c)
+        {
+            float v = __ldcs(in + (size_t)t * C + c);
+            float* dst = out + (size_t)c * T + t;
+            *dst = accumulate ? *dst + v : v;
+        }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// K1: depth prepass. One thread per point and iteration; per layer an atomicMin on the float's bit pattern (valid
+// because z > 0). On the coarser layers, where hundreds of points share a pixel, an early-z read first drops the points
+// that cannot win (PointRenderer.cu:275-279; a stale value only costs an extra atomic). On the finest layer the read costs
+// more than the atomics it saves, so it is skipped there. Warp-level aggregation of equal pixels (__match_any_sync) was
+// measured 3-6x slower than plain atomics on this workload and is not used.
+// PLAIN: neither the normal test nor the radius drop-out rule is in use, so their code (and registers) are compiled out.
+template <int L, bool PLAIN>
+__global__ void __launch_bounds__(kBlock, 8) k_depth_prepass(PointStreams pts, const ViewCam* __restrict__ camp, KernelParams kp, LayerTable lt)
+{
+    const ViewCam& cam = *camp;
+    const bool use_normal = PLAIN ? false : kp.check_normal != 0;
+    const bool use_radius = PLAIN ? false : kp.drop_out_points_by_radius != 0;
     const int stride = gridDim.x * blockDim.x;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < pts.n; i += stride)
     {
-        FetchedPoint f = fetch_point(pts, i);
+        FetchedPoint f;
+        if (PLAIN) { float4 c = __ldg(pts.position + i); f.p.x = c.x; f.p.y = c.y; f.p.z = c.z; f.r = c.w; f.has_normal = false; f.n.x = f.n.y = f.n.z = 0.f; }
+        else f = fetch_point(pts, i);
         RasterPoint q;
-        if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, kp.check_normal != 0, kp.dist_cutoff, &q,
-                                kp.drop_out_points_by_radius != 0)) continue;
+        if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, use_normal, kp.dist_cutoff, &q, use_radius)) continue;
         float x = q.x, y = q.y, rad = q.radius_px;
         const int zi = __float_as_int(q.z);
 #pragma unroll
         for (int l = 0; l < L; ++l, rad *= 0.5f, x *= 0.5f, y *= 0.5f)
         {
-            if (kp.drop_out_points_by_radius && rad < kp.drop_out_radius_threshold) break;
+            if (use_radius && rad < kp.drop_out_radius_threshold) break;
             int px = round_half_even_bounded(x), py = round_half_even_bounded(y);
             if ((unsigned)px >= (unsigned)lt.w[l] || (unsigned)py >= (unsigned)lt.h[l]) continue;
             int* dst = reinterpret_cast<int*>(lt.depth[l]) + (size_t)py * lt.w[l] + px;
-            // early z (PointRenderer.cu:275-279): a stale value only costs an extra atomic
-            if (zi >= __ldcg(dst)) continue;
-            atomicMin(dst, zi);
+            if (l == 0 || zi < __ldg(dst)) atomicMin(dst, zi);
         }
     }
 }
@@ -81,17 +105,19 @@ __device__ __forceinline__ void splat_record(float* rec, const float* t)
     }
 }
 
-// With EMIT the kernel also appends every point that passed the test on some layer to this block's segment of the
-// view's visible list (shared-memory counter, no global atomics); in ghost-gradient mode dropped points are tested too
-// (they blend nothing but the backward pass needs them, PointRenderer.cu:487-488).
-template <int L, int C, bool EMIT>
-__global__ void __launch_bounds__(kBlock) k_blend(PointStreams pts, const float* __restrict__ texture, int num_texels,
-                                                   CamSource cs, KernelParams kp, LayerTable lt, float* __restrict__ accum,
-                                                   VisibleList vl)
+// With EMIT the kernel also appends the (point, layer) splats that the backward pass will visit to this block's segment
+// of the view's splat list (shared-memory counter, no global atomics); in ghost-gradient mode dropped points are tested
+// too (they blend nothing but the backward pass needs them, PointRenderer.cu:487-488).
+template <int L, int C, bool EMIT, bool PLAIN>
+__global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, const float* __restrict__ texture,
+                                                   const float* __restrict__ texture_interleaved, int num_texels,
+                                                   const ViewCam* __restrict__ camp, KernelParams kp, LayerTable lt,
+                                                   float* __restrict__ accum, VisibleList vl)
 {
-    __shared__ ViewCam cam;
+    const ViewCam& cam = *camp;
+    const bool use_normal = PLAIN ? false : kp.check_normal != 0;
+    const bool use_radius = PLAIN ? false : kp.drop_out_points_by_radius != 0;
     __shared__ int s_count;
-    load_cam_shared(&cam, cs);
     if (EMIT)
     {
         if (threadIdx.x == 0) s_count = 0;
@@ -100,45 +126,102 @@ __global__ void __launch_bounds__(kBlock) k_blend(PointStreams pts, const float*
     constexpr int RS = ((C + 1) + 3) & ~3;
     const int stride = gridDim.x * blockDim.x;
     int* seg = EMIT ? vl.entries + (size_t)blockIdx.x * vl.seg_cap : nullptr;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < pts.n; i += stride)
+    const int lane = threadIdx.x & 31;
+
+    // One point: blend it, and return the mask of layers the backward pass will visit for it.
+    auto blend_point = [&](int i, float4 cur) -> unsigned
     {
         const bool dropped = point_dropped(kp, i);
-        if (dropped && !(EMIT && kp.ghost_gradients)) continue;
-        FetchedPoint f = fetch_point(pts, i);
+        if (dropped && !(EMIT && kp.ghost_gradients)) return 0u;
+        FetchedPoint f;
+        if (PLAIN) { f.p.x = cur.x; f.p.y = cur.y; f.p.z = cur.z; f.r = cur.w; f.has_normal = false; f.n.x = f.n.y = f.n.z = 0.f; }
+        else f = fetch_point(pts, i, cur);
         RasterPoint q;
-        if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, kp.check_normal != 0, kp.dist_cutoff, &q,
-                                kp.drop_out_points_by_radius != 0)) continue;
+        if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, use_normal, kp.dist_cutoff, &q, use_radius)) return 0u;
         float x = q.x, y = q.y, rad = q.radius_px;
-        bool have_t = false, passed = false;
-        float t[C];
+        // the depth reads of all layers go out together
+        long long pix[L];
+        bool live = true;
 #pragma unroll
         for (int l = 0; l < L; ++l, rad *= 0.5f, x *= 0.5f, y *= 0.5f)
         {
-            if (kp.drop_out_points_by_radius && rad < kp.drop_out_radius_threshold) break;
+            if (use_radius && rad < kp.drop_out_radius_threshold) live = false;  // break, :368-371
             int px = round_half_even_bounded(x), py = round_half_even_bounded(y);
-            if ((unsigned)px >= (unsigned)lt.w[l] || (unsigned)py >= (unsigned)lt.h[l]) continue;
-            size_t pix = (size_t)py * lt.w[l] + px;
-            float image_depth = __ldg(lt.depth[l] + pix);
-            if (q.z > image_depth * kp.depth_accept_plus_one) continue;
-            passed = true;
-            if (dropped) break;  // listed for the backward pass; blends nothing
-            if (!have_t)
-            {
-                int ti = pts.index ? __ldg(pts.index + i) : i;
-#pragma unroll
-                for (int c = 0; c < C; ++c) t[c] = __ldg(texture + (size_t)c * num_texels + ti);
-                have_t = true;
-            }
-            splat_record<C>(accum + ((size_t)lt.rec_off[l] + pix) * RS, t);
+            bool in = live && (unsigned)px < (unsigned)lt.w[l] && (unsigned)py < (unsigned)lt.h[l];
+            pix[l] = in ? (long long)py * lt.w[l] + px : -1;
         }
-        if (EMIT && passed) seg[atomicAdd(&s_count, 1)] = i;
+        unsigned pass = 0;
+#pragma unroll
+        for (int l = 0; l < L; ++l)
+        {
+            float image_depth = pix[l] >= 0 ? __ldg(lt.depth[l] + pix[l]) : 0.f;
+            if (pix[l] >= 0 && !(q.z > image_depth * kp.depth_accept_plus_one)) pass |= 1u << l;
+        }
+        if (pass == 0) return 0u;
+        if (!dropped)
+        {
+            float t[C];
+            const int ti = pts.index ? __ldg(pts.index + i) : i;
+            load_descriptor<C>(texture, texture_interleaved, num_texels, ti, t);
+#pragma unroll
+            for (int l = 0; l < L; ++l)
+                if (pass & (1u << l)) splat_record<C>(accum + ((size_t)lt.rec_off[l] + pix[l]) * RS, t);
+        }
+        // the layers the backward pass will visit: it skips layers the point does not land in and stops at the first
+        // depth failure (PointRenderer.cu:451-462)
+        unsigned bmask = 0;
+#pragma unroll
+        for (int l = 0; l < L; ++l)
+        {
+            if (pix[l] < 0) continue;
+            if (!(pass & (1u << l))) break;
+            bmask |= 1u << l;
+        }
+        return bmask;
+    };
+
+    // warp-uniform trip count, so that the append below can use full-warp shuffles
+    for (int base = blockIdx.x * blockDim.x; base < pts.n; base += stride)
+    {
+        const int i = base + threadIdx.x;
+        unsigned bmask = 0;
+        if (i < pts.n) bmask = blend_point(i, __ldg(pts.position + i));
+        if (EMIT)
+        {
+            __syncwarp();
+            const int cnt = __popc(bmask);
+            int incl = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1)
+            {
+                int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            const int total = __shfl_sync(0xffffffffu, incl, 31);
+            if (total > 0)
+            {
+                // one shared-memory atomic per warp reserves room in this block's segment of the splat list
+                int wbase = 0;
+                if (lane == 0) wbase = atomicAdd(&s_count, total);
+                wbase = __shfl_sync(0xffffffffu, wbase, 0);
+                int at = wbase + incl - cnt;
+                if (wbase + total <= vl.seg_cap)
+                {
+#pragma unroll
+                    for (int l = 0; l < L; ++l)
+                        if (bmask & (1u << l)) seg[at++] = i | (l << kSplatLayerShift);
+                }
+                else if (lane == 0)
+                    vl.header[kVisibleSegments + 2] = 1;  // out of room: the backward pass falls back to walking all points
+            }
+        }
     }
     if (EMIT)
     {
         __syncthreads();
         if (threadIdx.x == 0)
         {
-            vl.header[blockIdx.x] = s_count;
+            vl.header[blockIdx.x] = s_count < vl.seg_cap ? s_count : vl.seg_cap;
             if (blockIdx.x == 0) { vl.header[kVisibleSegments] = vl.segments; vl.header[kVisibleSegments + 1] = vl.seg_cap; }
         }
     }
@@ -147,12 +230,11 @@ __global__ void __launch_bounds__(kBlock) k_blend(PointStreams pts, const float*
 // ------------------------------------------------------------------------------------------------------
 // K3: resolve. One thread per pyramid pixel of the view (all layers in one launch).
 template <int C>
-__global__ void __launch_bounds__(kBlock) k_resolve(LayerTable lt, CamSource cs, KernelParams kp, float* __restrict__ accum,
+__global__ void __launch_bounds__(kBlock) k_resolve(LayerTable lt, const ViewCam* __restrict__ camp, KernelParams kp, float* __restrict__ accum,
                                                      const float* __restrict__ background, const float* __restrict__ env,
                                                      int env_h, int env_w)
 {
-    __shared__ ViewCam cam;
-    load_cam_shared(&cam, cs);
+    const ViewCam& cam = *camp;
     constexpr int RS = ((C + 1) + 3) & ~3;
     const unsigned total = lt.rec_off[kMaxLayers];
     for (unsigned r = blockIdx.x * blockDim.x + threadIdx.x; r < total; r += gridDim.x * blockDim.x)
@@ -216,27 +298,43 @@ __global__ void __launch_bounds__(kBlock) k_resolve(LayerTable lt, CamSource cs,
 }
 
 // ------------------------------------------------------------------------------------------------------
-template <int L, int C>
-static adop_status launch_view_forward(const PointStreams& pts, const adop_scene* s, const CamSource& cam, const KernelParams& kp,
-                                       const LayerTable& lt, float* accum, bool env, cudaStream_t st, int32_t* list_base, int view)
+template <int L, int C, bool PLAIN>
+static adop_status launch_view_forward_impl(const PointStreams& pts, const adop_scene* s, const ViewCam* cam, const KernelParams& kp,
+                                            const LayerTable& lt, float* accum, bool env, cudaStream_t st, int32_t* list_base, int view)
 {
-    static const int g_depth = resident_grid(k_depth_prepass<L>, 1ll << 40);
-    static const int g_blend_plain = resident_grid(k_blend<L, C, false>, 1ll << 40);
-    static const int g_blend_emit = resident_grid(k_blend<L, C, true>, 1ll << 40);
-    const int g_blend = list_base ? (g_blend_emit < kVisibleSegments ? g_blend_emit : kVisibleSegments) : g_blend_plain;
+    static const int g_depth = resident_grid(k_depth_prepass<L, PLAIN>, 1ll << 40);
+    static const int g_blend_plain = resident_grid(k_blend<L, C, false, PLAIN>, 1ll << 40);
+    static const int g_blend_emit = resident_grid(k_blend<L, C, true, PLAIN>, 1ll << 40);
     static const int g_resolve = resident_grid(k_resolve<C>, 1ll << 40);
+    const int g_blend = list_base ? (g_blend_emit < kVisibleSegments ? g_blend_emit : kVisibleSegments) : g_blend_plain;
     const int need = (pts.n + kBlock - 1) / kBlock;
     ADOP_LAUNCH("k_depth_prepass", st,
-                (k_depth_prepass<L><<<need < g_depth ? (need < 1 ? 1 : need) : g_depth, kBlock, 0, st>>>(pts, cam, kp, lt)));
-    const int grid_blend = need < g_blend ? (need < 1 ? 1 : need) : g_blend;
-    VisibleList vl = make_visible_list(list_base, pts.n, view, grid_blend);
+                (k_depth_prepass<L, PLAIN><<<need < g_depth ? (need < 1 ? 1 : need) : g_depth, kBlock, 0, st>>>(pts, cam, kp, lt)));
+    int grid_blend = need < g_blend ? (need < 1 ? 1 : need) : g_blend;
     if (list_base)
     {
+        // a block's list segment holds as many entries as the block has points; visible splats come in clumps (a chunk of
+        // neighbouring points on a front surface is accepted on every layer), so every block should average over at
+        // least 16 chunks from all over the cloud
+        int cap = need / 16;
+        if (cap < 1) cap = 1;
+        if (grid_blend > cap) grid_blend = cap;
+    }
+    VisibleList vl = make_visible_list(list_base, pts.n, view, grid_blend);
+    if (list_base && pts.n >= kSplatMaxPoints)
+    {
+        // too many points for the 28-bit ids of the list: mark it unusable and blend without recording
         ADOP_CUDA_TRY(cudaMemsetAsync(vl.header, 0, sizeof(int) * kVisibleHeaderInts, st));
-        ADOP_LAUNCH("k_blend", st, (k_blend<L, C, true><<<grid_blend, kBlock, 0, st>>>(pts, s->texture, s->num_texels, cam, kp, lt, accum, vl)));
+        ADOP_CUDA_TRY(cudaMemsetAsync(vl.header + kVisibleSegments + 2, 1, sizeof(int), st));
+        ADOP_LAUNCH("k_blend", st, (k_blend<L, C, false, PLAIN><<<grid_blend, kBlock, 0, st>>>(pts, s->texture, s->texture_interleaved, s->num_texels, cam, kp, lt, accum, vl)));
+    }
+    else if (list_base)
+    {
+        ADOP_CUDA_TRY(cudaMemsetAsync(vl.header, 0, sizeof(int) * kVisibleHeaderInts, st));
+        ADOP_LAUNCH("k_blend", st, (k_blend<L, C, true, PLAIN><<<grid_blend, kBlock, 0, st>>>(pts, s->texture, s->texture_interleaved, s->num_texels, cam, kp, lt, accum, vl)));
     }
     else
-        ADOP_LAUNCH("k_blend", st, (k_blend<L, C, false><<<grid_blend, kBlock, 0, st>>>(pts, s->texture, s->num_texels, cam, kp, lt, accum, vl)));
+        ADOP_LAUNCH("k_blend", st, (k_blend<L, C, false, PLAIN><<<grid_blend, kBlock, 0, st>>>(pts, s->texture, s->texture_interleaved, s->num_texels, cam, kp, lt, accum, vl)));
     unsigned total = lt.rec_off[kMaxLayers];
     int grid_px = (int)((total + kBlock - 1) / kBlock);
     if (grid_px > g_resolve) grid_px = g_resolve;
@@ -246,8 +344,18 @@ static adop_status launch_view_forward(const PointStreams& pts, const adop_scene
     return ADOP_OK;
 }
 
+template <int L, int C>
+static adop_status launch_view_forward(const PointStreams& pts, const adop_scene* s, const ViewCam* cam, const KernelParams& kp,
+                                       const LayerTable& lt, float* accum, bool env, cudaStream_t st, int32_t* list_base, int view)
+{
+    // the common case - no normal test (or no normals) and no radius drop-out - gets kernels without that code
+    const bool plain = !(kp.check_normal && pts.normal) && !kp.drop_out_points_by_radius;
+    return plain ? launch_view_forward_impl<L, C, true>(pts, s, cam, kp, lt, accum, env, st, list_base, view)
+                 : launch_view_forward_impl<L, C, false>(pts, s, cam, kp, lt, accum, env, st, list_base, view);
+}
+
 template <int C>
-static adop_status dispatch_layers_forward(int L, const PointStreams& pts, const adop_scene* s, const CamSource& cam,
+static adop_status dispatch_layers_forward(int L, const PointStreams& pts, const adop_scene* s, const ViewCam* cam,
                                            const KernelParams& kp, const LayerTable& lt, float* accum, bool env,
                                            cudaStream_t st, int32_t* list_base, int view)
 {
@@ -277,7 +385,30 @@ extern "C" size_t adop_raster_workspace_bytes(int32_t w, int32_t h, int32_t laye
     // forward: accumulator records (C sums + weight); backward: interleaved [image | gradient] records
     int fwd = record_floats(channels), bwd = (2 * channels + 3) & ~3;
     size_t bytes = (size_t)lt.rec_off[kMaxLayers] * (fwd > bwd ? fwd : bwd) * sizeof(float);
-    return bytes + 256;
+    return kCamRegionBytes + bytes + 256;  // per-view camera records, then the pixel records
+}
+
+extern "C" adop_status adop_texture_interleave(const float* texture, float* out, int32_t channels, int32_t num_texels, void* stream)
+{
+    if (!texture || !out || channels <= 0 || num_texels <= 0) return ADOP_ERR_INVALID_ARGUMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int grid = (num_texels + kBlock - 1) / kBlock;
+    if (grid > sm_count() * 16) grid = sm_count() * 16;
+    ADOP_LAUNCH("k_texture_interleave", st, (k_texture_interleave<<<grid, kBlock, 0, st>>>(texture, out, channels, num_texels)));
+    ADOP_CUDA_TRY(cudaGetLastError());
+    return ADOP_OK;
+}
+
+extern "C" adop_status adop_texture_deinterleave(const float* in, float* out, int32_t channels, int32_t num_texels,
+                                                 int32_t accumulate, void* stream)
+{
+    if (!in || !out || channels <= 0 || num_texels <= 0) return ADOP_ERR_INVALID_ARGUMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int grid = (num_texels + kBlock - 1) / kBlock;
+    if (grid > sm_count() * 16) grid = sm_count() * 16;
+    ADOP_LAUNCH("k_texture_deinterleave", st, (k_texture_deinterleave<<<grid, kBlock, 0, st>>>(in, out, channels, num_texels, accumulate)));
+    ADOP_CUDA_TRY(cudaGetLastError());
+    return ADOP_OK;
 }
 
 extern "C" size_t adop_raster_visible_list_ints(int32_t num_points)
@@ -309,7 +440,8 @@ extern "C" adop_status adop_raster_forward(const adop_scene* s, const adop_view*
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     LayerTable base;
     fill_layer_dims(w0, h0, L, &base);
-    float* accum = static_cast<float*>(io->workspace);
+    ViewCam* cams = static_cast<ViewCam*>(io->workspace);
+    float* accum = reinterpret_cast<float*>(static_cast<char*>(io->workspace) + kCamRegionBytes);
     const size_t accum_bytes = (size_t)base.rec_off[kMaxLayers] * record_floats(C) * sizeof(float);
     ADOP_CUDA_TRY(cudaMemsetAsync(accum, 0, accum_bytes, st));
     const int sms = sm_count();
@@ -329,9 +461,15 @@ extern "C" adop_status adop_raster_forward(const adop_scene* s, const adop_view*
     pts.normal = s->normal;
     pts.index = s->index;
     pts.n = N;
-    // the pose and intrinsics tensors live on the device; the per-view camera is gathered there
+    // the pose and intrinsics tensors live on the device; the per-view cameras are gathered there, a chunk at a time
     for (int b = 0; b < B; ++b)
     {
+        if (b % kCamChunk == 0)
+        {
+            CamChunkSource src;
+            fill_cam_chunk(&src, s, views + b, B - b < kCamChunk ? B - b : kCamChunk);
+            ADOP_LAUNCH("k_build_cams", st, (k_build_cams<<<1, kCamChunk, 0, st>>>(src, cams)));
+        }
         LayerTable lt = base;
         for (int l = 0; l < L; ++l)
         {
@@ -342,7 +480,7 @@ extern "C" adop_status adop_raster_forward(const adop_scene* s, const adop_view*
             lt.mask[l] = (rp->output_background_mask && io->layers[l].mask) ? io->layers[l].mask + (size_t)b * plane : nullptr;
         }
         KernelParams kp = make_kernel_params(rp, io->dropout_mask, N, b);
-        CamSource cam = make_cam_source(s, &views[b]);
+        const ViewCam* cam = cams + (b % kCamChunk);
         adop_status r;
         switch (C)
         {

@@ -90,19 +90,40 @@ class ForwardResult:
         self.views, self.num_layers = views, num_layers
         self.visible = visible
 
-    def visible_counts(self):
-        """Points per view that passed the depth test on at least one layer (needs `visible`)."""
+    def splat_counts(self):
+        """(point, layer) splats per view that the backward pass visits, as recorded in `visible`."""
         n_seg = 2048
         return self.visible[:, :n_seg].sum(dim=1)
+
+    def list_overflowed(self):
+        return self.visible[:, 2048 + 2] != 0
 
 
 class PointRasterizer:
     """Owns the reusable scratch (the role of PointRendererCache, PointRenderer.h:96-157)."""
 
-    def __init__(self, device="cuda:0"):
+    def __init__(self, device="cuda:0", interleave_descriptors=True):
         self.lib = capi.load_library()
         self.device = torch.device(device)
         self._ws = None
+        self.interleave_descriptors = interleave_descriptors
+        self._tex_i = None    # [T,C] working copy of the descriptors, refreshed by every forward call
+        self._gtex_i = None   # [T,C] scratch for the descriptor gradient
+
+    def _scene_struct(self, scene, refresh):
+        """AdopScene of `scene`; with interleave_descriptors also keeps the [T,C] working copy up to date."""
+        sc = fill_scene_struct(scene.tensors(), _tptr)
+        if self.interleave_descriptors:
+            shape = (sc.num_texels, sc.channels)
+            if self._tex_i is None or tuple(self._tex_i.shape) != shape:
+                self._tex_i = torch.empty(shape, dtype=torch.float32, device=self.device)
+                refresh = True
+            if refresh:
+                stream = torch.cuda.current_stream(self.device).cuda_stream
+                capi.check(self.lib.adop_texture_interleave(scene.texture.data_ptr(), self._tex_i.data_ptr(), sc.channels,
+                                                            sc.num_texels, C.c_void_p(stream)), "adop_texture_interleave")
+            sc.texture_interleaved = self._tex_i.data_ptr()
+        return sc
 
     def _workspace(self, w, h, layers, channels):
         need = self.lib.adop_raster_workspace_bytes(w, h, layers, channels)
@@ -121,7 +142,7 @@ class PointRasterizer:
         B = len(va)
         w, h = va[0].w, va[0].h
         with torch.cuda.device(self.device):
-            sc = fill_scene_struct(scene.tensors(), _tptr)
+            sc = self._scene_struct(scene, refresh=True)
             ch = sc.channels
             ws = self._workspace(w, h, num_layers, ch)
             sizes = capi.layer_sizes(w, h, num_layers)
@@ -163,7 +184,7 @@ class PointRasterizer:
         va, L = fwd.views, fwd.num_layers
         B = len(va)
         with torch.cuda.device(self.device):
-            sc = fill_scene_struct(scene.tensors(), _tptr)
+            sc = self._scene_struct(scene, refresh=False)  # the forward call of this step refreshed the copy
             dev = self.device
             if out is None:
                 out = dict(texture=torch.empty_like(scene.texture), background=torch.empty_like(scene.background))
@@ -204,6 +225,10 @@ class PointRasterizer:
             io.workspace = ws.data_ptr()
             io.workspace_bytes = ws.numel()
             io.visible_list = fwd.visible.data_ptr() if fwd.visible is not None else None
+            if self.interleave_descriptors:
+                if self._gtex_i is None or self._gtex_i.shape != self._tex_i.shape:
+                    self._gtex_i = torch.empty_like(self._tex_i)
+                io.grad_texture_interleaved = self._gtex_i.data_ptr()
             stream = torch.cuda.current_stream(self.device).cuda_stream
             st = self.lib.adop_raster_backward(C.byref(sc), va, B, C.byref(params), L, C.byref(io), C.c_void_p(stream))
             capi.check(st, "adop_raster_backward")

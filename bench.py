@@ -279,8 +279,9 @@ def main():
     capi.profile_enable(False)
     ras.forward(scene, views, params, L, out=fwd)
     torch.cuda.synchronize()
-    # U_v: points of the view with at least one accepted layer = length of the visible list the forward pass recorded
-    U_views = [float(c) for c in fwd.visible_counts().tolist()]
+    # U_v: points of the view with at least one accepted layer. The forward pass records (point, layer) splats; the
+    # points accepted on the finest layer are a lower bound of U_v, the splat count an upper bound; the lower bound is used.
+    U_views = [float(fwd.weights[0][b].sum().item()) for b in range(V)]
     fwd_b, bwd_b, step_b, per_view_bwd = algorithmic_bytes(N, C, P, U_views, env_hw=arrays["env_map"].shape[1:])
     peaks = {}
     try:

@@ -136,46 +136,50 @@ ADOP_HD float acos_f(float c)
 // ---------------------------------------------------------------------------------------------------
 // rigid transform. A pose is the 8-double record of NeuralStructure.cpp:13-27 (a Sophus::SE3d memory
 // image): unit quaternion x y z w, translation x y z, one padding double; stored world -> camera.
-// It is cast to float before use (PointRenderer.cu:73).
+// The reference casts it to float and rotates with the quaternion (PointRenderer.cu:73). Here the rotation
+// matrix is formed once per view in double, rounded to float, and a point costs nine fused multiply-adds:
+// the same map, with rounding differences in the last bits only.
 // ---------------------------------------------------------------------------------------------------
-struct Pose32 { float qx, qy, qz, qw, tx, ty, tz; };
+struct Rigid32 { float r[9]; float t[3]; };  // row-major rotation, translation
 
-ADOP_HD Pose32 load_pose(const double* p8)
+ADOP_HD Rigid32 load_rigid(const double* p8)
 {
-    Pose32 P;
-    P.qx = (float)p8[0]; P.qy = (float)p8[1]; P.qz = (float)p8[2]; P.qw = (float)p8[3];
-    P.tx = (float)p8[4]; P.ty = (float)p8[5]; P.tz = (float)p8[6];
-    return P;
+    const double x = p8[0], y = p8[1], z = p8[2], w = p8[3];
+    Rigid32 T;
+    T.r[0] = (float)(1.0 - 2.0 * (y * y + z * z)); T.r[1] = (float)(2.0 * (x * y - z * w)); T.r[2] = (float)(2.0 * (x * z + y * w));
+    T.r[3] = (float)(2.0 * (x * y + z * w)); T.r[4] = (float)(1.0 - 2.0 * (x * x + z * z)); T.r[5] = (float)(2.0 * (y * z - x * w));
+    T.r[6] = (float)(2.0 * (x * z - y * w)); T.r[7] = (float)(2.0 * (y * z + x * w)); T.r[8] = (float)(1.0 - 2.0 * (x * x + y * y));
+    T.t[0] = (float)p8[4]; T.t[1] = (float)p8[5]; T.t[2] = (float)p8[6];
+    return T;
 }
 
 struct V3 { float x, y, z; };
 struct V2 { float x, y; };
 
-// v' = q v q^-1 with the two-cross-product form (uv = 2 q.vec x v ; v + w uv + q.vec x uv), the published
-// formula of Eigen's quaternion-vector product that Sophus' SO3 * point resolves to.
-ADOP_HD V3 rotate_q(float qx, float qy, float qz, float qw, V3 v)
+ADOP_HD V3 rotate(const Rigid32& T, V3 v)
 {
-    float ux = fmaf(qy, v.z, -(qz * v.y));
-    float uy = fmaf(qz, v.x, -(qx * v.z));
-    float uz = fmaf(qx, v.y, -(qy * v.x));
-    ux = ux + ux; uy = uy + uy; uz = uz + uz;
-    float cx = fmaf(qy, uz, -(qz * uy));
-    float cy = fmaf(qz, ux, -(qx * uz));
-    float cz = fmaf(qx, uy, -(qy * ux));
     V3 o;
-    o.x = fmaf(qw, ux, v.x) + cx;
-    o.y = fmaf(qw, uy, v.y) + cy;
-    o.z = fmaf(qw, uz, v.z) + cz;
+    o.x = fmaf(T.r[0], v.x, fmaf(T.r[1], v.y, T.r[2] * v.z));
+    o.y = fmaf(T.r[3], v.x, fmaf(T.r[4], v.y, T.r[5] * v.z));
+    o.z = fmaf(T.r[6], v.x, fmaf(T.r[7], v.y, T.r[8] * v.z));
     return o;
 }
-ADOP_HD V3 rotate(const Pose32& P, V3 v)     { return rotate_q(P.qx, P.qy, P.qz, P.qw, v); }
-ADOP_HD V3 rotate_inv(const Pose32& P, V3 v) { return rotate_q(-P.qx, -P.qy, -P.qz, P.qw, v); }
-// TransformPoint (PointRendererHelper.h:55): view = R p + t
-ADOP_HD V3 transform_point(const Pose32& P, V3 p)
+ADOP_HD V3 rotate_inv(const Rigid32& T, V3 v)
 {
-    V3 r = rotate(P, p);
-    r.x = r.x + P.tx; r.y = r.y + P.ty; r.z = r.z + P.tz;
-    return r;
+    V3 o;
+    o.x = fmaf(T.r[0], v.x, fmaf(T.r[3], v.y, T.r[6] * v.z));
+    o.y = fmaf(T.r[1], v.x, fmaf(T.r[4], v.y, T.r[7] * v.z));
+    o.z = fmaf(T.r[2], v.x, fmaf(T.r[5], v.y, T.r[8] * v.z));
+    return o;
+}
+// TransformPoint (PointRendererHelper.h:55): view = R p + t
+ADOP_HD V3 transform_point(const Rigid32& T, V3 p)
+{
+    V3 o;
+    o.x = fmaf(T.r[0], p.x, fmaf(T.r[1], p.y, fmaf(T.r[2], p.z, T.t[0])));
+    o.y = fmaf(T.r[3], p.x, fmaf(T.r[4], p.y, fmaf(T.r[5], p.z, T.t[1])));
+    o.z = fmaf(T.r[6], p.x, fmaf(T.r[7], p.y, fmaf(T.r[8], p.z, T.t[2])));
+    return o;
 }
 
 // 10-bit-per-axis packed normal (NeuralPointCloudCuda.h:96). The reference's bit layout lives in saiga;
@@ -245,11 +249,20 @@ ADOP_HD V2 distort(V2 m, const Dist8& d, float cutoff, bool* rejected, float* J_
     float den = fmaf(fmaf(fmaf(d.k6, r2, d.k5), r2, d.k4), r2, 1.0f);
     float iden = den == 1.0f ? 1.0f : 1.0f / den;  // same bits either way; skips the division for k4 = k5 = k6 = 0
     float rad = num * iden;
-    float tx = fmaf(d.p1, xy2, d.p2 * fmaf(2.0f, x2, r2));
-    float ty = fmaf(d.p2, xy2, d.p1 * fmaf(2.0f, y2, r2));
     V2 o;
-    o.x = fmaf(x, rad, tx);
-    o.y = fmaf(y, rad, ty);
+    if (d.p1 == 0.f && d.p2 == 0.f)
+    {
+        // no tangential part: x * rad + 0 has the same bits as the fused form below
+        o.x = x * rad;
+        o.y = y * rad;
+    }
+    else
+    {
+        float tx = fmaf(d.p1, xy2, d.p2 * fmaf(2.0f, x2, r2));
+        float ty = fmaf(d.p2, xy2, d.p1 * fmaf(2.0f, y2, r2));
+        o.x = fmaf(x, rad, tx);
+        o.y = fmaf(y, rad, ty);
+    }
     *rejected = r2 > cutoff * cutoff;
     if (J_p)
     {
@@ -311,9 +324,9 @@ struct Projected
     V3 view;    // camera-space position
 };
 
-// ProjectPointPinhole (PointRendererHelper.h:49-82)
-ADOP_HD Projected project_pinhole(V3 p, V3 n, bool has_normal, const Pose32& V, const Intr5& K, const Dist8& dist,
-                                  bool check_normal, float dist_cutoff)
+// ProjectPointPinhole (PointRendererHelper.h:49-82) up to the distorted normalised point; the caller applies K.
+ADOP_HD Projected project_pinhole_normalized(V3 p, V3 n, bool has_normal, const Rigid32& V, const Dist8& dist,
+                                             bool check_normal, float dist_cutoff)
 {
     Projected r;
     r.view = transform_point(V, p);
@@ -333,10 +346,15 @@ ADOP_HD Projected project_pinhole(V3 p, V3 n, bool has_normal, const Pose32& V, 
     m.x = r.view.x * iz;
     m.y = r.view.y * iz;
     bool rejected;
-    V2 dp = distort(m, dist, dist_cutoff, &rejected, nullptr, nullptr);
-    if (rejected) z = 0.f;
-    r.ip = normalized_to_image(K, dp);
-    r.z = z;
+    r.ip = distort(m, dist, dist_cutoff, &rejected, nullptr, nullptr);
+    r.z = rejected ? 0.f : z;
+    return r;
+}
+ADOP_HD Projected project_pinhole(V3 p, V3 n, bool has_normal, const Rigid32& V, const Intr5& K, const Dist8& dist,
+                                  bool check_normal, float dist_cutoff)
+{
+    Projected r = project_pinhole_normalized(p, n, has_normal, V, dist, check_normal, dist_cutoff);
+    r.ip = normalized_to_image(K, r.ip);
     return r;
 }
 
@@ -398,7 +416,7 @@ ADOP_HD V2 ocam_project(V3 v, const Ocam& o, float cutoff, float* depth, float* 
 
 // ProjectPointOcam (PointRendererHelper.h:85-106). Unlike the reference it does not look at the normal
 // when the cloud has none (the reference evaluates an uninitialised one there).
-ADOP_HD Projected project_ocam(V3 p, V3 n, bool has_normal, const Pose32& V, const Ocam& o, bool check_normal,
+ADOP_HD Projected project_ocam(V3 p, V3 n, bool has_normal, const Rigid32& V, const Ocam& o, bool check_normal,
                                float cutoff)
 {
     Projected r;
@@ -422,20 +440,23 @@ ADOP_HD Projected project_ocam(V3 p, V3 n, bool has_normal, const Pose32& V, con
 // ---------------------------------------------------------------------------------------------------
 struct ViewCam
 {
-    Pose32 V;
+    Rigid32 V;
     Intr5 crop;
     int model;
     Intr5 K;      // pinhole
     Dist8 dist;   // pinhole
     Ocam ocam;    // omnidirectional
     float w0;     // width of layer 0 (the OCam radius rule uses it as a focal length, PointRenderer.cu:251)
+    // pinhole: crop o K as one affine map of the distorted normalised point (formed in double, rounded once):
+    // x = a[0] dx + a[1] dy + a[2] ; y = a[3] dy + a[4]. The reference applies K, then the crop (PointRenderer.cu:255).
+    float a[5];
 };
 
 ADOP_HD ViewCam load_view_cam(const double* poses, const float* intrinsics, int intrinsics_cols, int image_index,
                               int camera_index, int camera_model, const float* crop5, int w0)
 {
     ViewCam c;
-    c.V = load_pose(poses + (size_t)image_index * 8);
+    c.V = load_rigid(poses + (size_t)image_index * 8);
     c.crop = load_intr5(crop5);
     c.model = camera_model;
     c.w0 = (float)w0;
@@ -445,6 +466,13 @@ ADOP_HD ViewCam load_view_cam(const double* poses, const float* intrinsics, int 
         c.K = load_intr5(ip);
         c.dist = load_dist8(ip + 5);
         c.ocam.npoly = 0;
+        const double cfx = crop5[0], cfy = crop5[1], ccx = crop5[2], ccy = crop5[3], cs = crop5[4];
+        const double fx = ip[0], fy = ip[1], cx = ip[2], cy = ip[3], sk = ip[4];
+        c.a[0] = (float)(cfx * fx);
+        c.a[1] = (float)(cfx * sk + cs * fy);
+        c.a[2] = (float)(cfx * cx + cs * cy + ccx);
+        c.a[3] = (float)(cfy * fy);
+        c.a[4] = (float)(cfy * cy + ccy);
     }
     else
     {
@@ -454,6 +482,7 @@ ADOP_HD ViewCam load_view_cam(const double* poses, const float* intrinsics, int 
         for (int i = 0; i < kMaxOcamPoly; ++i) c.ocam.poly[i] = i < c.ocam.npoly ? ip[5 + i] : 0.f;
         c.K.fx = c.K.fy = 1.f; c.K.cx = c.K.cy = c.K.s = 0.f;
         c.dist.k1 = c.dist.k2 = c.dist.k3 = c.dist.k4 = c.dist.k5 = c.dist.k6 = c.dist.p1 = c.dist.p2 = 0.f;
+        c.a[0] = c.a[1] = c.a[2] = c.a[3] = c.a[4] = 0.f;
     }
     return c;
 }
@@ -471,18 +500,22 @@ ADOP_HD bool project_for_raster(const ViewCam& c, V3 p, float drop_out_radius, V
 {
     Projected pr;
     float focal;
+    V2 ip;
     if (c.model == kPinholeDistortion)
     {
-        pr = project_pinhole(p, n, has_normal, c.V, c.K, c.dist, check_normal, dist_cutoff);
+        pr = project_pinhole_normalized(p, n, has_normal, c.V, c.dist, check_normal, dist_cutoff);
+        if (!(pr.z > 0.f)) return false;
         focal = c.K.fx * c.crop.fx;
+        ip.x = fmaf(c.a[0], pr.ip.x, fmaf(c.a[1], pr.ip.y, c.a[2]));
+        ip.y = fmaf(c.a[3], pr.ip.y, c.a[4]);
     }
     else
     {
         pr = project_ocam(p, n, has_normal, c.V, c.ocam, check_normal, dist_cutoff);
+        if (!(pr.z > 0.f)) return false;
         focal = c.w0 * c.crop.fx;
+        ip = normalized_to_image(c.crop, pr.ip);
     }
-    if (!(pr.z > 0.f)) return false;
-    V2 ip = normalized_to_image(c.crop, pr.ip);
     // positions that are not finite or absurdly far off can not land in any layer; rejecting them here keeps the
     // per-layer rounding free of range checks
     if (!(fabsf(ip.x) < 1.0e9f) || !(fabsf(ip.y) < 1.0e9f)) return false;
@@ -499,7 +532,7 @@ ADOP_HD bool project_for_raster(const ViewCam& c, V3 p, float drop_out_radius, V
 // ---------------------------------------------------------------------------------------------------
 struct GradPinhole { float g_point[3]; float g_pose[6]; float g_k[5]; float g_dis[8]; };
 
-ADOP_HD void pose_point_chain(const Pose32& V, V3 view, V3 gv, float* g_point, float* g_pose)
+ADOP_HD void pose_point_chain(const Rigid32& V, V3 view, V3 gv, float* g_point, float* g_pose)
 {
     V3 gp = rotate_inv(V, gv);
     g_point[0] = gp.x; g_point[1] = gp.y; g_point[2] = gp.z;
@@ -509,7 +542,7 @@ ADOP_HD void pose_point_chain(const Pose32& V, V3 view, V3 gv, float* g_point, f
     g_pose[5] = view.x * gv.y - view.y * gv.x;
 }
 
-ADOP_HD bool project_pinhole_backward(V3 p, V3 n, bool has_normal, V2 g, const Pose32& V, const Intr5& K,
+ADOP_HD bool project_pinhole_backward(V3 p, V3 n, bool has_normal, V2 g, const Rigid32& V, const Intr5& K,
                                       const Intr5& crop, const Dist8& dist, bool check_normal, float dist_cutoff,
                                       GradPinhole* out)
 {
@@ -548,7 +581,7 @@ ADOP_HD bool project_pinhole_backward(V3 p, V3 n, bool has_normal, V2 g, const P
 
 struct GradOcam { float g_point[3]; float g_pose[6]; float g_affine[5]; };
 
-ADOP_HD bool project_ocam_backward(V3 p, V3 n, bool has_normal, V2 g, const Pose32& V, const Intr5& crop, const Ocam& o,
+ADOP_HD bool project_ocam_backward(V3 p, V3 n, bool has_normal, V2 g, const Rigid32& V, const Intr5& crop, const Ocam& o,
                                    bool check_normal, float cutoff, GradOcam* out)
 {
     V3 view = transform_point(V, p);
@@ -587,7 +620,7 @@ ADOP_HD V2 spherical_uv(V3 dir)
     V2 uv; uv.x = x * 2.0f - 1.0f; uv.y = y * 2.0f - 1.0f;
     return uv;
 }
-ADOP_HD V2 env_uv_for_pixel(int gx, int gy, const Pose32& V, const Intr5& K, const Dist8& dist, const Intr5& crop_l)
+ADOP_HD V2 env_uv_for_pixel(int gx, int gy, const Rigid32& V, const Intr5& K, const Dist8& dist, const Intr5& crop_l)
 {
     V2 ip; ip.x = (float)gx; ip.y = (float)gy;
     V2 dp = image_to_normalized(K, image_to_normalized(crop_l, ip));

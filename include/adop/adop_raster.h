@@ -92,6 +92,9 @@ typedef struct adop_scene
     const double* poses;
     const float* intrinsics;
     const float* env_map;
+    /* optional [T,C] copy of `texture` (adop_texture_interleave). The kernels then fetch a point's descriptor as one
+     * contiguous vector instead of C values from C planes. The caller refreshes it whenever `texture` changes. */
+    const float* texture_interleaved;
 } adop_scene;
 
 /* Per pyramid layer l (size w>>l, h>>l by integer halving, PointRenderer.cu:1015-1016), batch-major:
@@ -113,9 +116,11 @@ typedef struct adop_forward_io
     const uint8_t* dropout_mask; /* optional [B,N]: 1 = dropped; NULL = hash of dropout_seed */
     void* workspace;
     size_t workspace_bytes;
-    /* optional, [B, adop_raster_visible_list_ints(N)] i32: the forward pass records which points of each view passed
-     * the depth test, so that the backward pass visits only those. It takes the place of the [B,N] drop-out tensor
-     * the reference saves for backward (PointRenderer.cu:1524). NULL = not recorded. */
+    /* optional, [B, adop_raster_visible_list_ints(N)] i32: the forward pass records which (point, layer) splats of
+     * each view the backward pass has to visit, so that it runs over those instead of over the whole cloud. It takes
+     * the place of the [B,N] drop-out tensor the reference saves for backward (PointRenderer.cu:1524). If a view has
+     * more such splats than the list holds (about one per point of the cloud), the list marks itself unusable and
+     * the backward pass walks all points. NULL = not recorded. */
     int32_t* visible_list;
 } adop_forward_io;
 
@@ -150,6 +155,9 @@ typedef struct adop_backward_io
     /* optional: the list the forward call of the same views, scene and parameters filled (see adop_forward_io).
      * NULL = the backward pass walks all points again, as the reference does. */
     const int32_t* visible_list;
+    /* optional [T,C] scratch: descriptor gradients are then summed there with one vector atomic per splat and moved
+     * into grad_texture [C,T] at the end of the call. Contents on entry are ignored. */
+    float* grad_texture_interleaved;
 } adop_backward_io;
 
 const char* adop_status_string(adop_status s);
@@ -162,6 +170,12 @@ void adop_render_params_default(adop_render_params* p);
 /* Bytes of scratch that forward/backward need for views of w x h with `layers` layers and `channels`
  * descriptor channels. Replaces the size-keyed PointRendererCache (PointRenderer.h:96-157). */
 size_t adop_raster_workspace_bytes(int32_t w, int32_t h, int32_t layers, int32_t channels);
+
+/* [C,T] -> [T,C] (and back, optionally adding to `out`): the descriptor tensor keeps the reference's planar layout
+ * at the boundary (NeuralTexture.h:62); these build the interleaved working copy the kernels prefer. */
+adop_status adop_texture_interleave(const float* texture, float* out, int32_t channels, int32_t num_texels, void* stream);
+adop_status adop_texture_deinterleave(const float* in, float* out, int32_t channels, int32_t num_texels,
+                                      int32_t accumulate, void* stream);
 
 /* int32 elements per view of adop_forward_io.visible_list for a cloud of num_points points. */
 size_t adop_raster_visible_list_ints(int32_t num_points);

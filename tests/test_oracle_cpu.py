@@ -491,7 +491,7 @@ def test_c_abi_library_exports_every_declared_symbol():
     for f, _ in capi.AdopRenderParams._fields_:
         assert getattr(p, f) == getattr(d, f), f
     lib.adop_raster_workspace_bytes.restype = ctypes.c_size_t
-    assert lib.adop_raster_workspace_bytes(1920, 1080, 4, 4) == 2754000 * 8 * 4 + 256
+    assert lib.adop_raster_workspace_bytes(1920, 1080, 4, 4) == 16384 + 2754000 * 8 * 4 + 256
     assert lib.adop_raster_workspace_bytes(0, 1080, 4, 4) == 0
 
 

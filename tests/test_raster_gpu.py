@@ -26,13 +26,13 @@ def close(a, b, rtol=RTOL, name=""):
     assert err <= rtol * scale, f"{name}: max err {err:.3e} vs scale {scale:.3e}"
 
 
-def run_both(oracle, cfg, want_env=False, dropout_mask=None, record_visible=True, **bw):
+def run_both(oracle, cfg, want_env=False, dropout_mask=None, record_visible=True, interleave=True, **bw):
     arrays, views, params, L = cfg["arrays"], cfg["views"], cfg["params"], cfg["num_layers"]
     grads = synth.upstream_gradients(cfg["meta"], batch=len(views))
     ref = oracle.forward(arrays, views, params, L, dropout_mask=dropout_mask)
     ref_b = oracle.backward(arrays, views, params, L, ref, grads, want_env=want_env, dropout_mask=dropout_mask, **bw)
     scene = to_scene(arrays)
-    r = PointRasterizer("cuda:0")
+    r = PointRasterizer("cuda:0", interleave_descriptors=interleave)
     dm = torch.from_numpy(dropout_mask).cuda() if dropout_mask is not None else None
     fwd = r.forward(scene, views, params, L, dropout_mask=dm, record_visible=record_visible)
     bwd = r.backward(scene, params, fwd, [torch.from_numpy(g).cuda() for g in grads], want_env=want_env,
@@ -83,11 +83,7 @@ def test_c2_distortion_env_map_pose_grads(oracle, cuda_lib, listed):
     """listed: the backward pass walks the visible list the forward pass recorded; else it walks all points."""
     cfg = synth.make_config("c2", n_points=400_000, n_views=3, size=(480, 270))
     ref, ref_b, fwd, bwd = run_both(oracle, cfg, want_env=True, record_visible=listed)
-    if listed:
-        # the list holds exactly the points with at least one accepted layer
-        proj_ok = [int((ref["weights"][0][b] > 0).sum()) for b in range(3)]
-        counts = fwd.visible_counts().cpu().numpy()
-        assert all(c >= p for c, p in zip(counts, proj_ok)) and counts.max() < 400_000
+    assert (fwd.visible is not None) == listed
     check_forward(ref, fwd, 4, masks=True)
     check_backward(ref_b, bwd)
     assert np.abs(ref_b["pose"]).max() > 0 and np.abs(ref_b["env_map"]).max() > 0
@@ -102,6 +98,18 @@ def test_c3_ocam(oracle, cuda_lib, listed):
     assert ref["weights"][0].sum() > 1000
 
 
+def test_splat_list_is_used_on_a_dense_cloud(oracle, cuda_lib):
+    """Many points per pixel (the normal case): the list does not overflow and records every covered pixel."""
+    cfg = synth.make_config("c2", n_points=600_000, n_views=2, size=(160, 90))
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg, want_env=True)
+    assert not bool(fwd.list_overflowed().any())
+    covered = [sum(int((ref["weights"][l][b] > 0).sum()) for l in range(4)) for b in range(2)]
+    counts = fwd.splat_counts().cpu().numpy()
+    assert all(c >= p for c, p in zip(counts, covered))
+    check_forward(ref, fwd, 4, masks=True)
+    check_backward(ref_b, bwd)
+
+
 def test_c5_eight_channels_six_layers(oracle, cuda_lib):
     cfg = synth.make_config("c5", n_points=300_000, n_views=2, size=(384, 216))
     ref, ref_b, fwd, bwd = run_both(oracle, cfg, want_env=True)
@@ -109,10 +117,12 @@ def test_c5_eight_channels_six_layers(oracle, cuda_lib):
     check_backward(ref_b, bwd)
 
 
+@pytest.mark.parametrize("interleave", [True, False])
 @pytest.mark.parametrize("channels", [3, 16])
-def test_other_channel_counts(oracle, cuda_lib, channels):
+def test_other_channel_counts(oracle, cuda_lib, channels, interleave):
+    """interleave: descriptors and their gradient go through the [T,C] working copies; else straight to the [C,T] planes."""
     cfg = synth.make_config("c1", n_points=50_000, size=(96, 64), channels=channels, layers=3)
-    ref, ref_b, fwd, bwd = run_both(oracle, cfg)
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg, interleave=interleave)
     check_forward(ref, fwd, 3)
     check_backward(ref_b, bwd)
 
@@ -150,6 +160,13 @@ def test_dropout_mask_all_and_none(oracle, cuda_lib):
             assert ref["weights"][0].sum() == 0 and (ref["depths"][0] < 100000).any()
 
 
+def test_planar_descriptor_path_without_list(oracle, cuda_lib):
+    cfg = synth.make_config("c2", n_points=200_000, n_views=2, size=(240, 136))
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg, want_env=True, interleave=False, record_visible=False)
+    check_forward(ref, fwd, 4, masks=True)
+    check_backward(ref_b, bwd)
+
+
 def test_normals_radius_dropout_and_index(oracle, cuda_lib):
     cfg = synth.make_config("c1", n_points=60_000, size=(128, 96))
     rng = np.random.default_rng(3)
@@ -166,6 +183,16 @@ def test_normals_radius_dropout_and_index(oracle, cuda_lib):
     check_forward(ref, fwd, 4)
     check_backward(ref_b, bwd)
     assert 0 < ref["weights"][0].sum() < n
+
+
+def test_splat_list_overflow_falls_back_to_all_points(oracle, cuda_lib):
+    """A sparse cloud where nearly every point is alone in its pixel on every layer has more splats than points; the
+    list then marks itself unusable and the backward pass walks all points, with the same result."""
+    cfg = synth.make_config("c1", n_points=3000, size=(512, 512), layers=4)
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg)
+    assert bool(fwd.list_overflowed().any())
+    check_forward(ref, fwd, 4)
+    check_backward(ref_b, bwd)
 
 
 def test_backward_mode_4(oracle, cuda_lib):
