@@ -154,17 +154,23 @@ inline void fill_cam_chunk(CamChunkSource* c, const adop_scene* s, const adop_vi
 //   [0, kVisibleSegments)            number of entries of each segment (one segment per block of the blend launch)
 //   [kVisibleSegments + 0 / + 1]     segments in use / entries per segment (`seg_cap`), written by the blend kernel
 //   [kVisibleSegments + 2]           overflow flag: a segment ran out of room, the list is incomplete and not used
-//   [kVisibleHeaderInts, ...)        segments of `seg_cap` entries each: point id | layer << 28, unordered
+//   [kVisibleHeaderInts, ...)        segments of `seg_cap` entries each, unordered; an entry is four ints:
+//                                    point id | layer << 28, the pixel index inside that layer, and two floats that the
+//                                    backward pass fills with the splat's image-space gradient (its first kernel gathers
+//                                    pixel data with few registers, its second chains the gradient through the projection)
+// A segment holds as many entries as its block has points. A view typically has 0.2-0.3 splats per point, but they come
+// in clumps (whole chunks of neighbouring points on a front surface are accepted on every layer), so single blocks see
+// several times the average.
 constexpr unsigned kSplatPointMask = 0x0FFFFFFFu;
 constexpr int kSplatLayerShift = 28;
 constexpr int kSplatMaxPoints = 1 << 28;  // larger clouds are rendered without a list
 constexpr int kVisibleSegments = 2048;
 constexpr int kVisibleHeaderInts = kVisibleSegments + 8;
-inline size_t visible_list_ints(int num_points) { return (size_t)kVisibleHeaderInts + (size_t)num_points + (size_t)kVisibleSegments * kBlock; }
+inline size_t visible_list_ints(int num_points) { return (size_t)kVisibleHeaderInts + 4 * ((size_t)num_points + (size_t)kVisibleSegments * kBlock); }
 struct VisibleList
 {
     int* header;   // null = no list
-    int* entries;
+    int4* entries;
     int segments;  // blocks of the blend launch
     int seg_cap;   // entries per segment
 };
@@ -174,7 +180,7 @@ inline VisibleList make_visible_list(int32_t* base, int num_points, int view, in
     if (!base) { v.header = nullptr; v.entries = nullptr; v.segments = 0; v.seg_cap = 0; return v; }
     int* p = base + (size_t)view * visible_list_ints(num_points);
     v.header = p;
-    v.entries = p + kVisibleHeaderInts;
+    v.entries = reinterpret_cast<int4*>(p + kVisibleHeaderInts);  // 16-byte aligned: header and per-view size are multiples of 4 ints
     v.segments = segments;
     long long iters = ((long long)(num_points + kBlock - 1) / kBlock + segments - 1) / segments;
     v.seg_cap = (int)(iters * kBlock);

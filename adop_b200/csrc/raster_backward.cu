@@ -396,15 +396,90 @@ __device__ __forceinline__ int scan_segments(const int* __restrict__ header, int
     return s_prefix[kVisibleSegments - 1];
 }
 
-// K5 (splat list): one thread per (point, layer) pair that the backward pass has to visit, as recorded by the blend
-// kernel. Dense warps, no layer loop, no depth test (the forward pass already applied it, including the stop at a point's
-// first failure), and everything a splat needs is requested at once: weight, the pixel's record, the four neighbours.
-template <int C, int MODEL>
-__global__ void __launch_bounds__(kBlock) k_splat_backward_list(PointStreams pts, const ViewCam* __restrict__ camp, KernelParams kp, LayerTable lt,
-                                                                 BackwardTargets bt, VisibleList vl)
+// K5 (splat list): the backward pass over the (point, layer) splats that the blend kernel recorded, in dense warps, with
+// no layer loop and no depth test (the forward pass already applied it, including the stop at a point's first failure).
+// Two kernels, because one needs memory-level parallelism and the other registers:
+//   k_splat_gather: per splat, the pixel's weight and record, the four neighbour records and the point's descriptor are
+//                   requested at once (the pixel index comes with the list entry, nothing waits for a projection); it
+//                   adds the descriptor gradient and stores the splat's image-space gradient in the entry. ~40 registers.
+//   k_splat_chain:  per splat, re-projects the point with Jacobians and chains the stored gradient to the point, pose
+//                   and intrinsics gradients. ~100 registers, almost no memory traffic.
+__device__ __forceinline__ int4 list_entry(const VisibleList& vl, const int* s_prefix, int n_segments, int seg_cap, int t, size_t* where)
+{
+    int lo = 0, hi = n_segments - 1;
+    while (lo < hi)
+    {
+        int mid = (lo + hi) >> 1;
+        if (s_prefix[mid] > t) hi = mid; else lo = mid + 1;
+    }
+    const int before = lo ? s_prefix[lo - 1] : 0;
+    *where = (size_t)lo * seg_cap + (t - before);
+    return __ldg(vl.entries + *where);
+}
+constexpr int kNoStencil = 0x7fc00000;  // quiet NaN in the gradient slot: the splat has no ghost gradient
+
+template <int C>
+__global__ void __launch_bounds__(kBlock, 4) k_splat_gather(PointStreams pts, KernelParams kp, LayerTable lt, BackwardTargets bt,
+                                                            VisibleList vl, int want_geo)
 {
     constexpr int RB = (2 * C + 3) & ~3;
     if (__ldg(vl.header + kVisibleSegments + 2) != 0) return;  // the list overflowed: k_splat_backward_all takes over
+    __shared__ int s_prefix[kVisibleSegments];
+    __shared__ int s_warp[kBlock / 32];
+    const int work = scan_segments(vl.header, s_prefix, s_warp);
+    const int n_segments = __ldg(vl.header + kVisibleSegments);
+    const int seg_cap = __ldg(vl.header + kVisibleSegments + 1);
+    const int stride = gridDim.x * blockDim.x;
+    for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < work; t += stride)
+    {
+        size_t where;
+        const int4 e = list_entry(vl, s_prefix, n_segments, seg_cap, t, &where);
+        const int i = (int)((unsigned)e.x & kSplatPointMask);
+        const int l = (int)((unsigned)e.x >> kSplatLayerShift);
+        const bool drop_out = point_dropped(kp, i);
+        const bool point_grad = want_geo && ((kp.ghost_gradients && drop_out) || (!kp.ghost_gradients && !drop_out));
+        const int w = lt.w[l], h = lt.h[l];
+        const size_t pix = (size_t)e.y;
+        const int py = e.y / w, px = e.y - py * w;
+        const size_t rbase = (size_t)lt.rec_off[l] + pix;
+        const int edge = min(min(px, py), min(w - 1 - px, h - 1 - py));
+        const bool stencil = point_grad && edge > 2;
+        const int ti = pts.index ? __ldg(pts.index + i) : i;
+        const float wgt = __ldg(lt.weight[l] + pix);
+        const bool want_dg = !drop_out && bt.grad_texture && wgt != 0.f;
+        float2 g = make_float2(0.f, __int_as_float(kNoStencil));
+        if (drop_out || wgt != 0.f)  // :473
+        {
+            if (want_dg)
+            {
+                float rc[RB], dg[C];
+                load_record<C>(bt.records, rbase, rc);
+                const float iw = 1.f / wgt;
+#pragma unroll
+                for (int c = 0; c < C; ++c) dg[c] = iw * rc[C + c];
+                add_descriptor_gradient<C>(bt.grad_texture, bt.grad_texture_interleaved, bt.num_texels, ti, dg);
+            }
+            if (stencil)
+            {
+                const size_t nb[4] = {pix - 1, pix + 1, pix - (size_t)w, pix + (size_t)w};
+                float rn[4][RB], T_p[C];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) load_record<C>(bt.records, (size_t)lt.rec_off[l] + nb[k], rn[k]);
+                load_descriptor<C>(bt.texture, bt.texture_interleaved, bt.num_texels, ti, T_p);
+                V2 gg = stencil_gradient<C>(kp, T_p, rn, 0.f, lt.weight[l], lt.depth[l], nb);
+                g = make_float2(gg.x, gg.y);
+            }
+        }
+        // only the gradient half of the entry is written (the chain kernel reads the whole entry)
+        reinterpret_cast<float2*>(vl.entries + where)[1] = g;
+    }
+}
+
+template <int MODEL>
+__global__ void __launch_bounds__(kBlock) k_splat_chain(PointStreams pts, const ViewCam* __restrict__ camp, KernelParams kp,
+                                                         LayerTable lt, BackwardTargets bt, VisibleList vl)
+{
+    if (__ldg(vl.header + kVisibleSegments + 2) != 0) return;
     const ViewCam& cam = *camp;
     __shared__ GeoShared<MODEL> s_geo;
     __shared__ int s_prefix[kVisibleSegments];
@@ -413,72 +488,19 @@ __global__ void __launch_bounds__(kBlock) k_splat_backward_list(PointStreams pts
     const int work = scan_segments(vl.header, s_prefix, s_warp);
     const int n_segments = __ldg(vl.header + kVisibleSegments);
     const int seg_cap = __ldg(vl.header + kVisibleSegments + 1);
-    const bool want_geo = bt.grad_points || bt.grad_pose || bt.grad_intrinsics;
     GeoAccum<MODEL> acc;
     acc.clear();
     const int stride = gridDim.x * blockDim.x;
-    // t -> list entry: segment by binary search over the prefix sums
-    auto entry_of = [&](int t) -> unsigned
+    for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < work; t += stride)
     {
-        int lo = 0, hi = n_segments - 1;
-        while (lo < hi)
-        {
-            int mid = (lo + hi) >> 1;
-            if (s_prefix[mid] > t) hi = mid; else lo = mid + 1;
-        }
-        const int before = lo ? s_prefix[lo - 1] : 0;
-        return (unsigned)__ldg(vl.entries + (size_t)lo * seg_cap + (t - before));
-    };
-    int t = blockIdx.x * blockDim.x + threadIdx.x;
-    unsigned e_next = 0;
-    float4 p_next = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (t < work) { e_next = entry_of(t); p_next = __ldg(pts.position + (e_next & kSplatPointMask)); }
-    for (; t < work; t += stride)
-    {
-        // the next entry and its position are requested before this one is processed
-        const unsigned e = e_next;
-        const float4 p_cur = p_next;
-        if (stride < work - t) { e_next = entry_of(t + stride); p_next = __ldg(pts.position + (e_next & kSplatPointMask)); }
-        const int i = (int)(e & kSplatPointMask);
-        const int l = (int)(e >> kSplatLayerShift);
-        const bool drop_out = point_dropped(kp, i);
-        const bool point_grad = want_geo && ((kp.ghost_gradients && drop_out) || (!kp.ghost_gradients && !drop_out));
-        FetchedPoint f = fetch_point(pts, i, p_cur);
-        RasterPoint q;
-        if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, kp.check_normal != 0, kp.dist_cutoff, &q, false)) continue;
+        size_t where;
+        const int4 e = list_entry(vl, s_prefix, n_segments, seg_cap, t, &where);
+        if (e.w == kNoStencil) continue;
+        const int i = (int)((unsigned)e.x & kSplatPointMask);
+        const int l = (int)((unsigned)e.x >> kSplatLayerShift);
+        FetchedPoint f = fetch_point(pts, i);
+        V2 g; g.x = __int_as_float(e.z); g.y = __int_as_float(e.w);
         const float scale = __int_as_float((127 - l) << 23);  // 0.5^l, the same value l halvings give
-        const int px = round_half_even_bounded(q.x * scale), py = round_half_even_bounded(q.y * scale);
-        const int w = lt.w[l], h = lt.h[l];
-        if ((unsigned)px >= (unsigned)w || (unsigned)py >= (unsigned)h) continue;  // cannot happen for a recorded splat
-        const size_t pix = (size_t)py * w + px;
-        const float* __restrict__ W = lt.weight[l];
-        const float* __restrict__ D = lt.depth[l];
-        const size_t rbase = (size_t)lt.rec_off[l] + pix;
-        const int edge = min(min(px, py), min(w - 1 - px, h - 1 - py));
-        const bool stencil = point_grad && edge > 2;
-        const size_t nb[4] = {pix - 1, pix + 1, pix - (size_t)w, pix + (size_t)w};
-        const int ti = pts.index ? __ldg(pts.index + i) : i;
-        const float wgt = __ldg(W + pix);
-        float rc[RB], rn[4][RB], T_p[C];
-        const bool want_dg = !drop_out && bt.grad_texture;
-        if (want_dg) load_record<C>(bt.records, rbase, rc);
-        if (stencil)
-        {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) load_record<C>(bt.records, (size_t)lt.rec_off[l] + nb[k], rn[k]);
-            load_descriptor<C>(bt.texture, bt.texture_interleaved, bt.num_texels, ti, T_p);
-        }
-        if (!drop_out && wgt == 0.f) continue;  // :473
-        if (want_dg)
-        {
-            const float iw = 1.f / wgt;
-            float dg[C];
-#pragma unroll
-            for (int c = 0; c < C; ++c) dg[c] = iw * rc[C + c];
-            add_descriptor_gradient<C>(bt.grad_texture, bt.grad_texture_interleaved, bt.num_texels, ti, dg);
-        }
-        if (!stencil) continue;
-        V2 g = stencil_gradient<C>(kp, T_p, rn, q.z, W, D, nb);
         float gp[4] = {0.f, 0.f, 0.f, 0.f};
         if (chain_gradient<MODEL>(cam, kp, f, g, scale, gp, acc) && bt.grad_points)
             atomicAdd(bt.grad_points + i, make_float4(gp[0], gp[1], gp[2], gp[3]));
@@ -528,27 +550,38 @@ static adop_status launch_view_backward(const PointStreams& pts, const ViewCam* 
                                                   lt, cam, kp, bt.background, const_cast<float*>(bt.records), grad_background,
                                                   grad_env, env_h, env_w)));
     }
-    // With a splat list the dense kernel runs; the all-points kernel is launched behind it and returns at once unless
-    // the list's overflow flag is set (decided on the device, no host round trip).
-    const int* flag = vl.header ? vl.header + kVisibleSegments + 2 : nullptr;
+    // With a splat list the two dense kernels run; the all-points kernel is launched behind them and returns at once
+    // unless the list's overflow flag is set (decided on the device, no host round trip). The debug stencil rule
+    // (test_backward_mode 4) needs the point's depth next to its neighbours' and always takes the all-points kernel.
+    const bool use_list = vl.header && kp.test_backward_mode != 4;
+    const int* flag = use_list ? vl.header + kVisibleSegments + 2 : nullptr;
+    const int want_geo = (bt.grad_points || bt.grad_pose || bt.grad_intrinsics) ? 1 : 0;
+    if (use_list)
+    {
+        static const int gg = resident_grid(k_splat_gather<C>, 1ll << 40);
+        ADOP_LAUNCH("k_splat_gather", st, (k_splat_gather<C><<<gg, kBlock, 0, st>>>(pts, kp, lt, bt, vl, want_geo)));
+        if (want_geo)
+        {
+            if (model == kPinholeDistortion)
+            {
+                static const int g = resident_grid(k_splat_chain<kPinholeDistortion>, 1ll << 40);
+                ADOP_LAUNCH("k_splat_chain", st, (k_splat_chain<kPinholeDistortion><<<g, kBlock, 0, st>>>(pts, cam, kp, lt, bt, vl)));
+            }
+            else
+            {
+                static const int g = resident_grid(k_splat_chain<kOcam>, 1ll << 40);
+                ADOP_LAUNCH("k_splat_chain", st, (k_splat_chain<kOcam><<<g, kBlock, 0, st>>>(pts, cam, kp, lt, bt, vl)));
+            }
+        }
+    }
     if (model == kPinholeDistortion)
     {
-        if (vl.header)
-        {
-            static const int g = resident_grid(k_splat_backward_list<C, kPinholeDistortion>, 1ll << 40);
-            ADOP_LAUNCH("k_splat_backward_list", st, (k_splat_backward_list<C, kPinholeDistortion><<<g, kBlock, 0, st>>>(pts, cam, kp, lt, bt, vl)));
-        }
         static const int g = resident_grid(k_splat_backward_all<C, kPinholeDistortion>, 1ll << 40);
         ADOP_LAUNCH("k_splat_backward_all", st, (k_splat_backward_all<C, kPinholeDistortion><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(
                                                     pts, cam, kp, lt, bt, flag)));
     }
     else
     {
-        if (vl.header)
-        {
-            static const int g = resident_grid(k_splat_backward_list<C, kOcam>, 1ll << 40);
-            ADOP_LAUNCH("k_splat_backward_list", st, (k_splat_backward_list<C, kOcam><<<g, kBlock, 0, st>>>(pts, cam, kp, lt, bt, vl)));
-        }
         static const int g = resident_grid(k_splat_backward_all<C, kOcam>, 1ll << 40);
         ADOP_LAUNCH("k_splat_backward_all", st, (k_splat_backward_all<C, kOcam><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(
                                                     pts, cam, kp, lt, bt, flag)));

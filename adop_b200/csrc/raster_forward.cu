@@ -125,11 +125,11 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, const flo
     }
     constexpr int RS = ((C + 1) + 3) & ~3;
     const int stride = gridDim.x * blockDim.x;
-    int* seg = EMIT ? vl.entries + (size_t)blockIdx.x * vl.seg_cap : nullptr;
+    int4* seg = EMIT ? vl.entries + (size_t)blockIdx.x * vl.seg_cap : nullptr;
     const int lane = threadIdx.x & 31;
 
-    // One point: blend it, and return the mask of layers the backward pass will visit for it.
-    auto blend_point = [&](int i, float4 cur) -> unsigned
+    // One point: blend it, and return the mask of layers the backward pass will visit for it (their pixels in pix_out).
+    auto blend_point = [&](int i, float4 cur, int* pix_out) -> unsigned
     {
         const bool dropped = point_dropped(kp, i);
         if (dropped && !(EMIT && kp.ghost_gradients)) return 0u;
@@ -173,6 +173,7 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, const flo
 #pragma unroll
         for (int l = 0; l < L; ++l)
         {
+            pix_out[l] = (int)pix[l];
             if (pix[l] < 0) continue;
             if (!(pass & (1u << l))) break;
             bmask |= 1u << l;
@@ -185,7 +186,8 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, const flo
     {
         const int i = base + threadIdx.x;
         unsigned bmask = 0;
-        if (i < pts.n) bmask = blend_point(i, __ldg(pts.position + i));
+        int lpix[L];
+        if (i < pts.n) bmask = blend_point(i, __ldg(pts.position + i), lpix);
         if (EMIT)
         {
             __syncwarp();
@@ -209,7 +211,7 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, const flo
                 {
 #pragma unroll
                     for (int l = 0; l < L; ++l)
-                        if (bmask & (1u << l)) seg[at++] = i | (l << kSplatLayerShift);
+                        if (bmask & (1u << l)) seg[at++] = make_int4(i | (l << kSplatLayerShift), lpix[l], 0, 0);
                 }
                 else if (lane == 0)
                     vl.header[kVisibleSegments + 2] = 1;  // out of room: the backward pass falls back to walking all points

@@ -153,8 +153,9 @@ typedef struct adop_backward_io
     void* workspace;
     size_t workspace_bytes;
     /* optional: the list the forward call of the same views, scene and parameters filled (see adop_forward_io).
+     * The backward pass uses part of every entry as scratch, so a list serves one backward call.
      * NULL = the backward pass walks all points again, as the reference does. */
-    const int32_t* visible_list;
+    int32_t* visible_list;
     /* optional [T,C] scratch: descriptor gradients are then summed there with one vector atomic per splat and moved
      * into grad_texture [C,T] at the end of the call. Contents on entry are ignored. */
     float* grad_texture_interleaved;
