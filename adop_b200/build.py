@@ -59,6 +59,34 @@ def build_library(force=False, verbose=False):
     return LIB
 
 
+TORCH_OP_SRC = os.path.join(CSRC, "torch_op.cpp")
+TORCH_OP_LIB = os.path.join(PKG_DIR, "libadop_torch.so")
+
+
+def build_torch_op(force=False, verbose=False):
+    """The libTorch autograd operator over the C ABI (adop_b200/libadop_torch.so); links against libadop_raster.so."""
+    build_library()
+    deps = [TORCH_OP_SRC, os.path.join(ROOT, "include", "adop", "adop_raster.h"), LIB]
+    if not force and _newer(TORCH_OP_LIB, deps):
+        return TORCH_OP_LIB
+    import torch
+    from torch.utils import cpp_extension
+    tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cmd = [os.environ.get("CXX_HOST", "/usr/bin/g++"), "-O2", "-std=c++17", "-fPIC", "-shared", "-Wno-deprecated-declarations",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
+    for inc in cpp_extension.include_paths() + ["/usr/local/cuda/include", os.path.join(ROOT, "include")]:
+        cmd += ["-I", inc]
+    cmd += [TORCH_OP_SRC, "-o", TORCH_OP_LIB, "-L", tlib, "-L", PKG_DIR, "-ladop_raster", "-ltorch", "-ltorch_cpu", "-lc10",
+            "-ltorch_cuda", "-lc10_cuda", "-L", "/usr/local/cuda/lib64", "-lcudart",
+            "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{tlib}"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+    if r.returncode != 0:
+        raise RuntimeError("building the libTorch operator failed")
+    return TORCH_OP_LIB
+
+
 def build_oracle(force=False):
     """The CPU checker (test infrastructure; never loaded by the library)."""
     odir = os.path.join(ROOT, "oracle")
@@ -73,4 +101,5 @@ def build_oracle(force=False):
 
 if __name__ == "__main__":
     print(build_library(force="--force" in sys.argv, verbose=True))
+    print(build_torch_op(force="--force" in sys.argv, verbose=True))
     print(build_oracle(force="--force" in sys.argv))

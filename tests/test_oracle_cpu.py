@@ -516,3 +516,16 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(capi, "LIB_PATH", "/nonexistent/libadop_raster.so")
     with pytest.raises(capi.AdopError, match="no CPU fallback"):
         capi.load_library()
+
+
+def test_libtorch_operator_builds_and_registers():
+    """The C++ autograd operator links against the C-ABI library and registers the reference's entry points."""
+    from adop_b200 import build
+    build.build_torch_op()
+    torch.ops.load_library(build.TORCH_OP_LIB)
+    assert hasattr(torch.ops.adop, "blend_point_cloud") and hasattr(torch.ops.adop, "apply_tangent_to_pose")
+    info = torch.classes.adop.RenderInfo()
+    info.set_num_layers(4)
+    info.set_param("depth_accept", 0.01)
+    with pytest.raises(RuntimeError, match="unknown render parameter"):
+        info.set_param("no_such_field", 1.0)

@@ -1,0 +1,96 @@
+"""GPU parity of the fused tonemapper and of the pose update against the CPU checker, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from adop_b200.raster import Tonemapper, apply_tangent_to_pose
+from adop_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(seed, B=3, H=37, W=53, K=25, n=6, with_uv=True):
+    rng = np.random.default_rng(seed)
+    x = rng.uniform(-0.3, 2.5, (B, 3, H, W)).astype(np.float32)
+    fi = rng.integers(0, n, B).astype(np.int32)
+    exposure = rng.uniform(-2, 2, n).astype(np.float32)
+    wb = rng.normal(1, 0.05, (n, 3)).astype(np.float32)
+    wb[:, 1] = 1.0
+    vig = np.array([0.1, -0.05, 0.01, 0.02, -0.03], np.float32)
+    uv = None
+    if with_uv:
+        ys, xs = np.meshgrid(np.arange(H), np.arange(W), indexing="ij")
+        uv = np.stack([2 * xs / (W - 1) - 1, 2 * ys / (H - 1) - 1])[None].repeat(B, 0).astype(np.float32)
+        uv += rng.normal(0, 0.02, uv.shape).astype(np.float32)
+    response = np.sort(rng.uniform(0, 1, (3, K)), axis=1).astype(np.float32)
+    go = rng.normal(size=x.shape).astype(np.float32)
+    return dict(x=x, frame_index=fi, exposure=exposure, white_balance=wb, vignette=vig, uv=uv, response=response), go
+
+
+def _close(a, b, rtol=1e-4, name=""):
+    a = a.detach().cpu().numpy()
+    scale = max(float(np.abs(b).max()), 1e-12)
+    err = float(np.abs(a.astype(np.float64) - b).max())
+    assert err <= rtol * scale, f"{name}: {err:.3e} vs scale {scale:.3e}"
+
+
+@pytest.mark.parametrize("leak", [0.0, 0.01])
+@pytest.mark.parametrize("with_uv", [True, False])
+def test_tonemapper_forward_backward(oracle, cuda_lib, leak, with_uv):
+    c, go = _case(0, with_uv=with_uv)
+    H, W = c["x"].shape[2:]
+    kw = dict(image_size=(W, H), frame_index=c["frame_index"], exposure=c["exposure"], white_balance=c["white_balance"],
+              vignette=c["vignette"], uv=c["uv"], response=c["response"], leak=leak)
+    ref = oracle.tonemap_forward(c["x"], **kw)
+    ref_g = oracle.tonemap_backward(c["x"], go, **kw)
+    d = {k: (torch.from_numpy(v).cuda() if v is not None else None) for k, v in c.items()}
+    tm = Tonemapper((W, H), exposure=d["exposure"], white_balance=d["white_balance"], vignette=d["vignette"],
+                    response=d["response"], leak=leak)
+    out = tm.forward(d["x"], d["frame_index"], d["uv"])
+    _close(out, ref, rtol=1e-5, name="tonemapped image")
+    g = tm.backward(d["x"], torch.from_numpy(go).cuda(), d["frame_index"], d["uv"])
+    for k in ("x", "exposure", "white_balance", "vignette", "response"):
+        _close(g[k], ref_g[k], name="grad " + k)
+
+
+def test_tonemapper_without_response_is_a_clamp(oracle, cuda_lib):
+    c, go = _case(1, K=2)
+    x = torch.from_numpy(c["x"]).cuda()
+    tm = Tonemapper((53, 37))
+    out = tm.forward(x)
+    assert torch.equal(out, x.clamp(0, 1))
+    g = tm.backward(x, torch.from_numpy(go).cuda())
+    want = torch.from_numpy(go).cuda() * ((x > 0) & (x < 1))
+    assert torch.allclose(g["x"], want)
+
+
+def test_tonemapper_256_bin_response_hd_image(oracle, cuda_lib):
+    """The HDR-4K configuration's tonemapper parameters (256-entry response) on a smaller image."""
+    c, go = _case(2, B=2, H=135, W=240, K=256, n=4)
+    kw = dict(image_size=(240, 135), frame_index=c["frame_index"], exposure=c["exposure"], white_balance=c["white_balance"],
+              vignette=c["vignette"], uv=None, response=c["response"], leak=0.0)
+    ref = oracle.tonemap_forward(c["x"], **kw)
+    ref_g = oracle.tonemap_backward(c["x"], go, **kw)
+    d = {k: (torch.from_numpy(v).cuda() if v is not None else None) for k, v in c.items()}
+    tm = Tonemapper((240, 135), exposure=d["exposure"], white_balance=d["white_balance"], vignette=d["vignette"],
+                    response=d["response"])
+    _close(tm.forward(d["x"], d["frame_index"]), ref, rtol=1e-5)
+    g = tm.backward(d["x"], torch.from_numpy(go).cuda(), d["frame_index"])
+    for k in ("x", "exposure", "white_balance", "vignette", "response"):
+        _close(g[k], ref_g[k], name="grad " + k)
+
+
+def test_apply_tangent_to_pose(oracle, cuda_lib):
+    rng = np.random.default_rng(3)
+    n = 300
+    poses = np.stack([synth.look_at_pose(rng.normal(size=3) * 3 + 0.1, rng.normal(size=3)) for _ in range(n)])
+    tangents = rng.normal(size=(n, 6)) * 0.1
+    tangents[0] = 0
+    t_ref, p_ref = tangents.copy(), poses.copy()
+    oracle.apply_tangent(t_ref, p_ref)
+    t, p = torch.from_numpy(tangents).cuda(), torch.from_numpy(poses).cuda()
+    apply_tangent_to_pose(t, p)
+    assert float(t.abs().max()) == 0.0
+    assert np.abs(p.cpu().numpy() - p_ref).max() < 1e-12
+    with pytest.raises(TypeError):
+        apply_tangent_to_pose(t.float(), p)
