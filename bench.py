@@ -115,7 +115,7 @@ def cpu_reference_arm(args, rank, world):
     from adop_b200 import synth
     from tests.oracle_lib import Oracle
     ora = Oracle()
-    cores = ora.lib.adop_oracle_max_threads()
+    cores = os.cpu_count() or ora.lib.adop_oracle_max_threads()  # torchrun sets OMP_NUM_THREADS=1; ask for all cores anyway
     cfg = synth.make_config("c2", n_points=args.points, n_views=1)
     arrays = cfg["arrays"]
     stride = 4  # bounded sample: every 4th point of the Morton-sorted cloud, one view, full image size
@@ -236,34 +236,46 @@ def main():
     # ---- end-to-end through the public API with host buffers ---------------------------------------------------------
     # per step: host->device copy of the step's upstream gradient pyramid from pinned memory (it overlaps the forward
     # pass on a copy stream), forward, backward, device->host read of the pose / intrinsics / background gradients.
+    # The copies are double-buffered: step k+1's gradients travel while step k computes, so every step still pays for its own
+    # 705 MB over PCIe inside the timed region, but behind the kernels where it fits.
     copy_stream = torch.cuda.Stream(device=dev)
-    staged = [torch.empty_like(g) for g in grads_dev]
+    staged = [[torch.empty_like(g) for g in grads_dev] for _ in range(2)]
+    copied = [torch.cuda.Event(), torch.cuda.Event()]
+    consumed = [torch.cuda.Event(), torch.cuda.Event()]
     small_host = {k: torch.empty_like(bwd[k], device="cpu").pin_memory() for k in ("pose", "intrinsics", "background")}
     h2d_bytes = sum(g.numel() * 4 for g in grads_host) + len(views) * 40
     d2h_bytes = sum(v.numel() * v.element_size() for v in small_host.values())
+    main_stream = torch.cuda.current_stream(dev)
 
-    def step_e2e():
-        main_stream = torch.cuda.current_stream(dev)
-        copy_stream.wait_stream(main_stream)
+    def start_copy(slot):
+        copy_stream.wait_event(consumed[slot])  # the backward pass that last read this buffer is done
         with torch.cuda.stream(copy_stream):
-            for s, hsrc in zip(staged, grads_host):
-                s.copy_(hsrc, non_blocking=True)
-        ras.forward(scene, views, params, L, out=fwd)
-        main_stream.wait_stream(copy_stream)
-        ras.backward(scene, params, fwd, staged, want_env=True, normalize=normalize_local, out=bwd)
-        if world > 1:
-            adist.exchange_gradients(bwd)
-        for k, hdst in small_host.items():
-            hdst.copy_(bwd[k], non_blocking=True)
+            for s_, hsrc in zip(staged[slot], grads_host):
+                s_.copy_(hsrc, non_blocking=True)
+            copied[slot].record(copy_stream)
+
+    def run_e2e(n_steps):
+        for ev in consumed:
+            ev.record(main_stream)
+        start_copy(0)
+        for k in range(n_steps):
+            slot = k & 1
+            if k + 1 < n_steps:
+                start_copy(slot ^ 1)
+            ras.forward(scene, views, params, L, out=fwd)
+            main_stream.wait_event(copied[slot])
+            ras.backward(scene, params, fwd, staged[slot], want_env=True, normalize=normalize_local, out=bwd)
+            consumed[slot].record(main_stream)
+            if world > 1:
+                adist.exchange_gradients(bwd)
+            for kk, hdst in small_host.items():
+                hdst.copy_(bwd[kk], non_blocking=True)
         main_stream.synchronize()
 
-    for _ in range(3):
-        step_e2e()
+    run_e2e(3)
     barrier()
-    t0 = time.perf_counter()
     e0.record()
-    for _ in range(args.steps):
-        step_e2e()
+    run_e2e(args.steps)
     e1.record()
     barrier()
     ms_e2e = torch.tensor([e0.elapsed_time(e1)], device=dev)
@@ -314,7 +326,7 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from tests.oracle_lib import Oracle
         ora = Oracle()
-        cores = ora.lib.adop_oracle_max_threads()
+        cores = os.cpu_count() or ora.lib.adop_oracle_max_threads()
         stride = 4
         sub = dict(arrays)
         sub["position"] = np.ascontiguousarray(arrays["position"][::stride])
