@@ -1,0 +1,102 @@
+"""Run one of the benchmark configurations end to end on one GPU and print its timings as one JSON line.
+
+    python -m adop_b200.run_config c1|c2|c3|c4|c5 [--points N] [--views V] [--reps R]
+
+bench.py measures the headline configuration (c2) under the driver's contract; this runner covers the others:
+c1 (small cloud, 512x512), c3 (100 M points, omnidirectional camera, forward only, ms per frame), c4 (30 M points, 8 views),
+c5 (50 M points, 4K, 6 layers, 8 channels, plus the fused tonemapper forward + backward on the 4K frames).
+Times are CUDA-event times of whole calls after warm-up; per-kernel times come from the library's own event brackets.
+"""
+import argparse
+import json
+import statistics
+import sys
+
+import torch
+
+from . import capi, synth
+from .raster import PointRasterizer, Scene, Tonemapper
+
+
+def timed(fn, reps):
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
+    ev[0].record()
+    for i in range(reps):
+        fn()
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    return [ev[i].elapsed_time(ev[i + 1]) for i in range(reps)]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("config", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--points", type=int, default=None)
+    ap.add_argument("--views", type=int, default=None)
+    ap.add_argument("--reps", type=int, default=5)
+    args = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("needs a CUDA device")
+    dev = torch.device("cuda:0")
+    cfg = synth.make_config(args.config, n_points=args.points, n_views=args.views)
+    meta, params, L = cfg["meta"], cfg["params"], cfg["num_layers"]
+    forward_only = args.config == "c3"
+    scene = Scene(**{k: (torch.from_numpy(v).to(dev) if v is not None else None) for k, v in cfg["arrays"].items()})
+    ras = PointRasterizer(dev)
+    fwd = ras.forward(scene, cfg["views"], params, L, record_visible=not forward_only)
+    out = {"config": args.config, **{k: meta[k] for k in ("n_points", "n_views", "w", "h", "layers", "channels")}}
+    out["coverage_layer0"] = float((fwd.weights[0] > 0).float().mean())
+    out["accepted_layer0_per_view"] = float(fwd.weights[0].sum()) / meta["n_views"]
+    t_f = timed(lambda: ras.forward(scene, cfg["views"], params, L, out=fwd, record_visible=not forward_only), args.reps)
+    out["fwd_ms"] = statistics.median(t_f)
+    out["fwd_ms_per_view"] = out["fwd_ms"] / meta["n_views"]
+    total = out["fwd_ms"]
+    if not forward_only:
+        grads = [torch.randn_like(c) for c in fwd.colors]
+        has_env = scene.env_map is not None and params.composite_environment_map
+        bwd = ras.backward(scene, params, fwd, grads, want_env=has_env)
+        out["splat_list_overflowed"] = bool(fwd.list_overflowed().any())
+
+        def both():
+            ras.forward(scene, cfg["views"], params, L, out=fwd)
+            ras.backward(scene, params, fwd, grads, want_env=has_env, out=bwd)
+
+        t_fb = timed(both, args.reps)
+        total = statistics.median(t_fb)
+        out["fwd_bwd_ms"] = total
+        out["bwd_ms_per_view"] = (total - out["fwd_ms"]) / meta["n_views"]
+    out["gpts_per_s"] = meta["n_points"] * meta["n_views"] / (total * 1e-3) / 1e9
+    capi.profile_enable(True)
+    ras.forward(scene, cfg["views"], params, L, out=fwd, record_visible=not forward_only)
+    if not forward_only:
+        ras.backward(scene, params, fwd, grads, want_env=has_env, out=bwd)
+    torch.cuda.synchronize()
+    out["kernel_ms"] = {k: round(v[1], 4) for k, v in capi.profile_collect().items()}
+    capi.profile_enable(False)
+    if args.config == "c5":
+        # the fused tonemapper on the 4K frames: per-image exposure ~ U[-2,2] EV, white balance ~ N(1,0.05) with green fixed,
+        # vignette polynomial (0.1,-0.05,0.01), monotone 256-entry response (gamma 1/2.2 curve)
+        B, w, h = meta["n_views"], meta["w"], meta["h"]
+        g = torch.Generator(device=dev)
+        g.manual_seed(0)
+        exposure = (torch.rand(B, device=dev, generator=g) * 4 - 2)
+        wb = 1 + 0.05 * torch.randn((B, 3), device=dev, generator=g)
+        wb[:, 1] = 1.0
+        vig = torch.tensor([0.1, -0.05, 0.01, 0.0, 0.0], device=dev)
+        response = (torch.linspace(0, 1, 256, device=dev) ** (1 / 2.2)).repeat(3, 1).contiguous()
+        tm = Tonemapper((w, h), exposure=exposure, white_balance=wb.contiguous(), vignette=vig, response=response, leak=0.01)
+        x = fwd.colors[0][:, :3].contiguous()
+        fi = torch.arange(B, device=dev, dtype=torch.int32)
+        go = torch.randn_like(x)
+        tm.forward(x, fi)
+        tm.backward(x, go, fi)
+        out["tonemap_fwd_ms_per_image"] = statistics.median(timed(lambda: tm.forward(x, fi), args.reps)) / B
+        out["tonemap_bwd_ms_per_image"] = statistics.median(timed(lambda: tm.backward(x, go, fi), args.reps)) / B
+        px = w * h
+        out["tonemap_fwd_gbs"] = 24 * px / (out["tonemap_fwd_ms_per_image"] * 1e-3) / 1e9
+        out["tonemap_bwd_gbs"] = 36 * px / (out["tonemap_bwd_ms_per_image"] * 1e-3) / 1e9
+    print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
