@@ -46,7 +46,52 @@ __device__ __forceinline__ void tone_uv(const ToneArgs& a, int b, int xx, int yy
     }
 }
 
-// grid: (ceil(H*W / block), B)
+// VEC pixels per thread: 4 (128-bit loads and stores of every plane) when the plane size is a multiple of 4, else 1.
+template <int VEC>
+__device__ __forceinline__ void load_vec(const float* __restrict__ p, float* v)
+{
+    if (VEC == 4) { float4 a = __ldcs(reinterpret_cast<const float4*>(p)); v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; }
+    else v[0] = __ldcs(p);
+}
+template <int VEC>
+__device__ __forceinline__ void store_vec(float* __restrict__ p, const float* v)
+{
+    if (VEC == 4) __stcs(reinterpret_cast<float4*>(p), make_float4(v[0], v[1], v[2], v[3]));
+    else __stcs(p, v[0]);
+}
+// vignette geometry of VEC consecutive pixels starting at pix
+template <int VEC>
+__device__ __forceinline__ void tone_geometry(const ToneArgs& a, int b, size_t pix, size_t plane, float* du, float* dv, float* r2, float* fac)
+{
+    float u0[VEC], v0[VEC];
+    if (a.uv)
+    {
+        load_vec<VEC>(a.uv + ((size_t)b * 2 + 0) * plane + pix, u0);
+        load_vec<VEC>(a.uv + ((size_t)b * 2 + 1) * plane + pix, v0);
+    }
+    else
+    {
+        int yy = (int)(pix / a.W), xx = (int)(pix - (size_t)yy * a.W);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k)
+        {
+            u0[k] = 2.0f * ((float)xx / (float)(a.W - 1)) - 1.0f;
+            v0[k] = 2.0f * ((float)yy / (float)(a.H - 1)) - 1.0f;
+            if (++xx == a.W) { xx = 0; ++yy; }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < VEC; ++k)
+    {
+        du[k] = (u0[k] - a.vignette[3]) * a.aspect; dv[k] = v0[k] - a.vignette[4];
+        r2[k] = du[k] * du[k] + dv[k] * dv[k];
+        float r4 = r2[k] * r2[k], r6 = r4 * r2[k];
+        fac[k] = 1.f + a.vignette[0] * r2[k] + a.vignette[1] * r4 + a.vignette[2] * r6;
+    }
+}
+
+// grid: (ceil(H*W / (block * VEC)), B)
+template <int VEC>
 __global__ void __launch_bounds__(256) k_tonemap_forward(ToneArgs a, const float* __restrict__ x, float* __restrict__ out)
 {
     extern __shared__ float s_lut[];  // [3,K]
@@ -54,45 +99,44 @@ __global__ void __launch_bounds__(256) k_tonemap_forward(ToneArgs a, const float
     __syncthreads();
     const int b = blockIdx.y;
     const size_t plane = (size_t)a.H * a.W;
-    const size_t pix = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t pix = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (pix >= plane) return;
     const int fi = a.frame_index ? a.frame_index[b] : 0;
     const float ef = a.exposure ? 1.0f / exp2f(a.exposure[fi]) : 1.0f;
-    float fac = 1.f;
-    if (a.vignette)
-    {
-        int yy = (int)(pix / a.W), xx = (int)(pix - (size_t)yy * a.W);
-        float u0, v0;
-        tone_uv(a, b, xx, yy, pix, plane, &u0, &v0);
-        float du = (u0 - a.vignette[3]) * a.aspect, dv = v0 - a.vignette[4];
-        float r2 = du * du + dv * dv, r4 = r2 * r2, r6 = r4 * r2;
-        fac = 1.f + a.vignette[0] * r2 + a.vignette[1] * r4 + a.vignette[2] * r6;
-    }
+    float du[VEC], dv[VEC], r2[VEC], fac[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) fac[k] = 1.f;
+    if (a.vignette) tone_geometry<VEC>(a, b, pix, plane, du, dv, r2, fac);
 #pragma unroll
     for (int c = 0; c < 3; ++c)
     {
         const float wb = a.white_balance ? a.white_balance[(size_t)fi * 3 + c] : 1.0f;
-        float v = __ldcs(x + ((size_t)b * 3 + c) * plane + pix) * ef;
-        v = wb * v;
-        v = fac * v;
-        float o;
-        if (a.response)
+        float xin[VEC], o[VEC];
+        load_vec<VEC>(x + ((size_t)b * 3 + c) * plane + pix, xin);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k)
         {
-            float leak_add = 0.f;
-            if (a.leak > 0.f)
+            float v = xin[k] * ef;
+            v = wb * v;
+            v = fac[k] * v;
+            if (a.response)
             {
-                if (v < 0.f) leak_add = v * a.leak;
-                if (v > 1.f) leak_add = -a.leak / sqrtf(fabsf(v) + 1e-4f) + a.leak;
+                float leak_add = 0.f;
+                if (a.leak > 0.f)
+                {
+                    if (v < 0.f) leak_add = v * a.leak;
+                    if (v > 1.f) leak_add = -a.leak / sqrtf(fabsf(v) + 1e-4f) + a.leak;
+                }
+                float t = fminf(fmaxf(v, 0.f), 1.f) * (float)(a.K - 1);
+                int i0 = (int)floorf(t);
+                int i1 = i0 + 1 < a.K ? i0 + 1 : a.K - 1;
+                float fr = t - (float)i0;
+                o[k] = s_lut[c * a.K + i0] * (1.0f - fr) + s_lut[c * a.K + i1] * fr + leak_add;
             }
-            float t = fminf(fmaxf(v, 0.f), 1.f) * (float)(a.K - 1);
-            int i0 = (int)floorf(t);
-            int i1 = i0 + 1 < a.K ? i0 + 1 : a.K - 1;
-            float fr = t - (float)i0;
-            o = s_lut[c * a.K + i0] * (1.0f - fr) + s_lut[c * a.K + i1] * fr + leak_add;
+            else
+                o[k] = fminf(fmaxf(v, 0.f), 1.f);
         }
-        else
-            o = fminf(fmaxf(v, 0.f), 1.f);
-        __stcs(out + ((size_t)b * 3 + c) * plane + pix, o);
+        store_vec<VEC>(out + ((size_t)b * 3 + c) * plane + pix, o);
     }
 }
 
@@ -105,19 +149,24 @@ struct ToneGradPtrs
     float* grad_response;
 };
 
+// The response-curve gradient is a histogram-like scatter (two bins per pixel and channel, neighbouring pixels hit the same
+// bins): each warp group adds into its own copy in shared memory (`copies` of them, as many as fit), merged at the end.
+template <int VEC>
 __global__ void __launch_bounds__(256) k_tonemap_backward(ToneArgs a, const float* __restrict__ x, const float* __restrict__ grad_out,
-                                                           ToneGradPtrs g)
+                                                           ToneGradPtrs g, int copies)
 {
-    extern __shared__ float smem[];  // lut [3,K], then response gradient [3,K]
+    extern __shared__ float smem[];  // lut [3,K], then `copies` response gradients [3,K]
     float* s_lut = smem;
     float* s_gr = smem + 3 * a.K;
     __shared__ float s_small[9];  // exposure, wb[3], vignette[5]
-    for (int k = threadIdx.x; k < 3 * a.K; k += blockDim.x) { s_lut[k] = a.response[k]; s_gr[k] = 0.f; }
+    for (int k = threadIdx.x; k < 3 * a.K; k += blockDim.x) s_lut[k] = a.response[k];
+    for (int k = threadIdx.x; k < 3 * a.K * copies; k += blockDim.x) s_gr[k] = 0.f;
     if (threadIdx.x < 9) s_small[threadIdx.x] = 0.f;
     __syncthreads();
+    float* my_gr = s_gr + (size_t)((threadIdx.x >> 5) % copies) * 3 * a.K;
     const int b = blockIdx.y;
     const size_t plane = (size_t)a.H * a.W;
-    const size_t pix = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t pix = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     const bool live = pix < plane;
     const int fi = a.frame_index ? a.frame_index[b] : 0;
     const float ef = a.exposure ? 1.0f / exp2f(a.exposure[fi]) : 1.0f;
@@ -125,61 +174,62 @@ __global__ void __launch_bounds__(256) k_tonemap_backward(ToneArgs a, const floa
     float gE = 0.f, gWB[3] = {0.f, 0.f, 0.f}, gV[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
     if (live)
     {
-        float fac = 1.f, du = 0.f, dv = 0.f, r2 = 0.f, r4 = 0.f, r6 = 0.f;
-        if (a.vignette)
-        {
-            int yy = (int)(pix / a.W), xx = (int)(pix - (size_t)yy * a.W);
-            float u0, v0;
-            tone_uv(a, b, xx, yy, pix, plane, &u0, &v0);
-            du = (u0 - a.vignette[3]) * a.aspect; dv = v0 - a.vignette[4];
-            r2 = du * du + dv * dv; r4 = r2 * r2; r6 = r4 * r2;
-            fac = 1.f + a.vignette[0] * r2 + a.vignette[1] * r4 + a.vignette[2] * r6;
-        }
+        float du[VEC], dv[VEC], r2[VEC], fac[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) { fac[k] = 1.f; du[k] = dv[k] = r2[k] = 0.f; }
+        if (a.vignette) tone_geometry<VEC>(a, b, pix, plane, du, dv, r2, fac);
 #pragma unroll
         for (int c = 0; c < 3; ++c)
         {
             const float wb = a.white_balance ? a.white_balance[(size_t)fi * 3 + c] : 1.0f;
-            const float xin = __ldcs(x + ((size_t)b * 3 + c) * plane + pix);
-            const float go = __ldcs(grad_out + ((size_t)b * 3 + c) * plane + pix);
-            const float pre = wb * (xin * ef);
-            const float v = fac * pre;
-            float dv_out;
-            if (a.response)
+            float xin[VEC], go[VEC], gx[VEC];
+            load_vec<VEC>(x + ((size_t)b * 3 + c) * plane + pix, xin);
+            load_vec<VEC>(grad_out + ((size_t)b * 3 + c) * plane + pix, go);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k)
             {
-                float dleak = 0.f;
-                if (a.leak > 0.f)
+                const float pre = wb * (xin[k] * ef);
+                const float v = fac[k] * pre;
+                float dv_out;
+                if (a.response)
                 {
-                    if (v < 0.f) dleak = a.leak;
-                    if (v > 1.f) { float q = fabsf(v) + 1e-4f; dleak = 0.5f * a.leak / (q * sqrtf(q)); }
+                    float dleak = 0.f;
+                    if (a.leak > 0.f)
+                    {
+                        if (v < 0.f) dleak = a.leak;
+                        if (v > 1.f) { float q = fabsf(v) + 1e-4f; dleak = 0.5f * a.leak / (q * sqrtf(q)); }
+                    }
+                    float t = fminf(fmaxf(v, 0.f), 1.f) * (float)(a.K - 1);
+                    int i0 = (int)floorf(t);
+                    int i1 = i0 + 1 < a.K ? i0 + 1 : a.K - 1;
+                    float fr = t - (float)i0;
+                    if (g.grad_response)
+                    {
+                        atomicAdd(&my_gr[c * a.K + i0], go[k] * (1.0f - fr));
+                        atomicAdd(&my_gr[c * a.K + i1], go[k] * fr);
+                    }
+                    float inside = (v > 0.f && v < 1.f) ? 1.f : 0.f;
+                    dv_out = inside * (s_lut[c * a.K + i1] - s_lut[c * a.K + i0]) * (float)(a.K - 1) + dleak;
                 }
-                float t = fminf(fmaxf(v, 0.f), 1.f) * (float)(a.K - 1);
-                int i0 = (int)floorf(t);
-                int i1 = i0 + 1 < a.K ? i0 + 1 : a.K - 1;
-                float fr = t - (float)i0;
-                if (g.grad_response)
+                else
+                    dv_out = (v > 0.f && v < 1.f) ? 1.f : 0.f;
+                const float gv = go[k] * dv_out;
+                if (a.vignette)
                 {
-                    atomicAdd(&s_gr[c * a.K + i0], go * (1.0f - fr));
-                    atomicAdd(&s_gr[c * a.K + i1], go * fr);
+                    float gfac = gv * pre;
+                    float r4 = r2[k] * r2[k];
+                    gV[0] += gfac * r2[k]; gV[1] += gfac * r4; gV[2] += gfac * (r4 * r2[k]);
+                    float gr2 = gfac * (a.vignette[0] + 2.f * a.vignette[1] * r2[k] + 3.f * a.vignette[2] * r4);
+                    gV[3] += gr2 * 2.f * du[k] * (-a.aspect);
+                    gV[4] += gr2 * 2.f * dv[k] * (-1.f);
                 }
-                float inside = (v > 0.f && v < 1.f) ? 1.f : 0.f;
-                dv_out = inside * (s_lut[c * a.K + i1] - s_lut[c * a.K + i0]) * (float)(a.K - 1) + dleak;
+                const float gpre = gv * fac[k];
+                gWB[c] += gpre * (xin[k] * ef);
+                const float gxe = gpre * wb;
+                gE += gxe * xin[k] * ef * (-ln2);
+                gx[k] = gxe * ef;
             }
-            else
-                dv_out = (v > 0.f && v < 1.f) ? 1.f : 0.f;
-            const float gv = go * dv_out;
-            if (a.vignette)
-            {
-                float gfac = gv * pre;
-                gV[0] += gfac * r2; gV[1] += gfac * r4; gV[2] += gfac * r6;
-                float gr2 = gfac * (a.vignette[0] + 2.f * a.vignette[1] * r2 + 3.f * a.vignette[2] * r4);
-                gV[3] += gr2 * 2.f * du * (-a.aspect);
-                gV[4] += gr2 * 2.f * dv * (-1.f);
-            }
-            const float gpre = gv * fac;
-            gWB[c] = gpre * (xin * ef);
-            const float gxe = gpre * wb;
-            gE += gxe * xin * ef * (-ln2);
-            if (g.grad_x) __stcs(g.grad_x + ((size_t)b * 3 + c) * plane + pix, gxe * ef);
+            if (g.grad_x) store_vec<VEC>(g.grad_x + ((size_t)b * 3 + c) * plane + pix, gx);
         }
     }
     const bool lane0 = (threadIdx.x & 31) == 0;
@@ -197,7 +247,11 @@ __global__ void __launch_bounds__(256) k_tonemap_backward(ToneArgs a, const floa
         atomicAdd(g.grad_vignette + (threadIdx.x - 4), s_small[threadIdx.x]);
     if (g.grad_response && a.response)
         for (int k = threadIdx.x; k < 3 * a.K; k += blockDim.x)
-            if (s_gr[k] != 0.f) atomicAdd(g.grad_response + k, s_gr[k]);
+        {
+            float sum = 0.f;
+            for (int j = 0; j < copies; ++j) sum += s_gr[(size_t)j * 3 * a.K + k];
+            if (sum != 0.f) atomicAdd(g.grad_response + k, sum);
+        }
 }
 
 static adop_status make_tone_args(const adop_tonemap_params* p, ToneArgs* a)
@@ -236,8 +290,18 @@ extern "C" adop_status adop_tonemap_forward(const adop_tonemap_params* p, const 
     if (s != ADOP_OK) return s;
     if (!x || !out) return ADOP_ERR_INVALID_ARGUMENT;
     size_t plane = (size_t)a.H * a.W;
-    dim3 grid((unsigned)((plane + 255) / 256), (unsigned)a.B);
-    k_tonemap_forward<<<grid, 256, sizeof(float) * 3 * a.K, static_cast<cudaStream_t>(stream)>>>(a, x, out);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool vec = plane % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(a.uv)) & 15) == 0;
+    if (vec)
+    {
+        dim3 grid((unsigned)((plane / 4 + 255) / 256), (unsigned)a.B);
+        ADOP_LAUNCH("k_tonemap_forward", st, (k_tonemap_forward<4><<<grid, 256, sizeof(float) * 3 * a.K, st>>>(a, x, out)));
+    }
+    else
+    {
+        dim3 grid((unsigned)((plane + 255) / 256), (unsigned)a.B);
+        ADOP_LAUNCH("k_tonemap_forward", st, (k_tonemap_forward<1><<<grid, 256, sizeof(float) * 3 * a.K, st>>>(a, x, out)));
+    }
     ADOP_CUDA_TRY(cudaGetLastError());
     return ADOP_OK;
 }
@@ -262,8 +326,23 @@ extern "C" adop_status adop_tonemap_backward(const adop_tonemap_params* p, const
     gp.grad_x = g->grad_x; gp.grad_exposure = g->grad_exposure; gp.grad_white_balance = g->grad_white_balance;
     gp.grad_vignette = g->grad_vignette; gp.grad_response = g->grad_response;
     size_t plane = (size_t)a.H * a.W;
-    dim3 grid((unsigned)((plane + 255) / 256), (unsigned)a.B);
-    k_tonemap_backward<<<grid, 256, sizeof(float) * 6 * a.K, st>>>(a, x, grad_out, gp);
+    // private copies of the response gradient per warp group, as many as fit in 40 KB of shared memory
+    int copies = a.K > 0 ? (int)((40 * 1024) / (sizeof(float) * 3 * a.K)) - 1 : 1;
+    if (copies > 8) copies = 8;
+    if (copies < 1) copies = 1;
+    const size_t smem_bytes = sizeof(float) * 3 * a.K * (1 + copies);
+    const bool vec = plane % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(grad_out) |
+                                         reinterpret_cast<uintptr_t>(g->grad_x) | reinterpret_cast<uintptr_t>(a.uv)) & 15) == 0;
+    if (vec)
+    {
+        dim3 grid((unsigned)((plane / 4 + 255) / 256), (unsigned)a.B);
+        ADOP_LAUNCH("k_tonemap_backward", st, (k_tonemap_backward<4><<<grid, 256, smem_bytes, st>>>(a, x, grad_out, gp, copies)));
+    }
+    else
+    {
+        dim3 grid((unsigned)((plane + 255) / 256), (unsigned)a.B);
+        ADOP_LAUNCH("k_tonemap_backward", st, (k_tonemap_backward<1><<<grid, 256, smem_bytes, st>>>(a, x, grad_out, gp, copies)));
+    }
     ADOP_CUDA_TRY(cudaGetLastError());
     return ADOP_OK;
 }

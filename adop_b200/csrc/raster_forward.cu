@@ -30,20 +30,54 @@ __global__ void k_fill(float* __restrict__ dst, size_t n, float v)
 
 // [C,T] planes <-> [T,C] interleaved descriptors (one texel per thread; plane accesses are coalesced, interleaved
 // accesses are contiguous vectors)
+template <int C4>  // C4 = C / 4 when C is a multiple of 4 (vector stores), 0 = any C (scalar)
 __global__ void k_texture_interleave(const float* __restrict__ in, float* __restrict__ out, int C, int T)
 {
     for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < T; t += gridDim.x * blockDim.x)
-        for (int c = 0; c < C; ++c) out[(size_t)t * C + c] = __ldcs(in + (size_t)c * T + t);
+    {
+        if (C4 > 0)
+        {
+#pragma unroll
+            for (int k = 0; k < C4; ++k)
+            {
+                float4 v;
+                v.x = __ldcs(in + (size_t)(4 * k + 0) * T + t); v.y = __ldcs(in + (size_t)(4 * k + 1) * T + t);
+                v.z = __ldcs(in + (size_t)(4 * k + 2) * T + t); v.w = __ldcs(in + (size_t)(4 * k + 3) * T + t);
+                reinterpret_cast<float4*>(out + (size_t)t * (4 * C4))[k] = v;
+            }
+        }
+        else
+            for (int c = 0; c < C; ++c) out[(size_t)t * C + c] = __ldcs(in + (size_t)c * T + t);
+    }
 }
+template <int C4>
 __global__ void k_texture_deinterleave(const float* __restrict__ in, float* __restrict__ out, int C, int T, int accumulate)
 {
     for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < T; t += gridDim.x * blockDim.x)
-        for (int c = 0; c < C; ++c)
+    {
+        if (C4 > 0)
         {
-            float v = __ldcs(in + (size_t)t * C + c);
-            float* dst = out + (size_t)c * T + t;
-            *dst = accumulate ? *dst + v : v;
+#pragma unroll
+            for (int k = 0; k < C4; ++k)
+            {
+                const float4 v = __ldcs(reinterpret_cast<const float4*>(in + (size_t)t * (4 * C4)) + k);
+                const float vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                {
+                    float* dst = out + (size_t)(4 * k + j) * T + t;
+                    *dst = accumulate ? *dst + vv[j] : vv[j];
+                }
+            }
         }
+        else
+            for (int c = 0; c < C; ++c)
+            {
+                float v = __ldcs(in + (size_t)t * C + c);
+                float* dst = out + (size_t)c * T + t;
+                *dst = accumulate ? *dst + v : v;
+            }
+    }
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -396,7 +430,13 @@ extern "C" adop_status adop_texture_interleave(const float* texture, float* out,
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int grid = (num_texels + kBlock - 1) / kBlock;
     if (grid > sm_count() * 16) grid = sm_count() * 16;
-    ADOP_LAUNCH("k_texture_interleave", st, (k_texture_interleave<<<grid, kBlock, 0, st>>>(texture, out, channels, num_texels)));
+    switch (channels)
+    {
+        case 4: ADOP_LAUNCH("k_texture_interleave", st, (k_texture_interleave<1><<<grid, kBlock, 0, st>>>(texture, out, channels, num_texels))); break;
+        case 8: ADOP_LAUNCH("k_texture_interleave", st, (k_texture_interleave<2><<<grid, kBlock, 0, st>>>(texture, out, channels, num_texels))); break;
+        case 16: ADOP_LAUNCH("k_texture_interleave", st, (k_texture_interleave<4><<<grid, kBlock, 0, st>>>(texture, out, channels, num_texels))); break;
+        default: ADOP_LAUNCH("k_texture_interleave", st, (k_texture_interleave<0><<<grid, kBlock, 0, st>>>(texture, out, channels, num_texels))); break;
+    }
     ADOP_CUDA_TRY(cudaGetLastError());
     return ADOP_OK;
 }
@@ -408,7 +448,13 @@ extern "C" adop_status adop_texture_deinterleave(const float* in, float* out, in
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int grid = (num_texels + kBlock - 1) / kBlock;
     if (grid > sm_count() * 16) grid = sm_count() * 16;
-    ADOP_LAUNCH("k_texture_deinterleave", st, (k_texture_deinterleave<<<grid, kBlock, 0, st>>>(in, out, channels, num_texels, accumulate)));
+    switch (channels)
+    {
+        case 4: ADOP_LAUNCH("k_texture_deinterleave", st, (k_texture_deinterleave<1><<<grid, kBlock, 0, st>>>(in, out, channels, num_texels, accumulate))); break;
+        case 8: ADOP_LAUNCH("k_texture_deinterleave", st, (k_texture_deinterleave<2><<<grid, kBlock, 0, st>>>(in, out, channels, num_texels, accumulate))); break;
+        case 16: ADOP_LAUNCH("k_texture_deinterleave", st, (k_texture_deinterleave<4><<<grid, kBlock, 0, st>>>(in, out, channels, num_texels, accumulate))); break;
+        default: ADOP_LAUNCH("k_texture_deinterleave", st, (k_texture_deinterleave<0><<<grid, kBlock, 0, st>>>(in, out, channels, num_texels, accumulate))); break;
+    }
     ADOP_CUDA_TRY(cudaGetLastError());
     return ADOP_OK;
 }

@@ -133,7 +133,8 @@ class PointRasterizer:
             self._ws = torch.empty(need, dtype=torch.uint8, device=self.device)
         return self._ws
 
-    def forward(self, scene, views, params, num_layers, dropout_mask=None, out=None, record_visible=True):
+    def forward(self, scene, views, params, num_layers, dropout_mask=None, out=None, record_visible=True,
+                refresh_descriptors=True):
         """BlendPointCloudForward (PointRenderer.cu:1389-1531). `views`: list of dicts or an AdopView array.
 
         Returns a ForwardResult; result.colors + result.masks is the reference's return list.
@@ -142,7 +143,9 @@ class PointRasterizer:
         B = len(va)
         w, h = va[0].w, va[0].h
         with torch.cuda.device(self.device):
-            sc = self._scene_struct(scene, refresh=True)
+            # refresh_descriptors=False: the caller vouches that scene.texture has not changed since the last call (a viewer
+            # rendering frame after frame), so the [T,C] working copy is reused as it is
+            sc = self._scene_struct(scene, refresh=refresh_descriptors)
             ch = sc.channels
             ws = self._workspace(w, h, num_layers, ch)
             sizes = capi.layer_sizes(w, h, num_layers)
