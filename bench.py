@@ -30,6 +30,12 @@ UNIT = "Gpts/s"
 WORKLOAD = "c2: 10M points x 16 views/GPU, 1920x1080, L=4, C=4, pinhole k1=-0.1 k2=0.02, env 1024x512, fwd+bwd with pose grads"
 
 
+# DRAM bytes (read + write) per launch of the kernels that can dominate, from one ncu --set full capture of a one-view run of
+# this workload (profiles/point_kernels_c2_one_view_ncu_full.md); one launch there = one launch here. Valid for the default
+# workload only.
+NCU_TRAFFIC_BYTES = {"k_depth_prepass": 178.0e6, "k_blend": 440.1e6, "k_splat_gather": 500.9e6, "k_splat_chain": 200.7e6}
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -55,7 +61,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -316,7 +322,9 @@ def main():
     step_ms = ms_total / args.steps
     step_achieved = (fwd_b + bwd_b + step_b) / (step_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                "frac": achieved / peak,
+                "traffic": NCU_TRAFFIC_BYTES.get(dom_name) if (args.points == 10_000_000 and w == 1920) else None,
+                "peak_kind": peak_kind,
                 "algorithmic_bytes_per_launch": dom_bytes, "avg_launch_ms": dom_ms / dom_launches,
                 "step": {"algorithmic_bytes": fwd_b + bwd_b + step_b, "achieved": step_achieved, "frac": step_achieved / peak},
                 "kernel_ms_per_step": {k: v[1] / max(1, min(args.steps, 5)) for k, v in ktimes.items()}}
