@@ -32,20 +32,6 @@ struct ToneArgs
     const float* response;
 };
 
-__device__ __forceinline__ void tone_uv(const ToneArgs& a, int b, int xx, int yy, size_t pix, size_t plane, float* u0, float* v0)
-{
-    if (a.uv)
-    {
-        *u0 = __ldg(a.uv + ((size_t)b * 2 + 0) * plane + pix);
-        *v0 = __ldg(a.uv + ((size_t)b * 2 + 1) * plane + pix);
-    }
-    else
-    {
-        *u0 = 2.0f * ((float)xx / (float)(a.W - 1)) - 1.0f;
-        *v0 = 2.0f * ((float)yy / (float)(a.H - 1)) - 1.0f;
-    }
-}
-
 // VEC pixels per thread: 4 (128-bit loads and stores of every plane) when the plane size is a multiple of 4, else 1.
 template <int VEC>
 __device__ __forceinline__ void load_vec(const float* __restrict__ p, float* v)

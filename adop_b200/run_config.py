@@ -66,6 +66,17 @@ def main():
         t_fb = timed(both, args.reps)
         total = statistics.median(t_fb)
         out["fwd_bwd_ms"] = total
+        if args.config == "c1":
+            # launch-bound at this size: the same step captured once into a CUDA graph and replayed
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                both()
+                side.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    both()
+            torch.cuda.synchronize()
+            out["fwd_bwd_ms_cuda_graph"] = statistics.median(timed(graph.replay, max(args.reps, 20)))
         out["bwd_ms_per_view"] = (total - out["fwd_ms"]) / meta["n_views"]
     out["gpts_per_s"] = meta["n_points"] * meta["n_views"] / (total * 1e-3) / 1e9
     capi.profile_enable(True)

@@ -277,3 +277,73 @@ def test_argument_errors(cuda_lib):
     with pytest.raises(capi.AdopError):
         r.forward(Scene(**{k: (v.cpu() if v is not None else None) for k, v in scene.tensors().items()}),
                   cfg["views"], cfg["params"], 4)
+
+
+def test_c2_full_size_one_view_against_checker(oracle, cuda_lib):
+    """The benchmark's own size (10 M points, 1920x1080, 4 layers) for one view: depth and weight bit-exact, colours and all
+    gradients within tolerance. The checker runs with its OpenMP point loops (depth / weight do not depend on the order)."""
+    cfg = synth.make_config("c2", n_views=1)
+    arrays, views, params, L = cfg["arrays"], cfg["views"], cfg["params"], cfg["num_layers"]
+    grads = synth.upstream_gradients(cfg["meta"], batch=1)
+    ref = oracle.forward(arrays, views, params, L, threads=16)
+    ref_b = oracle.backward(arrays, views, params, L, ref, grads, want_env=True, threads=16)
+    scene = to_scene(arrays)
+    r = PointRasterizer("cuda:0")
+    fwd = r.forward(scene, views, params, L)
+    bwd = r.backward(scene, params, fwd, [torch.from_numpy(g).cuda() for g in grads], want_env=True)
+    torch.cuda.synchronize()
+    assert not bool(fwd.list_overflowed().any())
+    check_forward(ref, fwd, L, masks=True)
+    check_backward(ref_b, bwd)
+
+
+def test_full_size_properties_16_views(cuda_lib):
+    """Size-independent properties on the full benchmark batch (10 M points x 16 views), no checker involved:
+    every recorded splat is an accepted (point, layer) pair, so the list length lies between the points accepted on the
+    finest layer and the sum of all weights; the background mask is the indicator of weight > 0; depth is 100000 exactly
+    where nothing landed on the finest layer; a second forward pass reproduces depth and weight bit for bit."""
+    cfg = synth.make_config("c2")
+    scene = to_scene(cfg["arrays"])
+    r = PointRasterizer("cuda:0")
+    fwd = r.forward(scene, cfg["views"], cfg["params"], 4)
+    torch.cuda.synchronize()
+    assert not bool(fwd.list_overflowed().any())
+    splats = fwd.splat_counts().double()
+    w_all = sum(w.double().sum(dim=(1, 2, 3)) for w in fwd.weights)
+    w0 = fwd.weights[0].double().sum(dim=(1, 2, 3))
+    assert bool((splats <= w_all).all()) and bool((splats >= w0).all())
+    for l in range(4):
+        assert torch.equal(fwd.masks[l], (fwd.weights[l] > 0).float())
+        assert bool(((fwd.depths[l] < 100000) | (fwd.weights[l] == 0)).all())
+    d0, w0t = [d.clone() for d in fwd.depths], [w.clone() for w in fwd.weights]
+    fwd = r.forward(scene, cfg["views"], cfg["params"], 4, out=fwd)
+    for l in range(4):
+        assert torch.equal(fwd.depths[l], d0[l]) and torch.equal(fwd.weights[l], w0t[l])
+
+
+def test_forward_backward_replay_from_a_cuda_graph(oracle, cuda_lib):
+    """After one warm-up call nothing in the library synchronises or allocates, so a whole forward + backward step can be
+    captured into a CUDA graph and replayed (what a launch-bound small workload wants)."""
+    cfg = synth.make_config("c1", n_points=50_000, size=(128, 128))
+    arrays, views, params, L = cfg["arrays"], cfg["views"], cfg["params"], cfg["num_layers"]
+    grads = synth.upstream_gradients(cfg["meta"], batch=1)
+    ref = oracle.forward(arrays, views, params, L)
+    ref_b = oracle.backward(arrays, views, params, L, ref, grads)
+    scene = to_scene(arrays)
+    r = PointRasterizer("cuda:0")
+    g = [torch.from_numpy(x).cuda() for x in grads]
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        fwd = r.forward(scene, views, params, L)
+        bwd = r.backward(scene, params, fwd, g)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            r.forward(scene, views, params, L, out=fwd)
+            r.backward(scene, params, fwd, g, out=bwd)
+    for t in fwd.colors + fwd.depths + fwd.weights + [bwd["texture"], bwd["points"], bwd["pose"]]:
+        t.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    check_forward(ref, fwd, L)
+    check_backward(ref_b, bwd)
