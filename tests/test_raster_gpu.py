@@ -347,3 +347,72 @@ def test_forward_backward_replay_from_a_cuda_graph(oracle, cuda_lib):
     torch.cuda.synchronize()
     check_forward(ref, fwd, L)
     check_backward(ref_b, bwd)
+
+
+def test_many_views_crops_two_cameras_shared_texels(oracle, cuda_lib):
+    """70 views (more than one camera-record chunk of 64), each with its own crop transform (zoom + shift + skew, as the
+    training crops of Dataset.cpp:140-171 produce), two cameras with different intrinsics, views that repeat an image
+    index (their pose gradients add up), and an index tensor in which pairs of points share a descriptor."""
+    rng = np.random.default_rng(11)
+    cfg = synth.make_config("c2", n_points=60_000, n_views=8, size=(96, 64))
+    a = cfg["arrays"]
+    n = cfg["meta"]["n_points"]
+    a["index"] = (np.arange(n) // 2).astype(np.int32)           # two points per texel
+    a["texture"] = np.ascontiguousarray(a["texture"][:, : (n + 1) // 2])
+    intr2 = a["intrinsics"].copy()
+    intr2[0, :4] *= 1.1
+    intr2[0, 5:7] = [-0.05, 0.01]
+    a["intrinsics"] = np.ascontiguousarray(np.concatenate([a["intrinsics"], intr2]))
+    views = []
+    for k in range(70):
+        zoom = rng.uniform(0.8, 1.6)
+        views.append(dict(w=96, h=64, image_index=int(rng.integers(0, 8)), camera_index=int(k % 2), camera_model=0,
+                          crop=(zoom, zoom * rng.uniform(0.95, 1.05), rng.uniform(-20, 5), rng.uniform(-12, 4), rng.uniform(-0.02, 0.02))))
+    cfg["views"] = views
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg, want_env=True)
+    check_forward(ref, fwd, 4, masks=True)
+    check_backward(ref_b, bwd)
+    assert (ref_b["count_pose"] > 0).sum() >= 6 and np.all(ref_b["count_intrinsics"] > 0)
+
+
+def test_accumulate_adds_to_existing_gradients(cuda_lib):
+    """accumulate = 1 adds this call's sums to what the buffers hold (two half-batches = one full batch)."""
+    import ctypes as C
+    from adop_b200.raster import fill_scene_struct
+    cfg = synth.make_config("c2", n_points=80_000, n_views=4, size=(128, 72))
+    scene = to_scene(cfg["arrays"])
+    r = PointRasterizer("cuda:0", interleave_descriptors=False)
+    grads = [torch.from_numpy(g).cuda() for g in synth.upstream_gradients(cfg["meta"])]
+    fwd = r.forward(scene, cfg["views"], cfg["params"], 4)
+    full = r.backward(scene, cfg["params"], fwd, grads, want_env=True, normalize=False)
+    full = {k: (v.clone() if v is not None else None) for k, v in full.items()}
+    acc = None
+    lib = r.lib
+    for half in (slice(0, 2), slice(2, 4)):
+        views = cfg["views"][half]
+        f2 = r.forward(scene, views, cfg["params"], 4)
+        g2 = [g[half].contiguous() for g in grads]
+        if acc is None:
+            acc = r.backward(scene, cfg["params"], f2, g2, want_env=True, normalize=False)
+            continue
+        # second half: same buffers, accumulate = 1, straight through the C ABI
+        va = capi.make_views(views)
+        sc = fill_scene_struct(scene.tensors(), lambda t: t.data_ptr())
+        io = capi.AdopBackwardIO()
+        for l in range(4):
+            io.layers[l].color, io.layers[l].depth = f2.colors[l].data_ptr(), f2.depths[l].data_ptr()
+            io.layers[l].weight = f2.weights[l].data_ptr()
+            io.grad_color[l] = g2[l].data_ptr()
+        io.grad_texture, io.grad_background, io.grad_points = acc["texture"].data_ptr(), acc["background"].data_ptr(), acc["points"].data_ptr()
+        io.grad_pose, io.count_pose = acc["pose"].data_ptr(), acc["count_pose"].data_ptr()
+        io.grad_intrinsics, io.count_intrinsics = acc["intrinsics"].data_ptr(), acc["count_intrinsics"].data_ptr()
+        io.grad_env_map = acc["env_map"].data_ptr()
+        io.accumulate, io.normalize = 1, 0
+        ws = r._workspace(128, 72, 4, 4)
+        io.workspace, io.workspace_bytes = ws.data_ptr(), ws.numel()
+        io.visible_list = f2.visible.data_ptr()
+        st = lib.adop_raster_backward(C.byref(sc), va, 2, C.byref(cfg["params"]), 4, C.byref(io), None)
+        assert st == 0, lib.adop_last_error()
+    torch.cuda.synchronize()
+    for k in ("texture", "background", "points", "pose", "count_pose", "intrinsics", "count_intrinsics", "env_map"):
+        close(acc[k], full[k].cpu().numpy(), name=k)
