@@ -33,7 +33,7 @@ WORKLOAD = "c2: 10M points x 16 views/GPU, 1920x1080, L=4, C=4, pinhole k1=-0.1 
 # DRAM bytes (read + write) per launch of the kernels that can dominate, from one ncu --set full capture of a one-view run of
 # this workload (profiles/point_kernels_c2_one_view_ncu_full.md); one launch there = one launch here. Valid for the default
 # workload only.
-NCU_TRAFFIC_BYTES = {"k_depth_prepass": 178.0e6, "k_blend": 440.1e6, "k_splat_gather": 500.9e6, "k_splat_chain": 200.7e6}
+NCU_TRAFFIC_BYTES = {"k_blend": 440.1e6, "k_splat_gather": 500.9e6, "k_splat_chain": 200.7e6}
 
 
 def parse_args():
@@ -208,9 +208,9 @@ def main():
             ras.normalize_gradients({"points": None, "pose": ex["pose"], "count_pose": ex["count_pose"],
                                      "intrinsics": ex["intrinsics"], "count_intrinsics": ex["count_intrinsics"]})
 
-    # per step: interleave, depth fills, camera records (forward and backward), (prepass, blend, resolve) and (prepare, gather,
-    # chain, all-points fallback) per view, de-interleave, three normalisations
-    kernels_per_step = 1 + L + 2 + 3 * V + 4 * V + 1 + 3
+    # per step: interleave, depth fills, camera records (forward and backward), one depth prepass per group of four views,
+    # (blend, resolve) and (prepare, gather, chain, all-points fallback) per view, de-interleave, three normalisations
+    kernels_per_step = 1 + L + 2 + (V + 3) // 4 + 2 * V + 4 * V + 1 + 3
 
     def barrier():
         if world > 1:
@@ -315,7 +315,7 @@ def main():
     # algorithmic bytes of one launch (= one view) of each kernel that can dominate; a backward kernel is charged the whole
     # backward figure G_v of its view (the split of the backward pass into kernels is this implementation's business)
     U_mean = sum(U_views) / V
-    dom_bytes = {"k_depth_prepass": N * 16 + 4 * P,
+    dom_bytes = {"k_depth_prepass": N * 16 + 4 * 4 * P,  # one launch covers four views: the points once, four depth pyramids
                  "k_blend": N * 16 + U_mean * (4 + 4 * C),
                  "k_resolve": P * (4 * C + 8)}.get(dom_name, sum(per_view_bwd) / V)
     achieved = dom_bytes / (dom_ms / dom_launches * 1e-3) / 1e9
