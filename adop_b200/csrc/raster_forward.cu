@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, const flo
         if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, use_normal, kp.dist_cutoff, &q, use_radius)) return 0u;
         float x = q.x, y = q.y, rad = q.radius_px;
         // the depth reads of all layers go out together
-        long long pix[L];
+        int pix[L];  // pixel index inside the layer (a pyramid has fewer than 2^31 pixels), -1 = not in this layer
         bool live = true;
 #pragma unroll
         for (int l = 0; l < L; ++l, rad *= 0.5f, x *= 0.5f, y *= 0.5f)
@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, const flo
             if (use_radius && rad < kp.drop_out_radius_threshold) live = false;  // break, :368-371
             int px = round_half_even_bounded(x), py = round_half_even_bounded(y);
             bool in = live && (unsigned)px < (unsigned)lt.w[l] && (unsigned)py < (unsigned)lt.h[l];
-            pix[l] = in ? (long long)py * lt.w[l] + px : -1;
+            pix[l] = in ? py * lt.w[l] + px : -1;
         }
         unsigned pass = 0;
 #pragma unroll
@@ -214,7 +214,7 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, const flo
 #pragma unroll
         for (int l = 0; l < L; ++l)
         {
-            pix_out[l] = (int)pix[l];
+            pix_out[l] = pix[l];
             if (pix[l] < 0) continue;
             if (!(pass & (1u << l))) break;
             bmask |= 1u << l;
@@ -229,9 +229,8 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, const flo
         unsigned bmask = 0;
         int lpix[L];
         if (i < pts.n) bmask = blend_point(i, __ldg(pts.position + i), lpix);
-        if (EMIT)
+        if (EMIT && __any_sync(0xffffffffu, bmask != 0))
         {
-            __syncwarp();
             const int cnt = __popc(bmask);
             int incl = cnt;
 #pragma unroll
