@@ -9,7 +9,8 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG_DIR)
 CSRC = os.path.join(PKG_DIR, "csrc")
-SOURCES = ["capi_common.cu", "raster_forward.cu", "raster_forward_static.cu", "raster_backward.cu", "pose_tonemap.cu"]
+SOURCES = ["capi_common.cu", "raster_forward.cu", "raster_forward_static.cu", "raster_backward.cu", "pose_tonemap.cu",
+           "peer_reduce.cu"]
 LIB = os.path.join(PKG_DIR, "libadop_raster.so")
 
 # -fmad=false: the arithmetic header promises the same bits on host and device
@@ -39,11 +40,17 @@ def build_library(force=False, verbose=False):
     objdir = os.path.join(PKG_DIR, "build")
     os.makedirs(objdir, exist_ok=True)
     procs = []
-    for src in SOURCES:  # one nvcc per translation unit, side by side
+    objs = []
+    inc = os.path.join(ROOT, "include", "adop")
+    shared = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+    shared += [os.path.join(inc, f) for f in os.listdir(inc) if f.endswith(".h")]
+    for src in SOURCES:  # one nvcc per translation unit, side by side; objects newer than their sources are kept
         obj = os.path.join(objdir, src.replace(".cu", ".o"))
+        if not force and _newer(obj, [os.path.join(CSRC, src)] + shared):
+            objs.append(obj)
+            continue
         cmd = [nvcc] + flags + ["-I", os.path.join(ROOT, "include"), "-c", "-o", obj, os.path.join(CSRC, src)]
         procs.append((cmd, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
-    objs = []
     for cmd, obj, p in procs:
         out, _ = p.communicate()
         if verbose or p.returncode != 0:

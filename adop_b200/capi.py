@@ -74,6 +74,25 @@ class AdopTonemapGrads(C.Structure):
                 ("accumulate", C.c_int32)]
 
 
+class AdopPeerHandle(C.Structure):
+    _fields_ = [("bytes", C.c_ubyte * 64)]
+
+
+class AdopPeerLayout(C.Structure):
+    _fields_ = [("channels", C.c_int32), ("num_texels", C.c_int32), ("num_points", C.c_int32), ("num_images", C.c_int32),
+                ("num_cameras", C.c_int32), ("intrinsics_cols", C.c_int32), ("env_h", C.c_int32), ("env_w", C.c_int32),
+                ("background", C.c_int32), ("reserved", C.c_int32),
+                ("off_texture", C.c_size_t), ("off_points", C.c_size_t), ("off_pose", C.c_size_t),
+                ("off_count_pose", C.c_size_t), ("off_intrinsics", C.c_size_t), ("off_count_intrinsics", C.c_size_t),
+                ("off_background", C.c_size_t), ("off_env_map", C.c_size_t), ("total_bytes", C.c_size_t)]
+
+
+class AdopPeerReduceOut(C.Structure):
+    _fields_ = [("grad_texture_shard", C.c_void_p), ("grad_points_shard", C.c_void_p), ("grad_pose", C.c_void_p),
+                ("count_pose", C.c_void_p), ("grad_intrinsics", C.c_void_p), ("count_intrinsics", C.c_void_p),
+                ("grad_background", C.c_void_p), ("grad_env_map", C.c_void_p), ("normalize", C.c_int32)]
+
+
 class AdopKernelTime(C.Structure):
     _fields_ = [("name", C.c_char * 48), ("launches", C.c_int32), ("total_ms", C.c_float)]
 
@@ -85,6 +104,8 @@ EXPORTED_SYMBOLS = [
     "adop_tonemap_forward", "adop_tonemap_backward", "adop_profile_enable", "adop_profile_collect",
     "adop_raster_static_scratch_bytes", "adop_raster_forward_static", "adop_raster_visible_list_ints",
     "adop_texture_interleave", "adop_texture_deinterleave",
+    "adop_peer_alloc", "adop_peer_free", "adop_peer_open", "adop_peer_close", "adop_peer_layout_fill",
+    "adop_peer_shard_range", "adop_peer_reduce_gradients",
 ]
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
@@ -132,6 +153,18 @@ def load_library():
     lib.adop_tonemap_forward.argtypes = [C.POINTER(AdopTonemapParams), C.c_void_p, C.c_void_p, C.c_void_p]
     lib.adop_tonemap_backward.argtypes = [C.POINTER(AdopTonemapParams), C.c_void_p, C.c_void_p,
                                           C.POINTER(AdopTonemapGrads), C.c_void_p]
+    lib.adop_peer_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p), C.POINTER(AdopPeerHandle)]
+    lib.adop_peer_free.argtypes = [C.c_void_p]
+    lib.adop_peer_open.argtypes = [C.POINTER(AdopPeerHandle), C.POINTER(C.c_void_p)]
+    lib.adop_peer_close.argtypes = [C.c_void_p]
+    lib.adop_peer_layout_fill.argtypes = [C.POINTER(AdopPeerLayout)]
+    lib.adop_peer_shard_range.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
+    lib.adop_peer_shard_range.restype = None
+    lib.adop_peer_reduce_gradients.argtypes = [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.POINTER(AdopPeerLayout),
+                                               C.POINTER(AdopPeerReduceOut), C.c_void_p]
+    for name in ("adop_peer_alloc", "adop_peer_free", "adop_peer_open", "adop_peer_close", "adop_peer_layout_fill",
+                 "adop_peer_reduce_gradients"):
+        getattr(lib, name).restype = C.c_int
     lib.adop_profile_enable.argtypes = [C.c_int32]
     lib.adop_profile_enable.restype = C.c_int
     lib.adop_profile_collect.argtypes = [C.POINTER(AdopKernelTime), C.c_int32]

@@ -652,7 +652,9 @@ extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view
             ADOP_CUDA_TRY(cudaMemsetAsync(io->grad_env_map, 0, sizeof(float) * (size_t)C * s->env_h * s->env_w, st));
     }
 
-    if (io->grad_texture && io->grad_texture_interleaved)
+    // descriptor gradients stay in the [T,C] buffer when there is no [C,T] tensor to move them into
+    const bool interleaved_only = !io->grad_texture && io->grad_texture_interleaved;
+    if (io->grad_texture_interleaved && (io->grad_texture || !io->accumulate))
         ADOP_CUDA_TRY(cudaMemsetAsync(io->grad_texture_interleaved, 0, sizeof(float) * (size_t)C * T, st));
     LayerTable base;
     fill_layer_dims(views[0].w, views[0].h, L, &base);
@@ -684,10 +686,11 @@ extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view
         BackwardTargets bt;
         bt.texture = s->texture;
         bt.texture_interleaved = s->texture_interleaved;
-        bt.grad_texture_interleaved = io->grad_texture ? io->grad_texture_interleaved : nullptr;
+        bt.grad_texture_interleaved = io->grad_texture_interleaved;
         bt.num_texels = T;
         bt.background = s->background;
-        bt.grad_texture = io->grad_texture;
+        // the kernels take a non-null grad_texture as "descriptor gradients wanted" and write the [T,C] buffer if there is one
+        bt.grad_texture = interleaved_only ? io->grad_texture_interleaved : io->grad_texture;
         bt.grad_points = reinterpret_cast<float4*>(io->grad_points);
         bt.grad_pose = io->grad_pose ? io->grad_pose + (size_t)views[b].image_index * 6 : nullptr;
         bt.count_pose = io->grad_pose ? io->count_pose + views[b].image_index : nullptr;

@@ -72,3 +72,190 @@ def points_shard_is_aligned(num_points, world):
     """True when every rank's share of the flattened [N,4] tensor starts on a point boundary."""
     per = (num_points * 4 + world - 1) // world
     return per % 4 == 0
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# The same exchange as one kernel over peer memory (adop_peer_reduce_gradients): every rank keeps its gradient outputs in
+# one device block that the other ranks map through a CUDA IPC handle; after a stream-ordered barrier each rank reads
+# its share of every block over NVLink and writes final gradients (summed, normalised, descriptor gradients in [C,.]).
+# ----------------------------------------------------------------------------------------------------------------------
+class _DeviceSpan:
+    """A span of device memory for torch.as_tensor (CUDA array interface)."""
+
+    def __init__(self, ptr, shape, typestr, owner):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 2}
+        self._owner = owner
+
+
+def peer_layout(channels, num_texels, num_points=0, num_images=0, num_cameras=0, intrinsics_cols=0, env_hw=(0, 0),
+                background=True):
+    """adop_peer_layout for these tensor sizes (0 = tensor not exchanged); the same call on every rank."""
+    from . import capi
+    import ctypes as C
+    lay = capi.AdopPeerLayout()
+    lay.channels, lay.num_texels, lay.num_points = channels, num_texels, num_points
+    lay.num_images, lay.num_cameras, lay.intrinsics_cols = num_images, num_cameras, intrinsics_cols
+    lay.env_h, lay.env_w = env_hw
+    lay.background = 1 if background else 0
+    capi.check(capi.load_library().adop_peer_layout_fill(C.byref(lay)), "adop_peer_layout_fill")
+    return lay
+
+
+def peer_shard_range(count, rank, world):
+    """[lo, hi) of `count` texels or points that `rank` owns in the peer exchange (whole texels / points per rank)."""
+    per = (count + world - 1) // world
+    return min(count, rank * per), min(count, (rank + 1) * per)
+
+
+class PeerGradientExchange:
+    """Gradient block of this rank + the mapped blocks of the other ranks of `group` (all on one node).
+
+        ex = PeerGradientExchange(layout, device, group)
+        grads = ex.backward_outputs()            # pass as `out=` to PointRasterizer.backward(..., normalize=False)
+        ...backward...
+        result = ex.reduce()                      # dict of final gradients (owned shards + small tensors)
+
+    The barrier on either side of the kernel is a one-element all-reduce of the group's backend, in stream order."""
+
+    def __init__(self, layout, device, group=None):
+        from . import capi
+        import ctypes as C
+        self.capi, self.C = capi, C
+        self.lib = capi.load_library()
+        self.layout, self.device, self.group = layout, torch.device(device), group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("the peer exchange covers the GPUs of one node (at most 8 ranks)")
+        self._own = C.c_void_p()
+        self._opened = []
+        handle = capi.AdopPeerHandle()
+        # Every rank runs the same collectives whether or not its own CUDA calls succeed, so a failure on one rank
+        # (no peer access between two GPUs, IPC not permitted) ends in an exception on all of them, not in a hang.
+        problem = None
+        with torch.cuda.device(self.device):
+            try:
+                capi.check(self.lib.adop_peer_alloc(layout.total_bytes, C.byref(self._own), C.byref(handle)), "adop_peer_alloc")
+            except capi.AdopError as e:
+                problem = e
+                self._own = C.c_void_p()
+            mine = torch.tensor(list(bytes(handle.bytes)), dtype=torch.uint8, device=self.device)
+            everyone = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(everyone, mine, group=group)
+            self.blocks = (C.c_void_p * self.world)()
+            for r in range(self.world):
+                if problem is not None:
+                    break
+                if r == self.rank:
+                    self.blocks[r] = self._own.value
+                    continue
+                h = capi.AdopPeerHandle()
+                C.memmove(h.bytes, bytes(everyone[r].cpu().tolist()), 64)
+                ptr = C.c_void_p()
+                try:
+                    capi.check(self.lib.adop_peer_open(C.byref(h), C.byref(ptr)), "adop_peer_open")
+                except capi.AdopError as e:
+                    problem = e
+                    break
+                self._opened.append(ptr)
+                self.blocks[r] = ptr.value
+            self._flag = torch.zeros(1, device=self.device)
+            ok = torch.tensor([0.0 if problem is not None else 1.0], device=self.device)
+            # also: nobody may free its block before every rank has mapped it
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if float(ok.item()) == 0.0:
+                for ptr in self._opened:
+                    self.lib.adop_peer_close(ptr)
+                self._opened = []
+                dist.all_reduce(self._flag, group=group)
+                torch.cuda.synchronize(self.device)
+                if self._own.value:
+                    self.lib.adop_peer_free(self._own)
+                self._own = None
+                raise capi.AdopError(f"peer-memory exchange unavailable: {problem if problem is not None else 'another rank failed'}")
+            self._outputs = self._make_outputs()
+            self._results = self._make_results()
+
+    def _span(self, offset, shape, typestr, dtype):
+        n = 1
+        for d in shape:
+            n *= d
+        if n == 0:
+            return None
+        t = torch.as_tensor(_DeviceSpan(self._own.value + offset, shape, typestr, self), device=self.device)
+        assert t.dtype == dtype and t.data_ptr() == self._own.value + offset
+        return t
+
+    def _make_outputs(self):
+        lay = self.layout
+        f32, f64 = torch.float32, torch.float64
+        o = {"texture": None}
+        o["texture_interleaved"] = self._span(lay.off_texture, (lay.num_texels, lay.channels), "<f4", f32)
+        o["points"] = self._span(lay.off_points, (lay.num_points, 4), "<f4", f32)
+        o["pose"] = self._span(lay.off_pose, (lay.num_images, 6), "<f8", f64)
+        o["count_pose"] = self._span(lay.off_count_pose, (lay.num_images,), "<f4", f32)
+        o["intrinsics"] = self._span(lay.off_intrinsics, (lay.num_cameras, lay.intrinsics_cols), "<f4", f32)
+        o["count_intrinsics"] = self._span(lay.off_count_intrinsics, (lay.num_cameras,), "<f4", f32)
+        o["background"] = self._span(lay.off_background, (lay.channels if lay.background else 0,), "<f4", f32)
+        o["env_map"] = self._span(lay.off_env_map, (lay.channels, lay.env_h, lay.env_w), "<f4", f32)
+        return o
+
+    def _make_results(self):
+        lay, dev = self.layout, self.device
+        t_lo, t_hi = peer_shard_range(lay.num_texels, self.rank, self.world)
+        p_lo, p_hi = peer_shard_range(lay.num_points, self.rank, self.world)
+        r = {"texel_range": (t_lo, t_hi), "point_range": (p_lo, p_hi)}
+        r["texture_shard"] = torch.empty((lay.channels, t_hi - t_lo), device=dev) if t_hi > t_lo else None
+        r["points_shard"] = torch.empty((p_hi - p_lo, 4), device=dev) if p_hi > p_lo else None
+        has_pose, has_intr = lay.num_images > 0, lay.num_cameras > 0
+        r["pose"] = torch.empty((lay.num_images, 6), dtype=torch.float64, device=dev) if has_pose else None
+        r["count_pose"] = torch.empty((lay.num_images,), device=dev) if has_pose else None
+        r["intrinsics"] = torch.empty((lay.num_cameras, lay.intrinsics_cols), device=dev) if has_intr else None
+        r["count_intrinsics"] = torch.empty((lay.num_cameras,), device=dev) if has_intr else None
+        r["background"] = torch.empty((lay.channels,), device=dev) if lay.background else None
+        r["env_map"] = torch.empty((lay.channels, lay.env_h, lay.env_w), device=dev) if lay.env_h * lay.env_w > 0 else None
+        return r
+
+    def backward_outputs(self):
+        """The `out=` dict for PointRasterizer.backward: tensors inside this rank's block (texture stays [T,C])."""
+        return self._outputs
+
+    def reduce(self, normalize=True):
+        C, capi = self.C, self.capi
+        res = self._results
+        o = capi.AdopPeerReduceOut()
+
+        def p(name):
+            t = res.get(name)
+            return t.data_ptr() if t is not None else None
+
+        o.grad_texture_shard, o.grad_points_shard = p("texture_shard"), p("points_shard")
+        o.grad_pose, o.count_pose = p("pose"), p("count_pose")
+        o.grad_intrinsics, o.count_intrinsics = p("intrinsics"), p("count_intrinsics")
+        o.grad_background, o.grad_env_map = p("background"), p("env_map")
+        o.normalize = 1 if normalize else 0
+        with torch.cuda.device(self.device):
+            # every rank's backward pass is complete once this collective has run on every rank's stream ...
+            dist.all_reduce(self._flag, group=self.group)
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            capi.check(self.lib.adop_peer_reduce_gradients(self.blocks, self.world, self.rank, C.byref(self.layout),
+                                                           C.byref(o), C.c_void_p(stream)), "adop_peer_reduce_gradients")
+            # ... and nobody overwrites its block (the next backward pass) before every rank has read it
+            dist.all_reduce(self._flag, group=self.group)
+        return res
+
+    def close(self):
+        if self._own is None:
+            return
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            dist.all_reduce(self._flag, group=self.group)
+            torch.cuda.synchronize(self.device)
+            for ptr in self._opened:
+                self.lib.adop_peer_close(ptr)
+            self._opened = []
+            self._outputs = self._results = None
+            # the other ranks have closed their mappings of this block only after the next collective
+            dist.all_reduce(self._flag, group=self.group)
+            torch.cuda.synchronize(self.device)
+            self.lib.adop_peer_free(self._own)
+            self._own = None

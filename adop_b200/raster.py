@@ -228,7 +228,12 @@ class PointRasterizer:
             io.workspace = ws.data_ptr()
             io.workspace_bytes = ws.numel()
             io.visible_list = fwd.visible.data_ptr() if fwd.visible is not None else None
-            if self.interleave_descriptors:
+            if out.get("texture_interleaved") is not None:
+                # the caller keeps the descriptor gradients in [T,C] layout (the block the GPUs exchange, dist.py)
+                if out.get("texture") is not None:
+                    raise ValueError("give either texture [C,T] or texture_interleaved [T,C] as the output, not both")
+                io.grad_texture_interleaved = out["texture_interleaved"].data_ptr()
+            elif self.interleave_descriptors:
                 if self._gtex_i is None or self._gtex_i.shape != self._tex_i.shape:
                     self._gtex_i = torch.empty_like(self._tex_i)
                 io.grad_texture_interleaved = self._gtex_i.data_ptr()

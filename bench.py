@@ -45,6 +45,8 @@ def parse_args():
     ap.add_argument("--points", type=int, default=10_000_000)
     ap.add_argument("--views", type=int, default=16, help="views per GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: gradient exchange by the peer-memory kernel (default) or by NCCL reduce-scatter / all-reduce")
     return ap.parse_args()
 
 
@@ -195,11 +197,25 @@ def main():
     fwd = ras.forward(scene, views, params, L)
     bwd = ras.backward(scene, params, fwd, grads_dev, want_env=True, normalize=normalize_local)
     torch.cuda.synchronize()
+    # N > 1: all gradient outputs live in one block per rank that the other ranks map; one kernel reads every block
+    # over NVLink and writes the owned, summed, normalised gradients. NCCL reduce-scatter / all-reduce is the fallback.
+    peer = None
+    if world > 1 and args.exchange == "peer":
+        try:
+            layout = adist.peer_layout(C, bwd["texture"].shape[1], N, num_images=bwd["pose"].shape[0],
+                                       num_cameras=bwd["intrinsics"].shape[0], intrinsics_cols=bwd["intrinsics"].shape[1],
+                                       env_hw=tuple(arrays["env_map"].shape[1:]))
+            peer = adist.PeerGradientExchange(layout, dev)
+            bwd = peer.backward_outputs()
+        except capi.AdopError as e:
+            if rank == 0:
+                print(f"bench: {e}; using the NCCL exchange", file=sys.stderr, flush=True)
+    final = {}  # the step's final small gradients (what the end-to-end loop reads back)
 
-    def step():
-        ras.forward(scene, views, params, L, out=fwd)
-        ras.backward(scene, params, fwd, grads_dev, want_env=True, normalize=normalize_local, out=bwd)
-        if world > 1:
+    def exchange():
+        if peer is not None:
+            final.update(peer.reduce())
+        elif world > 1:
             ex = adist.exchange_gradients(bwd)
             # normalise the owned shard of the point gradients (sum / count), PointRenderer.cu:1620-1627
             if adist.points_shard_is_aligned(N, world):
@@ -207,10 +223,19 @@ def main():
                 ras.normalize_gradients({"points": shard.view(-1, 4), "pose": None, "intrinsics": None})
             ras.normalize_gradients({"points": None, "pose": ex["pose"], "count_pose": ex["count_pose"],
                                      "intrinsics": ex["intrinsics"], "count_intrinsics": ex["count_intrinsics"]})
+            final.update(ex)
+        else:
+            final.update(bwd)
+
+    def step():
+        ras.forward(scene, views, params, L, out=fwd)
+        ras.backward(scene, params, fwd, grads_dev, want_env=True, normalize=normalize_local, out=bwd)
+        exchange()
 
     # per step: interleave, depth fills, camera records (forward and backward), one depth prepass per group of four views,
-    # (blend, resolve) and (prepare, gather, chain, all-points fallback) per view, de-interleave, three normalisations
-    kernels_per_step = 1 + L + 2 + (V + 3) // 4 + 2 * V + 4 * V + 1 + 3
+    # (blend, resolve) and (prepare, gather, chain, all-points fallback) per view, then either de-interleave + three
+    # normalisations or the one peer-reduce kernel (NCCL's own kernels are not counted)
+    kernels_per_step = 1 + L + 2 + (V + 3) // 4 + 2 * V + 4 * V + (1 if peer is not None else 1 + 3)
 
     def barrier():
         if world > 1:
@@ -272,10 +297,9 @@ def main():
             main_stream.wait_event(copied[slot])
             ras.backward(scene, params, fwd, staged[slot], want_env=True, normalize=normalize_local, out=bwd)
             consumed[slot].record(main_stream)
-            if world > 1:
-                adist.exchange_gradients(bwd)
+            exchange()
             for kk, hdst in small_host.items():
-                hdst.copy_(bwd[kk], non_blocking=True)
+                hdst.copy_(final[kk], non_blocking=True)
         main_stream.synchronize()
 
     run_e2e(3)
@@ -294,6 +318,8 @@ def main():
     for _ in range(max(1, min(args.steps, 5))):
         ras.forward(scene, views, params, L, out=fwd)
         ras.backward(scene, params, fwd, grads_dev, want_env=True, normalize=normalize_local, out=bwd)
+        if peer is not None:
+            peer.reduce()
     torch.cuda.synchronize()
     ktimes = capi.profile_collect()
     capi.profile_enable(False)
@@ -358,16 +384,21 @@ def main():
                 "data": "synthetic",
                 "config": {"workload": WORKLOAD, "points": N, "views_per_gpu": V, "image": [w, h], "layers": L, "channels": C,
                            "l2": "inputs exceed L2: 160 MB of points and ~100 MB of image state per view stream per pass",
-                           "parallelism": f"view-sharded x{world}, gradients reduce-scattered" if world > 1 else "single GPU",
+                           "parallelism": ("single GPU" if world == 1 else
+                                           f"view-sharded x{world}, gradients exchanged by one peer-memory kernel over NVLink "
+                                           "(reduce-scatter + all-reduce + normalise)" if peer is not None else
+                                           f"view-sharded x{world}, gradients reduce-scattered by NCCL"),
                            "point_order": "Morton-sorted once (untimed), as the reference's scene preprocessing does"},
                 "fwd_ms_per_view": ktimes_ms(ktimes, ("k_texture_interleave", "k_fill", "k_build_cams", "k_depth_prepass", "k_blend",
                                                       "k_resolve"), V, args),
                 "bwd_ms_per_view": ktimes_ms(ktimes, ("k_prepare_backward", "k_splat_gather", "k_splat_chain", "k_splat_backward_all",
-                                                      "k_texture_deinterleave", "k_normalize"), V, args),
+                                                      "k_texture_deinterleave", "k_normalize", "k_peer_reduce"), V, args),
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
                 "gpu_launches": kernels_per_step * args.steps,
                 "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline}
         print(json.dumps(line), flush=True)
+    if peer is not None:
+        peer.close()
     if world > 1:
         dist.destroy_process_group()
 

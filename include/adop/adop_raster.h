@@ -157,7 +157,9 @@ typedef struct adop_backward_io
      * NULL = the backward pass walks all points again, as the reference does. */
     int32_t* visible_list;
     /* optional [T,C] scratch: descriptor gradients are then summed there with one vector atomic per splat and moved
-     * into grad_texture [C,T] at the end of the call. Contents on entry are ignored. */
+     * into grad_texture [C,T] at the end of the call. Contents on entry are ignored.
+     * With grad_texture == NULL the descriptor gradients STAY here, in [T,C] layout (zeroed first unless accumulate):
+     * the form adop_peer_reduce_gradients reads from every GPU. */
     float* grad_texture_interleaved;
 } adop_backward_io;
 
@@ -219,6 +221,70 @@ adop_status adop_raster_normalize_gradients(float* grad_points, int32_t num_poin
                                             const float* count_pose, int32_t num_images, float* grad_intrinsics,
                                             const float* count_intrinsics, int32_t num_cameras,
                                             int32_t intrinsics_cols, void* stream);
+
+/* ---- Gradient exchange between the GPUs of one node, over peer memory -------------------------------------------
+ * The reference renders on one GPU and has no counterpart to this section. Views are independent given the scene, so
+ * every GPU renders its own views of the replicated scene and the un-normalised gradient sums are added up afterwards.
+ * Each rank keeps ALL its gradient outputs of adop_raster_backward in one device block laid out by adop_peer_layout
+ * (the same on every rank), exported to the other processes as a CUDA IPC handle. adop_peer_reduce_gradients is one
+ * kernel that reads the blocks of all ranks with plain peer loads and, in that one pass,
+ *   - sums the descriptor gradients of the texels this rank owns, and writes them in the reference's [C,.] layout,
+ *   - sums the point gradients of the points this rank owns and divides by the summed counts (PointRenderer.cu:1620-1627),
+ *   - sums pose, intrinsics, background and environment-map gradients in full (every rank gets all of them) and
+ *     divides pose and intrinsics by their summed counts (PointRenderer.cu:1609-1637).
+ * It is reduce-scatter + all-reduce + de-interleave + NormalizeGradient in one pass over the data; sums run over the
+ * ranks in rank order, so every rank computes the same bits. The kernel does not wait for other GPUs: the caller
+ * orders it after every rank's backward pass and before anyone's next write to its block (a stream-ordered
+ * collective of the caller's communication library on either side, e.g. a one-element all-reduce). */
+typedef struct adop_peer_handle
+{
+    unsigned char bytes[64]; /* a cudaIpcMemHandle_t */
+} adop_peer_handle;
+
+/* cudaMalloc of `bytes` (zero-filled) on the current device, plus its handle for the other processes. */
+adop_status adop_peer_alloc(size_t bytes, void** ptr, adop_peer_handle* handle);
+adop_status adop_peer_free(void* ptr);
+/* Map another process's block into this process (peer access between the two GPUs is switched on as needed). */
+adop_status adop_peer_open(const adop_peer_handle* handle, void** ptr);
+adop_status adop_peer_close(void* ptr);
+
+/* Byte offsets of the gradient tensors inside a rank's block; a count of 0 leaves that tensor out. */
+typedef struct adop_peer_layout
+{
+    int32_t channels;        /* C */
+    int32_t num_texels;      /* T: descriptor gradients [T,C] f32 (adop_backward_io.grad_texture_interleaved) */
+    int32_t num_points;      /* N: point gradients [N,4] f32, count in .w */
+    int32_t num_images;      /* pose gradients [images,6] f64 + counts [images] f32 */
+    int32_t num_cameras;     /* intrinsics gradients [cameras, intrinsics_cols] f32 + counts [cameras] f32 */
+    int32_t intrinsics_cols;
+    int32_t env_h, env_w;    /* environment-map gradient [C,env_h,env_w] f32 */
+    int32_t background;      /* 1: background gradient [C] f32 */
+    int32_t reserved;
+    size_t off_texture, off_points, off_pose, off_count_pose, off_intrinsics, off_count_intrinsics, off_background,
+        off_env_map;
+    size_t total_bytes;
+} adop_peer_layout;
+/* Fills the offsets (256-byte aligned) and total_bytes from the counts. */
+adop_status adop_peer_layout_fill(adop_peer_layout* layout);
+/* Rank `rank` of `world` owns elements [*lo, *hi) of `count`: equal shares of ceil(count / world), the last ones shorter. */
+void adop_peer_shard_range(int32_t count, int32_t world, int32_t rank, int32_t* lo, int32_t* hi);
+
+typedef struct adop_peer_reduce_out
+{
+    float* grad_texture_shard;   /* [C, t_hi - t_lo] f32: the owned texels, channel planes as in grad_texture */
+    float* grad_points_shard;    /* [n_hi - n_lo, 4] f32: the owned points, xyz divided by the count, w = 0 */
+    double* grad_pose;           /* [images,6], divided by the counts */
+    float* count_pose;           /* [images], summed */
+    float* grad_intrinsics;      /* [cameras, cols], divided by the counts */
+    float* count_intrinsics;     /* [cameras], summed */
+    float* grad_background;      /* [C] */
+    float* grad_env_map;         /* [C,env_h,env_w] */
+    int32_t normalize;           /* 0: leave sums (points keep their count in w) */
+} adop_peer_reduce_out;
+/* blocks[r] = rank r's block as mapped in THIS process (own block: the pointer adop_peer_alloc gave), 1 <= world <= 8.
+ * Outputs whose tensor the layout leaves out, or that are NULL, are skipped. Outputs must not lie inside a block. */
+adop_status adop_peer_reduce_gradients(const void* const* blocks, int32_t world, int32_t rank,
+                                       const adop_peer_layout* layout, const adop_peer_reduce_out* out, void* stream);
 
 /* ApplyTangentToPose, src/lib/rendering/PointRenderer.cu:1646-1665: pose <- exp(tangent) * pose, tangent <- 0.
  * tangent [n,6] f64, pose [n,8] f64. */

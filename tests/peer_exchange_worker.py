@@ -1,0 +1,95 @@
+"""One rank of the two-GPU exchange test (started by test_peer_exchange_gpu.py through torch.distributed.run).
+
+Renders its share of the views of a small scene, exchanges the gradients over peer memory, and compares the result
+with (a) a single-GPU run over all views on this rank's GPU and (b) the NCCL exchange of the same gradients."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from adop_b200 import dist as adist  # noqa: E402
+from adop_b200 import synth  # noqa: E402
+from adop_b200.raster import PointRasterizer, Scene  # noqa: E402
+
+
+def close(a, b, what, rtol=1e-4, atol=1e-5):
+    scale = float(b.abs().max()) if b.numel() else 1.0
+    if not torch.allclose(a, b, rtol=rtol, atol=atol * max(scale, 1.0)):
+        raise AssertionError(f"{what}: max abs diff {float((a - b).abs().max())} at scale {scale}")
+
+
+def main():
+    out_dir = sys.argv[1]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    n_views = 2 * world
+    cfg = synth.make_config("c2", n_points=50000, n_views=n_views, size=(192, 108))
+    L, params = cfg["num_layers"], cfg["params"]
+    scene = Scene(**{k: (torch.from_numpy(v).to(dev) if v is not None else None) for k, v in cfg["arrays"].items()})
+    ras = PointRasterizer(dev)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(7)  # the same upstream gradients on every rank
+    fwd_all = ras.forward(scene, cfg["views"], params, L)
+    grads_all = [torch.randn(c.shape, device=dev, generator=gen) for c in fwd_all.colors]
+    ref = ras.backward(scene, params, fwd_all, grads_all, want_env=True, normalize=True)
+
+    mine = adist.shard_views(list(range(n_views)), rank, world)
+    views = [cfg["views"][i] for i in mine]
+    grads = [g[mine[0]:mine[-1] + 1].contiguous() for g in grads_all]
+    C_, T = scene.texture.shape
+    lay = adist.peer_layout(C_, T, scene.position.shape[0], num_images=ref["pose"].shape[0],
+                            num_cameras=ref["intrinsics"].shape[0], intrinsics_cols=ref["intrinsics"].shape[1],
+                            env_hw=tuple(scene.env_map.shape[1:]))
+    ex = adist.PeerGradientExchange(lay, dev)
+    for step in range(2):  # the second pass re-uses the blocks: covers the barrier after the kernel
+        fwd = ras.forward(scene, views, params, L)
+        ras.backward(scene, params, fwd, grads, want_env=True, normalize=False, out=ex.backward_outputs())
+        res = ex.reduce()
+        torch.cuda.synchronize()
+        t_lo, t_hi = res["texel_range"]
+        p_lo, p_hi = res["point_range"]
+        close(res["texture_shard"], ref["texture"][:, t_lo:t_hi], f"texture shard (pass {step})")
+        close(res["points_shard"], ref["points"][p_lo:p_hi], f"points shard (pass {step})")
+        close(res["pose"], ref["pose"], "pose")
+        close(res["intrinsics"], ref["intrinsics"], "intrinsics")
+        close(res["count_pose"], ref["count_pose"], "pose counts", 0, 0)
+        close(res["background"], ref["background"], "background")
+        close(res["env_map"], ref["env_map"], "environment map")
+    # every rank computed the same bits for the tensors that all ranks get
+    check = res["pose"].clone()
+    dist.broadcast(check, src=0)
+    assert torch.equal(check, res["pose"]), "pose gradients differ between ranks"
+
+    # the NCCL exchange of the same per-rank gradients
+    fwd = ras.forward(scene, views, params, L)
+    plain = ras.backward(scene, params, fwd, grads, want_env=True, normalize=False)
+    nccl = adist.exchange_gradients(plain)
+    tex_all = torch.empty_like(ref["texture"])
+    tex_all[:, t_lo:t_hi] = res["texture_shard"]
+    flat_lo, flat_hi = adist.shard_range(C_ * T, rank, world)
+    # the NCCL path shards the flattened [C,T] tensor; compare on the overlap of the two ownership rules
+    nccl_flat = torch.zeros(C_ * T, device=dev)
+    nccl_flat[flat_lo:flat_hi] = nccl["texture_shard"]
+    nccl_ct = nccl_flat.view(C_, T)
+    own = torch.zeros(C_ * T, dtype=torch.bool, device=dev)
+    own[flat_lo:flat_hi] = True
+    both = own.view(C_, T)[:, t_lo:t_hi]
+    close(res["texture_shard"][both], nccl_ct[:, t_lo:t_hi][both], "texture shard against the NCCL exchange")
+    close(nccl["pose"] / nccl["count_pose"].clamp(min=1)[:, None].double(), ref["pose"], "NCCL pose")
+    ex.close()
+    dist.barrier()
+    with open(os.path.join(out_dir, f"ok_{rank}"), "w") as f:
+        f.write("ok\n")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -75,3 +75,32 @@ def test_shard_helpers():
     assert sum(len(adist.shard_views(list(range(10)), r, 4)) for r in range(4)) == 10
     assert adist.shard_range(10, 3, 4) == (9, 10)
     assert adist.shard_range(8, 1, 4) == (2, 4)
+
+
+def test_peer_layout_and_shard_ranges():
+    """Host-side pieces of the peer-memory exchange: block layout and ownership ranges (no GPU needed)."""
+    import ctypes as C
+    from adop_b200 import capi
+    lib = capi.load_library()
+    lay = adist.peer_layout(4, 1000, 333, num_images=7, num_cameras=2, intrinsics_cols=13, env_hw=(8, 16))
+    offs = [lay.off_texture, lay.off_points, lay.off_pose, lay.off_count_pose, lay.off_intrinsics,
+            lay.off_count_intrinsics, lay.off_background, lay.off_env_map, lay.total_bytes]
+    sizes = [1000 * 4 * 4, 333 * 16, 7 * 6 * 8, 7 * 4, 2 * 13 * 4, 2 * 4, 4 * 4, 4 * 8 * 16 * 4]
+    assert all(o % 256 == 0 for o in offs)
+    for a, b, size in zip(offs[:-1], offs[1:], sizes):
+        assert b - a >= size and b - a < size + 256
+    empty = adist.peer_layout(3, 10, 0, background=False)
+    assert empty.off_points == empty.off_pose == empty.off_env_map and empty.total_bytes == 256
+    for count in (0, 1, 7, 8, 1000, 10_000_019):
+        for world in (1, 2, 3, 8):
+            covered = 0
+            for rank in range(world):
+                lo, hi = C.c_int32(), C.c_int32()
+                lib.adop_peer_shard_range(count, world, rank, C.byref(lo), C.byref(hi))
+                assert (lo.value, hi.value) == adist.peer_shard_range(count, rank, world)
+                assert lo.value == covered and hi.value >= lo.value
+                covered = hi.value
+            assert covered == count
+    bad = capi.AdopPeerLayout()
+    bad.channels = 0
+    assert lib.adop_peer_layout_fill(C.byref(bad)) != capi.ADOP_OK
