@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(kBlock) k_peer_reduce(PeerBlocks pb, adop_peer
         }
     }
     // ---- the small tensors, element by element: every rank sums all of them ----
-    const long long n_small = (long long)w.n_pose + w.n_count_pose + w.n_intr + w.n_count_intr + w.n_bg + w.n_env;
+    const long long n_small = (long long)w.n_pose + w.n_count_pose + w.n_intr + w.n_count_intr + w.n_bg;
     for (long long item = first; item < n_small; item += stride)
     {
         long long e = item;
@@ -191,19 +191,47 @@ __global__ void __launch_bounds__(kBlock) k_peer_reduce(PeerBlocks pb, adop_peer
             continue;
         }
         e -= w.n_count_intr;
-        if (e < w.n_bg)
         {
             float a = 0.f;
             for (int r = 0; r < pb.world; ++r) a += peer_load(reinterpret_cast<const float*>(pb.base[r] + lay.off_background) + e);
             out.grad_background[e] = a;
-            continue;
         }
-        e -= w.n_bg;
+    }
+    // ---- the environment-map gradient, four floats at a time (every rank sums all of it) ----
+    const long long env4 = (reinterpret_cast<uintptr_t>(out.grad_env_map) & 15) == 0 ? w.n_env / 4 : 0;
+    for (long long item = first; item < env4; item += stride * U)
+    {
+        float4 v[U][MAXR];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
         {
-            float a = 0.f;
-            for (int r = 0; r < pb.world; ++r) a += peer_load(reinterpret_cast<const float*>(pb.base[r] + lay.off_env_map) + e);
-            out.grad_env_map[e] = a;
+            const long long it = item + u * stride;
+            if (it < env4)
+            {
+#pragma unroll
+                for (int r = 0; r < MAXR; ++r)
+                    if (r < pb.world) v[u][r] = peer_load4(reinterpret_cast<const float4*>(pb.base[r] + lay.off_env_map) + it);
+            }
         }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+        {
+            const long long it = item + u * stride;
+            if (it < env4)
+            {
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int r = 0; r < MAXR; ++r)
+                    if (r < pb.world) { a.x += v[u][r].x; a.y += v[u][r].y; a.z += v[u][r].z; a.w += v[u][r].w; }
+                reinterpret_cast<float4*>(out.grad_env_map)[it] = a;
+            }
+        }
+    }
+    for (long long e = env4 * 4 + first; e < w.n_env; e += stride)
+    {
+        float a = 0.f;
+        for (int r = 0; r < pb.world; ++r) a += peer_load(reinterpret_cast<const float*>(pb.base[r] + lay.off_env_map) + e);
+        out.grad_env_map[e] = a;
     }
 }
 
@@ -352,8 +380,9 @@ extern "C" adop_status adop_peer_reduce_gradients(const void* const* blocks, int
         break;
     // the largest of the three parts decides the grid (each thread strides through all three)
     long long largest = w.t_n > w.p_n ? w.t_n : w.p_n;
-    const long long n_small = (long long)w.n_pose + w.n_count_pose + w.n_intr + w.n_count_intr + w.n_bg + w.n_env;
+    const long long n_small = (long long)w.n_pose + w.n_count_pose + w.n_intr + w.n_count_intr + w.n_bg;
     if (n_small > largest) largest = n_small;
+    if (w.n_env / 4 > largest) largest = w.n_env / 4;
     const long long need = (largest + kBlock - 1) / kBlock;
     switch (C)
     {
