@@ -11,6 +11,7 @@ ROOT = os.path.dirname(PKG_DIR)
 CSRC = os.path.join(PKG_DIR, "csrc")
 SOURCES = ["capi_common.cu", "raster_forward.cu", "raster_forward_static.cu", "raster_backward.cu", "pose_tonemap.cu",
            "peer_reduce.cu"]
+CONTRACTION_ALLOWED = {"pose_tonemap.cu"}
 LIB = os.path.join(PKG_DIR, "libadop_raster.so")
 
 # -fmad=false: the arithmetic header promises the same bits on host and device
@@ -49,7 +50,10 @@ def build_library(force=False, verbose=False):
         if not force and _newer(obj, [os.path.join(CSRC, src)] + shared):
             objs.append(obj)
             continue
-        cmd = [nvcc] + flags + ["-I", os.path.join(ROOT, "include"), "-c", "-o", obj, os.path.join(CSRC, src)]
+        # the rasterizer's arithmetic promises host/device bit equality (no contraction); the photometric kernels and the
+        # pose update are checked within a tolerance and may fuse multiply-adds
+        use = [f for f in flags if f != "-fmad=false"] if src in CONTRACTION_ALLOWED else flags
+        cmd = [nvcc] + use + ["-I", os.path.join(ROOT, "include"), "-c", "-o", obj, os.path.join(CSRC, src)]
         procs.append((cmd, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     for cmd, obj, p in procs:
         out, _ = p.communicate()
