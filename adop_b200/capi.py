@@ -58,7 +58,7 @@ class AdopBackwardIO(C.Structure):
                 ("grad_intrinsics", C.c_void_p), ("count_intrinsics", C.c_void_p), ("grad_env_map", C.c_void_p),
                 ("accumulate", C.c_int32), ("normalize", C.c_int32),
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("visible_list", C.c_void_p),
-                ("grad_texture_interleaved", C.c_void_p)]
+                ("grad_texture_interleaved", C.c_void_p), ("grad_env_map_interleaved", C.c_void_p)]
 
 
 class AdopTonemapParams(C.Structure):

@@ -204,6 +204,16 @@ inline int resident_grid(Kernel kernel, long long work_items)
     return g < 1 ? 1 : (int)g;
 }
 
+// layer that holds pyramid pixel (= accumulator record) r of a view
+__device__ __forceinline__ int layer_of_record(const LayerTable& lt, unsigned r)
+{
+    int l = 0;
+#pragma unroll
+    for (int k = 1; k < kMaxLayers; ++k)
+        if (k < lt.L && r >= lt.rec_off[k]) l = k;
+    return l;
+}
+
 struct FetchedPoint { V3 p; V3 n; float r; bool has_normal; };
 
 // DevicePointCloud::GetPoint (NeuralPointCloudCuda.h:82-103): one 128-bit load of xyz + radius

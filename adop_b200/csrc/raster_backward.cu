@@ -26,67 +26,128 @@ namespace adop {
 //  * with the fused composite, scatters the environment-map gradient (bilinear, 4 taps).
 __host__ __device__ inline int backward_record_floats(int C) { return (2 * C + 3) & ~3; }
 
+// The environment-map gradient of an uncovered pixel (bilinear scatter, 4 taps): as in the forward resolve kernel the
+// uncovered pixels are scattered single-pixel holes, so each warp parks them and works them off 32 at a time.
+template <int C>
+__device__ __forceinline__ void scatter_environment_gradient(const LayerTable& lt, const ViewCam& cam, const KernelParams& kp, unsigned r,
+                                                             float* __restrict__ grad_env, int env_h, int env_w, bool interleaved)
+{
+    const int l = layer_of_record(lt, r);
+    const unsigned pix = r - lt.rec_off[l];
+    const int w = lt.w[l];
+    const size_t plane = (size_t)w * lt.h[l];
+    const int gy = pix / w, gx = pix - gy * w;
+    float gup[C];
+#pragma unroll
+    for (int c = 0; c < C; ++c) gup[c] = __ldg(lt.grad[l] + c * plane + pix);
+    Intr5 crop_l = scale_intr(cam.crop, __int_as_float((127 - l) << 23));
+    V2 uv = env_uv_for_pixel(gx, gy, cam.V, cam.K, cam.dist, crop_l);
+    BilinearTap tp = bilinear_taps(uv, env_w, env_h);
+    const float om = 1.0f - kp.mask_background_value;
+    const float w00 = (1.0f - tp.wx) * (1.0f - tp.wy), w01 = tp.wx * (1.0f - tp.wy);
+    const float w10 = (1.0f - tp.wx) * tp.wy, w11 = tp.wx * tp.wy;
+    if (interleaved && C % 4 == 0)
+    {
+        // [eh,ew,C] scratch: one vector atomic per tap and four channels instead of one per channel
+        float4* e = reinterpret_cast<float4*>(grad_env);
+        const size_t t00 = ((size_t)tp.y0 * env_w + tp.x0) * (C / 4), t01 = ((size_t)tp.y0 * env_w + tp.x1) * (C / 4);
+        const size_t t10 = ((size_t)tp.y1 * env_w + tp.x0) * (C / 4), t11 = ((size_t)tp.y1 * env_w + tp.x1) * (C / 4);
+#pragma unroll
+        for (int k = 0; k < C / 4; ++k)
+        {
+            const float a = om * gup[4 * k], b = om * gup[4 * k + 1], c2 = om * gup[4 * k + 2], d = om * gup[4 * k + 3];
+            atomicAdd(e + t00 + k, make_float4(a * w00, b * w00, c2 * w00, d * w00));
+            atomicAdd(e + t01 + k, make_float4(a * w01, b * w01, c2 * w01, d * w01));
+            atomicAdd(e + t10 + k, make_float4(a * w10, b * w10, c2 * w10, d * w10));
+            atomicAdd(e + t11 + k, make_float4(a * w11, b * w11, c2 * w11, d * w11));
+        }
+        return;
+    }
+#pragma unroll
+    for (int c = 0; c < C; ++c)
+    {
+        float* e = grad_env + (size_t)c * env_h * env_w;
+        float ge = om * gup[c];
+        atomicAdd(e + (size_t)tp.y0 * env_w + tp.x0, ge * w00);
+        atomicAdd(e + (size_t)tp.y0 * env_w + tp.x1, ge * w01);
+        atomicAdd(e + (size_t)tp.y1 * env_w + tp.x0, ge * w10);
+        atomicAdd(e + (size_t)tp.y1 * env_w + tp.x1, ge * w11);
+    }
+}
+
 template <int C>
 __global__ void __launch_bounds__(kBlock) k_prepare_backward(LayerTable lt, const ViewCam* __restrict__ camp, KernelParams kp,
                                                               const float* __restrict__ background, float* __restrict__ records,
                                                               float* __restrict__ grad_background,
-                                                              float* __restrict__ grad_env, int env_h, int env_w)
+                                                              float* __restrict__ grad_env, int env_h, int env_w, bool env_interleaved)
 {
     constexpr int RB = (2 * C + 3) & ~3;
     const ViewCam& cam = *camp;
     __shared__ float s_bg[C];
+    __shared__ unsigned s_parked[kBlock / 32][64];
+    unsigned* parked = s_parked[threadIdx.x >> 5];
+    const int lane = threadIdx.x & 31;
+    int n_parked = 0;  // the same in every lane of the warp
     if (threadIdx.x < C) s_bg[threadIdx.x] = 0.f;
     __syncthreads();
     const unsigned total = lt.rec_off[kMaxLayers];
+    const unsigned stride = gridDim.x * blockDim.x;
     float g[C], bgc[C];
 #pragma unroll
     for (int c = 0; c < C; ++c) { g[c] = 0.f; bgc[c] = __ldg(background + c); }
-    for (unsigned r = blockIdx.x * blockDim.x + threadIdx.x; r < total; r += gridDim.x * blockDim.x)
+    // warp-uniform trip count: the parking uses full-warp votes
+    for (unsigned base = blockIdx.x * blockDim.x; base < total; base += stride)
     {
-        int l = 0;
-#pragma unroll
-        for (int k = 1; k < kMaxLayers; ++k)
-            if (k < lt.L && r >= lt.rec_off[k]) l = k;
-        const unsigned pix = r - lt.rec_off[l];
-        const int w = lt.w[l], h = lt.h[l];
-        const size_t plane = (size_t)w * h;
-        const bool covered = __ldg(lt.weight[l] + pix) != 0.f;
-        float rec[RB];
-#pragma unroll
-        for (int c = 0; c < C; ++c)
+        const unsigned r = base + threadIdx.x;
+        bool hole = false;
+        if (r < total)
         {
-            rec[C + c] = __ldcs(lt.grad[l] + c * plane + pix);
-            rec[c] = covered ? __ldg(lt.color[l] + c * plane + pix) : bgc[c];
-        }
-#pragma unroll
-        for (int k = 2 * C; k < RB; ++k) rec[k] = 0.f;
-        float4* dst = reinterpret_cast<float4*>(records + (size_t)r * RB);
-#pragma unroll
-        for (int k = 0; k < RB / 4; ++k) dst[k] = make_float4(rec[4 * k], rec[4 * k + 1], rec[4 * k + 2], rec[4 * k + 3]);
-        if (covered) continue;
-#pragma unroll
-        for (int c = 0; c < C; ++c) g[c] += rec[C + c];
-        if (grad_env)
-        {
-            int gy = pix / w, gx = pix - gy * w;
-            Intr5 crop_l = scale_intr(cam.crop, __int_as_float((127 - l) << 23));
-            V2 uv = env_uv_for_pixel(gx, gy, cam.V, cam.K, cam.dist, crop_l);
-            BilinearTap tp = bilinear_taps(uv, env_w, env_h);
-            const float om = 1.0f - kp.mask_background_value;
-            const float w00 = (1.0f - tp.wx) * (1.0f - tp.wy), w01 = tp.wx * (1.0f - tp.wy);
-            const float w10 = (1.0f - tp.wx) * tp.wy, w11 = tp.wx * tp.wy;
+            const int l = layer_of_record(lt, r);
+            const unsigned pix = r - lt.rec_off[l];
+            const size_t plane = (size_t)lt.w[l] * lt.h[l];
+            // every load of the pixel is requested before the coverage is known
+            const float wgt = __ldg(lt.weight[l] + pix);
+            float rec[RB];
 #pragma unroll
             for (int c = 0; c < C; ++c)
             {
-                float* e = grad_env + (size_t)c * env_h * env_w;
-                float ge = om * rec[C + c];
-                atomicAdd(e + (size_t)tp.y0 * env_w + tp.x0, ge * w00);
-                atomicAdd(e + (size_t)tp.y0 * env_w + tp.x1, ge * w01);
-                atomicAdd(e + (size_t)tp.y1 * env_w + tp.x0, ge * w10);
-                atomicAdd(e + (size_t)tp.y1 * env_w + tp.x1, ge * w11);
+                rec[C + c] = __ldcs(lt.grad[l] + c * plane + pix);
+                rec[c] = __ldg(lt.color[l] + c * plane + pix);
+            }
+            const bool covered = wgt != 0.f;
+            if (!covered)
+            {
+                // the image before the environment map was added (PointRenderer.cu:1523)
+#pragma unroll
+                for (int c = 0; c < C; ++c) rec[c] = bgc[c];
+            }
+#pragma unroll
+            for (int k = 2 * C; k < RB; ++k) rec[k] = 0.f;
+            float4* dst = reinterpret_cast<float4*>(records + (size_t)r * RB);
+#pragma unroll
+            for (int k = 0; k < RB / 4; ++k) dst[k] = make_float4(rec[4 * k], rec[4 * k + 1], rec[4 * k + 2], rec[4 * k + 3]);
+            if (!covered)
+            {
+#pragma unroll
+                for (int c = 0; c < C; ++c) g[c] += rec[C + c];
+                hole = grad_env != nullptr;
             }
         }
+        const unsigned vote = __ballot_sync(0xffffffffu, hole);
+        if (vote)
+        {
+            if (hole) parked[n_parked + __popc(vote & ((1u << lane) - 1u))] = r;
+            n_parked += __popc(vote);
+            __syncwarp();
+            if (n_parked >= 32)
+            {
+                n_parked -= 32;
+                scatter_environment_gradient<C>(lt, cam, kp, parked[n_parked + lane], grad_env, env_h, env_w, env_interleaved);
+            }
+            __syncwarp();
+        }
     }
+    if (lane < n_parked) scatter_environment_gradient<C>(lt, cam, kp, parked[lane], grad_env, env_h, env_w, env_interleaved);
     if (grad_background)
     {
 #pragma unroll
@@ -537,7 +598,7 @@ __global__ void k_normalize_intrinsics(float* g, const float* cnt, int n, int co
 // ------------------------------------------------------------------------------------------------------
 template <int C>
 static adop_status launch_view_backward(const PointStreams& pts, const ViewCam* cam, const KernelParams& kp, const LayerTable& lt,
-                                        const BackwardTargets& bt, float* grad_background, float* grad_env, int env_h, int env_w,
+                                        const BackwardTargets& bt, float* grad_background, float* grad_env, int env_h, int env_w, bool env_interleaved,
                                         cudaStream_t st, const VisibleList& vl, int model)
 {
     const int need = (pts.n + kBlock - 1) / kBlock;
@@ -548,7 +609,7 @@ static adop_status launch_view_backward(const PointStreams& pts, const ViewCam* 
         if (grid_px > cap) grid_px = cap;
         ADOP_LAUNCH("k_prepare_backward", st, (k_prepare_backward<C><<<grid_px, kBlock, 0, st>>>(
                                                   lt, cam, kp, bt.background, const_cast<float*>(bt.records), grad_background,
-                                                  grad_env, env_h, env_w)));
+                                                  grad_env, env_h, env_w, env_interleaved)));
     }
     // With a splat list the two dense kernels run; the all-points kernel is launched behind them and returns at once
     // unless the list's overflow flag is set (decided on the device, no host round trip). The debug stencil rule
@@ -652,6 +713,11 @@ extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view
             ADOP_CUDA_TRY(cudaMemsetAsync(io->grad_env_map, 0, sizeof(float) * (size_t)C * s->env_h * s->env_w, st));
     }
 
+    // environment-map gradient: summed in an [eh,ew,C] scratch with vector atomics when the caller gave one
+    const bool env_inter = env && io->grad_env_map_interleaved && C % 4 == 0 &&
+                           (reinterpret_cast<uintptr_t>(io->grad_env_map_interleaved) & 15) == 0;
+    if (env_inter)
+        ADOP_CUDA_TRY(cudaMemsetAsync(io->grad_env_map_interleaved, 0, sizeof(float) * (size_t)C * s->env_h * s->env_w, st));
     // descriptor gradients stay in the [T,C] buffer when there is no [C,T] tensor to move them into
     const bool interleaved_only = !io->grad_texture && io->grad_texture_interleaved;
     if (io->grad_texture_interleaved && (io->grad_texture || !io->accumulate))
@@ -697,16 +763,16 @@ extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view
         bt.grad_intrinsics = io->grad_intrinsics ? io->grad_intrinsics + (size_t)views[b].camera_index * cols : nullptr;
         bt.count_intrinsics = io->grad_intrinsics ? io->count_intrinsics + views[b].camera_index : nullptr;
         bt.records = reinterpret_cast<const float*>(static_cast<const char*>(io->workspace) + kCamRegionBytes);
-        float* ge = env ? io->grad_env_map : nullptr;
+        float* ge = env ? (env_inter ? io->grad_env_map_interleaved : io->grad_env_map) : nullptr;
         // the list's geometry (segments in use, entries per segment) sits in its header, written by the forward pass
         VisibleList vl = make_visible_list(const_cast<int32_t*>(io->visible_list), N, b, 1);
         adop_status r;
         switch (C)
         {
-            case 3: r = launch_view_backward<3>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, st, vl, views[b].camera_model); break;
-            case 4: r = launch_view_backward<4>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, st, vl, views[b].camera_model); break;
-            case 8: r = launch_view_backward<8>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, st, vl, views[b].camera_model); break;
-            case 16: r = launch_view_backward<16>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, st, vl, views[b].camera_model); break;
+            case 3: r = launch_view_backward<3>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, env_inter, st, vl, views[b].camera_model); break;
+            case 4: r = launch_view_backward<4>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, env_inter, st, vl, views[b].camera_model); break;
+            case 8: r = launch_view_backward<8>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, env_inter, st, vl, views[b].camera_model); break;
+            case 16: r = launch_view_backward<16>(pts, cam, kp, lt, bt, io->grad_background, ge, s->env_h, s->env_w, env_inter, st, vl, views[b].camera_model); break;
             default: return ADOP_ERR_UNSUPPORTED;
         }
         if (r != ADOP_OK) return r;
@@ -714,6 +780,12 @@ extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view
     if (io->grad_texture && io->grad_texture_interleaved)
     {
         adop_status ds = adop_texture_deinterleave(io->grad_texture_interleaved, io->grad_texture, C, T, io->accumulate ? 1 : 0, stream);
+        if (ds != ADOP_OK) return ds;
+    }
+    if (env_inter)
+    {
+        // [eh,ew,C] -> [C,eh,ew]; the tensor was zeroed above unless the caller accumulates
+        adop_status ds = adop_texture_deinterleave(io->grad_env_map_interleaved, io->grad_env_map, C, s->env_h * s->env_w, 1, stream);
         if (ds != ADOP_OK) return ds;
     }
     if (io->normalize)

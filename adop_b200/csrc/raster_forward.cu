@@ -124,8 +124,17 @@ __global__ void __launch_bounds__(kBlock, 8) k_depth_prepass(PointStreams pts, c
 
 // ------------------------------------------------------------------------------------------------------
 // K2: fuzzy-depth blend into the interleaved accumulator.
+// Accumulator layout. C % 4 == 0: the colour sums of a pixel are C/4 float4 (nothing padded) and the splat count goes
+// straight into the layer's weight image, which is an output anyway (PointRenderer.cu:1006), so the resolve kernel
+// neither writes the count nor clears a padded fifth value per pixel. Otherwise colours and count share one padded record.
 template <int C>
-__device__ __forceinline__ void splat_record(float* rec, const float* t)
+struct AccumLayout
+{
+    static constexpr bool kSplit = C % 4 == 0;
+    static constexpr int kFloats = kSplit ? C : ((C + 1) + 3) & ~3;
+};
+template <int C>
+__device__ __forceinline__ void splat_record(float* rec, float* weight, const float* t)
 {
     constexpr int full = C / 4;
     constexpr int rem = C % 4;
@@ -134,7 +143,7 @@ __device__ __forceinline__ void splat_record(float* rec, const float* t)
         atomicAdd(reinterpret_cast<float4*>(rec) + v, make_float4(t[4 * v], t[4 * v + 1], t[4 * v + 2], t[4 * v + 3]));
     if (rem == 0)
     {
-        atomicAdd(rec + C, 1.0f);
+        atomicAdd(weight, 1.0f);
     }
     else
     {
@@ -164,7 +173,7 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, const flo
         if (threadIdx.x == 0) s_count = 0;
         __syncthreads();
     }
-    constexpr int RS = ((C + 1) + 3) & ~3;
+    constexpr int RS = AccumLayout<C>::kFloats;
     const int stride = gridDim.x * blockDim.x;
     int4* seg = EMIT ? vl.entries + (size_t)blockIdx.x * vl.seg_cap : nullptr;
     const int lane = threadIdx.x & 31;
@@ -206,7 +215,7 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, const flo
             load_descriptor<C>(texture, texture_interleaved, num_texels, ti, t);
 #pragma unroll
             for (int l = 0; l < L; ++l)
-                if (pass & (1u << l)) splat_record<C>(accum + ((size_t)lt.rec_off[l] + pix[l]) * RS, t);
+                if (pass & (1u << l)) splat_record<C>(accum + ((size_t)lt.rec_off[l] + pix[l]) * RS, lt.weight[l] + pix[l], t);
         }
         // the layers the backward pass will visit: it skips layers the point does not land in and stops at the first
         // depth failure (PointRenderer.cu:451-462)
@@ -271,72 +280,111 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, const flo
 
 // ------------------------------------------------------------------------------------------------------
 // K3: resolve. One thread per pyramid pixel of the view (all layers in one launch).
+// Uncovered pixels that take the environment map need a ray through the inverse camera model and a spherical lookup,
+// a few hundred instructions, and they are scattered (single-pixel holes between splats), so that almost every warp
+// would run that code for a handful of lanes. Instead each warp parks its holes in a small queue of its own and works
+// them off 32 at a time with all lanes busy (measured on the 1080p pyramid with 15 % holes: 55 -> 28 us without the
+// environment map, which is what the parked version aims at).
+template <int C>
+__device__ __forceinline__ void resolve_environment_pixel(const LayerTable& lt, const ViewCam& cam, const KernelParams& kp, unsigned r,
+                                                          const float* __restrict__ background, const float* __restrict__ env,
+                                                          int env_h, int env_w)
+{
+    const int l = layer_of_record(lt, r);
+    const unsigned pix = r - lt.rec_off[l];
+    const int w = lt.w[l];
+    const size_t plane = (size_t)w * lt.h[l];
+    const int gy = pix / w, gx = pix - gy * w;
+    Intr5 crop_l = scale_intr(cam.crop, __int_as_float((127 - l) << 23));  // 0.5^l
+    V2 uv = env_uv_for_pixel(gx, gy, cam.V, cam.K, cam.dist, crop_l);
+    BilinearTap tp = bilinear_taps(uv, env_w, env_h);
+    const float one_minus_m = 1.0f - kp.mask_background_value;
+    float* color = lt.color[l] + pix;
+#pragma unroll
+    for (int c = 0; c < C; ++c)
+    {
+        const float* e = env + (size_t)c * env_h * env_w;
+        float e00 = __ldg(e + (size_t)tp.y0 * env_w + tp.x0), e01 = __ldg(e + (size_t)tp.y0 * env_w + tp.x1);
+        float e10 = __ldg(e + (size_t)tp.y1 * env_w + tp.x0), e11 = __ldg(e + (size_t)tp.y1 * env_w + tp.x1);
+        float top = e00 + (e01 - e00) * tp.wx;
+        float bot = e10 + (e11 - e10) * tp.wx;
+        float ev = top + (bot - top) * tp.wy;
+        color[c * plane] = __ldg(background + c) + one_minus_m * ev;
+    }
+}
+
 template <int C>
 __global__ void __launch_bounds__(kBlock) k_resolve(LayerTable lt, const ViewCam* __restrict__ camp, KernelParams kp, float* __restrict__ accum,
                                                      const float* __restrict__ background, const float* __restrict__ env,
                                                      int env_h, int env_w)
 {
     const ViewCam& cam = *camp;
-    constexpr int RS = ((C + 1) + 3) & ~3;
+    constexpr int RS = AccumLayout<C>::kFloats;
+    constexpr bool kSplit = AccumLayout<C>::kSplit;
+    __shared__ unsigned s_parked[kBlock / 32][64];
+    unsigned* parked = s_parked[threadIdx.x >> 5];
+    const int lane = threadIdx.x & 31;
+    int n_parked = 0;  // the same in every lane of the warp
     const unsigned total = lt.rec_off[kMaxLayers];
-    for (unsigned r = blockIdx.x * blockDim.x + threadIdx.x; r < total; r += gridDim.x * blockDim.x)
+    const unsigned stride = gridDim.x * blockDim.x;
+    // warp-uniform trip count: the parking uses full-warp votes
+    for (unsigned base = blockIdx.x * blockDim.x; base < total; base += stride)
     {
-        int l = 0;
-#pragma unroll
-        for (int k = 1; k < kMaxLayers; ++k)
-            if (k < lt.L && r >= lt.rec_off[k]) l = k;
-        const unsigned pix = r - lt.rec_off[l];
-        const int w = lt.w[l], h = lt.h[l];
-        const size_t plane = (size_t)w * h;
-        float4* rec = reinterpret_cast<float4*>(accum + (size_t)r * RS);
-        float v[RS];
-#pragma unroll
-        for (int k = 0; k < RS / 4; ++k)
+        const unsigned r = base + threadIdx.x;
+        bool hole = false;
+        if (r < total)
         {
-            float4 a = __ldcg(rec + k);
-            v[4 * k] = a.x; v[4 * k + 1] = a.y; v[4 * k + 2] = a.z; v[4 * k + 3] = a.w;
-        }
-        const float cou = v[C];
-        float* color = lt.color[l] + pix;
-        lt.weight[l][pix] = cou;
-        const float m = cou == 0.f ? kp.mask_background_value : 1.f;
-        if (lt.mask[l]) lt.mask[l][pix] = m;
-        if (cou == 0.f)
-        {
-            if (env)
+            const int l = layer_of_record(lt, r);
+            const unsigned pix = r - lt.rec_off[l];
+            const size_t plane = (size_t)lt.w[l] * lt.h[l];
+            float4* rec = reinterpret_cast<float4*>(accum + (size_t)r * RS);
+            // split layout: the blend kernel counted into the weight image itself (requested together with the record:
+            // a dependent second load costs more than the bytes it could save)
+            const float cou_split = kSplit ? __ldcg(lt.weight[l] + pix) : 0.f;
+            float v[RS];
+#pragma unroll
+            for (int k = 0; k < RS / 4; ++k)
             {
-                int gy = pix / w, gx = pix - gy * w;
-                Intr5 crop_l = scale_intr(cam.crop, __int_as_float((127 - l) << 23));  // 0.5^l
-                V2 uv = env_uv_for_pixel(gx, gy, cam.V, cam.K, cam.dist, crop_l);
-                BilinearTap tp = bilinear_taps(uv, env_w, env_h);
-                const float one_minus_m = 1.0f - m;
-#pragma unroll
-                for (int c = 0; c < C; ++c)
+                float4 a = __ldcg(rec + k);
+                v[4 * k] = a.x; v[4 * k + 1] = a.y; v[4 * k + 2] = a.z; v[4 * k + 3] = a.w;
+            }
+            const float cou = kSplit ? cou_split : v[C < RS ? C : 0];
+            float* color = lt.color[l] + pix;
+            if (!kSplit) lt.weight[l][pix] = cou;
+            if (lt.mask[l]) lt.mask[l][pix] = cou == 0.f ? kp.mask_background_value : 1.f;
+            if (cou == 0.f)
+            {
+                hole = env != nullptr;
+                if (!hole)
                 {
-                    const float* e = env + (size_t)c * env_h * env_w;
-                    float e00 = __ldg(e + (size_t)tp.y0 * env_w + tp.x0), e01 = __ldg(e + (size_t)tp.y0 * env_w + tp.x1);
-                    float e10 = __ldg(e + (size_t)tp.y1 * env_w + tp.x0), e11 = __ldg(e + (size_t)tp.y1 * env_w + tp.x1);
-                    float top = e00 + (e01 - e00) * tp.wx;
-                    float bot = e10 + (e11 - e10) * tp.wx;
-                    float ev = top + (bot - top) * tp.wy;
-                    color[c * plane] = __ldg(background + c) + one_minus_m * ev;
+#pragma unroll
+                    for (int c = 0; c < C; ++c) color[c * plane] = __ldg(background + c);
                 }
             }
             else
             {
 #pragma unroll
-                for (int c = 0; c < C; ++c) color[c * plane] = __ldg(background + c);
+                for (int c = 0; c < C; ++c) color[c * plane] = v[c] / cou;
+                // leave the record clean for the next view
+#pragma unroll
+                for (int k = 0; k < RS / 4; ++k) rec[k] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
-        else
+        const unsigned vote = __ballot_sync(0xffffffffu, hole);
+        if (vote)
         {
-#pragma unroll
-            for (int c = 0; c < C; ++c) color[c * plane] = v[c] / cou;
-            // leave the record clean for the next view
-#pragma unroll
-            for (int k = 0; k < RS / 4; ++k) rec[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (hole) parked[n_parked + __popc(vote & ((1u << lane) - 1u))] = r;
+            n_parked += __popc(vote);
+            __syncwarp();
+            if (n_parked >= 32)
+            {
+                n_parked -= 32;
+                resolve_environment_pixel<C>(lt, cam, kp, parked[n_parked + lane], background, env, env_h, env_w);
+            }
+            __syncwarp();
         }
     }
+    if (lane < n_parked) resolve_environment_pixel<C>(lt, cam, kp, parked[lane], background, env, env_h, env_w);
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -506,8 +554,12 @@ extern "C" adop_status adop_raster_forward(const adop_scene* s, const adop_view*
     fill_layer_dims(w0, h0, L, &base);
     ViewCam* cams = static_cast<ViewCam*>(io->workspace);
     float* accum = reinterpret_cast<float*>(static_cast<char*>(io->workspace) + kCamRegionBytes);
-    const size_t accum_bytes = (size_t)base.rec_off[kMaxLayers] * record_floats(C) * sizeof(float);
+    const bool split = C % 4 == 0;  // AccumLayout: colour sums only, the counts go into the weight images
+    const size_t accum_bytes = (size_t)base.rec_off[kMaxLayers] * (split ? C : record_floats(C)) * sizeof(float);
     ADOP_CUDA_TRY(cudaMemsetAsync(accum, 0, accum_bytes, st));
+    if (split)
+        for (int l = 0; l < L; ++l)
+            ADOP_CUDA_TRY(cudaMemsetAsync(io->layers[l].weight, 0, sizeof(float) * (size_t)B * base.w[l] * base.h[l], st));
     const int sms = sm_count();
     // depth.fill_(100000), PointRenderer.cu:1045 (weights and colours are written by the resolve kernel)
     for (int l = 0; l < L; ++l)

@@ -237,6 +237,11 @@ class PointRasterizer:
                 if self._gtex_i is None or self._gtex_i.shape != self._tex_i.shape:
                     self._gtex_i = torch.empty_like(self._tex_i)
                 io.grad_texture_interleaved = self._gtex_i.data_ptr()
+            if out.get("env_map") is not None and sc.channels % 4 == 0:
+                # [eh,ew,C] scratch for the environment-map gradient (vector atomics), kept between calls
+                if getattr(self, "_genv_i", None) is None or self._genv_i.numel() != out["env_map"].numel():
+                    self._genv_i = torch.empty(out["env_map"].numel(), dtype=torch.float32, device=dev)
+                io.grad_env_map_interleaved = self._genv_i.data_ptr()
             stream = torch.cuda.current_stream(self.device).cuda_stream
             st = self.lib.adop_raster_backward(C.byref(sc), va, B, C.byref(params), L, C.byref(io), C.c_void_p(stream))
             capi.check(st, "adop_raster_backward")

@@ -161,6 +161,9 @@ typedef struct adop_backward_io
      * With grad_texture == NULL the descriptor gradients STAY here, in [T,C] layout (zeroed first unless accumulate):
      * the form adop_peer_reduce_gradients reads from every GPU. */
     float* grad_texture_interleaved;
+    /* optional [env_h,env_w,C] scratch (C a multiple of 4): the environment-map gradient is summed there with one
+     * vector atomic per bilinear tap and added to grad_env_map [C,env_h,env_w] at the end of the call. */
+    float* grad_env_map_interleaved;
 } adop_backward_io;
 
 const char* adop_status_string(adop_status s);
