@@ -91,10 +91,10 @@ adop_status validate_common(const adop_scene* s, const adop_view* views, int B, 
     const int w = views[0].w, h = views[0].h;
     if (w <= 0 || h <= 0) return ADOP_ERR_INVALID_ARGUMENT;
     if ((w >> (L - 1)) <= 0 || (h >> (L - 1)) <= 0) return ADOP_ERR_INVALID_ARGUMENT;
-    // pyramid pixel count must fit the 32-bit record index
+    // pixel indices are 32-bit: a view's pyramid, and the layer-0 planes of a group of four views, must stay below 2^32
     unsigned long long total = 0;
     for (int l = 0, ww = w, hh = h; l < L; ++l, ww /= 2, hh /= 2) total += (unsigned long long)ww * hh;
-    if (total >= (1ull << 31)) return ADOP_ERR_SIZE_LIMIT;
+    if (total >= (1ull << 30)) return ADOP_ERR_SIZE_LIMIT;
     for (int b = 0; b < B; ++b)
     {
         const adop_view& v = views[b];

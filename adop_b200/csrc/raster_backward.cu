@@ -537,7 +537,7 @@ __global__ void __launch_bounds__(kBlock, 4) k_splat_gather(PointStreams pts, Ke
 }
 
 template <int MODEL>
-__global__ void __launch_bounds__(kBlock) k_splat_chain(PointStreams pts, const ViewCam* __restrict__ camp, KernelParams kp,
+__global__ void __launch_bounds__(kBlock, 4) k_splat_chain(PointStreams pts, const ViewCam* __restrict__ camp, KernelParams kp,
                                                          LayerTable lt, BackwardTargets bt, VisibleList vl)
 {
     if (__ldg(vl.header + kVisibleSegments + 2) != 0) return;

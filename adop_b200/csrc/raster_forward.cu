@@ -115,7 +115,8 @@ __global__ void __launch_bounds__(kBlock, 8) k_depth_prepass(PointStreams pts, c
                 int px = round_half_even_bounded(x), py = round_half_even_bounded(y);
                 if ((unsigned)px >= (unsigned)lt.w[l] || (unsigned)py >= (unsigned)lt.h[l]) continue;
                 // depth plane of view v of the group: the planes of a batch follow each other
-                int* dst = reinterpret_cast<int*>(lt.depth[l]) + ((size_t)v * lt.h[l] + py) * lt.w[l] + px;
+                // (32-bit index: a group's planes of one layer hold fewer than 2^31 pixels, checked by the entry point)
+                int* dst = reinterpret_cast<int*>(lt.depth[l]) + ((unsigned)(v * lt.h[l] + py) * (unsigned)lt.w[l] + (unsigned)px);
                 if (l == 0 || zi < __ldg(dst)) atomicMin(dst, zi);
             }
         }

@@ -65,6 +65,17 @@ ADOP_HD int round_half_even_bounded(float x)
 #endif
 }
 
+// 1 / x, correctly rounded on both sides (so the same bits): the device has it as one intrinsic, which is shorter
+// than the general division
+ADOP_HD float reciprocal(float x)
+{
+#if defined(__CUDA_ARCH__)
+    return __frcp_rn(x);
+#else
+    return 1.0f / x;
+#endif
+}
+
 // Counter-based hash for the per-(view,point) Bernoulli drop-out decision. The reference draws
 // bernoulli_() into a [B,N] float tensor (PointRenderer.cu:1081-1088); a hash needs no memory.
 ADOP_HD uint32_t hash_u32(uint32_t seed, uint32_t view, uint32_t point)
@@ -247,7 +258,7 @@ ADOP_HD V2 distort(V2 m, const Dist8& d, float cutoff, bool* rejected, float* J_
     float xy2 = (x + x) * y;
     float num = fmaf(fmaf(fmaf(d.k3, r2, d.k2), r2, d.k1), r2, 1.0f);
     float den = fmaf(fmaf(fmaf(d.k6, r2, d.k5), r2, d.k4), r2, 1.0f);
-    float iden = den == 1.0f ? 1.0f : 1.0f / den;  // same bits either way; skips the division for k4 = k5 = k6 = 0
+    float iden = den == 1.0f ? 1.0f : reciprocal(den);  // same bits either way; skips the division for k4 = k5 = k6 = 0
     float rad = num * iden;
     V2 o;
     if (d.p1 == 0.f && d.p2 == 0.f)
@@ -341,7 +352,7 @@ ADOP_HD Projected project_pinhole_normalized(V3 p, V3 n, bool has_normal, const 
         if (dt > 0.f) return r;
     }
     // DivideByZ (PointRendererHelper.h:70) as one reciprocal and two products
-    float iz = 1.0f / r.view.z;
+    float iz = reciprocal(r.view.z);
     V2 m;
     m.x = r.view.x * iz;
     m.y = r.view.y * iz;
@@ -373,7 +384,7 @@ ADOP_HD V2 ocam_project(V3 v, const Ocam& o, float cutoff, float* depth, float* 
 {
     float l2 = fmaf(v.x, v.x, v.y * v.y);
     float l = fmaxf(sqrtf(l2), 1.0e-12f);
-    float il = 1.0f / l;
+    float il = reciprocal(l);
     float t = -v.z * il;
     float theta = atan_f(t);
     float rho = 0.f, drho = 0.f;
@@ -554,7 +565,7 @@ ADOP_HD bool project_pinhole_backward(V3 p, V3 n, bool has_normal, V2 g, const R
         float dt = fmaf(view.z, vn.z, fmaf(view.y, vn.y, view.x * vn.x));
         if (dt > 0.f) return false;
     }
-    float iz = 1.0f / view.z;
+    float iz = reciprocal(view.z);
     V2 m; m.x = view.x * iz; m.y = view.y * iz;
     float Jp[4], Jd[16];
     bool rejected;
