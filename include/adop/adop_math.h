@@ -335,9 +335,25 @@ struct Projected
     V3 view;    // camera-space position
 };
 
+// distort() for the common calibration with only k1 and k2: the same bits as the general form (a zero k3 leaves
+// fmaf(k3, r2, k2) = k2, the denominator is exactly 1 and the tangential part is exactly 0) with six fewer
+// coefficients to fetch per point.
+ADOP_HD V2 distort_radial2(V2 m, float k1, float k2, float cutoff, bool* rejected)
+{
+    float x = m.x, y = m.y;
+    float x2 = x * x, y2 = y * y;
+    float r2 = x2 + y2;
+    float rad = fmaf(fmaf(k2, r2, k1), r2, 1.0f);
+    V2 o;
+    o.x = x * rad;
+    o.y = y * rad;
+    *rejected = r2 > cutoff * cutoff;
+    return o;
+}
+
 // ProjectPointPinhole (PointRendererHelper.h:49-82) up to the distorted normalised point; the caller applies K.
 ADOP_HD Projected project_pinhole_normalized(V3 p, V3 n, bool has_normal, const Rigid32& V, const Dist8& dist,
-                                             bool check_normal, float dist_cutoff)
+                                             bool check_normal, float dist_cutoff, bool radial2 = false)
 {
     Projected r;
     r.view = transform_point(V, p);
@@ -357,7 +373,8 @@ ADOP_HD Projected project_pinhole_normalized(V3 p, V3 n, bool has_normal, const 
     m.x = r.view.x * iz;
     m.y = r.view.y * iz;
     bool rejected;
-    r.ip = distort(m, dist, dist_cutoff, &rejected, nullptr, nullptr);
+    r.ip = radial2 ? distort_radial2(m, dist.k1, dist.k2, dist_cutoff, &rejected)
+                   : distort(m, dist, dist_cutoff, &rejected, nullptr, nullptr);
     r.z = rejected ? 0.f : z;
     return r;
 }
@@ -461,6 +478,7 @@ struct ViewCam
     // pinhole: crop o K as one affine map of the distorted normalised point (formed in double, rounded once):
     // x = a[0] dx + a[1] dy + a[2] ; y = a[3] dy + a[4]. The reference applies K, then the crop (PointRenderer.cu:255).
     float a[5];
+    int radial2;  // pinhole with k3 = k4 = k5 = k6 = p1 = p2 = 0: the projection takes distort_radial2
 };
 
 ADOP_HD ViewCam load_view_cam(const double* poses, const float* intrinsics, int intrinsics_cols, int image_index,
@@ -476,6 +494,8 @@ ADOP_HD ViewCam load_view_cam(const double* poses, const float* intrinsics, int 
     {
         c.K = load_intr5(ip);
         c.dist = load_dist8(ip + 5);
+        c.radial2 = (c.dist.k3 == 0.f && c.dist.k4 == 0.f && c.dist.k5 == 0.f && c.dist.k6 == 0.f && c.dist.p1 == 0.f &&
+                     c.dist.p2 == 0.f) ? 1 : 0;
         c.ocam.npoly = 0;
         const double cfx = crop5[0], cfy = crop5[1], ccx = crop5[2], ccy = crop5[3], cs = crop5[4];
         const double fx = ip[0], fy = ip[1], cx = ip[2], cy = ip[3], sk = ip[4];
@@ -494,6 +514,7 @@ ADOP_HD ViewCam load_view_cam(const double* poses, const float* intrinsics, int 
         c.K.fx = c.K.fy = 1.f; c.K.cx = c.K.cy = c.K.s = 0.f;
         c.dist.k1 = c.dist.k2 = c.dist.k3 = c.dist.k4 = c.dist.k5 = c.dist.k6 = c.dist.p1 = c.dist.p2 = 0.f;
         c.a[0] = c.a[1] = c.a[2] = c.a[3] = c.a[4] = 0.f;
+        c.radial2 = 0;
     }
     return c;
 }
@@ -514,7 +535,7 @@ ADOP_HD bool project_for_raster(const ViewCam& c, V3 p, float drop_out_radius, V
     V2 ip;
     if (c.model == kPinholeDistortion)
     {
-        pr = project_pinhole_normalized(p, n, has_normal, c.V, c.dist, check_normal, dist_cutoff);
+        pr = project_pinhole_normalized(p, n, has_normal, c.V, c.dist, check_normal, dist_cutoff, c.radial2 != 0);
         if (!(pr.z > 0.f)) return false;
         focal = c.K.fx * c.crop.fx;
         ip.x = fmaf(c.a[0], pr.ip.x, fmaf(c.a[1], pr.ip.y, c.a[2]));

@@ -361,7 +361,8 @@ def test_many_views_crops_two_cameras_shared_texels(oracle, cuda_lib):
     a["texture"] = np.ascontiguousarray(a["texture"][:, : (n + 1) // 2])
     intr2 = a["intrinsics"].copy()
     intr2[0, :4] *= 1.1
-    intr2[0, 5:7] = [-0.05, 0.01]
+    # the second camera has all eight distortion coefficients (the first one only k1, k2: the shorter radial-only form)
+    intr2[0, 5:13] = [-0.05, 0.01, 0.002, 0.01, -0.003, 0.001, 0.0005, -0.0004]
     a["intrinsics"] = np.ascontiguousarray(np.concatenate([a["intrinsics"], intr2]))
     views = []
     for k in range(70):
