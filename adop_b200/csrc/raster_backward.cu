@@ -635,17 +635,22 @@ static adop_status launch_view_backward(const PointStreams& pts, const ViewCam* 
             }
         }
     }
+    // Behind a splat list this launch is almost always a no-op that only reads the overflow flag, so it gets one block
+    // per SM (an empty launch costs by its block count); without a list it is the backward pass and fills the GPU.
+    const int fallback_cap = use_list ? sm_count() : (1 << 30);
     if (model == kPinholeDistortion)
     {
         static const int g = resident_grid(k_splat_backward_all<C, kPinholeDistortion>, 1ll << 40);
-        ADOP_LAUNCH("k_splat_backward_all", st, (k_splat_backward_all<C, kPinholeDistortion><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(
-                                                    pts, cam, kp, lt, bt, flag)));
+        int grid = need < g ? (need < 1 ? 1 : need) : g;
+        if (grid > fallback_cap) grid = fallback_cap;
+        ADOP_LAUNCH("k_splat_backward_all", st, (k_splat_backward_all<C, kPinholeDistortion><<<grid, kBlock, 0, st>>>(pts, cam, kp, lt, bt, flag)));
     }
     else
     {
         static const int g = resident_grid(k_splat_backward_all<C, kOcam>, 1ll << 40);
-        ADOP_LAUNCH("k_splat_backward_all", st, (k_splat_backward_all<C, kOcam><<<need < g ? (need < 1 ? 1 : need) : g, kBlock, 0, st>>>(
-                                                    pts, cam, kp, lt, bt, flag)));
+        int grid = need < g ? (need < 1 ? 1 : need) : g;
+        if (grid > fallback_cap) grid = fallback_cap;
+        ADOP_LAUNCH("k_splat_backward_all", st, (k_splat_backward_all<C, kOcam><<<grid, kBlock, 0, st>>>(pts, cam, kp, lt, bt, flag)));
     }
     ADOP_CUDA_TRY(cudaGetLastError());
     return ADOP_OK;
