@@ -30,10 +30,10 @@ UNIT = "Gpts/s"
 WORKLOAD = "c2: 10M points x 16 views/GPU, 1920x1080, L=4, C=4, pinhole k1=-0.1 k2=0.02, env 1024x512, fwd+bwd with pose grads"
 
 
-# DRAM bytes (read + write) per launch of the kernels that can dominate, from ncu --set full captures of one- and four-view
-# runs of this workload (profiles/point_kernels_c2_ncu_full.md); one launch there = one launch here. Valid for the default
+# DRAM bytes (read + write) per launch of the kernels that can dominate, from an ncu --set full capture of a four-view
+# run of this workload (profiles/point_kernels_c2_ncu_full.md); one launch there = one launch here. Valid for the default
 # workload only.
-NCU_TRAFFIC_BYTES = {"k_blend": 446.0e6, "k_splat_gather": 500.9e6, "k_splat_chain": 200.7e6, "k_depth_prepass": 242.5e6}
+NCU_TRAFFIC_BYTES = {"k_blend": 400.4e6, "k_splat_gather": 478.1e6, "k_splat_chain": 190.6e6, "k_depth_prepass": 243.0e6}
 
 
 def parse_args():
