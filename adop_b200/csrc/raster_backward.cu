@@ -479,8 +479,9 @@ __device__ __forceinline__ int4 list_entry(const VisibleList& vl, const int* s_p
 }
 constexpr int kNoStencil = 0x7fc00000;  // quiet NaN in the gradient slot: the splat has no ghost gradient
 
+// (resident blocks per SM by channel count: the four neighbour records of the stencil are 8C floats that want registers)
 template <int C>
-__global__ void __launch_bounds__(kBlock, 4) k_splat_gather(PointStreams pts, KernelParams kp, LayerTable lt, BackwardTargets bt,
+__global__ void __launch_bounds__(kBlock, C <= 4 ? 4 : (C <= 8 ? 2 : 1)) k_splat_gather(PointStreams pts, KernelParams kp, LayerTable lt, BackwardTargets bt,
                                                             VisibleList vl, int want_geo)
 {
     constexpr int RB = (2 * C + 3) & ~3;
