@@ -48,7 +48,8 @@ class AdopLayerBuffers(C.Structure):
 
 class AdopForwardIO(C.Structure):
     _fields_ = [("layers", AdopLayerBuffers * MAX_LAYERS), ("dropout_mask", C.c_void_p),
-                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("visible_list", C.c_void_p)]
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("visible_list", C.c_void_p),
+                ("packed_depth", C.c_void_p * MAX_LAYERS)]
 
 
 class AdopBackwardIO(C.Structure):

@@ -13,6 +13,8 @@
 //    one accumulator, small enough to stay in the 126 MB L2, is reused by every view of the batch.
 #include <cooperative_groups.h>
 
+#include <cstring>
+
 #include "common.cuh"
 
 namespace adop {
@@ -119,6 +121,42 @@ __global__ void __launch_bounds__(kBlock, 8) k_depth_prepass(PointStreams pts, c
                 int* dst = reinterpret_cast<int*>(lt.depth[l]) + ((unsigned)(v * lt.h[l] + py) * (unsigned)lt.w[l] + (unsigned)px);
                 if (l == 0 || zi < __ldg(dst)) atomicMin(dst, zi);
             }
+        }
+    }
+}
+
+// K1b (optional by-product): the packed depth|index word per pixel (PackIndex / ExtractIndex,
+// PointRendererHelper.h:21-34): one 64-bit atomicMin of (depth bits << 32 | point index) per layer the point lands in.
+// The winner of a pixel is the nearest point, the lowest index among equal depths, whatever order the points come in.
+struct PackedPlanes
+{
+    unsigned long long* plane[kMaxLayers];
+};
+__global__ void __launch_bounds__(kBlock) k_fill_u64(unsigned long long* __restrict__ dst, size_t n, unsigned long long v)
+{
+    for (size_t k = (size_t)blockIdx.x * blockDim.x + threadIdx.x; k < n; k += (size_t)gridDim.x * blockDim.x) dst[k] = v;
+}
+__global__ void __launch_bounds__(kBlock) k_depth_prepass_packed(PointStreams pts, const ViewCam* __restrict__ camp, KernelParams kp,
+                                                                  LayerTable lt, PackedPlanes out)
+{
+    const ViewCam& cam = *camp;
+    const bool use_normal = kp.check_normal != 0;
+    const bool use_radius = kp.drop_out_points_by_radius != 0;
+    const int stride = gridDim.x * blockDim.x;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < pts.n; i += stride)
+    {
+        FetchedPoint f = fetch_point(pts, i);
+        RasterPoint q;
+        if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, use_normal, kp.dist_cutoff, &q, use_radius)) continue;
+        float x = q.x, y = q.y, rad = q.radius_px;
+        const unsigned long long word = ((unsigned long long)__float_as_uint(q.z) << 32) | (unsigned)i;
+        for (int l = 0; l < lt.L; ++l, rad *= 0.5f, x *= 0.5f, y *= 0.5f)
+        {
+            if (use_radius && rad < kp.drop_out_radius_threshold) break;
+            int px = round_half_even_bounded(x), py = round_half_even_bounded(y);
+            if ((unsigned)px >= (unsigned)lt.w[l] || (unsigned)py >= (unsigned)lt.h[l]) continue;
+            unsigned long long* dst = out.plane[l] + ((unsigned)py * (unsigned)lt.w[l] + (unsigned)px);
+            if (word < __ldg(dst)) atomicMin(dst, word);
         }
     }
 }
@@ -571,6 +609,26 @@ extern "C" adop_status adop_raster_forward(const adop_scene* s, const adop_view*
         if (grid > sms * 16) grid = sms * 16;
         ADOP_LAUNCH("k_fill", st, (k_fill<<<grid, kBlock, 0, st>>>(io->layers[l].depth, n, kDepthInit)));
     }
+    // optional packed depth|index planes: all layers or none
+    const bool packed = io->packed_depth[0] != nullptr;
+    for (int l = 0; l < L; ++l)
+        if ((io->packed_depth[l] != nullptr) != packed || (reinterpret_cast<uintptr_t>(io->packed_depth[l]) & 7))
+            return ADOP_ERR_INVALID_ARGUMENT;
+    if (packed)
+    {
+        unsigned init_bits;
+        const float init_depth = kDepthInit;
+        memcpy(&init_bits, &init_depth, sizeof(init_bits));
+        const unsigned long long empty = ((unsigned long long)init_bits << 32) | 0xFFFFFFFFull;
+        for (int l = 0; l < L; ++l)
+        {
+            size_t n = (size_t)B * base.w[l] * base.h[l];
+            if (n == 0) continue;
+            int grid = (int)((n + kBlock - 1) / kBlock);
+            if (grid > sms * 16) grid = sms * 16;
+            ADOP_LAUNCH("k_fill", st, (k_fill_u64<<<grid, kBlock, 0, st>>>(reinterpret_cast<unsigned long long*>(io->packed_depth[l]), n, empty)));
+        }
+    }
     ADOP_CUDA_TRY(cudaGetLastError());
 
     PointStreams pts;
@@ -598,6 +656,16 @@ extern "C" adop_status adop_raster_forward(const adop_scene* s, const adop_view*
         }
         KernelParams kp = make_kernel_params(rp, io->dropout_mask, N, b);
         const ViewCam* cam = cams + (b % kCamChunk);
+        if (packed)
+        {
+            PackedPlanes pp;
+            for (int l = 0; l < kMaxLayers; ++l)
+                pp.plane[l] = l < L ? reinterpret_cast<unsigned long long*>(io->packed_depth[l]) + (size_t)b * base.w[l] * base.h[l] : nullptr;
+            static const int g_packed = resident_grid(k_depth_prepass_packed, 1ll << 40);
+            const int need = (N + kBlock - 1) / kBlock;
+            ADOP_LAUNCH("k_depth_prepass_packed", st, (k_depth_prepass_packed<<<need < g_packed ? (need < 1 ? 1 : need) : g_packed, kBlock, 0, st>>>(
+                                                          pts, cam, kp, lt, pp)));
+        }
         // depth prepass in groups of four consecutive views (a group never straddles a camera chunk: 64 = 16 x 4)
         const int depth_views = (b % 4 == 0) ? (B - b < 4 ? B - b : 4) : 0;
         adop_status r;

@@ -85,10 +85,11 @@ class ForwardResult:
     PointRenderer.cu:1514-1527): depth, weight and colour per layer, and the per-view list of points that passed the
     depth test (in place of the saved [B,N] drop-out tensor)."""
 
-    def __init__(self, colors, masks, depths, weights, views, num_layers, visible=None):
+    def __init__(self, colors, masks, depths, weights, views, num_layers, visible=None, packed=None):
         self.colors, self.masks, self.depths, self.weights = colors, masks, depths, weights
         self.views, self.num_layers = views, num_layers
         self.visible = visible
+        self.packed = packed  # optional per layer [B,1,h,w] int64: depth bits << 32 | index of the nearest point
 
     def splat_counts(self):
         """(point, layer) splats per view that the backward pass visits, as recorded in `visible`."""
@@ -134,7 +135,7 @@ class PointRasterizer:
         return self._ws
 
     def forward(self, scene, views, params, num_layers, dropout_mask=None, out=None, record_visible=True,
-                refresh_descriptors=True):
+                refresh_descriptors=True, packed_depth=False):
         """BlendPointCloudForward (PointRenderer.cu:1389-1531). `views`: list of dicts or an AdopView array.
 
         Returns a ForwardResult; result.colors + result.masks is the reference's return list.
@@ -159,7 +160,9 @@ class PointRasterizer:
                 if record_visible:
                     ints = self.lib.adop_raster_visible_list_ints(sc.num_points)
                     visible = torch.empty((B, ints), dtype=torch.int32, device=self.device)
-                out = ForwardResult(colors, masks, depths, weights, va, num_layers, visible)
+                packed = [torch.empty((B, 1, hh, ww), dtype=torch.int64, device=self.device) for ww, hh in sizes] \
+                    if packed_depth else None
+                out = ForwardResult(colors, masks, depths, weights, va, num_layers, visible, packed)
             else:
                 out.views = va
             io = capi.AdopForwardIO()
@@ -172,6 +175,9 @@ class PointRasterizer:
             io.workspace = ws.data_ptr()
             io.workspace_bytes = ws.numel()
             io.visible_list = out.visible.data_ptr() if out.visible is not None else None
+            if out.packed is not None:
+                for l in range(num_layers):
+                    io.packed_depth[l] = out.packed[l].data_ptr()
             stream = torch.cuda.current_stream(self.device).cuda_stream
             st = self.lib.adop_raster_forward(C.byref(sc), va, B, C.byref(params), num_layers, C.byref(io),
                                               C.c_void_p(stream))

@@ -122,6 +122,13 @@ typedef struct adop_forward_io
      * more such splats than the list holds (about one per point of the cloud), the list marks itself unusable and
      * the backward pass walks all points. NULL = not recorded. */
     int32_t* visible_list;
+    /* optional, per layer [B,1,h_l,w_l] u64 (all of the first num_layers entries or none): for every pixel the minimum
+     * over the points landing there of (bits of the depth << 32 | point index), the packed depth|index word of
+     * PackIndex / ExtractIndex (PointRendererHelper.h:21-34), which the reference's live path no longer uses. Its
+     * high word is bit-identical to `depth`; its low word names the nearest point (the lowest index among ties), which
+     * the 32-bit depth buffer cannot tell and which does not depend on the order the GPU visits the points in.
+     * Empty pixels hold (bits of 100000.0f << 32 | 0xFFFFFFFF). One extra pass over the points per view. */
+    uint64_t* packed_depth[ADOP_MAX_LAYERS];
 } adop_forward_io;
 
 /* Gradients (outputs) follow the reference's order {texture, background, points, pose tangents, intrinsics}

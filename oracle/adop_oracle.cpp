@@ -136,6 +136,40 @@ int adop_oracle_forward(const adop_scene* s, const adop_view* views, int B, cons
         for (size_t k = 0; k < (size_t)B * px; ++k) { io->layers[l].depth[k] = kDepthInit; io->layers[l].weight[k] = 0.f; }
         memset(io->layers[l].color, 0, sizeof(float) * (size_t)B * C * px);
     }
+    // the packed depth|index word of PointRendererHelper.h:21-34 (dead in the reference's live path), single-threaded
+    if (io->packed_depth[0])
+    {
+        uint32_t init_bits;
+        memcpy(&init_bits, &kDepthInit, 4);
+        for (int l = 0; l < L; ++l)
+        {
+            if (!io->packed_depth[l]) return ADOP_ERR_INVALID_ARGUMENT;
+            size_t px = (size_t)dims[l].w * dims[l].h;
+            for (size_t k = 0; k < (size_t)B * px; ++k) io->packed_depth[l][k] = ((uint64_t)init_bits << 32) | 0xFFFFFFFFull;
+        }
+        for (int b = 0; b < B; ++b)
+        {
+            ViewCam cam = view_cam(s, &views[b]);
+            for (int i = 0; i < N; ++i)
+            {
+                PointFetch f = fetch_point(s, i);
+                RasterPoint q;
+                if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, rp->check_normal != 0, rp->dist_cutoff, &q)) continue;
+                float x = q.x, y = q.y, rad = q.radius_px;
+                uint32_t zb;
+                memcpy(&zb, &q.z, 4);
+                const uint64_t word = ((uint64_t)zb << 32) | (uint32_t)i;
+                for (int l = 0; l < L; ++l, rad *= 0.5f, x *= 0.5f, y *= 0.5f)
+                {
+                    if (rp->drop_out_points_by_radius && rad < rp->drop_out_radius_threshold) break;
+                    int px = round_half_even(x), py = round_half_even(y);
+                    if (px < 0 || py < 0 || px >= dims[l].w || py >= dims[l].h) continue;
+                    uint64_t* d = io->packed_depth[l] + ((size_t)b * dims[l].h + py) * dims[l].w + px;
+                    if (word < *d) *d = word;
+                }
+            }
+        }
+    }
 
     for (int b = 0; b < B; ++b)
     {

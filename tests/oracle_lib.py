@@ -49,7 +49,7 @@ class Oracle:
         self.lib = lib
 
     # -- rasterizer ----------------------------------------------------------------------------------
-    def forward(self, arrays, views, params, num_layers, dropout_mask=None, threads=1):
+    def forward(self, arrays, views, params, num_layers, dropout_mask=None, threads=1, packed_depth=False):
         va = views if isinstance(views, C.Array) else capi.make_views(views)
         B = len(va)
         sc = fill_scene_struct(arrays, _nptr)
@@ -66,6 +66,10 @@ class Oracle:
             io.layers[l].weight = _nptr(out["weights"][l])
             io.layers[l].mask = _nptr(out["masks"][l]) if out["masks"] else None
         io.dropout_mask = _nptr(dropout_mask) if dropout_mask is not None else None
+        if packed_depth:
+            out["packed"] = [np.zeros((B, 1, h, w), np.uint64) for w, h in sizes]
+            for l in range(num_layers):
+                io.packed_depth[l] = _nptr(out["packed"][l])
         st = self.lib.adop_oracle_forward(C.byref(sc), va, B, C.byref(params), num_layers, C.byref(io), threads)
         assert st == 0, st
         out["views"] = va

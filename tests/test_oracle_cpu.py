@@ -529,3 +529,26 @@ def test_libtorch_operator_builds_and_registers():
     info.set_param("depth_accept", 0.01)
     with pytest.raises(RuntimeError, match="unknown render parameter"):
         info.set_param("no_such_field", 1.0)
+
+
+def test_packed_depth_index_word(oracle):
+    """The packed depth|index by-product: high word = the depth buffer's bits, low word = the lowest index among the points
+    that have that depth in the pixel (checked against a direct search), empty pixels hold (100000.0, 0xFFFFFFFF)."""
+    cfg = synth.make_config("c2", n_points=20000, n_views=2, size=(64, 36))
+    fwd = oracle.forward(cfg["arrays"], cfg["views"], cfg["params"], 3, packed_depth=True)
+    for l in range(3):
+        packed = fwd["packed"][l]
+        depth_bits = fwd["depths"][l].view(np.uint32)
+        assert np.array_equal((packed >> np.uint64(32)).astype(np.uint32), depth_bits)
+        idx = (packed & np.uint64(0xFFFFFFFF)).astype(np.uint32)
+        empty = fwd["depths"][l] == np.float32(100000.0)
+        assert np.all(idx[empty] == 0xFFFFFFFF) and np.all(idx[~empty] < 20000)
+    # direct search on layer 0 of view 0: the winner is the lowest index among the nearest points of the pixel
+    q = oracle.project(cfg["arrays"], cfg["views"][0], cfg["params"])
+    px, py = np.rint(q[:, 0]).astype(int), np.rint(q[:, 1]).astype(int)
+    ok = (q[:, 2] > 0) & (px >= 0) & (px < 64) & (py >= 0) & (py < 36)
+    idx0 = (fwd["packed"][0][0, 0] & np.uint64(0xFFFFFFFF)).astype(np.int64)
+    d0 = fwd["depths"][0][0, 0]
+    for y, x in zip(*np.nonzero(d0 < 100000.0)):
+        cand = np.nonzero(ok & (px == x) & (py == y) & (q[:, 2] == d0[y, x]))[0]
+        assert idx0[y, x] == cand.min()

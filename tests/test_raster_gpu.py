@@ -417,3 +417,22 @@ def test_accumulate_adds_to_existing_gradients(cuda_lib):
     torch.cuda.synchronize()
     for k in ("texture", "background", "points", "pose", "count_pose", "intrinsics", "count_intrinsics", "env_map"):
         close(acc[k], full[k].cpu().numpy(), name=k)
+
+
+@pytest.mark.gpu
+def test_packed_depth_index_word_matches_the_cpu_checker(oracle, cuda_lib):
+    """Optional packed depth|index planes: bit-exact against the CPU checker (the word does not depend on the order in
+    which the GPU visits the points), high word identical to the depth buffer, everything else unchanged."""
+    cfg = synth.make_config("c2", n_points=80_000, n_views=5, size=(160, 90))
+    ref = oracle.forward(cfg["arrays"], cfg["views"], cfg["params"], 4, packed_depth=True)
+    dev = torch.device("cuda:0")
+    scene = Scene(**{k: (torch.from_numpy(v).to(dev) if v is not None else None) for k, v in cfg["arrays"].items()})
+    ras = PointRasterizer(dev)
+    fwd = ras.forward(scene, cfg["views"], cfg["params"], 4, packed_depth=True)
+    plain = ras.forward(scene, cfg["views"], cfg["params"], 4)
+    torch.cuda.synchronize()
+    for l in range(4):
+        got = fwd.packed[l].cpu().numpy().view(np.uint64)
+        assert np.array_equal(got, ref["packed"][l])
+        assert np.array_equal((got >> np.uint64(32)).astype(np.uint32), fwd.depths[l].cpu().numpy().view(np.uint32))
+        assert torch.equal(fwd.depths[l], plain.depths[l]) and torch.equal(fwd.weights[l], plain.weights[l])
