@@ -125,7 +125,7 @@ inline void fill_layer_dims(int w, int h, int L, LayerTable* lt)
 // on the depth prepass: camera as a by-value kernel argument 72 us, through this pointer 82 us, in shared memory 90 us, in
 // an indexed __constant__ array 100 us; by-value needs the numbers on the host, which would cost a device-to-host sync.)
 constexpr int kCamChunk = 64;                      // views per chunk
-constexpr size_t kCamRegionBytes = 16384;          // head of the workspace, >= kCamChunk * sizeof(ViewCam)
+constexpr size_t kCamRegionBytes = 32768;          // head of the workspace, >= kCamChunk * sizeof(ViewCam)
 struct CamChunkSource
 {
     const double* poses;
@@ -202,6 +202,23 @@ inline int resident_grid(Kernel kernel, long long work_items)
     long long g = (long long)per_sm * sm_count();
     if (g > need) g = need;
     return g < 1 ? 1 : (int)g;
+}
+
+// Projection of the PLAIN kernels (no normal test, no radius rule): the five-vector camera record when the view's
+// camera allows it (pinhole, k1 and k2 only), else the general function. Same results either way.
+__device__ __forceinline__ bool project_plain(const ViewCam& cam, V3 p, float dist_cutoff, RasterPoint* q)
+{
+    const float4* hot = reinterpret_cast<const float4*>(cam.hot);
+    const float4 h4 = __ldg(hot + 4);
+    if (h4.w != 0.f)
+    {
+        const float4 h0 = __ldg(hot), h1 = __ldg(hot + 1), h2 = __ldg(hot + 2), h3 = __ldg(hot + 3);
+        return project_for_raster_hot(V4{h0.x, h0.y, h0.z, h0.w}, V4{h1.x, h1.y, h1.z, h1.w}, V4{h2.x, h2.y, h2.z, h2.w},
+                                      V4{h3.x, h3.y, h3.z, h3.w}, V4{h4.x, h4.y, h4.z, h4.w}, p, dist_cutoff, q);
+    }
+    V3 n;
+    n.x = n.y = n.z = 0.f;
+    return project_for_raster(cam, p, 0.f, n, false, false, dist_cutoff, q, false);
 }
 
 // layer that holds pyramid pixel (= accumulator record) r of a view

@@ -107,7 +107,8 @@ __global__ void __launch_bounds__(kBlock, 8) k_depth_prepass(PointStreams pts, c
         for (int v = 0; v < V; ++v)
         {
             RasterPoint q;
-            if (!project_for_raster(camp[v], f.p, f.r, f.n, f.has_normal, use_normal, kp.dist_cutoff, &q, use_radius)) continue;
+            if (PLAIN ? !project_plain(camp[v], f.p, kp.dist_cutoff, &q)
+                      : !project_for_raster(camp[v], f.p, f.r, f.n, f.has_normal, use_normal, kp.dist_cutoff, &q, use_radius)) continue;
             float x = q.x, y = q.y, rad = q.radius_px;
             const int zi = __float_as_int(q.z);
 #pragma unroll
@@ -226,7 +227,8 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, const flo
         if (PLAIN) { f.p.x = cur.x; f.p.y = cur.y; f.p.z = cur.z; f.r = cur.w; f.has_normal = false; f.n.x = f.n.y = f.n.z = 0.f; }
         else f = fetch_point(pts, i, cur);
         RasterPoint q;
-        if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, use_normal, kp.dist_cutoff, &q, use_radius)) return 0u;
+        if (PLAIN ? !project_plain(cam, f.p, kp.dist_cutoff, &q)
+                  : !project_for_raster(cam, f.p, f.r, f.n, f.has_normal, use_normal, kp.dist_cutoff, &q, use_radius)) return 0u;
         float x = q.x, y = q.y, rad = q.radius_px;
         // the depth reads of all layers go out together
         int pix[L];  // pixel index inside the layer (a pyramid has fewer than 2^31 pixels), -1 = not in this layer

@@ -479,7 +479,12 @@ struct ViewCam
     // x = a[0] dx + a[1] dy + a[2] ; y = a[3] dy + a[4]. The reference applies K, then the crop (PointRenderer.cu:255).
     float a[5];
     int radial2;  // pinhole with k3 = k4 = k5 = k6 = p1 = p2 = 0: the projection takes distort_radial2
+    // The same numbers once more, in the order the radial-only pinhole projection uses them, as five 16-byte vectors
+    // (project_for_raster_hot): rows of [R | t], then k1 k2 a0 a1, then a2 a3 a4 and a flag (1.0 = this record may be
+    // used: pinhole model, radial-only distortion).
+    alignas(16) float hot[20];
 };
+struct V4 { float x, y, z, w; };
 
 ADOP_HD ViewCam load_view_cam(const double* poses, const float* intrinsics, int intrinsics_cols, int image_index,
                               int camera_index, int camera_model, const float* crop5, int w0)
@@ -516,6 +521,14 @@ ADOP_HD ViewCam load_view_cam(const double* poses, const float* intrinsics, int 
         c.a[0] = c.a[1] = c.a[2] = c.a[3] = c.a[4] = 0.f;
         c.radial2 = 0;
     }
+    for (int r = 0; r < 3; ++r)
+    {
+        c.hot[4 * r] = c.V.r[3 * r]; c.hot[4 * r + 1] = c.V.r[3 * r + 1]; c.hot[4 * r + 2] = c.V.r[3 * r + 2];
+        c.hot[4 * r + 3] = c.V.t[r];
+    }
+    c.hot[12] = c.dist.k1; c.hot[13] = c.dist.k2; c.hot[14] = c.a[0]; c.hot[15] = c.a[1];
+    c.hot[16] = c.a[2]; c.hot[17] = c.a[3]; c.hot[18] = c.a[4];
+    c.hot[19] = (camera_model == kPinholeDistortion && c.radial2) ? 1.f : 0.f;
     return c;
 }
 
@@ -554,6 +567,33 @@ ADOP_HD bool project_for_raster(const ViewCam& c, V3 p, float drop_out_radius, V
     out->x = ip.x; out->y = ip.y; out->z = pr.z;
     // only the radius drop-out rule reads it (PointRenderer.cu:261-264); skipping it saves a division
     out->radius_px = want_radius ? focal * drop_out_radius / pr.z : 0.f;
+    return true;
+}
+
+// project_for_raster for the most common case — pinhole camera with k1, k2 only, no normal test, no radius rule —
+// reading the camera from the five vectors of ViewCam::hot (h3.w and h4.* hold k1 k2 a0 a1 | a2 a3 a4 flag). Operation
+// for operation the same arithmetic as the general function (transform_point, reciprocal, distort_radial2, the affine
+// map, the range check), so the same bits; a CPU test holds the two against each other.
+ADOP_HD bool project_for_raster_hot(V4 h0, V4 h1, V4 h2, V4 h3, V4 h4, V3 p, float dist_cutoff, RasterPoint* out)
+{
+    V3 view;
+    view.x = fmaf(h0.x, p.x, fmaf(h0.y, p.y, fmaf(h0.z, p.z, h0.w)));
+    view.y = fmaf(h1.x, p.x, fmaf(h1.y, p.y, fmaf(h1.z, p.z, h1.w)));
+    view.z = fmaf(h2.x, p.x, fmaf(h2.y, p.y, fmaf(h2.z, p.z, h2.w)));
+    float z = fmaxf(view.z, 0.f);
+    if (!(z > 0.f)) return false;
+    float iz = reciprocal(view.z);
+    float x = view.x * iz, y = view.y * iz;
+    float x2 = x * x, y2 = y * y;
+    float r2 = x2 + y2;
+    float rad = fmaf(fmaf(h3.y, r2, h3.x), r2, 1.0f);
+    float dx = x * rad, dy = y * rad;
+    if (r2 > dist_cutoff * dist_cutoff) return false;
+    float ix = fmaf(h3.z, dx, fmaf(h3.w, dy, h4.x));
+    float iy = fmaf(h4.y, dy, h4.z);
+    if (!(fabsf(ix) < 1.0e9f) || !(fabsf(iy) < 1.0e9f)) return false;
+    out->x = ix; out->y = iy; out->z = z;
+    out->radius_px = 0.f;
     return true;
 }
 

@@ -702,6 +702,25 @@ void adop_oracle_project(const adop_scene* s, const adop_view* v, const adop_ren
     }
 }
 
+// the five-vector form of the projection (project_for_raster_hot) on every point: out[i] = x, y, z, accepted (1 / 0);
+// returns 0 when the view's camera does not allow that form
+int adop_oracle_project_hot(const adop_scene* s, const adop_view* v, const adop_render_params* rp, float* out)
+{
+    ViewCam cam = view_cam(s, v);
+    if (cam.hot[19] == 0.f) return 0;
+    V4 h[5];
+    for (int k = 0; k < 5; ++k) { h[k].x = cam.hot[4 * k]; h[k].y = cam.hot[4 * k + 1]; h[k].z = cam.hot[4 * k + 2]; h[k].w = cam.hot[4 * k + 3]; }
+    for (int i = 0; i < s->num_points; ++i)
+    {
+        PointFetch f = fetch_point(s, i);
+        RasterPoint q;
+        bool ok = project_for_raster_hot(h[0], h[1], h[2], h[3], h[4], f.p, rp->dist_cutoff, &q);
+        out[(size_t)i * 4 + 0] = ok ? q.x : 0.f; out[(size_t)i * 4 + 1] = ok ? q.y : 0.f;
+        out[(size_t)i * 4 + 2] = ok ? q.z : 0.f; out[(size_t)i * 4 + 3] = ok ? 1.f : 0.f;
+    }
+    return 1;
+}
+
 // gradient chain of one point for an image-space gradient g (layer 0): out = g_point[3], g_pose[6], then
 // g_k[5] + g_dis[8] (pinhole) or g_affine[5] (OCam); returns 0 if the chain rejects the point
 int adop_oracle_project_backward(const adop_scene* s, const adop_view* v, const adop_render_params* rp, int point,

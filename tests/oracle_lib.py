@@ -39,6 +39,8 @@ class Oracle:
                         ("adop_oracle_unpack_normal", None, [C.c_int32, C.c_void_p]),
                         ("adop_oracle_project", None, [C.POINTER(capi.AdopScene), C.POINTER(capi.AdopView),
                                                        C.POINTER(capi.AdopRenderParams), C.c_void_p]),
+                        ("adop_oracle_project_hot", C.c_int, [C.POINTER(capi.AdopScene), C.POINTER(capi.AdopView),
+                                                              C.POINTER(capi.AdopRenderParams), C.c_void_p]),
                         ("adop_oracle_project_backward", C.c_int, [C.POINTER(capi.AdopScene), C.POINTER(capi.AdopView),
                                                                   C.POINTER(capi.AdopRenderParams), C.c_int, C.c_float,
                                                                   C.c_float, C.c_void_p]),
@@ -114,6 +116,14 @@ class Oracle:
         out = np.zeros((sc.num_points, 4), np.float32)
         self.lib.adop_oracle_project(C.byref(sc), va, C.byref(params), _nptr(out))
         return out
+
+    def project_hot(self, arrays, view, params):
+        """The five-vector form of the projection; None when the view's camera does not allow it."""
+        va = capi.make_views([view])
+        sc = fill_scene_struct(arrays, _nptr)
+        out = np.zeros((sc.num_points, 4), np.float32)
+        ok = self.lib.adop_oracle_project_hot(C.byref(sc), va, C.byref(params), _nptr(out))
+        return out if ok else None
 
     def project_backward(self, arrays, view, params, point, gx, gy):
         va = capi.make_views([view])

@@ -491,7 +491,7 @@ def test_c_abi_library_exports_every_declared_symbol():
     for f, _ in capi.AdopRenderParams._fields_:
         assert getattr(p, f) == getattr(d, f), f
     lib.adop_raster_workspace_bytes.restype = ctypes.c_size_t
-    assert lib.adop_raster_workspace_bytes(1920, 1080, 4, 4) == 16384 + 2754000 * 8 * 4 + 256
+    assert lib.adop_raster_workspace_bytes(1920, 1080, 4, 4) == 32768 + 2754000 * 8 * 4 + 256
     assert lib.adop_raster_workspace_bytes(0, 1080, 4, 4) == 0
 
 
@@ -552,3 +552,29 @@ def test_packed_depth_index_word(oracle):
     for y, x in zip(*np.nonzero(d0 < 100000.0)):
         cand = np.nonzero(ok & (px == x) & (py == y) & (q[:, 2] == d0[y, x]))[0]
         assert idx0[y, x] == cand.min()
+
+
+def test_five_vector_projection_has_the_same_bits_as_the_general_one(oracle):
+    """project_for_raster_hot (what the GPU's plain kernels use for pinhole cameras with k1, k2 only) against
+    project_for_raster, bit for bit, on points in front of, behind and far outside the camera; cameras with more
+    coefficients or the omnidirectional model do not offer the short form."""
+    cfg = synth.make_config("c2", n_points=200_000, n_views=3, size=(320, 180))
+    a = cfg["arrays"]
+    rng = np.random.default_rng(5)
+    a["position"][:5000, :3] *= 40.0                      # far outside: distortion cut-off and the range check
+    a["position"][5000:6000, :3] = rng.normal(0, 1e-3, (1000, 3)).astype(np.float32)
+    for view in cfg["views"]:
+        view = dict(view, crop=(1.3, 0.9, -20.5, 7.25, 0.01))
+        general = oracle.project(a, view, cfg["params"])
+        hot = oracle.project_hot(a, view, cfg["params"])
+        assert hot is not None
+        accepted = hot[:, 3] == 1
+        assert np.array_equal(accepted, general[:, 2] > 0)
+        assert np.array_equal(hot[:, :3].view(np.uint32), general[:, :3].view(np.uint32))
+        assert 0.2 < accepted.mean() < 1.0
+    full = dict(a)
+    full["intrinsics"] = a["intrinsics"].copy()
+    full["intrinsics"][0, 7] = 0.001                      # k3
+    assert oracle.project_hot(full, cfg["views"][0], cfg["params"]) is None
+    c3 = synth.make_config("c3", n_points=1000, size=(64, 36))
+    assert oracle.project_hot(c3["arrays"], c3["views"][0], c3["params"]) is None
