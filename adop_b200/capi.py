@@ -107,6 +107,7 @@ EXPORTED_SYMBOLS = [
     "adop_texture_interleave", "adop_texture_deinterleave",
     "adop_peer_alloc", "adop_peer_free", "adop_peer_open", "adop_peer_close", "adop_peer_layout_fill",
     "adop_peer_shard_range", "adop_peer_reduce_gradients",
+    "adop_points_morton_workspace_bytes", "adop_points_morton_order", "adop_points_permute",
 ]
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
@@ -166,6 +167,12 @@ def load_library():
     for name in ("adop_peer_alloc", "adop_peer_free", "adop_peer_open", "adop_peer_close", "adop_peer_layout_fill",
                  "adop_peer_reduce_gradients"):
         getattr(lib, name).restype = C.c_int
+    lib.adop_points_morton_workspace_bytes.argtypes = [C.c_int32]
+    lib.adop_points_morton_workspace_bytes.restype = C.c_size_t
+    lib.adop_points_morton_order.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.adop_points_morton_order.restype = C.c_int
+    lib.adop_points_permute.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
+    lib.adop_points_permute.restype = C.c_int
     lib.adop_profile_enable.argtypes = [C.c_int32]
     lib.adop_profile_enable.restype = C.c_int
     lib.adop_profile_collect.argtypes = [C.POINTER(AdopKernelTime), C.c_int32]

@@ -1,0 +1,366 @@
+// Point-cloud preprocessing on the GPU: the Morton-64 reorder that the rasterizer's memory behaviour depends on
+// (the reference calls point_cloud.ReorderMorton64() once per scene, src/lib/data/SceneData.cpp:100; the function itself
+// lives in saiga and is not in the reference tree, so the key below is this library's own definition, the same as the
+// numpy statement in adop_b200/synth.py: 21 bits per axis over the bounding box, x in the lowest interleaved bit).
+//
+//   k_bbox_partial / k_bbox_final   exact min / max of the positions (two deterministic stages)
+//   k_morton_keys                   float32 quantisation (no contraction: the same bits as numpy), bit interleave
+//   eight radix passes              least-significant digit first, 8 bits per pass, stable:
+//       k_radix_histogram           per-block digit counts of its tile (native integer shared-memory atomics)
+//       k_radix_scan                exclusive scan of the [digit][block] counts (one block walks the array)
+//       k_radix_scatter             rank inside the tile by warp match + per-warp digit counters, keys and point indices
+//                                   move to their sorted place
+//   k_permute_rows                  dst[i] = src[order[i]] for rows of 4..64 bytes (positions, normals, indices, planes)
+//
+// Integer / byte work bound by HBM: per pass a key is read twice and written once with its index (32 bytes), 8 passes.
+#include <cstdint>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace adop
+{
+
+constexpr int kRadixBits = 8;
+constexpr int kRadixBins = 1 << kRadixBits;
+constexpr int kRadixItems = 8;                        // keys per thread and tile
+constexpr int kRadixTile = kBlock * kRadixItems;      // 2048 keys per block
+constexpr int kRadixPasses = 8;                       // 63-bit keys
+constexpr int kBboxBlocks = 1024;
+static_assert(kBlock == kRadixBins, "one thread per digit");
+
+struct MortonWorkspace
+{
+    unsigned long long* keys[2];
+    int* index[2];
+    unsigned* hist;  // [kRadixBins][blocks]
+    float* bbox;     // [kBboxBlocks][6] partials, then [6] final at the end
+    int blocks;
+};
+
+static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+static size_t morton_layout(int n, char* base, MortonWorkspace* w)
+{
+    const int blocks = (n + kRadixTile - 1) / kRadixTile;
+    size_t at = 0;
+    auto take = [&](size_t bytes) { size_t o = at; at = align256(at + bytes); return o; };
+    size_t k0 = take(sizeof(unsigned long long) * (size_t)n), k1 = take(sizeof(unsigned long long) * (size_t)n);
+    size_t i0 = take(sizeof(int) * (size_t)n), i1 = take(sizeof(int) * (size_t)n);
+    size_t h = take(sizeof(unsigned) * (size_t)kRadixBins * (blocks > 0 ? blocks : 1));
+    size_t b = take(sizeof(float) * 6 * (kBboxBlocks + 1));
+    if (w)
+    {
+        w->keys[0] = reinterpret_cast<unsigned long long*>(base + k0);
+        w->keys[1] = reinterpret_cast<unsigned long long*>(base + k1);
+        w->index[0] = reinterpret_cast<int*>(base + i0);
+        w->index[1] = reinterpret_cast<int*>(base + i1);
+        w->hist = reinterpret_cast<unsigned*>(base + h);
+        w->bbox = reinterpret_cast<float*>(base + b);
+        w->blocks = blocks;
+    }
+    return at;
+}
+
+// ---- bounding box -------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void block_minmax(float* lo, float* hi, float* out6)
+{
+    __shared__ float s[kBlock / 32][6];
+#pragma unroll
+    for (int k = 0; k < 3; ++k)
+    {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+        {
+            lo[k] = fminf(lo[k], __shfl_xor_sync(0xffffffffu, lo[k], o));
+            hi[k] = fmaxf(hi[k], __shfl_xor_sync(0xffffffffu, hi[k], o));
+        }
+    }
+    if ((threadIdx.x & 31) == 0)
+    {
+#pragma unroll
+        for (int k = 0; k < 3; ++k) { s[threadIdx.x >> 5][k] = lo[k]; s[threadIdx.x >> 5][3 + k] = hi[k]; }
+    }
+    __syncthreads();
+    if (threadIdx.x < 6)
+    {
+        float v = s[0][threadIdx.x];
+        for (int wv = 1; wv < kBlock / 32; ++wv) v = threadIdx.x < 3 ? fminf(v, s[wv][threadIdx.x]) : fmaxf(v, s[wv][threadIdx.x]);
+        out6[threadIdx.x] = v;
+    }
+}
+
+__global__ void __launch_bounds__(kBlock) k_bbox_partial(const float4* __restrict__ pos, int n, float* __restrict__ partial)
+{
+    const float inf = __int_as_float(0x7f800000);
+    float lo[3] = {inf, inf, inf}, hi[3] = {-inf, -inf, -inf};
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+    {
+        const float4 p = __ldg(pos + i);
+        lo[0] = fminf(lo[0], p.x); lo[1] = fminf(lo[1], p.y); lo[2] = fminf(lo[2], p.z);
+        hi[0] = fmaxf(hi[0], p.x); hi[1] = fmaxf(hi[1], p.y); hi[2] = fmaxf(hi[2], p.z);
+    }
+    block_minmax(lo, hi, partial + 6 * blockIdx.x);
+}
+
+__global__ void __launch_bounds__(kBlock) k_bbox_final(const float* __restrict__ partial, int count, float* __restrict__ out6)
+{
+    const float inf = __int_as_float(0x7f800000);
+    float lo[3] = {inf, inf, inf}, hi[3] = {-inf, -inf, -inf};
+    for (int b = threadIdx.x; b < count; b += blockDim.x)
+    {
+#pragma unroll
+        for (int k = 0; k < 3; ++k) { lo[k] = fminf(lo[k], partial[6 * b + k]); hi[k] = fmaxf(hi[k], partial[6 * b + 3 + k]); }
+    }
+    block_minmax(lo, hi, out6);
+}
+
+// ---- keys ----------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long spread21(unsigned long long v)
+{
+    v &= 0x1FFFFFull;
+    v = (v | (v << 32)) & 0x1F00000000FFFFull;
+    v = (v | (v << 16)) & 0x1F0000FF0000FFull;
+    v = (v | (v << 8)) & 0x100F00F00F00F00Full;
+    v = (v | (v << 4)) & 0x10C30C30C30C30C3ull;
+    v = (v | (v << 2)) & 0x1249249249249249ull;
+    return v;
+}
+
+// q = min(trunc((p - lo) / span * 2097151), 2097151) in float32, one rounding per operation (this file is compiled
+// without contraction), span = max(hi - lo, 1e-12)
+__device__ __forceinline__ unsigned long long quantise21(float p, float lo, float hi)
+{
+    const float span = fmaxf(hi - lo, 1e-12f);
+    const float t = ((p - lo) / span) * 2097151.0f;
+    unsigned long long q = t > 0.f ? (unsigned long long)t : 0ull;  // NaN and negatives -> 0
+    return q < 2097151ull ? q : 2097151ull;
+}
+
+__global__ void __launch_bounds__(kBlock) k_morton_keys(const float4* __restrict__ pos, int n, const float* __restrict__ bbox,
+                                                         unsigned long long* __restrict__ keys, int* __restrict__ index)
+{
+    const float lx = bbox[0], ly = bbox[1], lz = bbox[2], hx = bbox[3], hy = bbox[4], hz = bbox[5];
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+    {
+        const float4 p = __ldg(pos + i);
+        keys[i] = spread21(quantise21(p.x, lx, hx)) | (spread21(quantise21(p.y, ly, hy)) << 1) | (spread21(quantise21(p.z, lz, hz)) << 2);
+        index[i] = i;
+    }
+}
+
+// ---- radix sort ----------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kBlock) k_radix_histogram(const unsigned long long* __restrict__ keys, int n, int shift,
+                                                             unsigned* __restrict__ hist, int blocks)
+{
+    __shared__ unsigned s_hist[kRadixBins];
+    s_hist[threadIdx.x] = 0;  // kBlock == kRadixBins
+    __syncthreads();
+    const int base = blockIdx.x * kRadixTile;
+#pragma unroll
+    for (int j = 0; j < kRadixItems; ++j)
+    {
+        const int i = base + j * kBlock + threadIdx.x;
+        if (i < n) atomicAdd(&s_hist[(unsigned)(__ldg(keys + i) >> shift) & (kRadixBins - 1)], 1u);
+    }
+    __syncthreads();
+    hist[(size_t)threadIdx.x * blocks + blockIdx.x] = s_hist[threadIdx.x];
+}
+
+// exclusive scan of count entries in place; one block, each thread takes a contiguous run per round
+__global__ void __launch_bounds__(1024) k_radix_scan(unsigned* __restrict__ data, size_t count)
+{
+    constexpr int PER = 8;
+    __shared__ unsigned s_warp[32];
+    __shared__ unsigned s_carry;
+    if (threadIdx.x == 0) s_carry = 0;
+    __syncthreads();
+    const size_t round = (size_t)blockDim.x * PER;
+    for (size_t base = 0; base < count; base += round)
+    {
+        unsigned v[PER];
+        unsigned sum = 0;
+        const size_t first = base + (size_t)threadIdx.x * PER;
+#pragma unroll
+        for (int k = 0; k < PER; ++k) { v[k] = first + k < count ? data[first + k] : 0u; sum += v[k]; }
+        unsigned incl = sum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1)
+        {
+            unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
+            if ((threadIdx.x & 31) >= o) incl += t;
+        }
+        if ((threadIdx.x & 31) == 31) s_warp[threadIdx.x >> 5] = incl;
+        __syncthreads();
+        if (threadIdx.x < 32)
+        {
+            unsigned w = s_warp[threadIdx.x], wi = w;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1)
+            {
+                unsigned t = __shfl_up_sync(0xffffffffu, wi, o);
+                if (threadIdx.x >= o) wi += t;
+            }
+            s_warp[threadIdx.x] = wi - w;  // exclusive over warps
+        }
+        __syncthreads();
+        unsigned run = s_carry + s_warp[threadIdx.x >> 5] + incl - sum;
+#pragma unroll
+        for (int k = 0; k < PER; ++k)
+        {
+            if (first + k < count) data[first + k] = run;
+            run += v[k];
+        }
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) s_carry = run;
+        __syncthreads();
+    }
+}
+
+__global__ void __launch_bounds__(kBlock) k_radix_scatter(const unsigned long long* __restrict__ keys_in, const int* __restrict__ index_in,
+                                                           int n, int shift, const unsigned* __restrict__ offsets, int blocks,
+                                                           unsigned long long* __restrict__ keys_out, int* __restrict__ index_out)
+{
+    // per-warp counters of the current group of 256 keys, ping-pong so that one barrier less is needed per group
+    __shared__ unsigned s_count[2][kBlock / 32][kRadixBins];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // thread d owns digit d: where the next key with that digit of this tile goes
+    unsigned my_base = offsets[(size_t)threadIdx.x * blocks + blockIdx.x];
+    const int base = blockIdx.x * kRadixTile;
+    for (int k = threadIdx.x; k < 2 * (kBlock / 32) * kRadixBins; k += kBlock) (&s_count[0][0][0])[k] = 0;
+    __syncthreads();
+#pragma unroll 1
+    for (int j = 0; j < kRadixItems; ++j)
+    {
+        unsigned(*cnt)[kRadixBins] = s_count[j & 1];
+        const int i = base + j * kBlock + threadIdx.x;
+        const bool live = i < n;
+        unsigned long long key = 0;
+        int idx = 0;
+        if (live) { key = __ldg(keys_in + i); idx = __ldg(index_in + i); }
+        // dead lanes get a digit value no live key can have, so they form their own group
+        const unsigned digit = live ? (unsigned)(key >> shift) & (kRadixBins - 1) : kRadixBins;
+        const unsigned peers = __match_any_sync(0xffffffffu, digit);
+        const unsigned rank = __popc(peers & ((1u << lane) - 1u));
+        if (live && rank == 0) cnt[warp][digit] = __popc(peers);
+        __syncthreads();
+        {
+            // digit d: running offsets over the warps (the order of the keys inside the tile is kept), then its base moves on
+            const unsigned d = threadIdx.x;
+            unsigned run = my_base;
+#pragma unroll
+            for (int w = 0; w < kBlock / 32; ++w)
+            {
+                const unsigned c = cnt[w][d];
+                cnt[w][d] = run;
+                run += c;
+            }
+            my_base = run;
+        }
+        __syncthreads();
+        if (live)
+        {
+            const unsigned at = cnt[warp][digit] + rank;
+            keys_out[at] = key;
+            index_out[at] = idx;
+        }
+        // clear the other buffer for the next group (nobody reads it any more: its readers passed the barrier above)
+        unsigned(*other)[kRadixBins] = s_count[(j + 1) & 1];
+#pragma unroll
+        for (int w = 0; w < kBlock / 32; ++w) other[w][threadIdx.x] = 0;
+        __syncthreads();
+    }
+}
+
+// ---- apply a permutation to rows -----------------------------------------------------------------------------------
+template <int WORDS>
+__global__ void __launch_bounds__(kBlock) k_permute_rows(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst,
+                                                          const int* __restrict__ order, int n)
+{
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+    {
+        const size_t from = (size_t)__ldg(order + i) * WORDS, to = (size_t)i * WORDS;
+        if (WORDS % 4 == 0)
+        {
+#pragma unroll
+            for (int k = 0; k < WORDS / 4; ++k)
+                reinterpret_cast<uint4*>(dst + to)[k] = __ldg(reinterpret_cast<const uint4*>(src + from) + k);
+        }
+        else
+        {
+#pragma unroll
+            for (int k = 0; k < WORDS; ++k) dst[to + k] = __ldg(src + from + k);
+        }
+    }
+}
+
+}  // namespace adop
+
+using namespace adop;
+
+extern "C" size_t adop_points_morton_workspace_bytes(int32_t num_points)
+{
+    if (num_points <= 0) return 0;
+    return morton_layout(num_points, nullptr, nullptr);
+}
+
+extern "C" adop_status adop_points_morton_order(const float* position, int32_t num_points, int32_t* order, void* workspace,
+                                                size_t workspace_bytes, void* stream)
+{
+    if (!position || !order || !workspace || num_points <= 0) return ADOP_ERR_INVALID_ARGUMENT;
+    if ((reinterpret_cast<uintptr_t>(position) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 255)) return ADOP_ERR_INVALID_ARGUMENT;
+    if (num_points > 0x7F000000) return ADOP_ERR_SIZE_LIMIT;
+    MortonWorkspace w;
+    if (workspace_bytes < morton_layout(num_points, static_cast<char*>(workspace), &w)) return ADOP_ERR_WORKSPACE_TOO_SMALL;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int n = num_points;
+    const float4* pos = reinterpret_cast<const float4*>(position);
+    int bbox_blocks = (n + kBlock - 1) / kBlock;
+    if (bbox_blocks > kBboxBlocks) bbox_blocks = kBboxBlocks;
+    float* bbox_final = w.bbox + 6 * kBboxBlocks;
+    ADOP_LAUNCH("k_bbox", st, (k_bbox_partial<<<bbox_blocks, kBlock, 0, st>>>(pos, n, w.bbox)));
+    ADOP_LAUNCH("k_bbox", st, (k_bbox_final<<<1, kBlock, 0, st>>>(w.bbox, bbox_blocks, bbox_final)));
+    int grid = (n + kBlock - 1) / kBlock;
+    if (grid > sm_count() * 8) grid = sm_count() * 8;
+    ADOP_LAUNCH("k_morton_keys", st, (k_morton_keys<<<grid, kBlock, 0, st>>>(pos, n, bbox_final, w.keys[0], w.index[0])));
+    int cur = 0;
+    for (int pass = 0; pass < kRadixPasses; ++pass)
+    {
+        const int shift = pass * kRadixBits;
+        // the last pass writes the point indices straight into the caller's array
+        int* index_out = pass == kRadixPasses - 1 ? order : w.index[cur ^ 1];
+        ADOP_LAUNCH("k_radix_histogram", st, (k_radix_histogram<<<w.blocks, kBlock, 0, st>>>(w.keys[cur], n, shift, w.hist, w.blocks)));
+        ADOP_LAUNCH("k_radix_scan", st, (k_radix_scan<<<1, 1024, 0, st>>>(w.hist, (size_t)kRadixBins * w.blocks)));
+        ADOP_LAUNCH("k_radix_scatter", st, (k_radix_scatter<<<w.blocks, kBlock, 0, st>>>(w.keys[cur], w.index[cur], n, shift, w.hist, w.blocks,
+                                                                                        w.keys[cur ^ 1], index_out)));
+        cur ^= 1;
+    }
+    ADOP_CUDA_TRY(cudaGetLastError());
+    return ADOP_OK;
+}
+
+extern "C" adop_status adop_points_permute(const void* src, void* dst, const int32_t* order, int32_t num_rows, int32_t row_bytes,
+                                           void* stream)
+{
+    if (!src || !dst || !order || num_rows <= 0 || src == dst) return ADOP_ERR_INVALID_ARGUMENT;
+    if (row_bytes <= 0 || row_bytes % 4 != 0) return ADOP_ERR_INVALID_ARGUMENT;
+    const bool wide = row_bytes % 16 == 0;
+    if (wide && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15)) return ADOP_ERR_INVALID_ARGUMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int grid = (num_rows + kBlock - 1) / kBlock;
+    if (grid > sm_count() * 16) grid = sm_count() * 16;
+    const uint32_t* s = static_cast<const uint32_t*>(src);
+    uint32_t* d = static_cast<uint32_t*>(dst);
+    switch (row_bytes / 4)
+    {
+        case 1: ADOP_LAUNCH("k_permute_rows", st, (k_permute_rows<1><<<grid, kBlock, 0, st>>>(s, d, order, num_rows))); break;
+        case 2: ADOP_LAUNCH("k_permute_rows", st, (k_permute_rows<2><<<grid, kBlock, 0, st>>>(s, d, order, num_rows))); break;
+        case 3: ADOP_LAUNCH("k_permute_rows", st, (k_permute_rows<3><<<grid, kBlock, 0, st>>>(s, d, order, num_rows))); break;
+        case 4: ADOP_LAUNCH("k_permute_rows", st, (k_permute_rows<4><<<grid, kBlock, 0, st>>>(s, d, order, num_rows))); break;
+        case 8: ADOP_LAUNCH("k_permute_rows", st, (k_permute_rows<8><<<grid, kBlock, 0, st>>>(s, d, order, num_rows))); break;
+        case 16: ADOP_LAUNCH("k_permute_rows", st, (k_permute_rows<16><<<grid, kBlock, 0, st>>>(s, d, order, num_rows))); break;
+        default: return ADOP_ERR_UNSUPPORTED;
+    }
+    ADOP_CUDA_TRY(cudaGetLastError());
+    return ADOP_OK;
+}

@@ -296,6 +296,22 @@ typedef struct adop_peer_reduce_out
 adop_status adop_peer_reduce_gradients(const void* const* blocks, int32_t world, int32_t rank,
                                        const adop_peer_layout* layout, const adop_peer_reduce_out* out, void* stream);
 
+/* ---- Point-cloud preprocessing on the GPU ----------------------------------------------------------------------
+ * point_cloud.ReorderMorton64(), called once per scene at src/lib/data/SceneData.cpp:100 (the function itself is saiga
+ * code that is not in the reference tree; the key is this library's definition: each coordinate quantised in float32
+ * to 21 bits over the cloud's bounding box, q = min(trunc((p - lo) / max(hi - lo, 1e-12) * 2097151), 2097151), bits
+ * interleaved with x lowest). The rasterizer's memory behaviour depends on this order.
+ *   position [N,4] f32 (device), order [N] i32 (device, out): order[i] = index of the point that comes i-th; points
+ *   with equal keys keep their original order (stable), so the result does not depend on the GPU's scheduling.
+ *   workspace: adop_points_morton_workspace_bytes(N) bytes, 256-byte aligned, contents irrelevant. */
+size_t adop_points_morton_workspace_bytes(int32_t num_points);
+adop_status adop_points_morton_order(const float* position, int32_t num_points, int32_t* order, void* workspace,
+                                     size_t workspace_bytes, void* stream);
+/* dst row i = src row order[i], rows of row_bytes bytes (4, 8, 12, 16, 32 or 64): positions [N,4], normals, indices,
+ * gradient rows, or one descriptor plane at a time. src and dst must not overlap. */
+adop_status adop_points_permute(const void* src, void* dst, const int32_t* order, int32_t num_rows, int32_t row_bytes,
+                                void* stream);
+
 /* ApplyTangentToPose, src/lib/rendering/PointRenderer.cu:1646-1665: pose <- exp(tangent) * pose, tangent <- 0.
  * tangent [n,6] f64, pose [n,8] f64. */
 adop_status adop_apply_tangent(double* tangent, double* pose, int32_t n, void* stream);
