@@ -7,7 +7,7 @@
 //   k_morton_keys                   float32 quantisation (no contraction: the same bits as numpy), bit interleave
 //   eight radix passes              least-significant digit first, 8 bits per pass, stable:
 //       k_radix_histogram           per-block digit counts of its tile (native integer shared-memory atomics)
-//       k_radix_scan                exclusive scan of the [digit][block] counts (one block walks the array)
+//       k_radix_scan                exclusive scan of each digit's per-block counts (one block per digit) + digit totals
 //       k_radix_scatter             rank inside the tile by warp match + per-warp digit counters, keys and point indices
 //                                   move to their sorted place
 //   k_permute_rows                  dst[i] = src[order[i]] for rows of 4..64 bytes (positions, normals, indices, planes)
@@ -35,6 +35,7 @@ struct MortonWorkspace
     int* index[2];
     unsigned* hist;  // [kRadixBins][blocks]
     float* bbox;     // [kBboxBlocks][6] partials, then [6] final at the end
+    unsigned* totals;  // [kRadixBins] keys per digit of the current pass
     int blocks;
 };
 
@@ -49,6 +50,7 @@ static size_t morton_layout(int n, char* base, MortonWorkspace* w)
     size_t i0 = take(sizeof(int) * (size_t)n), i1 = take(sizeof(int) * (size_t)n);
     size_t h = take(sizeof(unsigned) * (size_t)kRadixBins * (blocks > 0 ? blocks : 1));
     size_t b = take(sizeof(float) * 6 * (kBboxBlocks + 1));
+    size_t t = take(sizeof(unsigned) * kRadixBins);
     if (w)
     {
         w->keys[0] = reinterpret_cast<unsigned long long*>(base + k0);
@@ -57,6 +59,7 @@ static size_t morton_layout(int n, char* base, MortonWorkspace* w)
         w->index[1] = reinterpret_cast<int*>(base + i1);
         w->hist = reinterpret_cast<unsigned*>(base + h);
         w->bbox = reinterpret_cast<float*>(base + b);
+        w->totals = reinterpret_cast<unsigned*>(base + t);
         w->blocks = blocks;
     }
     return at;
@@ -167,22 +170,23 @@ __global__ void __launch_bounds__(kBlock) k_radix_histogram(const unsigned long 
     hist[(size_t)threadIdx.x * blocks + blockIdx.x] = s_hist[threadIdx.x];
 }
 
-// exclusive scan of count entries in place; one block, each thread takes a contiguous run per round
-__global__ void __launch_bounds__(1024) k_radix_scan(unsigned* __restrict__ data, size_t count)
+// One block per digit: exclusive scan of that digit's per-block counts in place, and the digit's total. (A first version
+// with a single block walking the whole [digit][block] array took 0.87 ms per pass for 10 M keys, 80 % of the sort.)
+__global__ void __launch_bounds__(kBlock) k_radix_scan(unsigned* __restrict__ data, int blocks, unsigned* __restrict__ totals)
 {
     constexpr int PER = 8;
-    __shared__ unsigned s_warp[32];
+    __shared__ unsigned s_warp[kBlock / 32];
     __shared__ unsigned s_carry;
+    unsigned* row = data + (size_t)blockIdx.x * blocks;
     if (threadIdx.x == 0) s_carry = 0;
     __syncthreads();
-    const size_t round = (size_t)blockDim.x * PER;
-    for (size_t base = 0; base < count; base += round)
+    for (int base = 0; base < blocks; base += kBlock * PER)
     {
         unsigned v[PER];
         unsigned sum = 0;
-        const size_t first = base + (size_t)threadIdx.x * PER;
+        const int first = base + threadIdx.x * PER;
 #pragma unroll
-        for (int k = 0; k < PER; ++k) { v[k] = first + k < count ? data[first + k] : 0u; sum += v[k]; }
+        for (int k = 0; k < PER; ++k) { v[k] = first + k < blocks ? row[first + k] : 0u; sum += v[k]; }
         unsigned incl = sum;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1)
@@ -192,40 +196,49 @@ __global__ void __launch_bounds__(1024) k_radix_scan(unsigned* __restrict__ data
         }
         if ((threadIdx.x & 31) == 31) s_warp[threadIdx.x >> 5] = incl;
         __syncthreads();
-        if (threadIdx.x < 32)
-        {
-            unsigned w = s_warp[threadIdx.x], wi = w;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1)
-            {
-                unsigned t = __shfl_up_sync(0xffffffffu, wi, o);
-                if (threadIdx.x >= o) wi += t;
-            }
-            s_warp[threadIdx.x] = wi - w;  // exclusive over warps
-        }
-        __syncthreads();
-        unsigned run = s_carry + s_warp[threadIdx.x >> 5] + incl - sum;
+        unsigned before = s_carry;
+        for (int w = 0; w < (int)(threadIdx.x >> 5); ++w) before += s_warp[w];
+        unsigned run = before + incl - sum;
 #pragma unroll
         for (int k = 0; k < PER; ++k)
         {
-            if (first + k < count) data[first + k] = run;
+            if (first + k < blocks) row[first + k] = run;
             run += v[k];
         }
         __syncthreads();
-        if (threadIdx.x == blockDim.x - 1) s_carry = run;
+        if (threadIdx.x == kBlock - 1) s_carry = run;
         __syncthreads();
     }
+    if (threadIdx.x == 0) totals[blockIdx.x] = s_carry;
 }
 
 __global__ void __launch_bounds__(kBlock) k_radix_scatter(const unsigned long long* __restrict__ keys_in, const int* __restrict__ index_in,
                                                            int n, int shift, const unsigned* __restrict__ offsets, int blocks,
+                                                           const unsigned* __restrict__ totals,
                                                            unsigned long long* __restrict__ keys_out, int* __restrict__ index_out)
 {
     // per-warp counters of the current group of 256 keys, ping-pong so that one barrier less is needed per group
     __shared__ unsigned s_count[2][kBlock / 32][kRadixBins];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    // thread d owns digit d: where the next key with that digit of this tile goes
-    unsigned my_base = offsets[(size_t)threadIdx.x * blocks + blockIdx.x];
+    // thread d owns digit d: where the next key with that digit of this tile goes = keys with smaller digits (exclusive
+    // scan of the 256 digit totals, done by every block for itself) + keys with this digit in earlier blocks
+    __shared__ unsigned s_tot[kBlock / 32];
+    unsigned my_base;
+    {
+        const unsigned t = totals[threadIdx.x];
+        unsigned incl = t;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1)
+        {
+            unsigned u = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += u;
+        }
+        if (lane == 31) s_tot[warp] = incl;
+        __syncthreads();
+        unsigned before = 0;
+        for (int w = 0; w < warp; ++w) before += s_tot[w];
+        my_base = before + incl - t + offsets[(size_t)threadIdx.x * blocks + blockIdx.x];
+    }
     const int base = blockIdx.x * kRadixTile;
     for (int k = threadIdx.x; k < 2 * (kBlock / 32) * kRadixBins; k += kBlock) (&s_count[0][0][0])[k] = 0;
     __syncthreads();
@@ -330,9 +343,9 @@ extern "C" adop_status adop_points_morton_order(const float* position, int32_t n
         // the last pass writes the point indices straight into the caller's array
         int* index_out = pass == kRadixPasses - 1 ? order : w.index[cur ^ 1];
         ADOP_LAUNCH("k_radix_histogram", st, (k_radix_histogram<<<w.blocks, kBlock, 0, st>>>(w.keys[cur], n, shift, w.hist, w.blocks)));
-        ADOP_LAUNCH("k_radix_scan", st, (k_radix_scan<<<1, 1024, 0, st>>>(w.hist, (size_t)kRadixBins * w.blocks)));
+        ADOP_LAUNCH("k_radix_scan", st, (k_radix_scan<<<kRadixBins, kBlock, 0, st>>>(w.hist, w.blocks, w.totals)));
         ADOP_LAUNCH("k_radix_scatter", st, (k_radix_scatter<<<w.blocks, kBlock, 0, st>>>(w.keys[cur], w.index[cur], n, shift, w.hist, w.blocks,
-                                                                                        w.keys[cur ^ 1], index_out)));
+                                                                                        w.totals, w.keys[cur ^ 1], index_out)));
         cur ^= 1;
     }
     ADOP_CUDA_TRY(cudaGetLastError());

@@ -28,9 +28,46 @@ def timed(fn, reps):
     return [ev[i].elapsed_time(ev[i + 1]) for i in range(reps)]
 
 
+def reorder(dev, args):
+    """Morton reorder of a c2-shaped cloud (default 10 M points): GPU time per kernel, keys/s, fraction of the HBM
+    roofline (32 bytes per key and pass: the key read for the histogram, key + index read and written by the scatter;
+    8 passes; 28 bytes per key to form the keys), and the numpy statement of the same sort timed beside it."""
+    import time
+    import numpy as np
+    from . import preprocess
+    n = args.points or 10_000_000
+    rng = np.random.default_rng(0)
+    xyz = rng.normal(0, 1.5, (n, 3)).astype(np.float32)
+    pos = torch.from_numpy(np.concatenate([xyz, np.ones((n, 1), np.float32)], axis=1)).to(dev)
+    order = preprocess.morton_order(pos)
+    torch.cuda.synchronize()
+    t = statistics.median(timed(lambda: preprocess.morton_order(pos), args.reps))
+    capi.profile_enable(True)
+    preprocess.morton_order(pos)
+    torch.cuda.synchronize()
+    kernel_ms = {k: round(v[1], 4) for k, v in capi.profile_collect().items()}
+    capi.profile_enable(False)
+    t_perm = statistics.median(timed(lambda: preprocess.permute_rows(pos, order), args.reps))
+    n_cpu = min(n, 2_000_000)
+    t0 = time.perf_counter()
+    want = synth.morton_order(xyz[:n_cpu])
+    t_cpu = time.perf_counter() - t0
+    same = bool(np.array_equal(preprocess.morton_order(pos[:n_cpu].contiguous()).cpu().numpy().astype(np.int64), want))
+    algo_bytes = n * (8 * 32 + 28)
+    peak = 6542.7
+    out = {"config": "reorder", "n_points": n, "morton_order_ms": t, "gkeys_per_s": n / (t * 1e-3) / 1e9,
+           "algorithmic_bytes": algo_bytes, "achieved_gbs": algo_bytes / (t * 1e-3) / 1e9,
+           "roofline_frac_of_measured_6542.7": algo_bytes / (t * 1e-3) / 1e9 / peak, "kernel_ms": kernel_ms,
+           "permute_positions_ms": t_perm, "permute_gbs": n * 36 / (t_perm * 1e-3) / 1e9,
+           "cpu_numpy": {"points": n_cpu, "seconds": t_cpu, "gkeys_per_s": n_cpu / t_cpu / 1e9, "cores": 1,
+                         "same_permutation_as_gpu": same}}
+    print(json.dumps(out), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("config", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("config", choices=["c1", "c2", "c3", "c4", "c5", "reorder"])
     ap.add_argument("--points", type=int, default=None)
     ap.add_argument("--views", type=int, default=None)
     ap.add_argument("--reps", type=int, default=5)
@@ -38,6 +75,8 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device")
     dev = torch.device("cuda:0")
+    if args.config == "reorder":
+        return reorder(dev, args)
     cfg = synth.make_config(args.config, n_points=args.points, n_views=args.views)
     meta, params, L = cfg["meta"], cfg["params"], cfg["num_layers"]
     forward_only = args.config == "c3"
