@@ -108,6 +108,8 @@ EXPORTED_SYMBOLS = [
     "adop_peer_alloc", "adop_peer_free", "adop_peer_open", "adop_peer_close", "adop_peer_layout_fill",
     "adop_peer_shard_range", "adop_peer_reduce_gradients",
     "adop_points_morton_workspace_bytes", "adop_points_morton_order", "adop_points_permute",
+    "adop_points_block_shuffle_order", "adop_points_sort_blocks_by_radius_order",
+    "adop_points_knn_workspace_bytes", "adop_points_knn_distance", "adop_points_radius_sample",
 ]
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
@@ -171,6 +173,16 @@ def load_library():
     lib.adop_points_morton_workspace_bytes.restype = C.c_size_t
     lib.adop_points_morton_order.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
     lib.adop_points_morton_order.restype = C.c_int
+    lib.adop_points_block_shuffle_order.argtypes = [C.c_int32, C.c_int32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.adop_points_block_shuffle_order.restype = C.c_int
+    lib.adop_points_sort_blocks_by_radius_order.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]
+    lib.adop_points_sort_blocks_by_radius_order.restype = C.c_int
+    lib.adop_points_knn_workspace_bytes.argtypes = [C.c_int32]
+    lib.adop_points_knn_workspace_bytes.restype = C.c_size_t
+    lib.adop_points_knn_distance.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.adop_points_knn_distance.restype = C.c_int
+    lib.adop_points_radius_sample.argtypes = [C.c_void_p, C.c_int32, C.c_uint32, C.c_void_p, C.c_void_p]
+    lib.adop_points_radius_sample.restype = C.c_int
     lib.adop_points_permute.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
     lib.adop_points_permute.restype = C.c_int
     lib.adop_profile_enable.argtypes = [C.c_int32]

@@ -307,6 +307,230 @@ __global__ void __launch_bounds__(kBlock) k_permute_rows(const uint32_t* __restr
     }
 }
 
+// ---- ComputeRadius(n), SceneData.cpp:441-484: distance to the n-th nearest other point, exact -----------------------
+// (the reference builds a saiga KD-tree on the host; here: a uniform grid over the bounding box, points sorted by cell
+// with the radix sort above, and per point a search over growing cubes of cells that stops as soon as the (n+1)-th
+// smallest squared distance found - the point itself included, as in the reference - cannot be beaten from outside
+// the cube). Distances are float32: ((dx*dx + dy*dy) + dz*dz), no contraction; the result is the square root of the
+// (n+1)-th smallest such value, which does not depend on the order in which the candidates are seen.
+constexpr int kGridMax = 256;   // cells per axis at most: 2^24 cells, three radix passes
+constexpr int kKnnMax = 16;
+
+struct GridParams
+{
+    float lo[3];
+    float cell;      // edge length of a cell
+    float inv_cell;
+    int dim[3];
+};
+
+__global__ void k_grid_params(const float* __restrict__ bbox, int n, float per_cell, GridParams* __restrict__ out)
+{
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    GridParams g;
+    float ext[3], longest = 0.f, volume = 1.f;
+    for (int k = 0; k < 3; ++k)
+    {
+        g.lo[k] = bbox[k];
+        ext[k] = fmaxf(bbox[3 + k] - bbox[k], 1e-12f);
+        longest = fmaxf(longest, ext[k]);
+    }
+    for (int k = 0; k < 3; ++k) volume *= fmaxf(ext[k], longest * 1e-3f);  // flat clouds: do not let one thin axis shrink the cells
+    float cell = cbrtf(volume * per_cell / (float)n);
+    cell = fmaxf(cell, longest / (float)kGridMax * 1.0001f);
+    g.cell = cell;
+    g.inv_cell = 1.0f / cell;
+    for (int k = 0; k < 3; ++k)
+    {
+        int d = (int)(ext[k] * g.inv_cell) + 1;
+        g.dim[k] = d < 1 ? 1 : (d > kGridMax ? kGridMax : d);
+    }
+    *out = g;
+}
+
+__device__ __forceinline__ int cell_coord(float p, float lo, float inv_cell, int dim)
+{
+    int c = (int)((p - lo) * inv_cell);
+    return c < 0 ? 0 : (c >= dim ? dim - 1 : c);
+}
+
+__global__ void __launch_bounds__(kBlock) k_cell_keys(const float4* __restrict__ pos, int n, const GridParams* __restrict__ gp,
+                                                       unsigned long long* __restrict__ keys, int* __restrict__ index)
+{
+    const GridParams g = *gp;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+    {
+        const float4 p = __ldg(pos + i);
+        const int cx = cell_coord(p.x, g.lo[0], g.inv_cell, g.dim[0]);
+        const int cy = cell_coord(p.y, g.lo[1], g.inv_cell, g.dim[1]);
+        const int cz = cell_coord(p.z, g.lo[2], g.inv_cell, g.dim[2]);
+        keys[i] = (unsigned long long)((cz * g.dim[1] + cy) * g.dim[0] + cx);
+        index[i] = i;
+    }
+}
+
+__global__ void __launch_bounds__(kBlock) k_cell_bounds(const unsigned long long* __restrict__ sorted_keys, int n, int* __restrict__ start,
+                                                         int* __restrict__ end)
+{
+    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < n; j += gridDim.x * blockDim.x)
+    {
+        const unsigned long long c = sorted_keys[j];
+        if (j == 0 || sorted_keys[j - 1] != c) start[c] = j;
+        if (j == n - 1 || sorted_keys[j + 1] != c) end[c] = j + 1;
+    }
+}
+
+// KT > 0: k known at compile time (the list of the k+1 smallest stays in registers); KT = 0: any k up to kKnnMax
+template <int KT>
+__global__ void __launch_bounds__(kBlock) k_knn_distance(const float4* __restrict__ sorted_pos, const int* __restrict__ order, int n,
+                                                          const GridParams* __restrict__ gp, const int* __restrict__ start,
+                                                          const int* __restrict__ end, int k_runtime, float* __restrict__ out)
+{
+    constexpr int KCAP = KT > 0 ? KT : kKnnMax;
+    const int k = KT > 0 ? KT : k_runtime;
+    const GridParams g = *gp;
+    const float inf = __int_as_float(0x7f800000);
+    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < n; j += gridDim.x * blockDim.x)
+    {
+        const float4 p = __ldg(sorted_pos + j);
+        const int cx = cell_coord(p.x, g.lo[0], g.inv_cell, g.dim[0]);
+        const int cy = cell_coord(p.y, g.lo[1], g.inv_cell, g.dim[1]);
+        const int cz = cell_coord(p.z, g.lo[2], g.inv_cell, g.dim[2]);
+        float best[KCAP + 1];
+        float kth = inf;
+        for (int r = 1;; ++r)
+        {
+#pragma unroll
+            for (int q = 0; q <= KCAP; ++q) best[q] = inf;
+            const int x0 = max(cx - r, 0), x1 = min(cx + r, g.dim[0] - 1);
+            const int y0 = max(cy - r, 0), y1 = min(cy + r, g.dim[1] - 1);
+            const int z0 = max(cz - r, 0), z1 = min(cz + r, g.dim[2] - 1);
+            for (int z = z0; z <= z1; ++z)
+                for (int y = y0; y <= y1; ++y)
+                {
+                    // the cells of a row are consecutive keys, and so are their points in the sorted array
+                    const int row = (z * g.dim[1] + y) * g.dim[0];
+                    int a = -1, b = -1;
+                    for (int x = x0; x <= x1; ++x)
+                    {
+                        const int e = __ldg(end + row + x);
+                        if (e == 0) continue;  // empty cell
+                        if (a < 0) a = __ldg(start + row + x);
+                        b = e;
+                    }
+                    for (int m = a; m < b; ++m)
+                    {
+                        const float4 o = __ldg(sorted_pos + m);
+                        const float dx = p.x - o.x, dy = p.y - o.y, dz = p.z - o.z;
+                        const float d2 = (dx * dx + dy * dy) + dz * dz;
+                        if (d2 < best[k])
+                        {
+                            // insertion into the ascending list of the k+1 smallest
+                            float carry = d2;
+#pragma unroll
+                            for (int q = 0; q <= KCAP; ++q)
+                                if (q <= k && carry < best[q]) { const float t = best[q]; best[q] = carry; carry = t; }
+                        }
+                    }
+                }
+            kth = best[k];
+            const bool whole = x0 == 0 && y0 == 0 && z0 == 0 && x1 == g.dim[0] - 1 && y1 == g.dim[1] - 1 && z1 == g.dim[2] - 1;
+            if (whole) break;
+            // nothing outside the cube is nearer than the nearest face that is not a face of the grid itself
+            float reach = inf;
+            if (x0 > 0) reach = fminf(reach, p.x - (g.lo[0] + (float)x0 * g.cell));
+            if (y0 > 0) reach = fminf(reach, p.y - (g.lo[1] + (float)y0 * g.cell));
+            if (z0 > 0) reach = fminf(reach, p.z - (g.lo[2] + (float)z0 * g.cell));
+            if (x1 < g.dim[0] - 1) reach = fminf(reach, (g.lo[0] + (float)(x1 + 1) * g.cell) - p.x);
+            if (y1 < g.dim[1] - 1) reach = fminf(reach, (g.lo[1] + (float)(y1 + 1) * g.cell) - p.y);
+            if (z1 < g.dim[2] - 1) reach = fminf(reach, (g.lo[2] + (float)(z1 + 1) * g.cell) - p.z);
+            reach -= 1.0e-4f * g.cell;  // cell faces are rounded numbers (up to 256 cells times one float32 rounding each)
+            if (reach > 0.f && kth <= reach * reach) break;
+        }
+        out[__ldg(order + j)] = sqrtf(kth);
+    }
+}
+
+// data(3) = data(0) * sqrt(1 / u), u uniform in (0, 1] (SceneData.cpp:476-482; the reference draws u from its global
+// random generator, here it is the counter hash of (seed, 1, point))
+__global__ void __launch_bounds__(kBlock) k_radius_sample(const float* __restrict__ distance, int n, unsigned seed, float* __restrict__ radius)
+{
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+    {
+        const float u = (float)((hash_u32(seed, 1u, (unsigned)i) >> 8) + 1u) * (1.0f / 16777216.0f);
+        radius[i] = distance[i] * sqrtf(1.0f / u);
+    }
+}
+
+// ---- RandomBlockShuffle(256) and SortBlocksByRadius(256), SceneData.cpp:101-103, 671-684 -----------------------------
+// Blocks of `block` consecutive points are put into a seeded pseudo-random order (key = hash_u32(seed, 0, block number),
+// ties by block number); points past the last full block stay where they are.
+__global__ void __launch_bounds__(kBlock) k_block_keys(int blocks, unsigned seed, unsigned long long* __restrict__ keys, int* __restrict__ index)
+{
+    for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < blocks; b += gridDim.x * blockDim.x)
+    {
+        keys[b] = ((unsigned long long)hash_u32(seed, 0u, (unsigned)b) << 32) | (unsigned)b;
+        index[b] = b;
+    }
+}
+__global__ void __launch_bounds__(kBlock) k_expand_block_order(const int* __restrict__ block_order, int blocks, int block, int n,
+                                                                int* __restrict__ order)
+{
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+    {
+        const int b = i / block;
+        order[i] = b < blocks ? __ldg(block_order + b) * block + (i - b * block) : i;
+    }
+}
+
+// Inside every full block of 256 points: ascending drop-out radius (position.w), equal radii by index. One thread block
+// per point block, bitonic network in shared memory on (orderable radius bits << 32 | index in block): keys are unique.
+__global__ void __launch_bounds__(kBlock) k_sort_blocks_by_radius(const float4* __restrict__ pos, int n, int* __restrict__ order)
+{
+    __shared__ unsigned long long s_key[kBlock];
+    const int base = blockIdx.x * kBlock;
+    if (base + kBlock > n)
+    {
+        // the incomplete last block is left alone (SceneData.cpp:673)
+        if (base + (int)threadIdx.x < n) order[base + threadIdx.x] = base + threadIdx.x;
+        return;
+    }
+    unsigned bits = __float_as_uint(__ldg(pos + base + threadIdx.x).w);
+    bits = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);  // total order of the floats as unsigned integers
+    s_key[threadIdx.x] = ((unsigned long long)bits << 32) | threadIdx.x;
+    __syncthreads();
+    for (int k = 2; k <= kBlock; k <<= 1)
+        for (int j = k >> 1; j > 0; j >>= 1)
+        {
+            const int partner = threadIdx.x ^ j;
+            if (partner > (int)threadIdx.x)
+            {
+                const unsigned long long a = s_key[threadIdx.x], b = s_key[partner];
+                const bool up = (threadIdx.x & k) == 0;
+                if ((a > b) == up) { s_key[threadIdx.x] = b; s_key[partner] = a; }
+            }
+            __syncthreads();
+        }
+    order[base + threadIdx.x] = base + (int)(s_key[threadIdx.x] & 0xFFFFFFFFu);
+}
+
+// keys[0] / index[0] of the workspace -> the sorted indices in `order` (stable); `passes` digits of 8 bits are sorted
+static void radix_sort_passes(const MortonWorkspace& w, int n, int passes, int* order, cudaStream_t st)
+{
+    int cur = 0;
+    for (int pass = 0; pass < passes; ++pass)
+    {
+        const int shift = pass * kRadixBits;
+        // the last pass writes the indices straight into the caller's array
+        int* index_out = pass == passes - 1 ? order : w.index[cur ^ 1];
+        ADOP_LAUNCH("k_radix_histogram", st, (k_radix_histogram<<<w.blocks, kBlock, 0, st>>>(w.keys[cur], n, shift, w.hist, w.blocks)));
+        ADOP_LAUNCH("k_radix_scan", st, (k_radix_scan<<<kRadixBins, kBlock, 0, st>>>(w.hist, w.blocks, w.totals)));
+        ADOP_LAUNCH("k_radix_scatter", st, (k_radix_scatter<<<w.blocks, kBlock, 0, st>>>(w.keys[cur], w.index[cur], n, shift, w.hist, w.blocks,
+                                                                                        w.totals, w.keys[cur ^ 1], index_out)));
+        cur ^= 1;
+    }
+}
+
 }  // namespace adop
 
 using namespace adop;
@@ -336,18 +560,7 @@ extern "C" adop_status adop_points_morton_order(const float* position, int32_t n
     int grid = (n + kBlock - 1) / kBlock;
     if (grid > sm_count() * 8) grid = sm_count() * 8;
     ADOP_LAUNCH("k_morton_keys", st, (k_morton_keys<<<grid, kBlock, 0, st>>>(pos, n, bbox_final, w.keys[0], w.index[0])));
-    int cur = 0;
-    for (int pass = 0; pass < kRadixPasses; ++pass)
-    {
-        const int shift = pass * kRadixBits;
-        // the last pass writes the point indices straight into the caller's array
-        int* index_out = pass == kRadixPasses - 1 ? order : w.index[cur ^ 1];
-        ADOP_LAUNCH("k_radix_histogram", st, (k_radix_histogram<<<w.blocks, kBlock, 0, st>>>(w.keys[cur], n, shift, w.hist, w.blocks)));
-        ADOP_LAUNCH("k_radix_scan", st, (k_radix_scan<<<kRadixBins, kBlock, 0, st>>>(w.hist, w.blocks, w.totals)));
-        ADOP_LAUNCH("k_radix_scatter", st, (k_radix_scatter<<<w.blocks, kBlock, 0, st>>>(w.keys[cur], w.index[cur], n, shift, w.hist, w.blocks,
-                                                                                        w.totals, w.keys[cur ^ 1], index_out)));
-        cur ^= 1;
-    }
+    radix_sort_passes(w, n, kRadixPasses, order, st);
     ADOP_CUDA_TRY(cudaGetLastError());
     return ADOP_OK;
 }
@@ -374,6 +587,119 @@ extern "C" adop_status adop_points_permute(const void* src, void* dst, const int
         case 16: ADOP_LAUNCH("k_permute_rows", st, (k_permute_rows<16><<<grid, kBlock, 0, st>>>(s, d, order, num_rows))); break;
         default: return ADOP_ERR_UNSUPPORTED;
     }
+    ADOP_CUDA_TRY(cudaGetLastError());
+    return ADOP_OK;
+}
+
+extern "C" adop_status adop_points_block_shuffle_order(int32_t num_points, int32_t block, uint32_t seed, int32_t* order, void* workspace,
+                                                       size_t workspace_bytes, void* stream)
+{
+    if (!order || !workspace || num_points <= 0 || block <= 0) return ADOP_ERR_INVALID_ARGUMENT;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255) return ADOP_ERR_INVALID_ARGUMENT;
+    if (num_points > 0x7F000000) return ADOP_ERR_SIZE_LIMIT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int blocks = num_points / block;
+    int grid = (num_points + kBlock - 1) / kBlock;
+    if (grid > sm_count() * 16) grid = sm_count() * 16;
+    if (blocks < 2)
+    {
+        ADOP_LAUNCH("k_expand_block_order", st, (k_expand_block_order<<<grid, kBlock, 0, st>>>(nullptr, 0, block, num_points, order)));
+        ADOP_CUDA_TRY(cudaGetLastError());
+        return ADOP_OK;
+    }
+    // the workspace of a Morton reorder of the same cloud is always large enough (one key per block of points here)
+    MortonWorkspace w;
+    if (workspace_bytes < morton_layout(blocks, static_cast<char*>(workspace), &w) + align256(sizeof(int) * (size_t)blocks))
+        return ADOP_ERR_WORKSPACE_TOO_SMALL;
+    int* block_order = reinterpret_cast<int*>(static_cast<char*>(workspace) + morton_layout(blocks, nullptr, nullptr));
+    int gb = (blocks + kBlock - 1) / kBlock;
+    ADOP_LAUNCH("k_block_keys", st, (k_block_keys<<<gb, kBlock, 0, st>>>(blocks, seed, w.keys[0], w.index[0])));
+    radix_sort_passes(w, blocks, kRadixPasses, block_order, st);
+    ADOP_LAUNCH("k_expand_block_order", st, (k_expand_block_order<<<grid, kBlock, 0, st>>>(block_order, blocks, block, num_points, order)));
+    ADOP_CUDA_TRY(cudaGetLastError());
+    return ADOP_OK;
+}
+
+extern "C" adop_status adop_points_sort_blocks_by_radius_order(const float* position, int32_t num_points, int32_t* order, void* stream)
+{
+    if (!position || !order || num_points <= 0 || (reinterpret_cast<uintptr_t>(position) & 15)) return ADOP_ERR_INVALID_ARGUMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = (num_points + kBlock - 1) / kBlock;
+    ADOP_LAUNCH("k_sort_blocks_by_radius", st, (k_sort_blocks_by_radius<<<grid, kBlock, 0, st>>>(reinterpret_cast<const float4*>(position),
+                                                                                                num_points, order)));
+    ADOP_CUDA_TRY(cudaGetLastError());
+    return ADOP_OK;
+}
+
+static size_t knn_extra_layout(int n, char* base, GridParams** gp, float4** sorted_pos, int** start, int** end, int** order, float** dist)
+{
+    size_t at = 0;
+    auto take = [&](size_t bytes) { size_t o = at; at = align256(at + bytes); return o; };
+    const size_t cells = (size_t)kGridMax * kGridMax * kGridMax;
+    size_t a = take(sizeof(GridParams)), b = take(sizeof(float4) * (size_t)n), c = take(sizeof(int) * cells), d = take(sizeof(int) * cells);
+    size_t e = take(sizeof(int) * (size_t)n), f = take(sizeof(float) * (size_t)n);
+    if (base)
+    {
+        *gp = reinterpret_cast<GridParams*>(base + a);
+        *sorted_pos = reinterpret_cast<float4*>(base + b);
+        *start = reinterpret_cast<int*>(base + c);
+        *end = reinterpret_cast<int*>(base + d);
+        *order = reinterpret_cast<int*>(base + e);
+        *dist = reinterpret_cast<float*>(base + f);
+    }
+    return at;
+}
+
+extern "C" size_t adop_points_knn_workspace_bytes(int32_t num_points)
+{
+    if (num_points <= 0) return 0;
+    return morton_layout(num_points, nullptr, nullptr) + knn_extra_layout(num_points, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr);
+}
+
+extern "C" adop_status adop_points_knn_distance(const float* position, int32_t num_points, int32_t k, float* distance, void* workspace,
+                                                size_t workspace_bytes, void* stream)
+{
+    if (!position || !distance || !workspace || num_points <= 0 || k < 1 || k > kKnnMax) return ADOP_ERR_INVALID_ARGUMENT;
+    if ((reinterpret_cast<uintptr_t>(position) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 255)) return ADOP_ERR_INVALID_ARGUMENT;
+    if (num_points > 0x7F000000) return ADOP_ERR_SIZE_LIMIT;
+    if (workspace_bytes < adop_points_knn_workspace_bytes(num_points)) return ADOP_ERR_WORKSPACE_TOO_SMALL;
+    MortonWorkspace w;
+    const size_t first = morton_layout(num_points, static_cast<char*>(workspace), &w);
+    GridParams* gp; float4* sorted_pos; int *start, *end, *order; float* dist_unused;
+    knn_extra_layout(num_points, static_cast<char*>(workspace) + first, &gp, &sorted_pos, &start, &end, &order, &dist_unused);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int n = num_points;
+    const float4* pos = reinterpret_cast<const float4*>(position);
+    int bbox_blocks = (n + kBlock - 1) / kBlock;
+    if (bbox_blocks > kBboxBlocks) bbox_blocks = kBboxBlocks;
+    float* bbox_final = w.bbox + 6 * kBboxBlocks;
+    ADOP_LAUNCH("k_bbox", st, (k_bbox_partial<<<bbox_blocks, kBlock, 0, st>>>(pos, n, w.bbox)));
+    ADOP_LAUNCH("k_bbox", st, (k_bbox_final<<<1, kBlock, 0, st>>>(w.bbox, bbox_blocks, bbox_final)));
+    ADOP_LAUNCH("k_grid_params", st, (k_grid_params<<<1, 32, 0, st>>>(bbox_final, n, 2.0f, gp)));
+    int grid = (n + kBlock - 1) / kBlock;
+    if (grid > sm_count() * 8) grid = sm_count() * 8;
+    ADOP_LAUNCH("k_cell_keys", st, (k_cell_keys<<<grid, kBlock, 0, st>>>(pos, n, gp, w.keys[0], w.index[0])));
+    radix_sort_passes(w, n, 3, order, st);  // 2^24 cells: three digits; the sorted keys end up in keys[1]
+    ADOP_LAUNCH("k_permute_rows", st, (k_permute_rows<4><<<grid, kBlock, 0, st>>>(reinterpret_cast<const uint32_t*>(position),
+                                                                                 reinterpret_cast<uint32_t*>(sorted_pos), order, n)));
+    const size_t cells = (size_t)kGridMax * kGridMax * kGridMax;
+    ADOP_CUDA_TRY(cudaMemsetAsync(end, 0, sizeof(int) * cells, st));  // end == 0 marks an empty cell; start is read only where end != 0
+    ADOP_LAUNCH("k_cell_bounds", st, (k_cell_bounds<<<grid, kBlock, 0, st>>>(w.keys[1], n, start, end)));
+    if (k == 4)  // ComputeRadius' default
+        ADOP_LAUNCH("k_knn_distance", st, (k_knn_distance<4><<<grid, kBlock, 0, st>>>(sorted_pos, order, n, gp, start, end, k, distance)));
+    else
+        ADOP_LAUNCH("k_knn_distance", st, (k_knn_distance<0><<<grid, kBlock, 0, st>>>(sorted_pos, order, n, gp, start, end, k, distance)));
+    ADOP_CUDA_TRY(cudaGetLastError());
+    return ADOP_OK;
+}
+
+extern "C" adop_status adop_points_radius_sample(const float* distance, int32_t num_points, uint32_t seed, float* radius, void* stream)
+{
+    if (!distance || !radius || num_points <= 0) return ADOP_ERR_INVALID_ARGUMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int grid = (num_points + kBlock - 1) / kBlock;
+    if (grid > sm_count() * 16) grid = sm_count() * 16;
+    ADOP_LAUNCH("k_radius_sample", st, (k_radius_sample<<<grid, kBlock, 0, st>>>(distance, num_points, seed, radius)));
     ADOP_CUDA_TRY(cudaGetLastError());
     return ADOP_OK;
 }

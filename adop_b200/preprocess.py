@@ -27,6 +27,54 @@ def morton_order(position):
     return order
 
 
+def block_shuffle_order(num_points, device, block=256, seed=0):
+    """RandomBlockShuffle(256): [N] int32 order that moves whole blocks of `block` points into a seeded pseudo-random order."""
+    lib = capi.load_library()
+    device = torch.device(device)
+    with torch.cuda.device(device):
+        order = torch.empty(num_points, dtype=torch.int32, device=device)
+        ws = torch.empty(max(lib.adop_points_morton_workspace_bytes(num_points), 4096), dtype=torch.uint8, device=device)
+        stream = torch.cuda.current_stream(device).cuda_stream
+        capi.check(lib.adop_points_block_shuffle_order(num_points, block, seed, order.data_ptr(), ws.data_ptr(), ws.numel(),
+                                                       C.c_void_p(stream)), "adop_points_block_shuffle_order")
+    return order
+
+
+def sort_blocks_by_radius_order(position):
+    """SortBlocksByRadius(256): [N] int32 order that sorts every full block of 256 points by position[:, 3] (then index)."""
+    lib = capi.load_library()
+    with torch.cuda.device(position.device):
+        order = torch.empty(position.shape[0], dtype=torch.int32, device=position.device)
+        stream = torch.cuda.current_stream(position.device).cuda_stream
+        capi.check(lib.adop_points_sort_blocks_by_radius_order(position.data_ptr(), position.shape[0], order.data_ptr(),
+                                                               C.c_void_p(stream)), "adop_points_sort_blocks_by_radius_order")
+    return order
+
+
+def knn_distance(position, k=4):
+    """ComputeRadius' first half: [N] float32 distance of every point to its k-th nearest other point (exact)."""
+    lib = capi.load_library()
+    n = position.shape[0]
+    with torch.cuda.device(position.device):
+        out = torch.empty(n, dtype=torch.float32, device=position.device)
+        ws = torch.empty(lib.adop_points_knn_workspace_bytes(n), dtype=torch.uint8, device=position.device)
+        stream = torch.cuda.current_stream(position.device).cuda_stream
+        capi.check(lib.adop_points_knn_distance(position.data_ptr(), n, k, out.data_ptr(), ws.data_ptr(), ws.numel(),
+                                                C.c_void_p(stream)), "adop_points_knn_distance")
+    return out
+
+
+def radius_sample(distance, seed=0):
+    """ComputeRadius' second half: drop-out radius = distance * sqrt(1 / u), u in (0,1] from the counter hash."""
+    lib = capi.load_library()
+    with torch.cuda.device(distance.device):
+        out = torch.empty_like(distance)
+        stream = torch.cuda.current_stream(distance.device).cuda_stream
+        capi.check(lib.adop_points_radius_sample(distance.data_ptr(), distance.numel(), seed, out.data_ptr(), C.c_void_p(stream)),
+                   "adop_points_radius_sample")
+    return out
+
+
 def permute_rows(t, order):
     """out[i] = t[order[i]] along the first dimension; rows of 4, 8, 12, 16, 32 or 64 bytes."""
     if not (t.is_cuda and t.is_contiguous() and order.is_cuda and order.dtype == torch.int32):

@@ -13,6 +13,7 @@ and point gradients are reduce-scattered with NCCL before normalisation.
 Prints ONE JSON line on rank 0.
 """
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -53,7 +54,7 @@ def parse_args():
 class ClockSampler:
     """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,timestamp")
 
     def __init__(self, gpu_index):
         self.gpu_index = gpu_index
@@ -74,7 +75,10 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
-    def stop(self):
+    def stop(self, window=None):
+        """window = (start, end) datetimes of the timed region: only samples taken inside it count. The sampler runs from
+        before the warm-up (nvidia-smi needs a moment to start), so the samples outside the window are under load too;
+        they are used only if the region was too short to catch one."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -82,22 +86,23 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, smax, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
         for ln in self.lines:
             parts = [p.strip() for p in ln.split(",")]
-            if len(parts) < 7:
+            if len(parts) < 8:
                 continue
             try:
-                sm.append(float(parts[0]))
-                smax = float(parts[1])
+                when = datetime.datetime.strptime(parts[7], "%Y/%m/%d %H:%M:%S.%f")
+                rows.append((when, float(parts[0]), float(parts[1]), [n for n, v in zip(names, parts[3:7]) if v.lower().startswith("active")]))
             except ValueError:
                 continue
-            for name, val in zip(names, parts[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
-                "samples": len(sm)}
+        inside = [r for r in rows if window and window[0] <= r[0] <= window[1]]
+        used = inside if inside else rows
+        sm = [r[1] for r in used]
+        reasons = sorted({n for r in used for n in r[3]})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": used[-1][2] if used else None, "reasons": reasons,
+                "samples": len(sm), "window": "timed region" if inside else "warm-up and timed region"}
 
 
 def algorithmic_bytes(N, C, P, U_views, normals=False, point_grads=True, env_hw=None):
@@ -243,21 +248,23 @@ def main():
         torch.cuda.synchronize()
 
     # ---- device-timed region (inputs resident in HBM) ---------------------------------------------------------------
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    wall0 = datetime.datetime.now()
     e0.record()
     for _ in range(args.steps):
         step()
     e1.record()
     barrier()
+    wall1 = datetime.datetime.now()
     ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop((wall0, wall1)) if rank == 0 else None
     t = torch.tensor([ms], device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -307,6 +307,26 @@ adop_status adop_peer_reduce_gradients(const void* const* blocks, int32_t world,
 size_t adop_points_morton_workspace_bytes(int32_t num_points);
 adop_status adop_points_morton_order(const float* position, int32_t num_points, int32_t* order, void* workspace,
                                      size_t workspace_bytes, void* stream);
+/* point_cloud.RandomBlockShuffle(256), SceneData.cpp:101 (saiga function; here: blocks of `block` consecutive points
+ * in ascending order of hash(seed, block number), the counter hash of the drop-out decision, ties by block number; the
+ * points behind the last full block keep their place). order [N] i32 as above. The workspace of a Morton reorder of
+ * the same cloud is large enough. */
+adop_status adop_points_block_shuffle_order(int32_t num_points, int32_t block, uint32_t seed, int32_t* order, void* workspace,
+                                            size_t workspace_bytes, void* stream);
+/* SceneData::SortBlocksByRadius(256), SceneData.cpp:671-684: inside every full block of 256 points ascending drop-out
+ * radius (position.w); equal radii by index (the reference's std::sort leaves their order open). */
+adop_status adop_points_sort_blocks_by_radius_order(const float* position, int32_t num_points, int32_t* order, void* stream);
+/* SceneData::ComputeRadius(n), SceneData.cpp:441-484. distance [N] f32 (out): for every point the distance to its
+ * k-th nearest OTHER point (the reference asks its KD-tree for k+1 neighbours, the point itself included, and takes the
+ * last), exact: the square root of the (k+1)-th smallest float32 value ((dx*dx + dy*dy) + dz*dz) over all points.
+ * 1 <= k <= 16 (the reference's default is 4); fewer than k+1 points in the cloud give +inf.
+ * adop_points_radius_sample then forms the drop-out radius data(3) = distance * sqrt(1 / u) (SceneData.cpp:476-482) with
+ * u in (0,1] from the counter hash of (seed, 1, point) instead of the reference's global random generator; the caller
+ * stores it in position.w. */
+size_t adop_points_knn_workspace_bytes(int32_t num_points);
+adop_status adop_points_knn_distance(const float* position, int32_t num_points, int32_t k, float* distance, void* workspace,
+                                     size_t workspace_bytes, void* stream);
+adop_status adop_points_radius_sample(const float* distance, int32_t num_points, uint32_t seed, float* radius, void* stream);
 /* dst row i = src row order[i], rows of row_bytes bytes (4, 8, 12, 16, 32 or 64): positions [N,4], normals, indices,
  * gradient rows, or one descriptor plane at a time. src and dst must not overlap. */
 adop_status adop_points_permute(const void* src, void* dst, const int32_t* order, int32_t num_rows, int32_t row_bytes,

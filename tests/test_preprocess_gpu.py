@@ -69,3 +69,100 @@ def test_reordering_a_scene_leaves_the_images_unchanged(cuda_lib):
     # the sorted cloud is in curve order: its keys are non-decreasing
     again = preprocess.morton_order(sorted_scene.position)
     assert torch.equal(again.cpu(), torch.arange(order.numel(), dtype=torch.int32))
+
+
+def _hash_u32(seed, view, point):
+    """numpy statement of hash_u32 (include/adop/adop_math.h)."""
+    with np.errstate(over="ignore"):
+        seed, view = np.uint32(seed), np.uint32(view)
+        h = seed * np.uint32(0x9E3779B1) + view * np.uint32(0x85EBCA77) + np.uint32(0x165667B1)
+        h = np.full(point.shape, h, np.uint32)
+        h ^= point.astype(np.uint32) + np.uint32(0x7F4A7C15) + (h << np.uint32(6)) + (h >> np.uint32(2))
+        h ^= h >> np.uint32(16); h *= np.uint32(0x7FEB352D)
+        h ^= h >> np.uint32(15); h *= np.uint32(0x846CA68B)
+        h ^= h >> np.uint32(16)
+    return h
+
+
+def test_numpy_hash_is_the_library_hash(oracle):
+    pts = np.array([0, 1, 2, 255, 256, 123456789, 2**31 - 1], np.int64)
+    for seed in (0, 7, 0xDEADBEEF):
+        want = np.array([oracle.lib.adop_oracle_hash(seed, 0, int(p)) for p in pts], np.uint32)
+        assert np.array_equal(_hash_u32(seed, 0, pts), want)
+
+
+@pytest.mark.parametrize("n,block,seed", [(10_000, 256, 0), (256 * 40, 256, 5), (100, 256, 1), (513, 256, 2), (1_000_003, 256, 9), (5000, 100, 3)])
+def test_block_shuffle_order(cuda_lib, n, block, seed):
+    blocks = n // block
+    keys = (_hash_u32(seed, 0, np.arange(blocks)).astype(np.uint64) << np.uint64(32)) | np.arange(blocks, dtype=np.uint64)
+    block_order = np.argsort(keys, kind="stable")
+    want = np.arange(n)
+    if blocks:
+        want[: blocks * block] = (block_order[:, None] * block + np.arange(block)[None, :]).reshape(-1)
+    got = preprocess.block_shuffle_order(n, "cuda:0", block=block, seed=seed).cpu().numpy()
+    assert np.array_equal(got, want)
+    assert np.array_equal(np.sort(got), np.arange(n))
+    if blocks > 8:
+        assert not np.array_equal(got, np.arange(n))
+
+
+@pytest.mark.parametrize("n", [256, 255, 1000, 256 * 300 + 17])
+def test_sort_blocks_by_radius_order(cuda_lib, n):
+    rng = np.random.default_rng(n)
+    w = rng.uniform(0, 1, n).astype(np.float32)
+    w[::7] = w[3]            # equal radii: ordered by index
+    w[5::50] = -w[5::50]     # the order is that of the floats, negative values included
+    pos = np.zeros((n, 4), np.float32)
+    pos[:, 3] = w
+    want = np.arange(n)
+    for b in range(n // 256):
+        sl = slice(b * 256, (b + 1) * 256)
+        want[sl] = b * 256 + np.lexsort((np.arange(256), w[sl]))
+    got = preprocess.sort_blocks_by_radius_order(torch.from_numpy(pos).cuda()).cpu().numpy()
+    assert np.array_equal(got, want)
+
+
+def _knn_brute_force(xyz, k):
+    """The (k+1)-th smallest float32 squared distance per point, square-rooted (all pairs)."""
+    x = xyz.astype(np.float32)
+    out = np.empty(len(x), np.float32)
+    for i in range(len(x)):
+        d = x[i] - x
+        d2 = (d[:, 0] * d[:, 0] + d[:, 1] * d[:, 1]) + d[:, 2] * d[:, 2]
+        out[i] = np.sqrt(np.partition(d2, k)[k]) if len(x) > k else np.inf
+    return out
+
+
+@pytest.mark.parametrize("n,k,shape", [(3000, 4, "ball"), (2500, 1, "ball"), (2000, 7, "sheet"), (1500, 16, "ball"), (3, 4, "ball"),
+                                         (4000, 4, "clumps")])
+def test_knn_distance_equals_all_pairs(cuda_lib, n, k, shape):
+    rng = np.random.default_rng(n + k)
+    xyz = rng.normal(0, 1, (n, 3)).astype(np.float32)
+    if shape == "sheet":
+        xyz[:, 2] = 0.25                                   # a flat cloud: zero extent on one axis
+    if shape == "clumps":
+        xyz[: n // 2] = xyz[: n // 2] * 0.001 + 5.0         # one dense clump far from a sparse cloud, plus duplicates
+        xyz[10:20] = xyz[9]
+    pos = np.concatenate([xyz, np.zeros((n, 1), np.float32)], axis=1)
+    got = preprocess.knn_distance(torch.from_numpy(pos).cuda(), k=k).cpu().numpy()
+    assert np.array_equal(got, _knn_brute_force(xyz, k))
+
+
+def test_knn_distance_against_a_kd_tree(cuda_lib):
+    """300 k points on surfaces (the benchmark's scene generator): scipy's KD-tree in float64 as the second opinion."""
+    from scipy.spatial import cKDTree
+    cfg = synth.make_config("c2", n_points=300_000, n_views=1, size=(64, 36))
+    pos = cfg["arrays"]["position"]
+    got = preprocess.knn_distance(torch.from_numpy(pos).cuda(), k=4).cpu().numpy()
+    want = cKDTree(pos[:, :3].astype(np.float64)).query(pos[:, :3].astype(np.float64), k=5)[0][:, 4]
+    assert np.allclose(got, want, rtol=2e-5, atol=1e-7)
+
+
+def test_radius_sample(cuda_lib):
+    n = 100_000
+    dist = np.random.default_rng(1).uniform(0.001, 0.1, n).astype(np.float32)
+    u = ((_hash_u32(3, 1, np.arange(n)) >> np.uint32(8)).astype(np.float32) + np.float32(1)) * np.float32(1.0 / 16777216.0)
+    want = dist * np.sqrt(np.float32(1.0) / u)
+    got = preprocess.radius_sample(torch.from_numpy(dist).cuda(), seed=3).cpu().numpy()
+    assert np.array_equal(got, want.astype(np.float32))
+    assert np.all(got >= dist)
