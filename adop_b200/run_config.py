@@ -53,11 +53,20 @@ def reorder(dev, args):
     want = synth.morton_order(xyz[:n_cpu])
     t_cpu = time.perf_counter() - t0
     same = bool(np.array_equal(preprocess.morton_order(pos[:n_cpu].contiguous()).cpu().numpy().astype(np.int64), want))
+    # the other preprocessing steps on a cloud shaped like the benchmark scene (points on surfaces)
+    surf = torch.from_numpy(synth.make_config("c2", n_points=n, n_views=1, size=(64, 36))["arrays"]["position"]).to(dev)
+    preprocess.knn_distance(surf, k=4)
+    torch.cuda.synchronize()
+    t_knn = statistics.median(timed(lambda: preprocess.knn_distance(surf, k=4), max(2, args.reps // 2)))
+    t_shuffle = statistics.median(timed(lambda: preprocess.block_shuffle_order(n, dev), args.reps))
+    t_radius = statistics.median(timed(lambda: preprocess.sort_blocks_by_radius_order(surf), args.reps))
     algo_bytes = n * (8 * 32 + 28)
     peak = 6542.7
     out = {"config": "reorder", "n_points": n, "morton_order_ms": t, "gkeys_per_s": n / (t * 1e-3) / 1e9,
            "algorithmic_bytes": algo_bytes, "achieved_gbs": algo_bytes / (t * 1e-3) / 1e9,
            "roofline_frac_of_measured_6542.7": algo_bytes / (t * 1e-3) / 1e9 / peak, "kernel_ms": kernel_ms,
+           "knn4_distance_ms": t_knn, "knn_mpts_per_s": n / (t_knn * 1e-3) / 1e6, "block_shuffle_order_ms": t_shuffle,
+           "sort_blocks_by_radius_ms": t_radius,
            "permute_positions_ms": t_perm, "permute_gbs": n * 36 / (t_perm * 1e-3) / 1e9,
            "cpu_numpy": {"points": n_cpu, "seconds": t_cpu, "gkeys_per_s": n_cpu / t_cpu / 1e9, "cores": 1,
                          "same_permutation_as_gpu": same}}
