@@ -212,17 +212,23 @@ __global__ void __launch_bounds__(kBlock) k_radix_scan(unsigned* __restrict__ da
     if (threadIdx.x == 0) totals[blockIdx.x] = s_carry;
 }
 
+// Stable scatter of one tile (2048 keys) per block. Warp w owns keys [256 w, 256 w + 256) of the tile and keeps them in
+// registers (8 rounds of 32 consecutive keys). Two block-wide barriers per tile:
+//   1. every warp counts its digits (match.any per round, the lowest lane of each group adds the group size);
+//   2. thread d turns the per-warp counts of digit d into starting offsets (digit base + warps before);
+//   3. every warp walks its rounds again: place = offset of its digit + keys of that digit in earlier rounds + rank in
+//      the round; the per-warp running counts live in the same shared array (warp-private, __syncwarp only).
+// (A first version handled 256 keys per group with three barriers each: 0.19 ms per pass for 10 M keys.)
 __global__ void __launch_bounds__(kBlock) k_radix_scatter(const unsigned long long* __restrict__ keys_in, const int* __restrict__ index_in,
                                                            int n, int shift, const unsigned* __restrict__ offsets, int blocks,
                                                            const unsigned* __restrict__ totals,
                                                            unsigned long long* __restrict__ keys_out, int* __restrict__ index_out)
 {
-    // per-warp counters of the current group of 256 keys, ping-pong so that one barrier less is needed per group
-    __shared__ unsigned s_count[2][kBlock / 32][kRadixBins];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    // thread d owns digit d: where the next key with that digit of this tile goes = keys with smaller digits (exclusive
-    // scan of the 256 digit totals, done by every block for itself) + keys with this digit in earlier blocks
+    __shared__ unsigned s_count[kBlock / 32][kRadixBins];
     __shared__ unsigned s_tot[kBlock / 32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // digit base: keys with smaller digits (exclusive scan of the 256 digit totals, done by every block for itself) + keys
+    // with this digit in earlier blocks
     unsigned my_base;
     {
         const unsigned t = totals[threadIdx.x];
@@ -234,54 +240,63 @@ __global__ void __launch_bounds__(kBlock) k_radix_scatter(const unsigned long lo
             if (lane >= o) incl += u;
         }
         if (lane == 31) s_tot[warp] = incl;
+#pragma unroll
+        for (int w = 0; w < kBlock / 32; ++w) s_count[w][threadIdx.x] = 0;
         __syncthreads();
         unsigned before = 0;
         for (int w = 0; w < warp; ++w) before += s_tot[w];
         my_base = before + incl - t + offsets[(size_t)threadIdx.x * blocks + blockIdx.x];
     }
-    const int base = blockIdx.x * kRadixTile;
-    for (int k = threadIdx.x; k < 2 * (kBlock / 32) * kRadixBins; k += kBlock) (&s_count[0][0][0])[k] = 0;
-    __syncthreads();
-#pragma unroll 1
+    const int first = blockIdx.x * kRadixTile + warp * (kRadixItems * 32) + lane;
+    unsigned long long key[kRadixItems];
+    int idx[kRadixItems];
+    unsigned digit[kRadixItems];
+#pragma unroll
     for (int j = 0; j < kRadixItems; ++j)
     {
-        unsigned(*cnt)[kRadixBins] = s_count[j & 1];
-        const int i = base + j * kBlock + threadIdx.x;
+        const int i = first + j * 32;
         const bool live = i < n;
-        unsigned long long key = 0;
-        int idx = 0;
-        if (live) { key = __ldg(keys_in + i); idx = __ldg(index_in + i); }
+        key[j] = live ? __ldg(keys_in + i) : 0ull;
+        idx[j] = live ? __ldg(index_in + i) : 0;
         // dead lanes get a digit value no live key can have, so they form their own group
-        const unsigned digit = live ? (unsigned)(key >> shift) & (kRadixBins - 1) : kRadixBins;
-        const unsigned peers = __match_any_sync(0xffffffffu, digit);
+        digit[j] = live ? (unsigned)(key[j] >> shift) & (kRadixBins - 1) : kRadixBins;
+    }
+    unsigned* cnt = s_count[warp];
+#pragma unroll
+    for (int j = 0; j < kRadixItems; ++j)
+    {
+        const unsigned peers = __match_any_sync(0xffffffffu, digit[j]);
+        if (digit[j] < kRadixBins && (peers & ((1u << lane) - 1u)) == 0) cnt[digit[j]] += __popc(peers);
+        __syncwarp();
+    }
+    __syncthreads();
+    {
+        const unsigned d = threadIdx.x;
+        unsigned run = my_base;
+#pragma unroll
+        for (int w = 0; w < kBlock / 32; ++w)
+        {
+            const unsigned c = s_count[w][d];
+            s_count[w][d] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kRadixItems; ++j)
+    {
+        const unsigned peers = __match_any_sync(0xffffffffu, digit[j]);
         const unsigned rank = __popc(peers & ((1u << lane) - 1u));
-        if (live && rank == 0) cnt[warp][digit] = __popc(peers);
-        __syncthreads();
+        unsigned at = 0;
+        if (digit[j] < kRadixBins) at = cnt[digit[j]] + rank;
+        __syncwarp();
+        if (digit[j] < kRadixBins && rank == 0) cnt[digit[j]] += __popc(peers);  // the next rounds of this warp start behind this group
+        __syncwarp();
+        if (digit[j] < kRadixBins)
         {
-            // digit d: running offsets over the warps (the order of the keys inside the tile is kept), then its base moves on
-            const unsigned d = threadIdx.x;
-            unsigned run = my_base;
-#pragma unroll
-            for (int w = 0; w < kBlock / 32; ++w)
-            {
-                const unsigned c = cnt[w][d];
-                cnt[w][d] = run;
-                run += c;
-            }
-            my_base = run;
+            keys_out[at] = key[j];
+            index_out[at] = idx[j];
         }
-        __syncthreads();
-        if (live)
-        {
-            const unsigned at = cnt[warp][digit] + rank;
-            keys_out[at] = key;
-            index_out[at] = idx;
-        }
-        // clear the other buffer for the next group (nobody reads it any more: its readers passed the barrier above)
-        unsigned(*other)[kRadixBins] = s_count[(j + 1) & 1];
-#pragma unroll
-        for (int w = 0; w < kBlock / 32; ++w) other[w][threadIdx.x] = 0;
-        __syncthreads();
     }
 }
 
