@@ -213,12 +213,16 @@ __global__ void __launch_bounds__(kBlock) k_radix_scan(unsigned* __restrict__ da
 }
 
 // Stable scatter of one tile (2048 keys) per block. Warp w owns keys [256 w, 256 w + 256) of the tile and keeps them in
-// registers (8 rounds of 32 consecutive keys). Two block-wide barriers per tile:
+// registers (8 rounds of 32 consecutive keys). Three block-wide barriers per tile:
 //   1. every warp counts its digits (match.any per round, the lowest lane of each group adds the group size);
-//   2. thread d turns the per-warp counts of digit d into starting offsets (digit base + warps before);
-//   3. every warp walks its rounds again: place = offset of its digit + keys of that digit in earlier rounds + rank in
-//      the round; the per-warp running counts live in the same shared array (warp-private, __syncwarp only).
-// (A first version handled 256 keys per group with three barriers each: 0.19 ms per pass for 10 M keys.)
+//   2. thread d turns the per-warp counts of digit d into places inside the tile sorted by digit (tile prefix of the
+//      digit + warps before), and remembers where the tile's run of digit d starts in the output;
+//   3. every warp walks its rounds again: place = its digit's place + keys of that digit in earlier rounds + rank in the
+//      round (per-warp running counts in the same shared array, __syncwarp only); keys and indices go to that place of
+//      a shared-memory copy of the tile;
+//   4. the tile leaves in sorted order: neighbouring threads write neighbouring addresses of a digit's run (8 keys per
+//      digit and tile on average), instead of every lane writing a sector of its own.
+// (Versions without the staged copy: 0.18-0.19 ms per pass for 10 M keys, stores 25 % efficient.)
 __global__ void __launch_bounds__(kBlock) k_radix_scatter(const unsigned long long* __restrict__ keys_in, const int* __restrict__ index_in,
                                                            int n, int shift, const unsigned* __restrict__ offsets, int blocks,
                                                            const unsigned* __restrict__ totals,
@@ -226,10 +230,13 @@ __global__ void __launch_bounds__(kBlock) k_radix_scatter(const unsigned long lo
 {
     __shared__ unsigned s_count[kBlock / 32][kRadixBins];
     __shared__ unsigned s_tot[kBlock / 32];
+    __shared__ unsigned s_tile_prefix[kRadixBins];   // keys of the tile with a smaller digit
+    __shared__ unsigned s_out_base[kRadixBins];      // where the tile's run of the digit starts in the output
+    __shared__ unsigned long long s_key[kRadixTile];
+    __shared__ int s_idx[kRadixTile];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     // digit base: keys with smaller digits (exclusive scan of the 256 digit totals, done by every block for itself) + keys
     // with this digit in earlier blocks
-    unsigned my_base;
     {
         const unsigned t = totals[threadIdx.x];
         unsigned incl = t;
@@ -245,9 +252,10 @@ __global__ void __launch_bounds__(kBlock) k_radix_scatter(const unsigned long lo
         __syncthreads();
         unsigned before = 0;
         for (int w = 0; w < warp; ++w) before += s_tot[w];
-        my_base = before + incl - t + offsets[(size_t)threadIdx.x * blocks + blockIdx.x];
+        s_out_base[threadIdx.x] = before + incl - t + offsets[(size_t)threadIdx.x * blocks + blockIdx.x];
     }
-    const int first = blockIdx.x * kRadixTile + warp * (kRadixItems * 32) + lane;
+    const int tile_base = blockIdx.x * kRadixTile;
+    const int first = tile_base + warp * (kRadixItems * 32) + lane;
     unsigned long long key[kRadixItems];
     int idx[kRadixItems];
     unsigned digit[kRadixItems];
@@ -271,8 +279,25 @@ __global__ void __launch_bounds__(kBlock) k_radix_scatter(const unsigned long lo
     }
     __syncthreads();
     {
+        // thread d: the tile's count of digit d, its exclusive prefix over the digits, then per-warp places inside the tile
         const unsigned d = threadIdx.x;
-        unsigned run = my_base;
+        unsigned mine = 0;
+#pragma unroll
+        for (int w = 0; w < kBlock / 32; ++w) mine += s_count[w][d];
+        unsigned incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1)
+        {
+            unsigned u = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += u;
+        }
+        __syncthreads();  // s_tot is reused: its readers above are done
+        if (lane == 31) s_tot[warp] = incl;
+        __syncthreads();
+        unsigned before = 0;
+        for (int w = 0; w < warp; ++w) before += s_tot[w];
+        unsigned run = before + incl - mine;
+        s_tile_prefix[d] = run;
 #pragma unroll
         for (int w = 0; w < kBlock / 32; ++w)
         {
@@ -294,9 +319,19 @@ __global__ void __launch_bounds__(kBlock) k_radix_scatter(const unsigned long lo
         __syncwarp();
         if (digit[j] < kRadixBins)
         {
-            keys_out[at] = key[j];
-            index_out[at] = idx[j];
+            s_key[at] = key[j];
+            s_idx[at] = idx[j];
         }
+    }
+    __syncthreads();
+    const int live_keys = min(kRadixTile, n - tile_base);
+    for (int e = threadIdx.x; e < live_keys; e += kBlock)
+    {
+        const unsigned long long k = s_key[e];
+        const unsigned d = (unsigned)(k >> shift) & (kRadixBins - 1);
+        const unsigned at = s_out_base[d] + ((unsigned)e - s_tile_prefix[d]);
+        keys_out[at] = k;
+        index_out[at] = s_idx[e];
     }
 }
 
