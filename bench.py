@@ -34,7 +34,7 @@ WORKLOAD = "c2: 10M points x 16 views/GPU, 1920x1080, L=4, C=4, pinhole k1=-0.1 
 # DRAM bytes (read + write) per launch of the kernels that can dominate, from an ncu --set full capture of a four-view
 # run of this workload (profiles/point_kernels_c2_ncu_full.md); one launch there = one launch here. Valid for the default
 # workload only.
-NCU_TRAFFIC_BYTES = {"k_blend": 400.4e6, "k_splat_gather": 478.1e6, "k_splat_chain": 190.6e6, "k_depth_prepass": 243.0e6}
+NCU_TRAFFIC_BYTES = {"k_blend": 405.7e6, "k_splat_gather": 479.1e6, "k_splat_chain": 191.1e6, "k_depth_prepass": 249.0e6}
 
 
 def parse_args():
