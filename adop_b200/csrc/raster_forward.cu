@@ -217,9 +217,18 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, const flo
     const int stride = gridDim.x * blockDim.x;
     int4* seg = EMIT ? vl.entries + (size_t)blockIdx.x * vl.seg_cap : nullptr;
     const int lane = threadIdx.x & 31;
+    // Only about a third of the lanes of a warp that has accepted points at all have one (11 of 32 on the 1080p
+    // benchmark scene), so the work on accepted points - descriptor load, atomics, the list entries - is not done where the
+    // point is tested: a warp parks its accepted points (index, layer mask, pixel per layer) in a queue of its own in
+    // shared memory and finishes them 32 at a time with every lane busy.
+    constexpr int PW = L + 2;
+    __shared__ int s_park[kBlock / 32][64 * PW];
+    int* park = s_park[threadIdx.x >> 5];
+    int n_parked = 0;  // the same in every lane of the warp
 
-    // One point: blend it, and return the mask of layers the backward pass will visit for it (their pixels in pix_out).
-    auto blend_point = [&](int i, float4 cur, int* pix_out) -> unsigned
+    // Tests one point against the depth buffers: 0 = nothing to do, else the mask of accepted layers, bit 31 = the point
+    // is dropped in this view (it blends nothing but the backward pass visits it in ghost-gradient mode).
+    auto test_point = [&](int i, float4 cur, int* pix) -> unsigned
     {
         const bool dropped = point_dropped(kp, i);
         if (dropped && !(EMIT && kp.ghost_gradients)) return 0u;
@@ -230,8 +239,8 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, const flo
         if (PLAIN ? !project_plain(cam, f.p, kp.dist_cutoff, &q)
                   : !project_for_raster(cam, f.p, f.r, f.n, f.has_normal, use_normal, kp.dist_cutoff, &q, use_radius)) return 0u;
         float x = q.x, y = q.y, rad = q.radius_px;
-        // the depth reads of all layers go out together
-        int pix[L];  // pixel index inside the layer (a pyramid has fewer than 2^31 pixels), -1 = not in this layer
+        // pixel index inside the layer (a pyramid has fewer than 2^31 pixels), -1 = not in this layer; the depth reads
+        // of all layers go out together
         bool live = true;
 #pragma unroll
         for (int l = 0; l < L; ++l, rad *= 0.5f, x *= 0.5f, y *= 0.5f)
@@ -249,37 +258,43 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, const flo
             if (pix[l] >= 0 && !(q.z > image_depth * kp.depth_accept_plus_one)) pass |= 1u << l;
         }
         if (pass == 0) return 0u;
-        if (!dropped)
-        {
-            float t[C];
-            const int ti = pts.index ? __ldg(pts.index + i) : i;
-            load_descriptor<C>(texture, texture_interleaved, num_texels, ti, t);
-#pragma unroll
-            for (int l = 0; l < L; ++l)
-                if (pass & (1u << l)) splat_record<C>(accum + ((size_t)lt.rec_off[l] + pix[l]) * RS, lt.weight[l] + pix[l], t);
-        }
-        // the layers the backward pass will visit: it skips layers the point does not land in and stops at the first
-        // depth failure (PointRenderer.cu:451-462)
-        unsigned bmask = 0;
-#pragma unroll
-        for (int l = 0; l < L; ++l)
-        {
-            pix_out[l] = pix[l];
-            if (pix[l] < 0) continue;
-            if (!(pass & (1u << l))) break;
-            bmask |= 1u << l;
-        }
-        return bmask;
+        return pass | (dropped ? 0x80000000u : 0u);
     };
 
-    // warp-uniform trip count, so that the append below can use full-warp shuffles
-    for (int base = blockIdx.x * blockDim.x; base < pts.n; base += stride)
+    // All 32 lanes together: blend the accepted point of every valid lane and append its splats to the list.
+    auto finish = [&](bool valid, const int* e)
     {
-        const int i = base + threadIdx.x;
         unsigned bmask = 0;
-        int lpix[L];
-        if (i < pts.n) bmask = blend_point(i, __ldg(pts.position + i), lpix);
-        if (EMIT && __any_sync(0xffffffffu, bmask != 0))
+        int i = 0;
+        int pix[L];
+#pragma unroll
+        for (int l = 0; l < L; ++l) pix[l] = -1;
+        if (valid)
+        {
+            i = e[0];
+            const unsigned code = (unsigned)e[1];
+#pragma unroll
+            for (int l = 0; l < L; ++l) pix[l] = e[2 + l];
+            if (!(code >> 31))
+            {
+                float t[C];
+                const int ti = pts.index ? __ldg(pts.index + i) : i;
+                load_descriptor<C>(texture, texture_interleaved, num_texels, ti, t);
+#pragma unroll
+                for (int l = 0; l < L; ++l)
+                    if (code & (1u << l)) splat_record<C>(accum + ((size_t)lt.rec_off[l] + pix[l]) * RS, lt.weight[l] + pix[l], t);
+            }
+            // the layers the backward pass will visit: it skips layers the point does not land in and stops at the
+            // first depth failure (PointRenderer.cu:451-462)
+#pragma unroll
+            for (int l = 0; l < L; ++l)
+            {
+                if (pix[l] < 0) continue;
+                if (!(code & (1u << l))) break;
+                bmask |= 1u << l;
+            }
+        }
+        if (EMIT)
         {
             const int cnt = __popc(bmask);
             int incl = cnt;
@@ -301,13 +316,43 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, const flo
                 {
 #pragma unroll
                     for (int l = 0; l < L; ++l)
-                        if (bmask & (1u << l)) seg[at++] = make_int4(i | (l << kSplatLayerShift), lpix[l], 0, 0);
+                        if (bmask & (1u << l)) seg[at++] = make_int4(i | (l << kSplatLayerShift), pix[l], 0, 0);
                 }
                 else if (lane == 0)
                     vl.header[kVisibleSegments + 2] = 1;  // out of room: the backward pass falls back to walking all points
             }
         }
+    };
+
+    // warp-uniform trip count: parking and finishing use full-warp votes and shuffles
+    for (int base = blockIdx.x * blockDim.x; base < pts.n; base += stride)
+    {
+        const int i = base + threadIdx.x;
+        unsigned code = 0;
+        int pix[L];
+        if (i < pts.n) code = test_point(i, __ldg(pts.position + i), pix);
+        const unsigned vote = __ballot_sync(0xffffffffu, code != 0);
+        if (vote)
+        {
+            if (code)
+            {
+                int* e = park + (n_parked + __popc(vote & ((1u << lane) - 1u))) * PW;
+                e[0] = i;
+                e[1] = (int)code;
+#pragma unroll
+                for (int l = 0; l < L; ++l) e[2 + l] = pix[l];
+            }
+            n_parked += __popc(vote);
+            __syncwarp();
+            if (n_parked >= 32)
+            {
+                n_parked -= 32;
+                finish(true, park + (n_parked + lane) * PW);
+            }
+            __syncwarp();
+        }
     }
+    if (n_parked > 0) finish(lane < n_parked, park + lane * PW);
     if (EMIT)
     {
         __syncthreads();
