@@ -34,7 +34,7 @@ WORKLOAD = "c2: 10M points x 16 views/GPU, 1920x1080, L=4, C=4, pinhole k1=-0.1 
 # DRAM bytes (read + write) per launch of the kernels that can dominate, from an ncu --set full capture of a four-view
 # run of this workload (profiles/point_kernels_c2_ncu_full.md); one launch there = one launch here. Valid for the default
 # workload only.
-NCU_TRAFFIC_BYTES = {"k_blend": 405.7e6, "k_splat_gather": 479.1e6, "k_splat_chain": 191.1e6, "k_depth_prepass": 249.0e6}
+NCU_TRAFFIC_BYTES = {"k_blend": 395.0e6, "k_splat_gather": 480.1e6, "k_splat_chain": 190.1e6, "k_depth_prepass": 245.4e6}
 
 
 def parse_args():
@@ -74,6 +74,12 @@ class ClockSampler:
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
+
+    def wait_ready(self, timeout=8.0):
+        """nvidia-smi can take a few hundred ms to print its first sample, longer than a short timed region: wait for it."""
+        t_end = time.time() + timeout
+        while self.proc is not None and not self.lines and time.time() < t_end and self.proc.poll() is None:
+            time.sleep(0.01)
 
     def stop(self, window=None):
         """window = (start, end) datetimes of the timed region: only samples taken inside it count. The sampler runs from
@@ -251,6 +257,7 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        sampler.wait_ready()
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
