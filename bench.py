@@ -352,12 +352,17 @@ def main():
     peak_kind = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
     dom = max(ktimes.items(), key=lambda kv: kv[1][1])
     dom_name, (dom_launches, dom_ms) = dom
-    # algorithmic bytes of one launch (= one view) of each kernel that can dominate; a backward kernel is charged the whole
-    # backward figure G_v of its view (the split of the backward pass into kernels is this implementation's business)
+    # algorithmic bytes of one launch (= one view) of each kernel that can dominate: what that kernel itself has to move
+    # at the least. Gather: per splat the list entry (16), the pixel's weight (4), the descriptor and its gradient (2 x 4C),
+    # and every pixel record [image | gradient] once (8C per pyramid pixel). Chain: per splat the list entry, the point
+    # and its gradient (16 each). Prepare: 2C + 1 planes read, one record written per pixel.
     U_mean = sum(U_views) / V
     dom_bytes = {"k_depth_prepass": N * 16 + 4 * 4 * P,  # one launch covers four views: the points once, four depth pyramids
                  "k_blend": N * 16 + U_mean * (4 + 4 * C),
-                 "k_resolve": P * (4 * C + 8)}.get(dom_name, sum(per_view_bwd) / V)
+                 "k_resolve": P * (4 * C + 8),
+                 "k_prepare_backward": P * (8 * C + 4 + 8 * C),
+                 "k_splat_gather": U_mean * (16 + 4 + 8 * C) + P * 8 * C,
+                 "k_splat_chain": U_mean * 48}.get(dom_name, sum(per_view_bwd) / V)
     achieved = dom_bytes / (dom_ms / dom_launches * 1e-3) / 1e9
     step_ms = ms_total / args.steps
     step_achieved = (fwd_b + bwd_b + step_b) / (step_ms * 1e-3) / 1e9
