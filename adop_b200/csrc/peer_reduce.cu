@@ -382,8 +382,13 @@ extern "C" adop_status adop_peer_reduce_gradients(const void* const* blocks, int
     long long largest = w.t_n > w.p_n ? w.t_n : w.p_n;
     const long long n_small = (long long)w.n_pose + w.n_count_pose + w.n_intr + w.n_count_intr + w.n_bg;
     if (n_small > largest) largest = n_small;
-    if (w.n_env / 4 > largest) largest = w.n_env / 4;
-    const long long need = (largest + kBlock - 1) / kBlock;
+    // the environment map goes four floats at a time when its size allows, else float by float: count what the kernel
+    // will loop over, and never launch an empty grid (a tail of one to three floats is work too)
+    const bool env_vec = (reinterpret_cast<uintptr_t>(out->grad_env_map) & 15) == 0;
+    const long long n_env_items = env_vec ? (w.n_env / 4 > w.n_env % 4 ? w.n_env / 4 : w.n_env % 4) : w.n_env;
+    if (n_env_items > largest) largest = n_env_items;
+    long long need = (largest + kBlock - 1) / kBlock;
+    if (need < 1) need = 1;
     switch (C)
     {
         ADOP_PEER_CASE(3)

@@ -120,7 +120,11 @@ __global__ void __launch_bounds__(kBlock, 8) k_depth_prepass(PointStreams pts, c
                 // depth plane of view v of the group: the planes of a batch follow each other
                 // (32-bit index: a group's planes of one layer hold fewer than 2^31 pixels, checked by the entry point)
                 int* dst = reinterpret_cast<int*>(lt.depth[l]) + ((unsigned)(v * lt.h[l] + py) * (unsigned)lt.w[l] + (unsigned)px);
-                if (l == 0 || zi < __ldg(dst)) atomicMin(dst, zi);
+                // early z: the plane is being updated by other blocks' atomicMin while it is read, so the read goes through L2
+                // (__ldcg), not the non-coherent path. A value that is older than the latest minimum can only be
+                // LARGER than the true one (depths only decrease), so it never drops a point that should win; at worst
+                // it lets through an atomic that changes nothing.
+                if (l == 0 || zi < __ldcg(dst)) atomicMin(dst, zi);
             }
         }
     }
@@ -157,7 +161,7 @@ __global__ void __launch_bounds__(kBlock) k_depth_prepass_packed(PointStreams pt
             int px = round_half_even_bounded(x), py = round_half_even_bounded(y);
             if ((unsigned)px >= (unsigned)lt.w[l] || (unsigned)py >= (unsigned)lt.h[l]) continue;
             unsigned long long* dst = out.plane[l] + ((unsigned)py * (unsigned)lt.w[l] + (unsigned)px);
-            if (word < __ldg(dst)) atomicMin(dst, word);
+            if (word < __ldcg(dst)) atomicMin(dst, word);  // coherent read of a plane under update, see k_depth_prepass
         }
     }
 }

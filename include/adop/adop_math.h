@@ -98,7 +98,7 @@ ADOP_HD bool dropout_decision(float p, uint32_t seed, uint32_t view, uint32_t po
 }
 
 // ---------------------------------------------------------------------------------------------------
-// own atan / atan2 / acos (coefficients: include/adop/fit_atan_poly.py)
+// own atan / atan2 / acos (coefficients: least-squares fit on Chebyshev nodes, tests/golden/fit_atan_poly.py)
 // ---------------------------------------------------------------------------------------------------
 ADOP_HD float atan_core(float x)  // |x| <= tan(pi/8)
 {

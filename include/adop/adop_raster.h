@@ -210,7 +210,9 @@ adop_status adop_raster_forward(const adop_scene* scene, const adop_view* views,
  *   - Limit: adop_raster_workspace_bytes(w, h, layers, channels) must not exceed that size (e.g. 1024 x 576 with
  *     4 layers and 4 channels fits); larger views return ADOP_ERR_SIZE_LIMIT and adop_last_error() names both sizes.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
- *     current). Make that first call outside any stream capture.
+ *     current). Make that first call outside any stream capture. With CUDA's lazy module loading that first call is
+ *     also the one that loads this library's device code and the array itself onto the GPU, so it can need (and fail
+ *     for lack of) device memory: make it at start-up, while memory is still available.
  *   - The function itself calls no cudaMalloc / cudaFree and no allocating library routine.
  *   - All calls on a device share the one array. Each call clears what it needs before use, so earlier contents do
  *     not leak into results, but two calls whose kernels overlap on the GPU (different streams, different threads)

@@ -2,7 +2,7 @@
 
 atan(x) ~= x + x^3 * (c0 + c1 z + c2 z^2 + c3 z^3 + c4 z^4),  z = x^2,  |x| <= tan(pi/8).
 Least squares on Chebyshev nodes in float64; prints the coefficients and the max relative error.
-Run:  python include/adop/fit_atan_poly.py
+Run:  python tests/golden/fit_atan_poly.py
 """
 import numpy as np
 

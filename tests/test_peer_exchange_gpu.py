@@ -112,6 +112,25 @@ def test_reduce_kernel_with_all_blocks_on_one_gpu(cuda_lib, channels, world, tex
         assert torch.equal(res_env, total("env_map"))
 
 
+@pytest.mark.parametrize("channels,env_hw", [(3, (1, 1)), (3, (1, 2)), (4, (1, 1))])
+def test_reduce_kernel_with_only_a_tiny_environment_map(cuda_lib, channels, env_hw):
+    """The only work is an environment-map gradient of one to three floats (fewer than one 16-byte vector): the launch
+    must not come out empty."""
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(17)
+    lay = adist.peer_layout(channels, 0, 0, num_images=0, num_cameras=0, intrinsics_cols=0, env_hw=env_hw, background=False)
+    blocks = [_fill_block(lay, dev, gen) for _ in range(2)]
+    ptrs = (C.c_void_p * 2)(*[b[0].data_ptr() for b in blocks])
+    out = capi.AdopPeerReduceOut()
+    res_env = torch.full((channels,) + env_hw, float("nan"), device=dev)
+    out.grad_env_map = res_env.data_ptr()
+    out.normalize = 1
+    capi.check(cuda_lib.adop_peer_reduce_gradients(ptrs, 2, 0, C.byref(lay), C.byref(out), None), "adop_peer_reduce_gradients")
+    torch.cuda.synchronize()
+    assert torch.equal(res_env, blocks[0][1]["env_map"] + blocks[1][1]["env_map"])
+
+
 def test_reduce_rejects_bad_arguments(cuda_lib):
     lay = adist.peer_layout(4, 16, 16)
     out = capi.AdopPeerReduceOut()

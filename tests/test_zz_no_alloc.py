@@ -76,6 +76,39 @@ def test_static_scratch_forward_matches_workspace_forward_twice(cuda_lib):
     _compare(lib, synth.make_config("c2", n_points=300_000, n_views=3, size=(640, 360), seed=5))
 
 
+def test_static_scratch_forward_leaves_device_memory_in_use_unchanged(cuda_lib):
+    """The entry point's contract is that it allocates nothing. After one warm-up call (the first call on a device loads
+    the module with its 32 MiB array and looks up the array's address), the driver's free-memory figure must be the same
+    before and after a call, outputs and inputs being allocated beforehand."""
+    lib = cuda_lib
+    dev = torch.device("cuda:0")
+    cfg = synth.make_config("c2", n_points=100_000, n_views=2, size=(320, 180))
+    scene = Scene(**{k: (torch.from_numpy(v).to(dev) if v is not None else None) for k, v in cfg["arrays"].items()})
+    views, params, L = cfg["views"], cfg["params"], cfg["num_layers"]
+    st, *_ = _forward(lib, "adop_raster_forward_static", scene, views, params, L, None)  # warm-up: module load, address
+    assert st == capi.ADOP_OK, lib.adop_last_error()
+    # everything the measured call touches exists before the first reading
+    va = capi.make_views(views)
+    B = len(va)
+    sc = fill_scene_struct(scene.tensors(), lambda t: t.data_ptr())
+    sizes = capi.layer_sizes(va[0].w, va[0].h, L)
+    f32 = dict(dtype=torch.float32, device=dev)
+    bufs = [[torch.empty((B, ch, h, w), **f32) for w, h in sizes] for ch in (sc.channels, 1, 1, 1)]
+    io = capi.AdopForwardIO()
+    for l in range(L):
+        io.layers[l].color, io.layers[l].depth = bufs[0][l].data_ptr(), bufs[1][l].data_ptr()
+        io.layers[l].weight, io.layers[l].mask = bufs[2][l].data_ptr(), bufs[3][l].data_ptr()
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    torch.cuda.synchronize(dev)
+    free_before, _ = torch.cuda.mem_get_info(dev)
+    st = lib.adop_raster_forward_static(C.byref(sc), va, B, C.byref(params), L, C.byref(io), C.c_void_p(stream))
+    torch.cuda.synchronize(dev)
+    free_after, _ = torch.cuda.mem_get_info(dev)
+    assert st == capi.ADOP_OK, lib.adop_last_error()
+    assert free_after == free_before, f"device memory in use changed by {free_before - free_after} bytes across the call"
+    assert float(bufs[2][0].sum()) > 0
+
+
 def test_static_scratch_rejects_views_beyond_its_size(cuda_lib):
     lib = cuda_lib
     cfg = synth.make_config("c2", n_points=1000, n_views=1, size=(1920, 1080))
