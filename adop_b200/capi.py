@@ -101,6 +101,7 @@ class AdopKernelTime(C.Structure):
 # every symbol include/adop/adop_raster.h declares
 EXPORTED_SYMBOLS = [
     "adop_status_string", "adop_last_error", "adop_render_params_default", "adop_raster_workspace_bytes",
+    "adop_raster_workspace_bytes_full",
     "adop_raster_forward", "adop_raster_backward", "adop_raster_normalize_gradients", "adop_apply_tangent",
     "adop_tonemap_forward", "adop_tonemap_backward", "adop_profile_enable", "adop_profile_collect",
     "adop_raster_static_scratch_bytes", "adop_raster_forward_static", "adop_raster_visible_list_ints",
@@ -137,6 +138,8 @@ def load_library():
     lib.adop_render_params_default.restype = None
     lib.adop_raster_workspace_bytes.restype = C.c_size_t
     lib.adop_raster_workspace_bytes.argtypes = [C.c_int32] * 4
+    lib.adop_raster_workspace_bytes_full.restype = C.c_size_t
+    lib.adop_raster_workspace_bytes_full.argtypes = [C.c_int32] * 6
     lib.adop_raster_forward.argtypes = [C.POINTER(AdopScene), C.POINTER(AdopView), C.c_int32,
                                         C.POINTER(AdopRenderParams), C.c_int32, C.POINTER(AdopForwardIO), C.c_void_p]
     lib.adop_raster_forward_static.argtypes = lib.adop_raster_forward.argtypes
@@ -147,7 +150,7 @@ def load_library():
     lib.adop_texture_interleave.restype = C.c_int
     lib.adop_texture_deinterleave.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
     lib.adop_texture_deinterleave.restype = C.c_int
-    lib.adop_raster_visible_list_ints.argtypes = [C.c_int32]
+    lib.adop_raster_visible_list_ints.argtypes = [C.c_int32] * 4
     lib.adop_raster_visible_list_ints.restype = C.c_size_t
     lib.adop_raster_backward.argtypes = [C.POINTER(AdopScene), C.POINTER(AdopView), C.c_int32,
                                          C.POINTER(AdopRenderParams), C.c_int32, C.POINTER(AdopBackwardIO), C.c_void_p]

@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <string.h>
 
 #include "adop/adop_math.h"
 #include "adop/adop_raster.h"
@@ -52,6 +53,31 @@ struct PointStreams
     const int32_t* index;   // may be null (identity)
     int n;
 };
+
+// Which chunk of kBlock consecutive points a block works on in its k-th round. The cloud is Morton-sorted, so a plain
+// grid-stride loop has all resident blocks inside one small region of space at any time, and their atomics (depth
+// minima, accumulator sums, tile counters) pile up on a few image tiles and L2 slices. Here the cloud is cut into G
+// superblocks of `rounds` chunks; in round k block b takes chunk k of superblock (b + k * spread) mod G (spread coprime
+// to G): at any time the blocks are spread over the whole cloud, and over its rounds a block samples superblocks from
+// all over the cloud, so that blocks carry similar loads.
+struct ChunkSchedule
+{
+    int rounds;   // K = ceil(chunks / G)
+    int spread;   // S
+    int chunks;   // ceil(n / kBlock)
+};
+inline ChunkSchedule make_chunk_schedule(int n_points, int grid)
+{
+    ChunkSchedule c;
+    c.chunks = (n_points + kBlock - 1) / kBlock;
+    if (grid < 1) grid = 1;
+    c.rounds = (c.chunks + grid - 1) / grid;
+    int s = grid / 29 + 1;
+    auto gcd = [](int a, int b) { while (b) { int t = a % b; a = b; b = t; } return a; };
+    while (gcd(s, grid) != 1) ++s;
+    c.spread = s;
+    return c;
+}
 
 // the handful of RenderParams fields the kernels read (Settings.h:16-52)
 struct KernelParams
@@ -146,45 +172,117 @@ inline void fill_cam_chunk(CamChunkSource* c, const adop_scene* s, const adop_vi
     }
 }
 
-// Splat list of one view: every (point, layer) pair that the backward pass has to visit - the point passed the fuzzy
-// depth test on that layer and on every finer layer it landed in (the backward pass stops at the first failure,
-// PointRenderer.cu:462). Written by the blend kernel, consumed by the backward kernel; it takes the role of the
-// reference's saved [B,N] drop-out tensor as the per-view state carried from forward to backward (:1524).
-// Layout per view, in int32:
-//   [0, kVisibleSegments)            number of entries of each segment (one segment per block of the blend launch)
-//   [kVisibleSegments + 0 / + 1]     segments in use / entries per segment (`seg_cap`), written by the blend kernel
-//   [kVisibleSegments + 2]           overflow flag: a segment ran out of room, the list is incomplete and not used
-//   [kVisibleHeaderInts, ...)        segments of `seg_cap` entries each, unordered; an entry is four ints:
-//                                    point id | layer << 28, the pixel index inside that layer, and two floats that the
-//                                    backward pass fills with the splat's image-space gradient (its first kernel gathers
-//                                    pixel data with few registers, its second chains the gradient through the projection)
-// A segment holds as many entries as its block has points. A view typically has 0.2-0.3 splats per point, but they come
-// in clumps (whole chunks of neighbouring points on a front surface are accepted on every layer), so single blocks see
-// several times the average.
-constexpr unsigned kSplatPointMask = 0x0FFFFFFFu;
-constexpr int kSplatLayerShift = 28;
-constexpr int kSplatMaxPoints = 1 << 28;  // larger clouds are rendered without a list
-constexpr int kVisibleSegments = 2048;
+// Visible list of one view: the points that passed the fuzzy depth test on their finest layer, each with the float image
+// position the forward pass computed for it and two layer masks, grouped by screen tile. It takes the role of the
+// reference's saved [B,N] drop-out tensor as the per-view state carried from forward to backward (PointRenderer.cu:1524).
+// An entry is four 32-bit words:
+//   point id | dropped << 31        (dropped: the drop-out decision of this view; such points are listed in ghost mode only)
+//   forward mask | backward mask << 8
+//                                   forward mask: layers on which the point is blended (it landed there and passed the
+//                                   depth test; the forward pass goes on after a failure, :380); backward mask: the layers
+//                                   the backward pass visits (it stops at the first failure, :462); never 0 in the list
+//   x, y                            image position at full resolution as float bits; layer l's pixel is
+//                                   rne(x * 0.5^l), rne(y * 0.5^l), the same arithmetic as in the forward pass
+// Entries are grouped by screen tile (kTileW x kTileH pixels of layer 0; a point's pixels on the coarser layers lie in the
+// corresponding quarter-size regions, give or take a pixel of rounding): every tile owns a bucket of `cap` slots, the
+// blend kernel appends to it behind a per-tile cursor (a run of lanes with the same tile takes consecutive slots behind
+// one atomic). A bucket holds max(2048, 2 N / tiles) entries: four visible points per pixel of the tile, or twice the
+// tile's share of the whole cloud. A view that needs more marks its list unusable and the backward pass walks all points.
+// The backward pass overwrites each entry with the work item of its chain kernel, so a list serves one backward call
+// with geometry gradients; it is then marked consumed and a further call walks all points.
+// Layout of the list per view, in int32:
+//   [0, kVisibleHeaderInts)         control words (kListUnusable, kListConsumed, kListGo below), the rest is reserved
+//   [.., + T)                       entries in each tile's bucket (fill cursors; may exceed cap when the list overflowed)
+//   entries                         T buckets of cap entries, 4 ints each
+constexpr int kVisibleSegments = 2048;    // most blocks the depth prepass writes candidate segments with
 constexpr int kVisibleHeaderInts = kVisibleSegments + 8;
-inline size_t visible_list_ints(int num_points) { return (size_t)kVisibleHeaderInts + 4 * ((size_t)num_points + (size_t)kVisibleSegments * kBlock); }
+constexpr int kTileW = 32, kTileH = 16;   // screen tile, in layer-0 pixels (shifts 5 and 4 below)
+constexpr int kTileShiftX = 5, kTileShiftY = 4;
+constexpr unsigned kEntryDropped = 0x80000000u;
+
+struct TileTable
+{
+    int n_tiles;
+    int tiles_x, tiles_y;
+    int w0, h0;
+    int cap;      // entries per bucket
+};
+inline TileTable make_tile_table(int w, int h, int num_points)
+{
+    TileTable t;
+    t.w0 = w; t.h0 = h;
+    t.tiles_x = (w + kTileW - 1) / kTileW;
+    t.tiles_y = (h + kTileH - 1) / kTileH;
+    t.n_tiles = t.tiles_x * t.tiles_y;
+    long long cap = 2ll * num_points / t.n_tiles;
+    if (cap < 2048) cap = 2048;
+    if (cap > num_points) cap = num_points;  // a bucket never needs more room than the cloud has points
+    if (cap < 4) cap = 4;
+    t.cap = (int)((cap + 3) & ~3ll);
+    return t;
+}
+inline size_t tile_table_ints(int n_tiles) { return ((size_t)n_tiles + 3) & ~(size_t)3; }
+inline size_t entry_capacity(int num_points) { return (size_t)num_points + (size_t)kVisibleSegments * kBlock; }
+inline size_t visible_list_ints(int num_points, int w, int h)
+{
+    const TileTable t = make_tile_table(w, h, num_points);
+    return (size_t)kVisibleHeaderInts + tile_table_ints(t.n_tiles) + 4 * (size_t)t.n_tiles * t.cap;
+}
 struct VisibleList
 {
-    int* header;   // null = no list
-    int4* entries;
-    int segments;  // blocks of the blend launch
-    int seg_cap;   // entries per segment
+    int* header;     // null = no list
+    int* tile_cur;   // [n_tiles] entries in each bucket
+    int4* entries;   // bucket t: entries + t * cap
 };
-inline VisibleList make_visible_list(int32_t* base, int num_points, int view, int segments)
+inline VisibleList make_visible_list(int32_t* base, int num_points, int w, int h, int view)
 {
     VisibleList v;
-    if (!base) { v.header = nullptr; v.entries = nullptr; v.segments = 0; v.seg_cap = 0; return v; }
-    int* p = base + (size_t)view * visible_list_ints(num_points);
+    memset(&v, 0, sizeof(v));
+    if (!base) return v;
+    const int n_tiles = make_tile_table(w, h, num_points).n_tiles;
+    int* p = base + (size_t)view * visible_list_ints(num_points, w, h);
     v.header = p;
-    v.entries = reinterpret_cast<int4*>(p + kVisibleHeaderInts);  // 16-byte aligned: header and per-view size are multiples of 4 ints
-    v.segments = segments;
-    long long iters = ((long long)(num_points + kBlock - 1) / kBlock + segments - 1) / segments;
-    v.seg_cap = (int)(iters * kBlock);
+    v.tile_cur = p + kVisibleHeaderInts;
+    // 16-byte aligned: header, tile table and per-view size are multiples of 4 ints
+    v.entries = reinterpret_cast<int4*>(p + kVisibleHeaderInts + tile_table_ints(n_tiles));
     return v;
+}
+// ints at the head of a view's list that the forward pass clears before the blend kernel appends
+inline size_t visible_list_clear_ints(int w, int h, int num_points) { return (size_t)kVisibleHeaderInts + make_tile_table(w, h, num_points).n_tiles; }
+#if defined(__CUDACC__)
+// screen tile of an image position (clamped into the image: positions just outside layer 0 can still land in a coarser layer)
+__device__ __forceinline__ int tile_of_position(const TileTable& tt, float x, float y)
+{
+    const int px = min(max(round_half_even_bounded(x), 0), tt.w0 - 1), py = min(max(round_half_even_bounded(y), 0), tt.h0 - 1);
+    return (py >> kTileShiftY) * tt.tiles_x + (px >> kTileShiftX);
+}
+// Header words of the list that steer the backward pass on the device (no host round trip):
+//   [kVisibleSegments + 2]  set by the forward pass: the list is not usable (a bucket overflowed)
+//   [kVisibleSegments + 3]  set by the last kernel of a backward pass that turned the entries into work items: consumed
+//   [kVisibleSegments + 4]  written by the first kernel of every backward pass (the tile kernel): 1 = this pass runs on the
+//                           list, 0 = the all-points kernels behind it do the work. The later kernels of the pass read
+//                           this word only, so nothing races with the mark in [+3].
+constexpr int kListUnusable = kVisibleSegments + 2, kListConsumed = kVisibleSegments + 3, kListGo = kVisibleSegments + 4;
+#endif
+
+// Large region of a full workspace (behind the camera records and pixel records).
+// Forward: candidate streams - the depth prepass leaves, per view of its group of up to four, the points that landed inside
+// the image as (x, y, depth, point id) records, one segment per block, so that the blend kernel neither reads the
+// positions again nor projects a second time.
+constexpr int kCandViews = 4;
+struct LargeRegion
+{
+    size_t cand_rec, cand_count, total;  // byte offsets from the region's start (forward)
+};
+inline LargeRegion large_region_layout(int num_points, int num_views)
+{
+    const int v = num_views < kCandViews ? (num_views < 1 ? 1 : num_views) : kCandViews;
+    const size_t cap = entry_capacity(num_points);
+    LargeRegion r;
+    r.cand_rec = 0;
+    r.cand_count = r.cand_rec + (size_t)v * cap * 16;
+    r.total = r.cand_count + (size_t)v * kVisibleSegments * sizeof(int) + 256;
+    return r;
 }
 
 adop_status validate_common(const adop_scene* s, const adop_view* views, int B, const adop_render_params* rp, int L);
@@ -312,6 +410,28 @@ __device__ __forceinline__ bool point_dropped(const KernelParams& kp, int i)
 {
     if (kp.dropout_mask) return kp.dropout_mask[i] == 1;
     return dropout_decision(kp.dropout, kp.dropout_seed, (uint32_t)kp.batch_slot, (uint32_t)i);
+}
+// Lanes whose key equals their lower neighbour's form a run (keys of neighbouring points mostly do). Returns the lane
+// that starts this lane's run and the run's length: the first lane of a run can then speak for all of it (one atomic
+// per run instead of one per lane). Cheaper than __match_any_sync, which was measured to dominate the kernels that
+// used it (MIO-pipe bound); equal keys that are not adjacent simply form separate runs.
+__device__ __forceinline__ void warp_runs(int key, int lane, int* start_lane, int* length)
+{
+    const int prev = __shfl_up_sync(0xffffffffu, key, 1);
+    const unsigned starts = __ballot_sync(0xffffffffu, lane == 0 || key != prev);
+    const unsigned at_or_below = starts & (0xffffffffu >> (31 - lane));
+    const int s = 31 - __clz(at_or_below);
+    const unsigned above = lane == 31 ? 0u : (starts & (0xfffffffeu << lane));
+    const int e = above ? __ffs(above) - 1 : 32;
+    *start_lane = s;
+    *length = e - s;
+}
+// chunk of round k of this block, or -1 when the round has none (the last superblocks can be short)
+__device__ __forceinline__ int scheduled_chunk(const ChunkSchedule& cs, int k)
+{
+    const int sb = (int)((blockIdx.x + (unsigned)k * (unsigned)cs.spread) % gridDim.x);
+    const int chunk = sb * cs.rounds + k;
+    return chunk < cs.chunks ? chunk : -1;
 }
 __device__ __forceinline__ float warp_sum(float v)
 {

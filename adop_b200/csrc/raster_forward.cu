@@ -92,41 +92,92 @@ __global__ void k_texture_deinterleave(const float* __restrict__ in, float* __re
 // V consecutive views of the batch per launch (camera records and depth planes of a batch are consecutive): the point
 // is loaded once and projected V times. Measured on the 4-layer prepass: 120 / 101 / 93 us per view for V = 1 / 2 / 4,
 // 149 us for V = 8 (too many depth pyramids in flight), so groups of four are used.
-template <int L, bool PLAIN, int V>
-__global__ void __launch_bounds__(kBlock, 8) k_depth_prepass(PointStreams pts, const ViewCam* __restrict__ camp, KernelParams kp, LayerTable lt)
+// CAND: every point that lands inside the image of view v is also appended, as (x, y, depth, point id), to this block's
+// segment of view v's candidate stream (warp vote + one shared-memory atomic per warp and view; a segment has room for
+// every point of the block, so it cannot overflow). The blend kernel then reads those records instead of the positions
+// and does not project again: it sees the same float x, y, depth, hence takes the same decisions bit for bit.
+struct CandOut
 {
+    float4* rec;          // view v: rec + v * view_stride
+    int* count;           // view v: count + v * kVisibleSegments, one entry per block
+    size_t view_stride;   // records per view
+    int seg_cap;          // records per block segment
+};
+template <int L, bool PLAIN, int V, bool CAND>
+__global__ void __launch_bounds__(kBlock, 8) k_depth_prepass(PointStreams pts, ChunkSchedule sched, const ViewCam* __restrict__ camp, KernelParams kp,
+                                                           LayerTable lt, CandOut co)
+{
+    static_assert(!CAND || PLAIN, "candidate records carry no drop-out radius");
     const bool use_normal = PLAIN ? false : kp.check_normal != 0;
     const bool use_radius = PLAIN ? false : kp.drop_out_points_by_radius != 0;
-    const int stride = gridDim.x * blockDim.x;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < pts.n; i += stride)
+    __shared__ int s_cnt[V];
+    const int lane = threadIdx.x & 31;
+    if (CAND)
     {
+        if (threadIdx.x < V) s_cnt[threadIdx.x] = 0;
+        __syncthreads();
+    }
+    // warp-uniform trip count (the candidate append votes across the warp)
+    for (int k = 0; k < sched.rounds; ++k)
+    {
+        const int chunk = scheduled_chunk(sched, k);
+        if (chunk < 0) continue;  // block-uniform
+        const int i = chunk * kBlock + threadIdx.x;
+        const bool valid = i < pts.n;
         FetchedPoint f;
-        if (PLAIN) { float4 c = __ldg(pts.position + i); f.p.x = c.x; f.p.y = c.y; f.p.z = c.z; f.r = c.w; f.has_normal = false; f.n.x = f.n.y = f.n.z = 0.f; }
-        else f = fetch_point(pts, i);
+        f.p.x = f.p.y = f.p.z = f.r = 0.f; f.has_normal = false; f.n.x = f.n.y = f.n.z = 0.f;
+        if (valid)
+        {
+            if (PLAIN) { float4 c = __ldg(pts.position + i); f.p.x = c.x; f.p.y = c.y; f.p.z = c.z; f.r = c.w; }
+            else f = fetch_point(pts, i);
+        }
 #pragma unroll
         for (int v = 0; v < V; ++v)
         {
             RasterPoint q;
-            if (PLAIN ? !project_plain(camp[v], f.p, kp.dist_cutoff, &q)
-                      : !project_for_raster(camp[v], f.p, f.r, f.n, f.has_normal, use_normal, kp.dist_cutoff, &q, use_radius)) continue;
-            float x = q.x, y = q.y, rad = q.radius_px;
-            const int zi = __float_as_int(q.z);
-#pragma unroll
-            for (int l = 0; l < L; ++l, rad *= 0.5f, x *= 0.5f, y *= 0.5f)
+            q.x = q.y = q.z = q.radius_px = 0.f;
+            bool in_image = false;
+            if (valid && (PLAIN ? project_plain(camp[v], f.p, kp.dist_cutoff, &q)
+                                : project_for_raster(camp[v], f.p, f.r, f.n, f.has_normal, use_normal, kp.dist_cutoff, &q, use_radius)))
             {
-                if (use_radius && rad < kp.drop_out_radius_threshold) break;
-                int px = round_half_even_bounded(x), py = round_half_even_bounded(y);
-                if ((unsigned)px >= (unsigned)lt.w[l] || (unsigned)py >= (unsigned)lt.h[l]) continue;
-                // depth plane of view v of the group: the planes of a batch follow each other
-                // (32-bit index: a group's planes of one layer hold fewer than 2^31 pixels, checked by the entry point)
-                int* dst = reinterpret_cast<int*>(lt.depth[l]) + ((unsigned)(v * lt.h[l] + py) * (unsigned)lt.w[l] + (unsigned)px);
-                // early z: the plane is being updated by other blocks' atomicMin while it is read, so the read goes through L2
-                // (__ldcg), not the non-coherent path. A value that is older than the latest minimum can only be
-                // LARGER than the true one (depths only decrease), so it never drops a point that should win; at worst
-                // it lets through an atomic that changes nothing.
-                if (l == 0 || zi < __ldcg(dst)) atomicMin(dst, zi);
+                float x = q.x, y = q.y, rad = q.radius_px;
+                const int zi = __float_as_int(q.z);
+#pragma unroll
+                for (int l = 0; l < L; ++l, rad *= 0.5f, x *= 0.5f, y *= 0.5f)
+                {
+                    if (use_radius && rad < kp.drop_out_radius_threshold) break;
+                    int px = round_half_even_bounded(x), py = round_half_even_bounded(y);
+                    if ((unsigned)px >= (unsigned)lt.w[l] || (unsigned)py >= (unsigned)lt.h[l]) continue;
+                    in_image = true;
+                    // depth plane of view v of the group: the planes of a batch follow each other
+                    // (32-bit index: a group's planes of one layer hold fewer than 2^31 pixels, checked by the entry point)
+                    int* dst = reinterpret_cast<int*>(lt.depth[l]) + ((unsigned)(v * lt.h[l] + py) * (unsigned)lt.w[l] + (unsigned)px);
+                    // early z: the plane is being updated by other blocks' atomicMin while it is read, so the read goes through L2
+                    // (__ldcg), not the non-coherent path. A value that is older than the latest minimum can only be
+                    // LARGER than the true one (depths only decrease), so it never drops a point that should win; at worst
+                    // it lets through an atomic that changes nothing.
+                    if (l == 0 || zi < __ldcg(dst)) atomicMin(dst, zi);
+                }
+            }
+            if (CAND)
+            {
+                const unsigned vote = __ballot_sync(0xffffffffu, in_image);
+                if (vote)
+                {
+                    int wbase = 0;
+                    if (lane == 0) wbase = atomicAdd(&s_cnt[v], __popc(vote));
+                    wbase = __shfl_sync(0xffffffffu, wbase, 0);
+                    if (in_image)
+                        co.rec[(size_t)v * co.view_stride + (size_t)blockIdx.x * co.seg_cap + wbase + __popc(vote & ((1u << lane) - 1u))] =
+                            make_float4(q.x, q.y, q.z, __int_as_float(i));
+                }
             }
         }
+    }
+    if (CAND)
+    {
+        __syncthreads();
+        if (threadIdx.x < V) co.count[threadIdx.x * kVisibleSegments + blockIdx.x] = s_cnt[threadIdx.x];
     }
 }
 
@@ -199,173 +250,184 @@ __device__ __forceinline__ void splat_record(float* rec, float* weight, const fl
     }
 }
 
-// With EMIT the kernel also appends the (point, layer) splats that the backward pass will visit to this block's segment
-// of the view's splat list (shared-memory counter, no global atomics); in ghost-gradient mode dropped points are tested
-// too (they blend nothing but the backward pass needs them, PointRenderer.cu:487-488).
-template <int L, int C, bool EMIT, bool PLAIN>
-__global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, const float* __restrict__ texture,
+// One kernel tests every candidate (or, without candidate streams, every point of the cloud) against the depth buffers
+// and blends the accepted ones. Only about a third of the lanes of a warp that has accepted points at all have one (11 of
+// 32 on the 1080p benchmark scene), so the work on accepted points - descriptor load, atomics, the list entry - is not
+// done where the point is tested: a warp parks its accepted points (index, layer masks, image position) in a queue of its
+// own in shared memory and finishes them 32 at a time with every lane busy.
+// EMIT: the points the backward pass will visit are also written to the visible list, straight into the bucket of their
+// screen tile (a run of lanes with the same tile takes consecutive slots behind one atomic). In ghost-gradient mode
+// dropped points are tested too (they blend nothing but the backward pass needs them, PointRenderer.cu:487-488).
+// CAND: block b reads the candidate segment that block b of the depth prepass wrote, (x, y, depth, point id) records,
+// instead of the positions, and does not project.
+struct CandIn
+{
+    const float4* rec;   // this view's records
+    const int* count;    // this view's per-block counts
+    int seg_cap;
+};
+template <int L, int C, bool PLAIN, bool CAND, bool EMIT>
+__global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, ChunkSchedule sched, CandIn cs, const float* __restrict__ texture,
                                                    const float* __restrict__ texture_interleaved, int num_texels,
-                                                   const ViewCam* __restrict__ camp, KernelParams kp, LayerTable lt,
+                                                   const ViewCam* __restrict__ camp, KernelParams kp, LayerTable lt, TileTable tt,
                                                    float* __restrict__ accum, VisibleList vl)
 {
+    static_assert(!CAND || PLAIN, "candidate records carry no drop-out radius");
     const ViewCam& cam = *camp;
     const bool use_normal = PLAIN ? false : kp.check_normal != 0;
     const bool use_radius = PLAIN ? false : kp.drop_out_points_by_radius != 0;
-    __shared__ int s_count;
-    if (EMIT)
-    {
-        if (threadIdx.x == 0) s_count = 0;
-        __syncthreads();
-    }
     constexpr int RS = AccumLayout<C>::kFloats;
-    const int stride = gridDim.x * blockDim.x;
-    int4* seg = EMIT ? vl.entries + (size_t)blockIdx.x * vl.seg_cap : nullptr;
     const int lane = threadIdx.x & 31;
-    // Only about a third of the lanes of a warp that has accepted points at all have one (11 of 32 on the 1080p
-    // benchmark scene), so the work on accepted points - descriptor load, atomics, the list entries - is not done where the
-    // point is tested: a warp parks its accepted points (index, layer mask, pixel per layer) in a queue of its own in
-    // shared memory and finishes them 32 at a time with every lane busy.
-    constexpr int PW = L + 2;
-    __shared__ int s_park[kBlock / 32][64 * PW];
-    int* park = s_park[threadIdx.x >> 5];
+    // parked record: point id | dropped, forward mask | backward mask << 8, x, y
+    __shared__ int4 s_park[kBlock / 32][64];
+    int4* park = s_park[threadIdx.x >> 5];
     int n_parked = 0;  // the same in every lane of the warp
 
-    // Tests one point against the depth buffers: 0 = nothing to do, else the mask of accepted layers, bit 31 = the point
-    // is dropped in this view (it blends nothing but the backward pass visits it in ghost-gradient mode).
-    auto test_point = [&](int i, float4 cur, int* pix) -> unsigned
+    // masks of a projected point: forward mask (layers to blend: landed and passed the depth test) | backward mask << 8
+    // (the layers the backward pass will visit: it skips layers the point does not land in and stops at the first depth
+    // failure, PointRenderer.cu:451-462)
+    auto test_layers = [&](float x, float y, float z, float rad) -> unsigned
     {
-        const bool dropped = point_dropped(kp, i);
-        if (dropped && !(EMIT && kp.ghost_gradients)) return 0u;
-        FetchedPoint f;
-        if (PLAIN) { f.p.x = cur.x; f.p.y = cur.y; f.p.z = cur.z; f.r = cur.w; f.has_normal = false; f.n.x = f.n.y = f.n.z = 0.f; }
-        else f = fetch_point(pts, i, cur);
-        RasterPoint q;
-        if (PLAIN ? !project_plain(cam, f.p, kp.dist_cutoff, &q)
-                  : !project_for_raster(cam, f.p, f.r, f.n, f.has_normal, use_normal, kp.dist_cutoff, &q, use_radius)) return 0u;
-        float x = q.x, y = q.y, rad = q.radius_px;
-        // pixel index inside the layer (a pyramid has fewer than 2^31 pixels), -1 = not in this layer; the depth reads
-        // of all layers go out together
+        int lin[L];
+        bool in[L];
         bool live = true;
 #pragma unroll
         for (int l = 0; l < L; ++l, rad *= 0.5f, x *= 0.5f, y *= 0.5f)
         {
             if (use_radius && rad < kp.drop_out_radius_threshold) live = false;  // break, :368-371
             int px = round_half_even_bounded(x), py = round_half_even_bounded(y);
-            bool in = live && (unsigned)px < (unsigned)lt.w[l] && (unsigned)py < (unsigned)lt.h[l];
-            pix[l] = in ? py * lt.w[l] + px : -1;
+            in[l] = live && (unsigned)px < (unsigned)lt.w[l] && (unsigned)py < (unsigned)lt.h[l];
+            lin[l] = py * lt.w[l] + px;
         }
-        unsigned pass = 0;
+        unsigned pass = 0;  // the depth reads of all layers go out together
 #pragma unroll
         for (int l = 0; l < L; ++l)
         {
-            float image_depth = pix[l] >= 0 ? __ldg(lt.depth[l] + pix[l]) : 0.f;
-            if (pix[l] >= 0 && !(q.z > image_depth * kp.depth_accept_plus_one)) pass |= 1u << l;
+            float image_depth = in[l] ? __ldg(lt.depth[l] + lin[l]) : 0.f;
+            if (in[l] && !(z > image_depth * kp.depth_accept_plus_one)) pass |= 1u << l;
         }
-        if (pass == 0) return 0u;
-        return pass | (dropped ? 0x80000000u : 0u);
-    };
-
-    // All 32 lanes together: blend the accepted point of every valid lane and append its splats to the list.
-    auto finish = [&](bool valid, const int* e)
-    {
+        if (!EMIT) return pass;
         unsigned bmask = 0;
-        int i = 0;
-        int pix[L];
 #pragma unroll
-        for (int l = 0; l < L; ++l) pix[l] = -1;
-        if (valid)
+        for (int l = 0; l < L; ++l)
         {
-            i = e[0];
-            const unsigned code = (unsigned)e[1];
+            if (!in[l]) continue;
+            if (!(pass & (1u << l))) break;
+            bmask |= 1u << l;
+        }
+        return pass | (bmask << 8);
+    };
+    // one candidate / point -> parked record (y = 0: nothing to do)
+    auto make_entry = [&](int i, float4 cur) -> int4
+    {
+        const bool dropped = point_dropped(kp, i);
+        if (dropped && !(EMIT && kp.ghost_gradients)) return make_int4(0, 0, 0, 0);
+        float x, y;
+        unsigned masks;
+        if (CAND)
+        {
+            x = cur.x; y = cur.y;
+            masks = test_layers(cur.x, cur.y, cur.z, 0.f);
+        }
+        else
+        {
+            FetchedPoint f;
+            if (PLAIN) { f.p.x = cur.x; f.p.y = cur.y; f.p.z = cur.z; f.r = cur.w; f.has_normal = false; f.n.x = f.n.y = f.n.z = 0.f; }
+            else f = fetch_point(pts, i, cur);
+            RasterPoint q;
+            if (PLAIN ? !project_plain(cam, f.p, kp.dist_cutoff, &q)
+                      : !project_for_raster(cam, f.p, f.r, f.n, f.has_normal, use_normal, kp.dist_cutoff, &q, use_radius)) return make_int4(0, 0, 0, 0);
+            x = q.x; y = q.y;
+            masks = test_layers(q.x, q.y, q.z, q.radius_px);
+        }
+        if (dropped) masks &= 0xff00u;  // a dropped point blends nothing
+        return make_int4((int)((unsigned)i | (dropped ? kEntryDropped : 0u)), (int)masks, __float_as_int(x), __float_as_int(y));
+    };
+    // All 32 lanes together: blend the accepted point of every valid lane and write its list entry.
+    auto finish = [&](bool valid, int4 e)
+    {
+        const unsigned code = valid ? ((unsigned)e.y & 0xffu) : 0u;
+        if (code)
+        {
+            const int i = (int)((unsigned)e.x & ~kEntryDropped);
+            float t[C];
+            const int ti = pts.index ? __ldg(pts.index + i) : i;
+            load_descriptor<C>(texture, texture_interleaved, num_texels, ti, t);
+            float x = __int_as_float(e.z), y = __int_as_float(e.w);
 #pragma unroll
-            for (int l = 0; l < L; ++l) pix[l] = e[2 + l];
-            if (!(code >> 31))
-            {
-                float t[C];
-                const int ti = pts.index ? __ldg(pts.index + i) : i;
-                load_descriptor<C>(texture, texture_interleaved, num_texels, ti, t);
-#pragma unroll
-                for (int l = 0; l < L; ++l)
-                    if (code & (1u << l)) splat_record<C>(accum + ((size_t)lt.rec_off[l] + pix[l]) * RS, lt.weight[l] + pix[l], t);
-            }
-            // the layers the backward pass will visit: it skips layers the point does not land in and stops at the
-            // first depth failure (PointRenderer.cu:451-462)
-#pragma unroll
-            for (int l = 0; l < L; ++l)
-            {
-                if (pix[l] < 0) continue;
-                if (!(code & (1u << l))) break;
-                bmask |= 1u << l;
-            }
+            for (int l = 0; l < L; ++l, x *= 0.5f, y *= 0.5f)
+                if (code & (1u << l))
+                {
+                    const int lin = round_half_even_bounded(y) * lt.w[l] + round_half_even_bounded(x);
+                    splat_record<C>(accum + ((size_t)lt.rec_off[l] + lin) * RS, lt.weight[l] + lin, t);
+                }
         }
         if (EMIT)
         {
-            const int cnt = __popc(bmask);
-            int incl = cnt;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1)
+            const bool keep = valid && ((unsigned)e.y >> 8) != 0;
+            if (__ballot_sync(0xffffffffu, keep))
             {
-                int v = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += v;
-            }
-            const int total = __shfl_sync(0xffffffffu, incl, 31);
-            if (total > 0)
-            {
-                // one shared-memory atomic per warp reserves room in this block's segment of the splat list
-                int wbase = 0;
-                if (lane == 0) wbase = atomicAdd(&s_count, total);
-                wbase = __shfl_sync(0xffffffffu, wbase, 0);
-                int at = wbase + incl - cnt;
-                if (wbase + total <= vl.seg_cap)
+                const int tile = keep ? tile_of_position(tt, __int_as_float(e.z), __int_as_float(e.w)) : -1;
+                int run_start, run_len;
+                warp_runs(tile, lane, &run_start, &run_len);
+                int slot = 0;
+                if (keep && run_start == lane) slot = atomicAdd(vl.tile_cur + tile, run_len);
+                slot = __shfl_sync(0xffffffffu, slot, run_start) + (lane - run_start);
+                if (keep)
                 {
-#pragma unroll
-                    for (int l = 0; l < L; ++l)
-                        if (bmask & (1u << l)) seg[at++] = make_int4(i | (l << kSplatLayerShift), pix[l], 0, 0);
+                    if (slot < tt.cap) vl.entries[(size_t)tile * tt.cap + slot] = e;
+                    else vl.header[kListUnusable] = 1;  // the bucket is full: the backward pass walks all points instead
                 }
-                else if (lane == 0)
-                    vl.header[kVisibleSegments + 2] = 1;  // out of room: the backward pass falls back to walking all points
             }
         }
     };
-
-    // warp-uniform trip count: parking and finishing use full-warp votes and shuffles
-    for (int base = blockIdx.x * blockDim.x; base < pts.n; base += stride)
+    auto park_and_finish = [&](int4 e)
     {
-        const int i = base + threadIdx.x;
-        unsigned code = 0;
-        int pix[L];
-        if (i < pts.n) code = test_point(i, __ldg(pts.position + i), pix);
-        const unsigned vote = __ballot_sync(0xffffffffu, code != 0);
+        const bool keep = e.y != 0;
+        const unsigned vote = __ballot_sync(0xffffffffu, keep);
         if (vote)
         {
-            if (code)
-            {
-                int* e = park + (n_parked + __popc(vote & ((1u << lane) - 1u))) * PW;
-                e[0] = i;
-                e[1] = (int)code;
-#pragma unroll
-                for (int l = 0; l < L; ++l) e[2 + l] = pix[l];
-            }
+            if (keep) park[n_parked + __popc(vote & ((1u << lane) - 1u))] = e;
             n_parked += __popc(vote);
             __syncwarp();
             if (n_parked >= 32)
             {
                 n_parked -= 32;
-                finish(true, park + (n_parked + lane) * PW);
+                finish(true, park[n_parked + lane]);
             }
             __syncwarp();
         }
-    }
-    if (n_parked > 0) finish(lane < n_parked, park + lane * PW);
-    if (EMIT)
+    };
+    // warp-uniform trip counts: parking and finishing use full-warp votes and shuffles
+    if (CAND)
     {
-        __syncthreads();
-        if (threadIdx.x == 0)
+        const int cnt = __ldg(cs.count + blockIdx.x);
+        const float4* rec = cs.rec + (size_t)blockIdx.x * cs.seg_cap;
+        for (int k0 = 0; k0 < cnt; k0 += kBlock)
         {
-            vl.header[blockIdx.x] = s_count < vl.seg_cap ? s_count : vl.seg_cap;
-            if (blockIdx.x == 0) { vl.header[kVisibleSegments] = vl.segments; vl.header[kVisibleSegments + 1] = vl.seg_cap; }
+            const int k = k0 + threadIdx.x;
+            int4 e = make_int4(0, 0, 0, 0);
+            if (k < cnt)
+            {
+                const float4 c = __ldcs(rec + k);
+                e = make_entry(__float_as_int(c.w), c);
+            }
+            park_and_finish(e);
         }
     }
+    else
+    {
+        for (int k = 0; k < sched.rounds; ++k)
+        {
+            const int chunk = scheduled_chunk(sched, k);
+            if (chunk < 0) continue;  // block-uniform
+            const int i = chunk * kBlock + threadIdx.x;
+            int4 e = make_int4(0, 0, 0, 0);
+            if (i < pts.n) e = make_entry(i, __ldg(pts.position + i));
+            park_and_finish(e);
+        }
+    }
+    if (n_parked > 0) finish(lane < n_parked, lane < n_parked ? park[lane] : make_int4(0, 0, 0, 0));
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -478,87 +540,118 @@ __global__ void __launch_bounds__(kBlock) k_resolve(LayerTable lt, const ViewCam
 }
 
 // ------------------------------------------------------------------------------------------------------
+// What one forward call decided once for all its views.
+struct ForwardPlan
+{
+    float* accum;
+    bool env;
+    int32_t* list_base;   // null = no visible list
+    int w, h;             // layer-0 size (geometry of the visible list)
+    int num_views;
+    char* large;          // large region of a full workspace (candidate streams), null = small workspace
+    LargeRegion lr;
+    size_t cand_view_stride;  // records per candidate stream
+    TileTable tiles;
+};
+
 template <int L, int C, bool PLAIN>
 static adop_status launch_view_forward_impl(const PointStreams& pts, const adop_scene* s, const ViewCam* cam, const KernelParams& kp,
-                                            const LayerTable& lt, float* accum, bool env, cudaStream_t st, int32_t* list_base, int view,
-                                            int depth_views)
+                                            const LayerTable& lt, const ForwardPlan& plan, cudaStream_t st, int view, int depth_views)
 {
-    static const int g_depth = resident_grid(k_depth_prepass<L, PLAIN, 4>, 1ll << 40);
-    static const int g_blend_plain = resident_grid(k_blend<L, C, false, PLAIN>, 1ll << 40);
-    static const int g_blend_emit = resident_grid(k_blend<L, C, true, PLAIN>, 1ll << 40);
+    constexpr bool kCand = PLAIN;  // candidate streams exist when neither the normal test nor the radius rule is in use
+    static const int g_depth = resident_grid(k_depth_prepass<L, PLAIN, 4, false>, 1ll << 40);
+    static const int g_depth_cand = resident_grid(k_depth_prepass<L, PLAIN, 4, kCand>, 1ll << 40);
+    static const int g_blend = resident_grid(k_blend<L, C, PLAIN, false, false>, 1ll << 40);
+    static const int g_blend_emit = resident_grid(k_blend<L, C, PLAIN, false, true>, 1ll << 40);
+    static const int g_blend_cand = resident_grid(k_blend<L, C, PLAIN, kCand, false>, 1ll << 40);
+    static const int g_blend_cand_emit = resident_grid(k_blend<L, C, PLAIN, kCand, true>, 1ll << 40);
     static const int g_resolve = resident_grid(k_resolve<C>, 1ll << 40);
-    const int g_blend = list_base ? (g_blend_emit < kVisibleSegments ? g_blend_emit : kVisibleSegments) : g_blend_plain;
     const int need = (pts.n + kBlock - 1) / kBlock;
+    const bool cand = kCand && plan.large != nullptr;
+    const bool emit = plan.list_base != nullptr;
+    // With candidate streams the depth prepass and the blend kernel run on the same grid (block b of the blend kernel reads
+    // what block b of the prepass wrote).
+    int grid_blend = cand ? (emit ? g_blend_cand_emit : g_blend_cand) : (emit ? g_blend_emit : g_blend);
+    if (cand)
+    {
+        if (grid_blend > g_depth_cand) grid_blend = g_depth_cand;
+        if (grid_blend > kVisibleSegments) grid_blend = kVisibleSegments;
+    }
+    if (grid_blend > need) grid_blend = need < 1 ? 1 : need;
+    const int seg_cap = (int)((((long long)need + grid_blend - 1) / grid_blend) * kBlock);
+    CandOut co;
+    co.rec = cand ? reinterpret_cast<float4*>(plan.large + plan.lr.cand_rec) : nullptr;
+    co.count = cand ? reinterpret_cast<int*>(plan.large + plan.lr.cand_count) : nullptr;
+    co.view_stride = plan.cand_view_stride;
+    co.seg_cap = seg_cap;
     // the depth prepass of this view was done by the launch of its group's first view, unless this is that view
-    const int grid_depth = need < g_depth ? (need < 1 ? 1 : need) : g_depth;
-    switch (depth_views)
+    if (depth_views > 0)
     {
-        case 1: ADOP_LAUNCH("k_depth_prepass", st, (k_depth_prepass<L, PLAIN, 1><<<grid_depth, kBlock, 0, st>>>(pts, cam, kp, lt))); break;
-        case 2: ADOP_LAUNCH("k_depth_prepass", st, (k_depth_prepass<L, PLAIN, 2><<<grid_depth, kBlock, 0, st>>>(pts, cam, kp, lt))); break;
-        case 3: ADOP_LAUNCH("k_depth_prepass", st, (k_depth_prepass<L, PLAIN, 3><<<grid_depth, kBlock, 0, st>>>(pts, cam, kp, lt))); break;
-        case 4: ADOP_LAUNCH("k_depth_prepass", st, (k_depth_prepass<L, PLAIN, 4><<<grid_depth, kBlock, 0, st>>>(pts, cam, kp, lt))); break;
-        default: break;
+        const int grid_depth = cand ? grid_blend : (need < g_depth ? (need < 1 ? 1 : need) : g_depth);
+#define ADOP_PREPASS(VV)                                                                                                         \
+    if (cand) ADOP_LAUNCH("k_depth_prepass", st, (k_depth_prepass<L, PLAIN, VV, kCand><<<grid_depth, kBlock, 0, st>>>(pts, make_chunk_schedule(pts.n, grid_depth), cam, kp, lt, co))); \
+    else ADOP_LAUNCH("k_depth_prepass", st, (k_depth_prepass<L, PLAIN, VV, false><<<grid_depth, kBlock, 0, st>>>(pts, make_chunk_schedule(pts.n, grid_depth), cam, kp, lt, co)));
+        switch (depth_views)
+        {
+            case 1: ADOP_PREPASS(1) break;
+            case 2: ADOP_PREPASS(2) break;
+            case 3: ADOP_PREPASS(3) break;
+            default: ADOP_PREPASS(4) break;
+        }
+#undef ADOP_PREPASS
     }
-    int grid_blend = need < g_blend ? (need < 1 ? 1 : need) : g_blend;
-    if (list_base)
+    VisibleList vl = make_visible_list(plan.list_base, pts.n, plan.w, plan.h, view);
+    if (vl.header) ADOP_CUDA_TRY(cudaMemsetAsync(vl.header, 0, sizeof(int) * visible_list_clear_ints(plan.w, plan.h, pts.n), st));
+    CandIn ci;
+    ci.rec = cand ? co.rec + (size_t)(view % kCandViews) * plan.cand_view_stride : nullptr;
+    ci.count = cand ? co.count + (view % kCandViews) * kVisibleSegments : nullptr;
+    ci.seg_cap = seg_cap;
+#define ADOP_BLEND(CAND_, EMIT_)                                                                                                 \
+    ADOP_LAUNCH("k_blend", st, (k_blend<L, C, PLAIN, CAND_, EMIT_><<<grid_blend, kBlock, 0, st>>>(                               \
+                                   pts, make_chunk_schedule(pts.n, grid_blend), ci, s->texture, s->texture_interleaved, s->num_texels, cam, kp, lt, plan.tiles, plan.accum, vl)))
+    if (cand)
     {
-        // a block's list segment holds as many entries as the block has points; visible splats come in clumps (a chunk of
-        // neighbouring points on a front surface is accepted on every layer), so every block should average over at
-        // least 16 chunks from all over the cloud
-        int cap = need / 16;
-        if (cap < 1) cap = 1;
-        if (grid_blend > cap) grid_blend = cap;
-    }
-    VisibleList vl = make_visible_list(list_base, pts.n, view, grid_blend);
-    if (list_base && pts.n >= kSplatMaxPoints)
-    {
-        // too many points for the 28-bit ids of the list: mark it unusable and blend without recording
-        ADOP_CUDA_TRY(cudaMemsetAsync(vl.header, 0, sizeof(int) * kVisibleHeaderInts, st));
-        ADOP_CUDA_TRY(cudaMemsetAsync(vl.header + kVisibleSegments + 2, 1, sizeof(int), st));
-        ADOP_LAUNCH("k_blend", st, (k_blend<L, C, false, PLAIN><<<grid_blend, kBlock, 0, st>>>(pts, s->texture, s->texture_interleaved, s->num_texels, cam, kp, lt, accum, vl)));
-    }
-    else if (list_base)
-    {
-        ADOP_CUDA_TRY(cudaMemsetAsync(vl.header, 0, sizeof(int) * kVisibleHeaderInts, st));
-        ADOP_LAUNCH("k_blend", st, (k_blend<L, C, true, PLAIN><<<grid_blend, kBlock, 0, st>>>(pts, s->texture, s->texture_interleaved, s->num_texels, cam, kp, lt, accum, vl)));
+        if (emit) ADOP_BLEND(kCand, true); else ADOP_BLEND(kCand, false);
     }
     else
-        ADOP_LAUNCH("k_blend", st, (k_blend<L, C, false, PLAIN><<<grid_blend, kBlock, 0, st>>>(pts, s->texture, s->texture_interleaved, s->num_texels, cam, kp, lt, accum, vl)));
+    {
+        if (emit) ADOP_BLEND(false, true); else ADOP_BLEND(false, false);
+    }
+#undef ADOP_BLEND
     unsigned total = lt.rec_off[kMaxLayers];
     int grid_px = (int)((total + kBlock - 1) / kBlock);
     if (grid_px > g_resolve) grid_px = g_resolve;
-    ADOP_LAUNCH("k_resolve", st, (k_resolve<C><<<grid_px, kBlock, 0, st>>>(lt, cam, kp, accum, s->background,
-                                                                          env ? s->env_map : nullptr, s->env_h, s->env_w)));
+    ADOP_LAUNCH("k_resolve", st, (k_resolve<C><<<grid_px, kBlock, 0, st>>>(lt, cam, kp, plan.accum, s->background,
+                                                                          plan.env ? s->env_map : nullptr, s->env_h, s->env_w)));
     ADOP_CUDA_TRY(cudaGetLastError());
     return ADOP_OK;
 }
 
 template <int L, int C>
 static adop_status launch_view_forward(const PointStreams& pts, const adop_scene* s, const ViewCam* cam, const KernelParams& kp,
-                                       const LayerTable& lt, float* accum, bool env, cudaStream_t st, int32_t* list_base, int view,
-                                       int depth_views)
+                                       const LayerTable& lt, const ForwardPlan& plan, cudaStream_t st, int view, int depth_views)
 {
     // the common case - no normal test (or no normals) and no radius drop-out - gets kernels without that code
     const bool plain = !(kp.check_normal && pts.normal) && !kp.drop_out_points_by_radius;
-    return plain ? launch_view_forward_impl<L, C, true>(pts, s, cam, kp, lt, accum, env, st, list_base, view, depth_views)
-                 : launch_view_forward_impl<L, C, false>(pts, s, cam, kp, lt, accum, env, st, list_base, view, depth_views);
+    return plain ? launch_view_forward_impl<L, C, true>(pts, s, cam, kp, lt, plan, st, view, depth_views)
+                 : launch_view_forward_impl<L, C, false>(pts, s, cam, kp, lt, plan, st, view, depth_views);
 }
 
 template <int C>
 static adop_status dispatch_layers_forward(int L, const PointStreams& pts, const adop_scene* s, const ViewCam* cam,
-                                           const KernelParams& kp, const LayerTable& lt, float* accum, bool env,
-                                           cudaStream_t st, int32_t* list_base, int view, int depth_views)
+                                           const KernelParams& kp, const LayerTable& lt, const ForwardPlan& plan,
+                                           cudaStream_t st, int view, int depth_views)
 {
     switch (L)
     {
-        case 1: return launch_view_forward<1, C>(pts, s, cam, kp, lt, accum, env, st, list_base, view, depth_views);
-        case 2: return launch_view_forward<2, C>(pts, s, cam, kp, lt, accum, env, st, list_base, view, depth_views);
-        case 3: return launch_view_forward<3, C>(pts, s, cam, kp, lt, accum, env, st, list_base, view, depth_views);
-        case 4: return launch_view_forward<4, C>(pts, s, cam, kp, lt, accum, env, st, list_base, view, depth_views);
-        case 5: return launch_view_forward<5, C>(pts, s, cam, kp, lt, accum, env, st, list_base, view, depth_views);
-        case 6: return launch_view_forward<6, C>(pts, s, cam, kp, lt, accum, env, st, list_base, view, depth_views);
-        case 7: return launch_view_forward<7, C>(pts, s, cam, kp, lt, accum, env, st, list_base, view, depth_views);
-        case 8: return launch_view_forward<8, C>(pts, s, cam, kp, lt, accum, env, st, list_base, view, depth_views);
+        case 1: return launch_view_forward<1, C>(pts, s, cam, kp, lt, plan, st, view, depth_views);
+        case 2: return launch_view_forward<2, C>(pts, s, cam, kp, lt, plan, st, view, depth_views);
+        case 3: return launch_view_forward<3, C>(pts, s, cam, kp, lt, plan, st, view, depth_views);
+        case 4: return launch_view_forward<4, C>(pts, s, cam, kp, lt, plan, st, view, depth_views);
+        case 5: return launch_view_forward<5, C>(pts, s, cam, kp, lt, plan, st, view, depth_views);
+        case 6: return launch_view_forward<6, C>(pts, s, cam, kp, lt, plan, st, view, depth_views);
+        case 7: return launch_view_forward<7, C>(pts, s, cam, kp, lt, plan, st, view, depth_views);
+        case 8: return launch_view_forward<8, C>(pts, s, cam, kp, lt, plan, st, view, depth_views);
     }
     return ADOP_ERR_INVALID_ARGUMENT;
 }
@@ -576,6 +669,21 @@ extern "C" size_t adop_raster_workspace_bytes(int32_t w, int32_t h, int32_t laye
     int fwd = record_floats(channels), bwd = (2 * channels + 3) & ~3;
     size_t bytes = (size_t)lt.rec_off[kMaxLayers] * (fwd > bwd ? fwd : bwd) * sizeof(float);
     return kCamRegionBytes + bytes + 256;  // per-view camera records, then the pixel records
+}
+
+// The small workspace rounded up to 256 bytes = where the large region of a full workspace starts.
+static size_t workspace_large_offset(int32_t w, int32_t h, int32_t layers, int32_t channels)
+{
+    return (adop_raster_workspace_bytes(w, h, layers, channels) + 255) & ~(size_t)255;
+}
+
+extern "C" size_t adop_raster_workspace_bytes_full(int32_t num_points, int32_t num_views, int32_t w, int32_t h, int32_t layers,
+                                                   int32_t channels)
+{
+    const size_t small = adop_raster_workspace_bytes(w, h, layers, channels);
+    if (small == 0 || num_points < 0 || num_views <= 0) return 0;
+    // candidate streams of a group of views
+    return workspace_large_offset(w, h, layers, channels) + large_region_layout(num_points, num_views).total;
 }
 
 extern "C" adop_status adop_texture_interleave(const float* texture, float* out, int32_t channels, int32_t num_texels, void* stream)
@@ -613,9 +721,10 @@ extern "C" adop_status adop_texture_deinterleave(const float* in, float* out, in
     return ADOP_OK;
 }
 
-extern "C" size_t adop_raster_visible_list_ints(int32_t num_points)
+extern "C" size_t adop_raster_visible_list_ints(int32_t num_points, int32_t w, int32_t h, int32_t layers)
 {
-    return num_points < 0 ? 0 : visible_list_ints(num_points);
+    if (num_points < 0 || w <= 0 || h <= 0 || layers <= 0 || layers > ADOP_MAX_LAYERS) return 0;
+    return visible_list_ints(num_points, w, h);
 }
 
 extern "C" adop_status adop_raster_forward(const adop_scene* s, const adop_view* views, int32_t B,
@@ -687,6 +796,20 @@ extern "C" adop_status adop_raster_forward(const adop_scene* s, const adop_view*
     pts.normal = s->normal;
     pts.index = s->index;
     pts.n = N;
+    ForwardPlan plan;
+    plan.accum = accum;
+    plan.env = env;
+    plan.list_base = io->visible_list;
+    plan.w = w0; plan.h = h0;
+    plan.num_views = B;
+    plan.tiles = make_tile_table(w0, h0, N);
+    plan.large = nullptr;
+    plan.lr = large_region_layout(N, B);
+    plan.cand_view_stride = entry_capacity(N);
+    // A workspace of adop_raster_workspace_bytes_full has a large region behind the pixel records: candidate streams from
+    // the depth prepass to the accept kernel, and the accept kernel's entry segments.
+    if (io->workspace_bytes >= adop_raster_workspace_bytes_full(N, B, w0, h0, L, C))
+        plan.large = static_cast<char*>(io->workspace) + workspace_large_offset(w0, h0, L, C);
     // the pose and intrinsics tensors live on the device; the per-view cameras are gathered there, a chunk at a time
     for (int b = 0; b < B; ++b)
     {
@@ -722,10 +845,10 @@ extern "C" adop_status adop_raster_forward(const adop_scene* s, const adop_view*
         adop_status r;
         switch (C)
         {
-            case 3: r = dispatch_layers_forward<3>(L, pts, s, cam, kp, lt, accum, env, st, io->visible_list, b, depth_views); break;
-            case 4: r = dispatch_layers_forward<4>(L, pts, s, cam, kp, lt, accum, env, st, io->visible_list, b, depth_views); break;
-            case 8: r = dispatch_layers_forward<8>(L, pts, s, cam, kp, lt, accum, env, st, io->visible_list, b, depth_views); break;
-            case 16: r = dispatch_layers_forward<16>(L, pts, s, cam, kp, lt, accum, env, st, io->visible_list, b, depth_views); break;
+            case 3: r = dispatch_layers_forward<3>(L, pts, s, cam, kp, lt, plan, st, b, depth_views); break;
+            case 4: r = dispatch_layers_forward<4>(L, pts, s, cam, kp, lt, plan, st, b, depth_views); break;
+            case 8: r = dispatch_layers_forward<8>(L, pts, s, cam, kp, lt, plan, st, b, depth_views); break;
+            case 16: r = dispatch_layers_forward<16>(L, pts, s, cam, kp, lt, plan, st, b, depth_views); break;
             default: return ADOP_ERR_UNSUPPORTED;
         }
         if (r != ADOP_OK) return r;

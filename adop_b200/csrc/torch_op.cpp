@@ -118,7 +118,8 @@ static adop_scene make_scene(RenderInfo& info, const Tensor& texture, const Tens
 
 static void ensure_workspace(RenderInfo& info, const adop_scene& sc, const torch::TensorOptions& opt)
 {
-    const size_t need = adop_raster_workspace_bytes(info.images[0].w, info.images[0].h, (int32_t)info.num_layers, sc.channels);
+    const size_t need = adop_raster_workspace_bytes_full(sc.num_points, (int32_t)info.images.size(), info.images[0].w, info.images[0].h,
+                                                         (int32_t)info.num_layers, sc.channels);
     TORCH_CHECK(need > 0, "invalid view size / layer count");
     if (!info.workspace.defined() || (size_t)info.workspace.numel() < need)
         info.workspace = torch::empty({(int64_t)need}, opt.dtype(torch::kUInt8));
@@ -163,7 +164,7 @@ struct PointRender : public torch::autograd::Function<PointRender>
                 io.layers[l].mask = mask.back().data_ptr<float>();
             }
         }
-        Tensor visible = torch::empty({B, (int64_t)adop_raster_visible_list_ints(sc.num_points)}, opt.dtype(torch::kInt32));
+        Tensor visible = torch::empty({B, (int64_t)adop_raster_visible_list_ints(sc.num_points, info->images[0].w, info->images[0].h, L)}, opt.dtype(torch::kInt32));
         io.visible_list = visible.data_ptr<int32_t>();
         io.workspace = info->workspace.data_ptr();
         io.workspace_bytes = (size_t)info->workspace.numel();

@@ -91,23 +91,32 @@ class ForwardResult:
         self.visible = visible
         self.packed = packed  # optional per layer [B,1,h,w] int64: depth bits << 32 | index of the nearest point
 
-    def splat_counts(self):
-        """(point, layer) splats per view that the backward pass visits, as recorded in `visible`."""
-        n_seg = 2048
-        return self.visible[:, :n_seg].sum(dim=1)
+    def _tiles(self):
+        w, h = self.views[0].w, self.views[0].h
+        return ((w + 31) // 32) * ((h + 15) // 16)
 
-    def list_overflowed(self):
+    def entry_counts(self):
+        """Listed points per view (points with at least one accepted layer), as recorded in `visible`."""
+        header, t = 2048 + 8, self._tiles()
+        return self.visible[:, header: header + t].sum(dim=1)
+
+    def list_unusable(self):
+        """True for views whose list is marked as not usable (the backward pass then walks all points)."""
         return self.visible[:, 2048 + 2] != 0
 
 
 class PointRasterizer:
     """Owns the reusable scratch (the role of PointRendererCache, PointRenderer.h:96-157)."""
 
-    def __init__(self, device="cuda:0", interleave_descriptors=True):
+    def __init__(self, device="cuda:0", interleave_descriptors=True, full_workspace=True):
+        """full_workspace: size the scratch with adop_raster_workspace_bytes_full (about 64 bytes per point more), which
+        lets the forward pass hand projected points from the depth prepass to the blend kernel and the backward pass chain
+        each visible point once; False keeps the small workspace and the kernels that do without."""
         self.lib = capi.load_library()
         self.device = torch.device(device)
         self._ws = None
         self.interleave_descriptors = interleave_descriptors
+        self.full_workspace = full_workspace
         self._tex_i = None    # [T,C] working copy of the descriptors, refreshed by every forward call
         self._gtex_i = None   # [T,C] scratch for the descriptor gradient
 
@@ -126,8 +135,11 @@ class PointRasterizer:
             sc.texture_interleaved = self._tex_i.data_ptr()
         return sc
 
-    def _workspace(self, w, h, layers, channels):
-        need = self.lib.adop_raster_workspace_bytes(w, h, layers, channels)
+    def _workspace(self, w, h, layers, channels, num_points=0, num_views=1):
+        if self.full_workspace:
+            need = self.lib.adop_raster_workspace_bytes_full(num_points, num_views, w, h, layers, channels)
+        else:
+            need = self.lib.adop_raster_workspace_bytes(w, h, layers, channels)
         if need == 0:
             raise ValueError("invalid size")
         if self._ws is None or self._ws.numel() < need:
@@ -148,7 +160,7 @@ class PointRasterizer:
             # rendering frame after frame), so the [T,C] working copy is reused as it is
             sc = self._scene_struct(scene, refresh=refresh_descriptors)
             ch = sc.channels
-            ws = self._workspace(w, h, num_layers, ch)
+            ws = self._workspace(w, h, num_layers, ch, sc.num_points, B)
             sizes = capi.layer_sizes(w, h, num_layers)
             if out is None:
                 f32 = dict(dtype=torch.float32, device=self.device)
@@ -158,7 +170,7 @@ class PointRasterizer:
                 masks = [torch.empty((B, 1, hh, ww), **f32) for ww, hh in sizes] if params.output_background_mask else []
                 visible = None
                 if record_visible:
-                    ints = self.lib.adop_raster_visible_list_ints(sc.num_points)
+                    ints = self.lib.adop_raster_visible_list_ints(sc.num_points, w, h, num_layers)
                     visible = torch.empty((B, ints), dtype=torch.int32, device=self.device)
                 packed = [torch.empty((B, 1, hh, ww), dtype=torch.int64, device=self.device) for ww, hh in sizes] \
                     if packed_depth else None
@@ -230,7 +242,7 @@ class PointRasterizer:
             io.grad_env_map = p("env_map")
             io.accumulate = 0
             io.normalize = 1 if normalize else 0
-            ws = self._workspace(va[0].w, va[0].h, L, sc.channels)
+            ws = self._workspace(va[0].w, va[0].h, L, sc.channels, sc.num_points, B)
             io.workspace = ws.data_ptr()
             io.workspace_bytes = ws.numel()
             io.visible_list = fwd.visible.data_ptr() if fwd.visible is not None else None

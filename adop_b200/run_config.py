@@ -105,7 +105,7 @@ def main():
         grads = [torch.randn_like(c) for c in fwd.colors]
         has_env = scene.env_map is not None and params.composite_environment_map
         bwd = ras.backward(scene, params, fwd, grads, want_env=has_env)
-        out["splat_list_overflowed"] = bool(fwd.list_overflowed().any())
+        out["visible_list_unusable"] = bool(fwd.list_unusable().any())
 
         def both():
             ras.forward(scene, cfg["views"], params, L, out=fwd)

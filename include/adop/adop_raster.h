@@ -116,7 +116,7 @@ typedef struct adop_forward_io
     const uint8_t* dropout_mask; /* optional [B,N]: 1 = dropped; NULL = hash of dropout_seed */
     void* workspace;
     size_t workspace_bytes;
-    /* optional, [B, adop_raster_visible_list_ints(N)] i32: the forward pass records which (point, layer) splats of
+    /* optional, [B, adop_raster_visible_list_ints(N, w, h, layers)] i32: the forward pass records which (point, layer) splats of
      * each view the backward pass has to visit, so that it runs over those instead of over the whole cloud. It takes
      * the place of the [B,N] drop-out tensor the reference saves for backward (PointRenderer.cu:1524). If a view has
      * more such splats than the list holds (about one per point of the cloud), the list marks itself unusable and
@@ -160,7 +160,8 @@ typedef struct adop_backward_io
     void* workspace;
     size_t workspace_bytes;
     /* optional: the list the forward call of the same views, scene and parameters filled (see adop_forward_io).
-     * The backward pass uses part of every entry as scratch, so a list serves one backward call.
+     * The backward pass groups its entries by screen tile inside the same buffer (so it is not const) and leaves what
+     * the forward pass wrote untouched: a list can serve several backward calls.
      * NULL = the backward pass walks all points again, as the reference does. */
     int32_t* visible_list;
     /* optional [T,C] scratch: descriptor gradients are then summed there with one vector atomic per splat and moved
@@ -183,6 +184,14 @@ void adop_render_params_default(adop_render_params* p);
 /* Bytes of scratch that forward/backward need for views of w x h with `layers` layers and `channels`
  * descriptor channels. Replaces the size-keyed PointRendererCache (PointRenderer.h:96-157). */
 size_t adop_raster_workspace_bytes(int32_t w, int32_t h, int32_t layers, int32_t channels);
+/* The same plus room that grows with the cloud (16 bytes per point and view of a group of up to four views, about
+ * 64 N bytes): with a workspace of at least this size the depth prepass hands the projected in-image points of each view to
+ * the blend kernel (which then neither reads the cloud again nor projects a second time), and the backward pass over a
+ * splat list keeps one image-space gradient sum per point, so that the projection chain runs once per visible point
+ * instead of once per (point, layer). A smaller workspace (at least adop_raster_workspace_bytes) selects the kernels
+ * that do without. Same results either way. */
+size_t adop_raster_workspace_bytes_full(int32_t num_points, int32_t num_views, int32_t w, int32_t h, int32_t layers,
+                                        int32_t channels);
 
 /* [C,T] -> [T,C] (and back, optionally adding to `out`): the descriptor tensor keeps the reference's planar layout
  * at the boundary (NeuralTexture.h:62); these build the interleaved working copy the kernels prefer. */
@@ -190,8 +199,9 @@ adop_status adop_texture_interleave(const float* texture, float* out, int32_t ch
 adop_status adop_texture_deinterleave(const float* in, float* out, int32_t channels, int32_t num_texels,
                                       int32_t accumulate, void* stream);
 
-/* int32 elements per view of adop_forward_io.visible_list for a cloud of num_points points. */
-size_t adop_raster_visible_list_ints(int32_t num_points);
+/* int32 elements per view of adop_forward_io.visible_list for a cloud of num_points points rendered into views of
+ * w x h with `layers` layers (the list keeps a small table per screen tile besides 16 bytes per point). */
+size_t adop_raster_visible_list_ints(int32_t num_points, int32_t w, int32_t h, int32_t layers);
 
 /* BlendPointCloudForward, src/lib/rendering/PointRenderer.cu:1389-1531: depth prepass, fuzzy-depth blend,
  * combine-and-fill, mask, and (optionally) the environment-map composite of RenderModule.cpp:106-127.

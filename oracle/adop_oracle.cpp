@@ -286,6 +286,7 @@ int adop_oracle_backward(const adop_scene* s, const adop_view* views, int B, con
     (void)threads;
 #endif
     const bool par = threads != 1;
+    std::vector<double> intr_sum(io->grad_intrinsics ? (size_t)s->num_cameras * s->intrinsics_cols : 0, 0.0);
     const int cols = s->intrinsics_cols;
 
     if (!io->accumulate)
@@ -449,15 +450,15 @@ int adop_oracle_backward(const adop_scene* s, const adop_view* views, int B, con
                     memcpy(g_pose, o.g_pose, sizeof(g_pose));
                     if (io->grad_intrinsics)  // :645-682
                     {
-                        float* gi = io->grad_intrinsics + (size_t)vw.camera_index * cols;
+                        double* gi = intr_sum.data() + (size_t)vw.camera_index * cols;
                         float kf = rp->K_gradient_factor;
                         o.g_k[4] = 0.f;
                         float df = rp->distortion_gradient_factor;
                         o.g_dis[2] *= 0.25f;
                         o.g_dis[3] *= 0.1f; o.g_dis[4] *= 0.1f; o.g_dis[5] *= 0.1f;
                         o.g_dis[6] *= 0.1f; o.g_dis[7] *= 0.1f;
-                        for (int k = 0; k < 5; ++k) { if (par) atomic_add_float(gi + k, kf * o.g_k[k]); else gi[k] += kf * o.g_k[k]; }
-                        for (int k = 0; k < 8; ++k) { if (par) atomic_add_float(gi + 5 + k, df * o.g_dis[k]); else gi[5 + k] += df * o.g_dis[k]; }
+                        for (int k = 0; k < 5; ++k) { if (par) atomic_add_double(gi + k, (double)(kf * o.g_k[k])); else gi[k] += (double)(kf * o.g_k[k]); }
+                        for (int k = 0; k < 8; ++k) { if (par) atomic_add_double(gi + 5 + k, (double)(df * o.g_dis[k])); else gi[5 + k] += (double)(df * o.g_dis[k]); }
                         float* ci = io->count_intrinsics + vw.camera_index;
                         if (par) atomic_add_float(ci, 1.f / 1024.f); else *ci += 1.f / 1024.f;
                     }
@@ -472,8 +473,8 @@ int adop_oracle_backward(const adop_scene* s, const adop_view* views, int B, con
                     memcpy(g_pose, o.g_pose, sizeof(g_pose));
                     if (io->grad_intrinsics)  // :711-719
                     {
-                        float* gi = io->grad_intrinsics + (size_t)vw.camera_index * cols;
-                        for (int k = 0; k < 5; ++k) { if (par) atomic_add_float(gi + k, o.g_affine[k]); else gi[k] += o.g_affine[k]; }
+                        double* gi = intr_sum.data() + (size_t)vw.camera_index * cols;
+                        for (int k = 0; k < 5; ++k) { if (par) atomic_add_double(gi + k, (double)o.g_affine[k]); else gi[k] += (double)o.g_affine[k]; }
                         float* ci = io->count_intrinsics + vw.camera_index;
                         if (par) atomic_add_float(ci, 1.f); else *ci += 1.f;
                     }
@@ -494,6 +495,11 @@ int adop_oracle_backward(const adop_scene* s, const adop_view* views, int B, con
             }
         }
     }
+
+    // the per-camera sums run over millions of cancelling terms: they are formed in double here (the reference adds float
+    // atomics in an order of its own, PointRenderer.cu:645-682), so that this checker is the better-conditioned side
+    if (io->grad_intrinsics)
+        for (size_t k = 0; k < intr_sum.size(); ++k) io->grad_intrinsics[k] = (float)((double)io->grad_intrinsics[k] + intr_sum[k]);
 
     if (io->normalize)  // NormalizeGradient, PointRenderer.cu:1534-1547, 1609-1637
     {

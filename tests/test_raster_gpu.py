@@ -1,7 +1,10 @@
 """GPU parity of the rasterizer against the CPU checker, through the C ABI.
 
-Bar: depth and weight buffers bit-exact (integer-like data); colours and gradients within 1e-4 relative (float atomics
-add in a different order on the GPU), scaled by the magnitude of the tensor where values cancel.
+Bar: depth, weight and mask buffers bit-exact (integer-like data); colours of pixels that hold exactly one splat
+bit-exact (nothing is summed); everything that the GPU sums with float atomics in an order of its own (colours of
+multi-splat pixels, all gradients) per element within |a - b| <= 1e-4 |b| + 1e-5 max|b|: 1e-4 relative where atomic
+ordering differs, and a floor of 1e-5 of the tensor's largest magnitude for elements whose terms cancel. Results that
+involve no atomics are held to 1e-5 relative (RTOL_EXACT_ORDER).
 """
 import numpy as np
 import pytest
@@ -12,18 +15,41 @@ from adop_b200.raster import PointRasterizer, Scene
 
 pytestmark = pytest.mark.gpu
 
-RTOL = 1e-4
+RTOL = 1e-4              # sums formed by float atomics in GPU order
+RTOL_EXACT_ORDER = 1e-5  # no atomics involved
+FLOOR = 1e-5             # of the tensor's largest magnitude: the cancellation floor
+floor_report = {}        # name -> (elements that needed the floor, elements): printed at the end of the session
 
 
 def to_scene(arrays, dev="cuda:0"):
     return Scene(**{k: (torch.from_numpy(v).to(dev) if v is not None else None) for k, v in arrays.items()})
 
 
-def close(a, b, rtol=RTOL, name=""):
+def close(a, b, rtol=RTOL, name="", floor=FLOOR):
+    """Per element: |a - b| <= rtol |b| + floor max|b|. Records how many elements passed only thanks to the floor."""
     a = a.detach().cpu().numpy() if isinstance(a, torch.Tensor) else a
-    scale = max(float(np.abs(b).max()), 1e-12)
-    err = float(np.abs(a.astype(np.float64) - b.astype(np.float64)).max())
-    assert err <= rtol * scale, f"{name}: max err {err:.3e} vs scale {scale:.3e}"
+    a64, b64 = a.astype(np.float64), np.asarray(b).astype(np.float64)
+    scale = max(float(np.abs(b64).max()), 1e-30) if b64.size else 1.0
+    err = np.abs(a64 - b64)
+    rel_ok = err <= rtol * np.abs(b64)
+    ok = err <= rtol * np.abs(b64) + floor * scale
+    needed = int((ok & ~rel_ok).sum())
+    seen = floor_report.get(name, (0, 0))
+    floor_report[name] = (seen[0] + needed, seen[1] + int(b64.size))
+    if not ok.all():
+        worst = int(np.argmax(err - rtol * np.abs(b64)))
+        raise AssertionError(f"{name}: {int((~ok).sum())} of {b64.size} elements off; worst |a-b| = {err.flat[worst]:.3e} at "
+                             f"b = {b64.flat[worst]:.3e} (max|b| = {scale:.3e})")
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _print_floor_report():
+    yield
+    if floor_report:
+        print("\nelements that needed the cancellation floor (1e-5 of the tensor's maximum):")
+        for name, (needed, total) in sorted(floor_report.items()):
+            if total:
+                print(f"  {name:24s} {needed:>10d} of {total:>12d} ({100.0 * needed / total:.4f} %)")
 
 
 def run_both(oracle, cfg, want_env=False, dropout_mask=None, record_visible=True, interleave=True, **bw):
@@ -45,8 +71,14 @@ def check_forward(ref, fwd, L, masks=False):
     for l in range(L):
         d = fwd.depths[l].cpu().numpy()
         assert np.array_equal(d.view(np.uint32), ref["depths"][l].view(np.uint32)), f"depth layer {l} not bit-exact"
-        assert np.array_equal(fwd.weights[l].cpu().numpy(), ref["weights"][l]), f"weight layer {l}"
-        close(fwd.colors[l], ref["colors"][l], name=f"colour layer {l}")
+        w = fwd.weights[l].cpu().numpy()
+        assert np.array_equal(w, ref["weights"][l]), f"weight layer {l}"
+        c = fwd.colors[l].cpu().numpy()
+        close(c, ref["colors"][l], name=f"colour layer {l}")
+        # a pixel with at most one splat sums nothing: its colour is the descriptor (or the background / environment
+        # map) itself, whatever the order of the atomics
+        single = np.broadcast_to(w <= 1, c.shape)
+        close(c[single], ref["colors"][l][single], rtol=RTOL_EXACT_ORDER, floor=0.0, name=f"colour layer {l}, <= 1 splat")
         if masks:
             assert np.array_equal(fwd.masks[l].cpu().numpy(), ref["masks"][l])
 
@@ -98,14 +130,16 @@ def test_c3_ocam(oracle, cuda_lib, listed):
     assert ref["weights"][0].sum() > 1000
 
 
-def test_splat_list_is_used_on_a_dense_cloud(oracle, cuda_lib):
-    """Many points per pixel (the normal case): the list does not overflow and records every covered pixel."""
+def test_visible_list_is_used_on_a_dense_cloud(oracle, cuda_lib):
+    """Many points per pixel (the normal case): the list holds at least one point per covered pixel of the finest layer
+    and at most one entry per accepted (point, layer) pair."""
     cfg = synth.make_config("c2", n_points=600_000, n_views=2, size=(160, 90))
     ref, ref_b, fwd, bwd = run_both(oracle, cfg, want_env=True)
-    assert not bool(fwd.list_overflowed().any())
-    covered = [sum(int((ref["weights"][l][b] > 0).sum()) for l in range(4)) for b in range(2)]
-    counts = fwd.splat_counts().cpu().numpy()
-    assert all(c >= p for c, p in zip(counts, covered))
+    assert not bool(fwd.list_unusable().any())
+    covered = [int((ref["weights"][0][b] > 0).sum()) for b in range(2)]
+    accepted = [sum(int(ref["weights"][l][b].sum()) for l in range(4)) for b in range(2)]
+    counts = fwd.entry_counts().cpu().numpy()
+    assert all(p <= c <= a for c, p, a in zip(counts, covered, accepted))
     check_forward(ref, fwd, 4, masks=True)
     check_backward(ref_b, bwd)
 
@@ -185,14 +219,77 @@ def test_normals_radius_dropout_and_index(oracle, cuda_lib):
     assert 0 < ref["weights"][0].sum() < n
 
 
-def test_splat_list_overflow_falls_back_to_all_points(oracle, cuda_lib):
-    """A sparse cloud where nearly every point is alone in its pixel on every layer has more splats than points; the
-    list then marks itself unusable and the backward pass walks all points, with the same result."""
-    cfg = synth.make_config("c1", n_points=3000, size=(512, 512), layers=4)
-    ref, ref_b, fwd, bwd = run_both(oracle, cfg)
-    assert bool(fwd.list_overflowed().any())
-    check_forward(ref, fwd, 4)
+def test_unusable_list_falls_back_to_all_points(oracle, cuda_lib):
+    """A list whose header says that it is not usable: the backward pass finds the mark on the device (no host round
+    trip), its tile kernels return at once and the all-points kernels behind them do the work, with the same result."""
+    cfg = synth.make_config("c2", n_points=150_000, n_views=2, size=(240, 136))
+    arrays, views, params, L = cfg["arrays"], cfg["views"], cfg["params"], cfg["num_layers"]
+    grads = synth.upstream_gradients(cfg["meta"], batch=len(views))
+    ref = oracle.forward(arrays, views, params, L)
+    ref_b = oracle.backward(arrays, views, params, L, ref, grads, want_env=True)
+    scene = to_scene(arrays)
+    r = PointRasterizer("cuda:0")
+    fwd = r.forward(scene, views, params, L)
+    fwd.visible[:, 2048 + 2] = 1
+    assert bool(fwd.list_unusable().all())
+    bwd = r.backward(scene, params, fwd, [torch.from_numpy(g).cuda() for g in grads], want_env=True)
+    torch.cuda.synchronize()
+    check_forward(ref, fwd, L, masks=True)
     check_backward(ref_b, bwd)
+
+
+def test_overflowing_tile_bucket_marks_the_list_unusable(oracle, cuda_lib):
+    """A cluster of coplanar points that all pass the depth test inside one screen tile: more visible points than a tile's
+    bucket holds (2048 here). The forward pass marks the list unusable and the backward pass walks all points."""
+    cfg = synth.make_config("c1", n_points=6000, size=(64, 64), layers=2)
+    rng = np.random.default_rng(5)
+    pos = cfg["arrays"]["position"]
+    pos[:, 0] = rng.uniform(-0.1, -0.02, pos.shape[0])  # image x in 7 .. 27, y in 37 .. 47: one 32 x 16 tile
+    pos[:, 1] = rng.uniform(0.02, 0.1, pos.shape[0])
+    pos[:, 2] = 3.0
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg)
+    assert bool(fwd.list_unusable().all())
+    assert ref["weights"][0].sum() > 2048
+    check_forward(ref, fwd, 2)
+    check_backward(ref_b, bwd)
+
+
+def test_second_backward_on_the_same_list(oracle, cuda_lib):
+    """The backward pass turns the list's entries into work items, so the list serves one backward call; it is marked
+    consumed and a second call on the same forward result walks all points: same gradients."""
+    cfg = synth.make_config("c2", n_points=150_000, n_views=2, size=(240, 136))
+    arrays, views, params, L = cfg["arrays"], cfg["views"], cfg["params"], cfg["num_layers"]
+    grads = [torch.from_numpy(g).cuda() for g in synth.upstream_gradients(cfg["meta"], batch=len(views))]
+    scene = to_scene(arrays)
+    r = PointRasterizer("cuda:0")
+    fwd = r.forward(scene, views, params, L)
+    first = {k: (v.clone() if v is not None else None) for k, v in r.backward(scene, params, fwd, grads, want_env=True).items()}
+    assert bool((fwd.visible[:, 2048 + 3] == 1).all())
+    second = r.backward(scene, params, fwd, grads, want_env=True)
+    torch.cuda.synchronize()
+    for k in ("texture", "background", "points", "pose", "intrinsics", "env_map"):
+        close(second[k], first[k].cpu().numpy(), name=f"second backward {k}")
+
+
+def test_small_workspace_matches_full_workspace(cuda_lib):
+    """With the full workspace the depth prepass hands projected points to the blend kernel; with the small one the blend
+    kernel projects again. Same depth and weight bits, colours and gradients within the atomic-order tolerance."""
+    cfg = synth.make_config("c2", n_points=300_000, n_views=5, size=(320, 180))
+    scene = to_scene(cfg["arrays"])
+    grads = [torch.from_numpy(g).cuda() for g in synth.upstream_gradients(cfg["meta"])]
+    out = []
+    for full in (False, True):
+        r = PointRasterizer("cuda:0", full_workspace=full)
+        fwd = r.forward(scene, cfg["views"], cfg["params"], 4)
+        bwd = r.backward(scene, cfg["params"], fwd, grads, want_env=True)
+        out.append((fwd, bwd))
+    torch.cuda.synchronize()
+    (fa, ba), (fb, bb) = out
+    for l in range(4):
+        assert torch.equal(fa.depths[l], fb.depths[l]) and torch.equal(fa.weights[l], fb.weights[l])
+        close(fa.colors[l], fb.colors[l].cpu().numpy(), name=f"small vs full colour {l}")
+    for k in ("texture", "background", "points", "pose", "intrinsics", "env_map"):
+        close(ba[k], bb[k].cpu().numpy(), name=f"small vs full grad {k}")
 
 
 def test_backward_mode_4(oracle, cuda_lib):
@@ -292,14 +389,14 @@ def test_c2_full_size_one_view_against_checker(oracle, cuda_lib):
     fwd = r.forward(scene, views, params, L)
     bwd = r.backward(scene, params, fwd, [torch.from_numpy(g).cuda() for g in grads], want_env=True)
     torch.cuda.synchronize()
-    assert not bool(fwd.list_overflowed().any())
+    assert not bool(fwd.list_unusable().any())
     check_forward(ref, fwd, L, masks=True)
     check_backward(ref_b, bwd)
 
 
 def test_full_size_properties_16_views(cuda_lib):
     """Size-independent properties on the full benchmark batch (10 M points x 16 views), no checker involved:
-    every recorded splat is an accepted (point, layer) pair, so the list length lies between the points accepted on the
+    every listed point has at least one accepted layer, so the list length lies between the points accepted on the
     finest layer and the sum of all weights; the background mask is the indicator of weight > 0; depth is 100000 exactly
     where nothing landed on the finest layer; a second forward pass reproduces depth and weight bit for bit."""
     cfg = synth.make_config("c2")
@@ -307,8 +404,8 @@ def test_full_size_properties_16_views(cuda_lib):
     r = PointRasterizer("cuda:0")
     fwd = r.forward(scene, cfg["views"], cfg["params"], 4)
     torch.cuda.synchronize()
-    assert not bool(fwd.list_overflowed().any())
-    splats = fwd.splat_counts().double()
+    assert not bool(fwd.list_unusable().any())
+    splats = fwd.entry_counts().double()
     w_all = sum(w.double().sum(dim=(1, 2, 3)) for w in fwd.weights)
     w0 = fwd.weights[0].double().sum(dim=(1, 2, 3))
     assert bool((splats <= w_all).all()) and bool((splats >= w0).all())
@@ -409,7 +506,7 @@ def test_accumulate_adds_to_existing_gradients(cuda_lib):
         io.grad_intrinsics, io.count_intrinsics = acc["intrinsics"].data_ptr(), acc["count_intrinsics"].data_ptr()
         io.grad_env_map = acc["env_map"].data_ptr()
         io.accumulate, io.normalize = 1, 0
-        ws = r._workspace(128, 72, 4, 4)
+        ws = r._workspace(128, 72, 4, 4, scene.position.shape[0], 2)
         io.workspace, io.workspace_bytes = ws.data_ptr(), ws.numel()
         io.visible_list = f2.visible.data_ptr()
         st = lib.adop_raster_backward(C.byref(sc), va, 2, C.byref(cfg["params"]), 4, C.byref(io), None)
