@@ -457,6 +457,7 @@ __global__ void __launch_bounds__(kBlock) k_splat_backward_all(PointStreams pts,
 // keeps several independent loads per thread in flight and as many blocks resident as registers and shared memory allow.
 constexpr int kTileThreads = 256;
 constexpr int kTilePass = 2 * kTileThreads;  // points of a tile that are staged and sorted in shared memory at a time
+constexpr int kSortBins = kMaxLayers * kTileH;  // sort key of a point: (layers it visits, image row)
 // staged region of layer l: rows [ (y0 >> l) - 1, + rows ), columns [ start, + pitch ), start = x0 - 4 on layer 0 and
 // ((x0 >> l) - 1) & ~3 on the others (a multiple of four, so that rows can be copied as aligned 16-byte pieces)
 __host__ __device__ constexpr int region_pitch(int l) { return l == 0 ? kTileW + 8 : (l == 1 ? 24 : (l == 2 ? 16 : 12)); }
@@ -639,7 +640,7 @@ __global__ void __launch_bounds__(kTileThreads, C <= 4 ? (DEEP ? 3 : 4) : (C <= 
     constexpr int STRIDE = PlaneStride<DEEP>::value;
     constexpr int LMAX = DEEP ? kMaxLayers : 4;
     extern __shared__ __align__(16) float s_tile[];
-    __shared__ int s_hist[kMaxLayers + 1];
+    __shared__ int s_hist[kSortBins];
     // plane p of layer l: s_tile[p * STRIDE + region_offset(l) + row * pitch + col]
     int4* sE = reinterpret_cast<int4*>(s_tile + (size_t)STRIDE * (2 * C + 1));
     unsigned short* sOrder = reinterpret_cast<unsigned short*>(sE + kTilePass);
@@ -662,32 +663,51 @@ __global__ void __launch_bounds__(kTileThreads, C <= 4 ? (DEEP ? 3 : 4) : (C <= 
             __syncthreads();  // the previous readers of the staged data are done
             if (pass0 == 0) stage_regions<C, 0, STRIDE, LMAX>(lt, s_tile, x0, y0);
             for (int q = threadIdx.x; q < n_pass; q += kTileThreads) async_copy_16(sE + q, ent + pass0 + q);
-            if (threadIdx.x <= kMaxLayers) s_hist[threadIdx.x] = 0;
+            if (threadIdx.x < kSortBins) s_hist[threadIdx.x] = 0;
             async_copy_wait_all();
             __syncthreads();
-            // ---- order the points by their coarsest layer (the warps then walk the same layers in all lanes)
-            int cls[kTilePass / kTileThreads], rank[kTilePass / kTileThreads];
+            // ---- order the points: by their coarsest layer, most layers first (the warps then walk the same layers in all
+            // lanes), and within that by image row (the lanes of a warp then read mostly one row of the staged planes, in
+            // different columns: few shared-memory bank conflicts)
+            int key[kTilePass / kTileThreads], rank[kTilePass / kTileThreads];
 #pragma unroll
             for (int j = 0; j < kTilePass / kTileThreads; ++j)
             {
                 const int q = j * kTileThreads + threadIdx.x;
-                cls[j] = -1;
+                key[j] = -1;
                 if (q < n_pass)
                 {
-                    const unsigned bmask = ((unsigned)sE[q].y >> 8) & 0xffu;
-                    cls[j] = 32 - __clz(bmask);  // 1 .. kMaxLayers (the backward mask of a listed point is not 0)
-                    rank[j] = atomicAdd(&s_hist[cls[j]], 1);
+                    const int4 e = sE[q];
+                    const unsigned bmask = ((unsigned)e.y >> 8) & 0xffu;
+                    const int cls = 32 - __clz(bmask);  // 1 .. kMaxLayers (the backward mask of a listed point is not 0)
+                    const int row = min(max(round_half_even_bounded(__int_as_float(e.w)) - y0, 0), kTileH - 1);
+                    key[j] = (kMaxLayers - cls) * kTileH + row;
+                    rank[j] = atomicAdd(&s_hist[key[j]], 1);
                 }
+            }
+            __syncthreads();
+            if (threadIdx.x < 32)
+            {
+                // exclusive prefix sums of the kSortBins counts: four bins per lane
+                constexpr int per = kSortBins / 32;
+                int v[per], sum = 0;
+#pragma unroll
+                for (int k = 0; k < per; ++k) { v[k] = s_hist[threadIdx.x * per + k]; sum += v[k]; }
+                int incl = sum;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1)
+                {
+                    int t = __shfl_up_sync(0xffffffffu, incl, o);
+                    if ((int)threadIdx.x >= o) incl += t;
+                }
+                int run = incl - sum;
+#pragma unroll
+                for (int k = 0; k < per; ++k) { s_hist[threadIdx.x * per + k] = run; run += v[k]; }
             }
             __syncthreads();
 #pragma unroll
             for (int j = 0; j < kTilePass / kTileThreads; ++j)
-            {
-                if (cls[j] < 0) continue;
-                int before = 0;  // the classes with more layers come first
-                for (int k = kMaxLayers; k > cls[j]; --k) before += s_hist[k];
-                sOrder[before + rank[j]] = (unsigned short)(j * kTileThreads + threadIdx.x);
-            }
+                if (key[j] >= 0) sOrder[s_hist[key[j]] + rank[j]] = (unsigned short)(j * kTileThreads + threadIdx.x);
             __syncthreads();
             // ---- the points
             for (int sidx = threadIdx.x; sidx < n_pass; sidx += kTileThreads)
@@ -725,12 +745,22 @@ __global__ void __launch_bounds__(kTileThreads, C <= 4 ? (DEEP ? 3 : 4) : (C <= 
 // per four pyramid pixels reads the weights; the holes, scattered single pixels, are parked per warp and worked off 32
 // at a time (gradient of each channel; for the environment map the ray through the inverse camera model and the bilinear
 // scatter).
-template <int C>
-__global__ void __launch_bounds__(kBlock) k_hole_gradients(LayerTable lt, const ViewCam* __restrict__ camp, KernelParams kp,
-                                                            float* __restrict__ grad_background, float* __restrict__ grad_env, int env_h, int env_w,
-                                                            bool env_interleaved, const int* __restrict__ run_if_nonzero)
+struct HoleArgs
 {
-    if (run_if_nonzero && __ldg(run_if_nonzero) == 0) return;  // the all-points path's preparation kernel does this work
+    float* grad_background;
+    float* grad_env;
+    int env_h, env_w;
+    bool env_interleaved;
+};
+// part of k_chain_and_holes: `block` of `blocks` thread blocks
+template <int C>
+__device__ __forceinline__ void hole_gradients_part(const LayerTable& lt, const ViewCam* __restrict__ camp, const KernelParams& kp, const HoleArgs& ha,
+                                                    int block, int blocks)
+{
+    float* __restrict__ grad_background = ha.grad_background;
+    float* __restrict__ grad_env = ha.grad_env;
+    const int env_h = ha.env_h, env_w = ha.env_w;
+    const bool env_interleaved = ha.env_interleaved;
     const ViewCam& cam = *camp;
     __shared__ float s_bg[C];
     __shared__ unsigned s_parked[kBlock / 32][160];
@@ -756,8 +786,8 @@ __global__ void __launch_bounds__(kBlock) k_hole_gradients(LayerTable lt, const 
     };
     const unsigned total = lt.rec_off[kMaxLayers];
     const unsigned groups = (total + 3) / 4;
-    const unsigned stride = gridDim.x * blockDim.x;
-    for (unsigned base = blockIdx.x * blockDim.x; base < groups; base += stride)  // warp-uniform trip count
+    const unsigned stride = (unsigned)blocks * blockDim.x;
+    for (unsigned base = (unsigned)block * blockDim.x; base < groups; base += stride)  // warp-uniform trip count
     {
         // four consecutive pyramid pixels per thread (they may straddle a layer boundary: the weights are read one by one)
         const unsigned r0 = (base + threadIdx.x) * 4;
@@ -903,11 +933,11 @@ __device__ __forceinline__ bool chain_gradient_sum(const ViewCam& cam, const Ker
     return true;
 }
 
+// part of k_chain_and_holes: `block` of `blocks` thread blocks
 template <int MODEL>
-__global__ void __launch_bounds__(kBlock, MODEL == kPinholeDistortion ? 4 : 3)
-    k_point_chain(PointStreams pts, const ViewCam* __restrict__ camp, KernelParams kp, BackwardTargets bt, VisibleList vl, TileTable tt)
+__device__ __forceinline__ void point_chain_part(const PointStreams& pts, const ViewCam* __restrict__ camp, const KernelParams& kp, const BackwardTargets& bt,
+                                                 const VisibleList& vl, const TileTable& tt, int block, int blocks)
 {
-    if (__ldg(vl.header + kListGo) == 0) return;
     __shared__ ViewCam s_cam;
     __shared__ GeoShared<MODEL> s_geo;
     // points with a gradient are parked per warp, with their position, and chained 32 at a time with every lane busy
@@ -947,7 +977,7 @@ __global__ void __launch_bounds__(kBlock, MODEL == kPinholeDistortion ? 4 : 3)
         }
     };
     constexpr int U = 2;  // items per thread and round: their dependent loads (item -> position) are in flight together
-    for (int tile = blockIdx.x; tile < tt.n_tiles; tile += gridDim.x)
+    for (int tile = block; tile < tt.n_tiles; tile += blocks)
     {
         const int total = min(__ldg(vl.tile_cur + tile), tt.cap);
         const float4* work = reinterpret_cast<const float4*>(vl.entries + (size_t)tile * tt.cap);  // the tile kernel's work items
@@ -1010,6 +1040,19 @@ __global__ void __launch_bounds__(kBlock, MODEL == kPinholeDistortion ? 4 : 3)
     geo_block_reduce<MODEL>(&s_geo, acc, bt);
 }
 
+// The chain kernel and the hole kernel of one view in one launch: they are independent, the first waits on memory most of
+// the time and the second on arithmetic, so side by side they take little more than the longer of the two.
+// Blocks [0, chain_blocks) chain the tile kernel's work items, the others walk the uncovered pixels.
+template <int C, int MODEL>
+__global__ void __launch_bounds__(kBlock, MODEL == kPinholeDistortion ? 4 : 3)
+    k_chain_and_holes(PointStreams pts, const ViewCam* __restrict__ camp, KernelParams kp, LayerTable lt, BackwardTargets bt, VisibleList vl, TileTable tt,
+                      HoleArgs ha, int chain_blocks)
+{
+    if (__ldg(vl.header + kListGo) == 0) return;  // the all-points kernels do this work
+    if ((int)blockIdx.x < chain_blocks) point_chain_part<MODEL>(pts, camp, kp, bt, vl, tt, (int)blockIdx.x, chain_blocks);
+    else hole_gradients_part<C>(lt, camp, kp, ha, (int)blockIdx.x - chain_blocks, (int)gridDim.x - chain_blocks);
+}
+
 // ------------------------------------------------------------------------------------------------------
 // NormalizeGradient, PointRenderer.cu:1534-1547
 __global__ void k_normalize_points(float4* g, int n)
@@ -1069,26 +1112,32 @@ static adop_status launch_view_backward(const PointStreams& pts, const ViewCam* 
         const int grid_tiles = tt.n_tiles < g_tiles ? (tt.n_tiles < 1 ? 1 : tt.n_tiles) : g_tiles;
         if (deep) ADOP_LAUNCH("k_backward_tiles", st, (k_backward_tiles<C, true><<<grid_tiles, kTileThreads, smem, st>>>(pts, kp, lt, tt, bt, vl, want_geo)));
         else ADOP_LAUNCH("k_backward_tiles", st, (k_backward_tiles<C, false><<<grid_tiles, kTileThreads, smem, st>>>(pts, kp, lt, tt, bt, vl, want_geo)));
-        if (grad_env || grad_background)
+        if (grad_env || grad_background || want_geo)
         {
-            static const int cap = resident_grid(k_hole_gradients<C>, 1ll << 40);
-            unsigned groups = (lt.rec_off[kMaxLayers] + 3) / 4;
-            int grid_px = (int)((groups + kBlock - 1) / kBlock);
-            if (grid_px > cap) grid_px = cap;
-            ADOP_LAUNCH("k_hole_gradients", st, (k_hole_gradients<C><<<grid_px, kBlock, 0, st>>>(lt, cam, kp, grad_background, grad_env, env_h, env_w,
-                                                                                                env_interleaved, go)));
-        }
-        if (want_geo)
-        {
+            HoleArgs ha;
+            ha.grad_background = grad_background; ha.grad_env = grad_env; ha.env_h = env_h; ha.env_w = env_w; ha.env_interleaved = env_interleaved;
+            const unsigned groups = (lt.rec_off[kMaxLayers] + 3) / 4;
+            const int hole_need = (grad_env || grad_background) ? (int)((groups + kBlock - 1) / kBlock) : 0;
             if (model == kPinholeDistortion)
             {
-                static const int g = resident_grid(k_point_chain<kPinholeDistortion>, 1ll << 40);
-                ADOP_LAUNCH("k_point_chain", st, (k_point_chain<kPinholeDistortion><<<g < tt.n_tiles ? g : tt.n_tiles, kBlock, 0, st>>>(pts, cam, kp, bt, vl, tt)));
+                static const int g = resident_grid(k_chain_and_holes<C, kPinholeDistortion>, 1ll << 40);
+                // the chain blocks get three quarters of the resident blocks when both parts have work
+                int chain_blocks = want_geo ? (hole_need ? g * 3 / 4 : g) : 0;
+                if (chain_blocks > tt.n_tiles) chain_blocks = tt.n_tiles;
+                int hole_blocks = g - chain_blocks < hole_need ? g - chain_blocks : hole_need;
+                if (hole_need && hole_blocks < 1) hole_blocks = 1;
+                ADOP_LAUNCH("k_chain_and_holes", st, (k_chain_and_holes<C, kPinholeDistortion><<<chain_blocks + hole_blocks, kBlock, 0, st>>>(
+                                                         pts, cam, kp, lt, bt, vl, tt, ha, chain_blocks)));
             }
             else
             {
-                static const int g = resident_grid(k_point_chain<kOcam>, 1ll << 40);
-                ADOP_LAUNCH("k_point_chain", st, (k_point_chain<kOcam><<<g < tt.n_tiles ? g : tt.n_tiles, kBlock, 0, st>>>(pts, cam, kp, bt, vl, tt)));
+                static const int g = resident_grid(k_chain_and_holes<C, kOcam>, 1ll << 40);
+                int chain_blocks = want_geo ? (hole_need ? g * 3 / 4 : g) : 0;
+                if (chain_blocks > tt.n_tiles) chain_blocks = tt.n_tiles;
+                int hole_blocks = g - chain_blocks < hole_need ? g - chain_blocks : hole_need;
+                if (hole_need && hole_blocks < 1) hole_blocks = 1;
+                ADOP_LAUNCH("k_chain_and_holes", st, (k_chain_and_holes<C, kOcam><<<chain_blocks + hole_blocks, kBlock, 0, st>>>(
+                                                         pts, cam, kp, lt, bt, vl, tt, ha, chain_blocks)));
             }
         }
     }

@@ -367,12 +367,14 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, ChunkSche
             const bool keep = valid && ((unsigned)e.y >> 8) != 0;
             if (__ballot_sync(0xffffffffu, keep))
             {
+                // the lanes of one tile take consecutive slots behind one atomic (32 Morton neighbours spread over a few
+                // tiles: grouping all lanes of a tile, not only adjacent ones, sends a third of the atomics)
                 const int tile = keep ? tile_of_position(tt, __int_as_float(e.z), __int_as_float(e.w)) : -1;
-                int run_start, run_len;
-                warp_runs(tile, lane, &run_start, &run_len);
+                const unsigned same = __match_any_sync(0xffffffffu, tile);
+                const int leader = __ffs(same) - 1;
                 int slot = 0;
-                if (keep && run_start == lane) slot = atomicAdd(vl.tile_cur + tile, run_len);
-                slot = __shfl_sync(0xffffffffu, slot, run_start) + (lane - run_start);
+                if (keep && leader == lane) slot = atomicAdd(vl.tile_cur + tile, __popc(same));
+                slot = __shfl_sync(0xffffffffu, slot, leader) + __popc(same & ((1u << lane) - 1u));
                 if (keep)
                 {
                     if (slot < tt.cap) vl.entries[(size_t)tile * tt.cap + slot] = e;

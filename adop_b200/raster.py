@@ -108,10 +108,10 @@ class ForwardResult:
 class PointRasterizer:
     """Owns the reusable scratch (the role of PointRendererCache, PointRenderer.h:96-157)."""
 
-    def __init__(self, device="cuda:0", interleave_descriptors=True, full_workspace=True):
-        """full_workspace: size the scratch with adop_raster_workspace_bytes_full (about 64 bytes per point more), which
-        lets the forward pass hand projected points from the depth prepass to the blend kernel and the backward pass chain
-        each visible point once; False keeps the small workspace and the kernels that do without."""
+    def __init__(self, device="cuda:0", interleave_descriptors=True, full_workspace=False):
+        """full_workspace: size the scratch with adop_raster_workspace_bytes_full (about 64 bytes per point more), which lets
+        the depth prepass hand projected points to the blend kernel instead of the blend kernel projecting again; False keeps
+        the small workspace."""
         self.lib = capi.load_library()
         self.device = torch.device(device)
         self._ws = None

@@ -46,6 +46,9 @@ def parse_args():
     ap.add_argument("--points", type=int, default=10_000_000)
     ap.add_argument("--views", type=int, default=16, help="views per GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--candidates", action="store_true",
+                    help="size the scratch with room for candidate streams (the depth prepass then hands projected points to "
+                         "the blend kernel; measured slightly slower overall than projecting twice)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: gradient exchange by the peer-memory kernel (default) or by NCCL reduce-scatter / all-reduce")
     return ap.parse_args()
@@ -212,7 +215,7 @@ def main():
     w, h = cfg["meta"]["w"], cfg["meta"]["h"]
     P = sum(a * b for a, b in capi.layer_sizes(w, h, L))
     scene = Scene(**{k: (torch.from_numpy(v).to(dev) if v is not None else None) for k, v in arrays.items()})
-    ras = PointRasterizer(dev)
+    ras = PointRasterizer(dev, full_workspace=args.candidates)
     gen = torch.Generator(device=dev)
     gen.manual_seed(1234 + rank)
     grads_dev = [torch.randn((V, C, hh, ww), device=dev, generator=gen) for ww, hh in capi.layer_sizes(w, h, L)]
@@ -260,7 +263,7 @@ def main():
     # per step: interleave, depth fills, camera records (forward and backward), one depth prepass per group of four views,
     # (blend, resolve) and (prepare, gather, chain, all-points fallback) per view, then either de-interleave + three
     # normalisations or the one peer-reduce kernel (NCCL's own kernels are not counted)
-    kernels_per_step = 1 + L + 2 + (V + 3) // 4 + 5 * V + 5 * V + (2 if peer is not None else 2 + 3)
+    kernels_per_step = 1 + L + 2 + (V + 3) // 4 + 2 * V + 4 * V + (2 if peer is not None else 2 + 3)
 
     def barrier():
         if world > 1:
@@ -412,7 +415,7 @@ def main():
                            "point_order": "Morton-sorted once (untimed), as the reference's scene preprocessing does"},
                 "fwd_ms_per_view": ktimes_ms(ktimes, ("k_texture_interleave", "k_fill", "k_build_cams", "k_depth_prepass", "k_blend", "k_accept",
                                                       "k_bin_offsets", "k_bin_scatter", "k_splat", "k_resolve"), V, args),
-                "bwd_ms_per_view": ktimes_ms(ktimes, ("k_prepare_backward", "k_backward_tiles", "k_hole_gradients", "k_point_chain", "k_splat_backward_all",
+                "bwd_ms_per_view": ktimes_ms(ktimes, ("k_prepare_backward", "k_backward_tiles", "k_chain_and_holes", "k_splat_backward_all",
                                                       "k_texture_deinterleave", "k_normalize", "k_peer_reduce"), V, args),
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
                 "gpu_launches": kernels_per_step * args.steps,
