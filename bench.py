@@ -31,10 +31,13 @@ UNIT = "Gpts/s"
 WORKLOAD = "c2: 10M points x 16 views/GPU, 1920x1080, L=4, C=4, pinhole k1=-0.1 k2=0.02, env 1024x512, fwd+bwd with pose grads"
 
 
-# DRAM bytes (read + write) per launch of the kernels that can dominate, from an ncu --set full capture of a four-view
-# run of this workload (profiles/point_kernels_c2_ncu_full.md); one launch there = one launch here. Valid for the default
-# workload only.
-NCU_TRAFFIC_BYTES = {"k_blend": 395.0e6, "k_splat_gather": 480.1e6, "k_splat_chain": 190.1e6, "k_depth_prepass": 245.4e6}
+# DRAM bytes (read + write) per launch of the kernels that can dominate, from ncu captures of a four-view run of this
+# workload (profiles/point_kernels_c2_ncu.md); one launch there = one launch here. Valid for the default workload only.
+NCU_TRAFFIC_BYTES = {}
+try:
+    NCU_TRAFFIC_BYTES = json.load(open(os.path.join(ROOT, "profiles", "c2_kernel_dram_bytes.json")))
+except (OSError, ValueError):
+    pass
 
 
 def parse_args():
@@ -46,6 +49,8 @@ def parse_args():
     ap.add_argument("--points", type=int, default=10_000_000)
     ap.add_argument("--views", type=int, default=16, help="views per GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-c4", action="store_true", help="N > 1: skip the 30 M point record")
+    ap.add_argument("--no-extras", action="store_true", help="N = 1: skip the tonemapper / Morton reorder record")
     ap.add_argument("--candidates", action="store_true",
                     help="size the scratch with room for candidate streams (the depth prepass then hands projected points to "
                          "the blend kernel; measured slightly slower overall than projecting twice)")
@@ -178,6 +183,143 @@ def cpu_reference_arm(args, rank, world):
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+def exchange_check(peer, dist, torch):
+    """Largest relative difference (|a - b| / max|b| per tensor) between what the peer-memory kernel just produced and the
+    same sums formed by NCCL all-reduces of the raw gradient blocks, on this rank's shards. Outside any timed region."""
+    res = peer.reduce()  # the blocks still hold this step's raw sums
+    raw = peer.backward_outputs()
+    worst = 0.0
+
+    def rel(a, b):
+        scale = float(b.abs().max())
+        return float((a.double() - b.double()).abs().max()) / scale if scale > 0 else 0.0
+
+    tex = raw["texture_interleaved"].clone()
+    dist.all_reduce(tex)
+    t_lo, t_hi = res["texel_range"]
+    worst = max(worst, rel(res["texture_shard"], tex[t_lo:t_hi].t()))
+    del tex
+    pts = raw["points"].clone()
+    dist.all_reduce(pts)
+    p_lo, p_hi = res["point_range"]
+    mine = pts[p_lo:p_hi]
+    want = mine.clone()
+    nz = mine[:, 3] > 0
+    want[nz, :3] = mine[nz, :3] / mine[nz, 3:4]
+    want[:, 3] = 0
+    worst = max(worst, rel(res["points_shard"], want))
+    del pts
+    pose, cnt = raw["pose"].clone(), raw["count_pose"].clone()
+    dist.all_reduce(pose)
+    dist.all_reduce(cnt)
+    pose = torch.where(cnt[:, None] > 0, pose / cnt[:, None].double().clamp(min=1), pose)
+    worst = max(worst, rel(res["pose"], pose))
+    t = torch.tensor([worst], device=pose.device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def measure_c4(rank, world, dev, steps, exchange):
+    """The multi-GPU configuration (30 M points, 8 views per GPU, 1080p): forward + backward + gradient exchange, timed
+    like the headline (barrier, CUDA events, maximum over ranks). Returns the record for the bench line."""
+    import torch
+    import torch.distributed as dist
+    from adop_b200 import capi, synth
+    from adop_b200 import dist as adist
+    from adop_b200.raster import PointRasterizer, Scene
+    V, n_points = 8, 30_000_000
+    cfg = synth.make_config("c4", n_points=n_points, n_views=V * world)
+    arrays, params, L = cfg["arrays"], cfg["params"], cfg["num_layers"]
+    views = capi.make_views([cfg["views"][i] for i in adist.shard_views(list(range(V * world)), rank, world)])
+    C = cfg["meta"]["channels"]
+    scene = Scene(**{k: (torch.from_numpy(v).to(dev) if v is not None else None) for k, v in arrays.items()})
+    ras = PointRasterizer(dev)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4321 + rank)
+    grads = [torch.randn((V, C, hh, ww), device=dev, generator=gen) for ww, hh in capi.layer_sizes(cfg["meta"]["w"], cfg["meta"]["h"], L)]
+    fwd = ras.forward(scene, views, params, L)
+    bwd = ras.backward(scene, params, fwd, grads, want_env=True, normalize=False)
+    peer = None
+    if exchange == "peer":
+        try:
+            layout = adist.peer_layout(C, bwd["texture"].shape[1], n_points, num_images=bwd["pose"].shape[0],
+                                       num_cameras=bwd["intrinsics"].shape[0], intrinsics_cols=bwd["intrinsics"].shape[1],
+                                       env_hw=tuple(arrays["env_map"].shape[1:]))
+            peer = adist.PeerGradientExchange(layout, dev)
+            bwd = peer.backward_outputs()
+        except capi.AdopError:
+            peer = None
+
+    def step():
+        ras.forward(scene, views, params, L, out=fwd)
+        ras.backward(scene, params, fwd, grads, want_env=True, normalize=False, out=bwd)
+        if peer is not None:
+            peer.reduce()
+        else:
+            adist.exchange_gradients(bwd)
+
+    for _ in range(3):
+        step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / steps
+    capi.profile_enable(True)
+    step()
+    torch.cuda.synchronize()
+    kt = capi.profile_collect()
+    capi.profile_enable(False)
+    check = exchange_check(peer, dist, torch) if peer is not None else None
+    if peer is not None:
+        peer.close()
+    return {"workload": "c4: 30M points x 8 views/GPU, 1920x1080, L=4, C=4", "points": n_points, "views_per_gpu": V,
+            "value": n_points * V * world / (ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ms,
+            "exchange_ms": kt["k_peer_reduce"][1] if "k_peer_reduce" in kt else None,
+            "exchange": "peer-memory kernel" if peer is not None else "NCCL", "exchange_check": check}
+
+
+def single_gpu_extras(dev):
+    """Two kernels outside the headline that have a roofline of their own: the tonemapper's backward pass on a 4K frame
+    (36 bytes per pixel) and the Morton reorder of a 10 M point cloud (8 radix passes)."""
+    import statistics
+    import numpy as np
+    import torch
+    from adop_b200 import preprocess
+    from adop_b200.raster import Tonemapper
+    from adop_b200.run_config import timed
+    w, h = 3840, 2160
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+    exposure = torch.rand(1, device=dev, generator=g) * 4 - 2
+    wb = (1 + 0.05 * torch.randn((1, 3), device=dev, generator=g)).contiguous()
+    vig = torch.tensor([0.1, -0.05, 0.01, 0.0, 0.0], device=dev)
+    response = (torch.linspace(0, 1, 256, device=dev) ** (1 / 2.2)).repeat(3, 1).contiguous()
+    tm = Tonemapper((w, h), exposure=exposure, white_balance=wb, vignette=vig, response=response, leak=0.01)
+    x = torch.rand((1, 3, h, w), device=dev, generator=g)
+    go = torch.randn((1, 3, h, w), device=dev, generator=g)
+    fi = torch.zeros(1, device=dev, dtype=torch.int32)
+    for _ in range(3):
+        tm.backward(x, go, fi)
+    t_b = statistics.median(timed(lambda: tm.backward(x, go, fi), 10))
+    t_f = statistics.median(timed(lambda: tm.forward(x, fi), 10))
+    n = 10_000_000
+    rng = np.random.default_rng(0)
+    pos = torch.from_numpy(np.concatenate([rng.normal(0, 1.5, (n, 3)).astype(np.float32), np.ones((n, 1), np.float32)], axis=1)).to(dev)
+    for _ in range(2):
+        preprocess.morton_order(pos)
+    t_r = statistics.median(timed(lambda: preprocess.morton_order(pos), 5))
+    return {"tonemap_4k_backward_gbs": 36 * w * h / (t_b * 1e-3) / 1e9, "tonemap_4k_forward_gbs": 24 * w * h / (t_f * 1e-3) / 1e9,
+            "morton_reorder_10m_gkeys_per_s": n / (t_r * 1e-3) / 1e9, "morton_reorder_10m_ms": t_r}
 
 
 def main():
@@ -369,25 +511,36 @@ def main():
     peak_kind = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
     dom = max(ktimes.items(), key=lambda kv: kv[1][1])
     dom_name, (dom_launches, dom_ms) = dom
-    # algorithmic bytes of one launch (= one view) of each kernel that can dominate: what that kernel itself has to move
-    # at the least. Gather: per splat the list entry (16), the pixel's weight (4), the descriptor and its gradient (2 x 4C),
-    # and every pixel record [image | gradient] once (8C per pyramid pixel). Chain: per splat the list entry, the point
-    # and its gradient (16 each). Prepare: 2C + 1 planes read, one record written per pixel.
+    # Algorithmic bytes of one launch (= one view, four for the depth prepass) of each kernel that can dominate, two ways:
+    #  "survey": the kernel's share of the per-view formula above (forward N*2*16 + U(4+4C) + P(4C+8), backward
+    #            N*16 + U(4+4C) + P(8C+8)); the backward formula assumes that every position is read again, which this
+    #            backward pass does not do, so the tile kernel is charged the backward formula without its N*16 term;
+    #  "own":    what this kernel has to move at the least in this design (adds the depth planes the blend kernel reads, the
+    #            visible-list entry it writes or reads, 16 bytes per visible point, and the read-modify-write of the gradient
+    #            rows the backward kernels add into).
     U_mean = sum(U_views) / V
-    dom_bytes = {"k_depth_prepass": N * 16 + 4 * 4 * P,  # one launch covers four views: the points once, four depth pyramids
-                 "k_blend": N * 16 + U_mean * (4 + 4 * C),
+    survey_bytes = {"k_depth_prepass": N * 16 + 4 * 4 * P,  # one launch covers four views: the points once, four depth pyramids
+                    "k_blend": N * 16 + U_mean * (4 + 4 * C),
+                    "k_resolve": P * (4 * C + 8),
+                    "k_backward_tiles": U_mean * (4 + 4 * C) + P * (8 * C + 8),
+                    "k_chain_and_holes": U_mean * (16 + 16) + 4 * P}
+    own_bytes = {"k_depth_prepass": N * 16 + 4 * 4 * P,
+                 "k_blend": N * 16 + 4 * P + U_mean * (4 * C + 16),
                  "k_resolve": P * (4 * C + 8),
-                 "k_prepare_backward": P * (8 * C + 4 + 8 * C),
-                 "k_splat_gather": U_mean * (16 + 4 + 8 * C) + P * 8 * C,
-                 "k_splat_chain": U_mean * 48}.get(dom_name, sum(per_view_bwd) / V)
-    achieved = dom_bytes / (dom_ms / dom_launches * 1e-3) / 1e9
+                 "k_backward_tiles": P * (8 * C + 4) + U_mean * (16 + 4 * C + 2 * 4 * C + 16),
+                 "k_chain_and_holes": U_mean * (16 + 16 + 2 * 16) + 4 * P}
+    dom_survey = survey_bytes.get(dom_name, sum(per_view_bwd) / V)
+    dom_own = own_bytes.get(dom_name, dom_survey)
+    dom_s = dom_ms / dom_launches * 1e-3
     step_ms = ms_total / args.steps
     step_achieved = (fwd_b + bwd_b + step_b) / (step_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak,
+    roofline = {"bound": "hbm", "kernel": dom_name, "achieved": dom_own / dom_s / 1e9, "peak": peak, "unit": "GB/s",
+                "frac": dom_own / dom_s / 1e9 / peak,
+                "frac_survey_bytes": dom_survey / dom_s / 1e9 / peak,
                 "traffic": NCU_TRAFFIC_BYTES.get(dom_name) if (args.points == 10_000_000 and w == 1920) else None,
                 "peak_kind": peak_kind,
-                "algorithmic_bytes_per_launch": dom_bytes, "avg_launch_ms": dom_ms / dom_launches,
+                "algorithmic_bytes_per_launch": dom_own, "algorithmic_bytes_per_launch_survey": dom_survey,
+                "avg_launch_ms": dom_ms / dom_launches,
                 "step": {"algorithmic_bytes": fwd_b + bwd_b + step_b, "achieved": step_achieved, "frac": step_achieved / peak},
                 "kernel_ms_per_step": {k: v[1] / max(1, min(args.steps, 5)) for k, v in ktimes.items()}}
 
@@ -402,6 +555,22 @@ def main():
         cpu_baseline = {"value": cpu_value, "unit": UNIT, "cores": cores, "kind": "port",
                         "sample": f"{len(cpu_times)} x (1 full view: all {N} points, full 1080p pyramid, fwd+bwd with all gradients)"}
 
+    # ---- records outside the headline: the exchange check and the 30 M point configuration (N > 1), two more kernels (N = 1)
+    check = exchange_check(peer, dist, torch) if peer is not None else None
+    c4 = None
+    extras = None
+    if world > 1 and not args.no_c4:
+        if peer is not None:
+            peer.close()
+            peer = None
+        final.clear()
+        del fwd, bwd, scene, grads_dev, staged
+        ras = None
+        torch.cuda.empty_cache()
+        c4 = measure_c4(rank, world, dev, max(3, min(args.steps, 10)), args.exchange)
+    elif world == 1 and not args.no_extras:
+        extras = single_gpu_extras(dev)
+    parallelism_peer = check is not None
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
                 "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
@@ -410,9 +579,12 @@ def main():
                            "l2": "inputs exceed L2: 160 MB of points and ~100 MB of image state per view stream per pass",
                            "parallelism": ("single GPU" if world == 1 else
                                            f"view-sharded x{world}, gradients exchanged by one peer-memory kernel over NVLink "
-                                           "(reduce-scatter + all-reduce + normalise)" if peer is not None else
+                                           "(reduce-scatter + all-reduce + normalise)" if parallelism_peer else
                                            f"view-sharded x{world}, gradients reduce-scattered by NCCL"),
-                           "point_order": "Morton-sorted once (untimed), as the reference's scene preprocessing does"},
+                           "point_order": "Morton-sorted once (untimed), as the reference's scene preprocessing does",
+                           "e2e": "per step 705 MB host->device (the upstream gradient pyramid, pinned, double-buffered behind the kernels); "
+                                  "device->host only the pose, intrinsics and background gradients (836 B): the descriptor and point "
+                                  "gradients (320 MB) and the image pyramid stay on the device, where the optimiser and the U-Net use them"},
                 "fwd_ms_per_view": ktimes_ms(ktimes, ("k_texture_interleave", "k_fill", "k_build_cams", "k_depth_prepass", "k_blend", "k_accept",
                                                       "k_bin_offsets", "k_bin_scatter", "k_splat", "k_resolve"), V, args),
                 "bwd_ms_per_view": ktimes_ms(ktimes, ("k_prepare_backward", "k_backward_tiles", "k_chain_and_holes", "k_splat_backward_all",
@@ -420,6 +592,11 @@ def main():
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
                 "gpu_launches": kernels_per_step * args.steps,
                 "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline}
+        if world > 1:
+            line["exchange_check"] = check  # peer-memory kernel against NCCL all-reduces of the same gradients: largest relative difference
+            line["c4"] = c4
+        if extras is not None:
+            line["extra"] = extras
         print(json.dumps(line), flush=True)
     if peer is not None:
         peer.close()
