@@ -5,6 +5,7 @@
 //   NeuralRenderInfo             (PointRenderer.h:25-34), registered as a custom class (RenderInfo.cpp:11-15) -> adop::RenderInfo
 //   BlendPointCloud              (PointRenderer.h:52, RenderInfo.cpp:19-31)                        -> adop::blend_point_cloud
 //   ApplyTangentToPose           (PointRenderer.h:63)                                              -> adop::apply_tangent_to_pose
+//   NeuralCameraImpl::forward    (src/lib/models/NeuralCamera.h:128-129)                          -> adop::tonemap (adop::Tonemap)
 // Same differentiable inputs in the same order (texture [C,N], background [C], points [N,4], pose tangents [I,6] f64,
 // intrinsics [K,cols]), same outputs (L colour tensors, then L masks when requested), gradients in the same order.
 // The reference's NeuralRenderInfo points at a NeuralScene (which needs the whole saiga library); RenderInfo carries the
@@ -130,17 +131,41 @@ static void ensure_workspace(RenderInfo& info, const adop_scene& sc, const torch
     }
 }
 
+// What a forward call used and its backward call must use again, whatever happens to the RenderInfo in between (a second
+// forward with other views or another drop-out seed, gradient accumulation, an evaluation render): the reference keeps its
+// per-call state in the autograd context as well (the saved drop-out tensor, PointRenderer.cu:1524).
+// "no tensor" as an argument of an autograd function: an empty one (an undefined tensor has no device to dispatch on)
+static Tensor none_like(const Tensor& x) { return torch::empty({0}, x.options()); }
+static bool has(const Tensor& t) { return t.defined() && t.numel() > 0; }
+static Tensor blob_of(const void* data, size_t bytes)
+{
+    Tensor t = torch::empty({(int64_t)bytes}, torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCPU));
+    memcpy(t.data_ptr(), data, bytes);
+    return t;
+}
+
 struct PointRender : public torch::autograd::Function<PointRender>
 {
-    // returns a tensor for every layer, then (if requested) a mask for every layer
+    // returns a tensor for every layer, then (if requested) a mask for every layer.
+    // env_map: an undefined tensor takes the RenderInfo's environment map (no gradient for it); a defined one is the
+    // differentiable texture of EnvironmentMapImpl (RenderModule.cpp:106-127, EnvironmentMap.cu:107-156) and gets one.
     static variable_list forward(AutogradContext* ctx, Variable texture, Variable background_color, Variable points,
-                                 Variable pose_tangents, Variable intrinsics, torch::IValue info_value)
+                                 Variable pose_tangents, Variable intrinsics, Variable env_map, torch::IValue info_value)
     {
         auto info = info_value.toCustomClass<RenderInfo>();
         TORCH_CHECK(!info->images.empty(), "RenderInfo has no views");
         c10::cuda::CUDAGuard guard(texture.device());
         cudaStream_t stream = c10::cuda::getCurrentCUDAStream().stream();
         adop_scene sc = make_scene(*info, texture, background_color, points, intrinsics);
+        if (has(env_map))
+        {
+            TORCH_CHECK(env_map.is_cuda() && env_map.is_contiguous() && env_map.scalar_type() == torch::kFloat32, "env_map: contiguous float32 CUDA tensor");
+            TORCH_CHECK(env_map.dim() == 3 || (env_map.dim() == 4 && env_map.size(0) == 1), "env_map must be [C,h,w] or [1,C,h,w]");
+            TORCH_CHECK(env_map.size(env_map.dim() - 3) == sc.channels, "env_map must have as many channels as the descriptors");
+            sc.env_map = env_map.data_ptr<float>();
+            sc.env_h = (int32_t)env_map.size(env_map.dim() - 2);
+            sc.env_w = (int32_t)env_map.size(env_map.dim() - 1);
+        }
         const int B = (int)info->images.size(), L = (int)info->num_layers, C = sc.channels;
         auto opt = texture.options();
         ensure_workspace(*info, sc, opt);
@@ -170,18 +195,28 @@ struct PointRender : public torch::autograd::Function<PointRender>
         io.workspace_bytes = (size_t)info->workspace.numel();
         check_status(adop_raster_forward(&sc, info->images.data(), B, &info->params, L, &io, stream), "adop_raster_forward");
 
-        // saved for backward: depth, weight per layer, then the colours (PointRenderer.cu:1514-1527); the splat list
+        // saved for backward: depth, weight per layer, then the colours (PointRenderer.cu:1514-1527); the visible list
         // takes the place of the drop-out tensor
         variable_list save;
         for (int l = 0; l < L; ++l) { save.push_back(depth[l]); save.push_back(weight[l]); }
         save.insert(save.end(), color.begin(), color.end());
         save.push_back(visible);
         save.push_back(texture); save.push_back(background_color); save.push_back(points); save.push_back(intrinsics);
+        save.push_back(has(env_map) ? env_map : (info->env_map ? *info->env_map : none_like(texture)));
+        save.push_back(info->poses);
         ctx->save_for_backward(save);
-        ctx->saved_data["render_info"] = info_value;
+        ctx->saved_data["render_info"] = info_value;  // for its reusable buffers only
+        ctx->saved_data["params"] = blob_of(&info->params, sizeof(adop_render_params));
+        ctx->saved_data["views"] = blob_of(info->images.data(), sizeof(adop_view) * info->images.size());
+        ctx->saved_data["num_layers"] = (int64_t)L;
+        ctx->saved_data["has_normal"] = info->normal.has_value();
+        ctx->saved_data["has_index"] = info->index.has_value();
+        if (info->normal) ctx->saved_data["normal"] = *info->normal;
+        if (info->index) ctx->saved_data["index"] = *info->index;
         ctx->saved_data["need_points"] = points.requires_grad();
         ctx->saved_data["need_pose"] = pose_tangents.requires_grad();
         ctx->saved_data["need_intrinsics"] = intrinsics.requires_grad();
+        ctx->saved_data["need_env"] = has(env_map) && env_map.requires_grad() && info->params.composite_environment_map != 0;
         ctx->saved_data["num_tangents"] = pose_tangents.size(0);
         variable_list out = color;
         out.insert(out.end(), mask.begin(), mask.end());
@@ -192,13 +227,29 @@ struct PointRender : public torch::autograd::Function<PointRender>
     static variable_list backward(AutogradContext* ctx, variable_list grad_output)
     {
         auto info = ctx->saved_data["render_info"].toCustomClass<RenderInfo>();
-        const int B = (int)info->images.size(), L = (int)info->num_layers;
+        // the call's own copies of everything that can change on the RenderInfo between forward and backward
+        Tensor params_blob = ctx->saved_data["params"].toTensor(), views_blob = ctx->saved_data["views"].toTensor();
+        adop_render_params params;
+        memcpy(&params, params_blob.data_ptr(), sizeof(params));
+        std::vector<adop_view> views((size_t)views_blob.numel() / sizeof(adop_view));
+        memcpy(views.data(), views_blob.data_ptr(), sizeof(adop_view) * views.size());
+        const int B = (int)views.size(), L = (int)ctx->saved_data["num_layers"].toInt();
         auto saved = ctx->get_saved_variables();
-        TORCH_CHECK((int)saved.size() == 3 * L + 5, "unexpected number of saved tensors");
+        TORCH_CHECK((int)saved.size() == 3 * L + 7, "unexpected number of saved tensors");
         Tensor texture = saved[3 * L + 1], background = saved[3 * L + 2], points = saved[3 * L + 3], intrinsics = saved[3 * L + 4];
+        Tensor env_map = saved[3 * L + 5], poses = saved[3 * L + 6];
         c10::cuda::CUDAGuard guard(texture.device());
         cudaStream_t stream = c10::cuda::getCurrentCUDAStream().stream();
-        adop_scene sc = make_scene(*info, texture, background, points, intrinsics);
+        RenderInfo call;  // the scene as the forward call saw it
+        call.poses = poses;
+        if (ctx->saved_data["has_normal"].toBool()) call.normal = ctx->saved_data["normal"].toTensor();
+        if (ctx->saved_data["has_index"].toBool()) call.index = ctx->saved_data["index"].toTensor();
+        if (has(env_map)) call.env_map = env_map;
+        adop_scene sc = make_scene(call, texture, background, points, intrinsics);
+        // the shared [T,C] working copy may belong to a later forward call by now: rebuild it from this call's descriptors
+        ensure_workspace(*info, sc, texture.options());
+        check_status(adop_texture_interleave(sc.texture, info->texture_interleaved.data_ptr<float>(), sc.channels, sc.num_texels, stream),
+                     "adop_texture_interleave");
         sc.texture_interleaved = info->texture_interleaved.data_ptr<float>();
         adop_backward_io io{};
         std::vector<Tensor> grads(L);
@@ -216,7 +267,7 @@ struct PointRender : public torch::autograd::Function<PointRender>
         Tensor visible = saved[3 * L];
         io.visible_list = visible.data_ptr<int32_t>();
         Tensor g_texture = torch::empty_like(texture), g_background = torch::empty_like(background);
-        Tensor g_points, g_pose, c_pose, g_intr, c_intr;
+        Tensor g_points, g_pose, c_pose, g_intr, c_intr, g_env, g_env_scratch;
         io.grad_texture = g_texture.data_ptr<float>();
         io.grad_texture_interleaved = info->grad_texture_interleaved.data_ptr<float>();
         io.grad_background = g_background.data_ptr<float>();
@@ -229,7 +280,7 @@ struct PointRender : public torch::autograd::Function<PointRender>
         {
             g_pose = torch::empty({ctx->saved_data["num_tangents"].toInt(), 6}, texture.options().dtype(torch::kFloat64));
             c_pose = torch::empty({g_pose.size(0)}, texture.options());
-            TORCH_CHECK(g_pose.size(0) == info->poses.size(0), "one pose tangent per pose");
+            TORCH_CHECK(g_pose.size(0) == poses.size(0), "one pose tangent per pose");
             io.grad_pose = g_pose.data_ptr<double>();
             io.count_pose = c_pose.data_ptr<float>();
         }
@@ -240,14 +291,24 @@ struct PointRender : public torch::autograd::Function<PointRender>
             io.grad_intrinsics = g_intr.data_ptr<float>();
             io.count_intrinsics = c_intr.data_ptr<float>();
         }
+        if (ctx->saved_data["need_env"].toBool())
+        {
+            g_env = torch::empty_like(env_map);
+            io.grad_env_map = g_env.data_ptr<float>();
+            if (sc.channels % 4 == 0)
+            {
+                g_env_scratch = torch::empty_like(env_map);
+                io.grad_env_map_interleaved = g_env_scratch.data_ptr<float>();
+            }
+        }
         io.accumulate = 0;
         io.normalize = 1;
         io.workspace = info->workspace.data_ptr();
         io.workspace_bytes = (size_t)info->workspace.numel();
-        check_status(adop_raster_backward(&sc, info->images.data(), B, &info->params, L, &io, stream), "adop_raster_backward");
-        // {texture, background, points, pose tangents, intrinsics} and nothing for the info object
+        check_status(adop_raster_backward(&sc, views.data(), B, &params, L, &io, stream), "adop_raster_backward");
+        // {texture, background, points, pose tangents, intrinsics}, the environment map, and nothing for the info object
         // (PointRenderer.cu:1641-1643, RenderInfo.cpp:56)
-        return {g_texture, g_background, g_points, g_pose, g_intr, Variable()};
+        return {g_texture, g_background, g_points, g_pose, g_intr, g_env, Variable()};
     }
 };
 
@@ -255,7 +316,15 @@ struct PointRender : public torch::autograd::Function<PointRender>
 static std::vector<Tensor> blend_point_cloud(Tensor texture, Tensor background_color, Tensor points, Tensor pose_tangents,
                                              Tensor intrinsics, c10::intrusive_ptr<RenderInfo> info)
 {
-    return PointRender::apply(texture, background_color, points, pose_tangents, intrinsics, torch::IValue(info));
+    return PointRender::apply(texture, background_color, points, pose_tangents, intrinsics, none_like(texture), torch::IValue(info));
+}
+// The same with the environment map as a differentiable input: with composite_environment_map set, the composite
+// out = img + (1 - mask) * grid_sample(env_map, uv) of RenderModule.cpp:106-127 is part of the operator, and the gradient
+// of the texture of EnvironmentMapImpl (EnvironmentMap.cu:107-156) comes back through it.
+static std::vector<Tensor> blend_point_cloud_environment(Tensor texture, Tensor background_color, Tensor points, Tensor pose_tangents,
+                                                         Tensor intrinsics, Tensor env_map, c10::intrusive_ptr<RenderInfo> info)
+{
+    return PointRender::apply(texture, background_color, points, pose_tangents, intrinsics, env_map, torch::IValue(info));
 }
 
 // ApplyTangentToPose (PointRenderer.cu:1659-1665)
@@ -270,6 +339,107 @@ static void apply_tangent_to_pose(Tensor tangent, Tensor pose)
                  "adop_apply_tangent");
 }
 
+// NeuralCameraImpl::forward (src/lib/models/NeuralCamera.h:128-129, NeuralCamera.cpp:258-335) as one autograd function over
+// the fused kernels: exposure, white balance, vignette (VignetteNetImpl::forward, :22-42) and camera response
+// (CameraResponseNetImpl::forward, :87-135). Parameter tensors in the reference's shapes (NeuralCamera.h:45-46,114,135-139):
+//   exposures_values [n,1,1,1], white_balance_values [n,3,1,1], vignette_params [3], vignette_center [1,2,1,1],
+//   response [1,3,1,K]; an undefined tensor switches the stage off (enable_exposure / enable_white_balance /
+//   enable_vignette / no camera_response: clamp to [0,1]). frame_index [B] int32 selects the rows; uv [B,2,H,W] or undefined.
+struct Tonemap : public torch::autograd::Function<Tonemap>
+{
+    static adop_tonemap_params make_params(const Tensor& x, const Tensor& frame_index, const Tensor& uv, const Tensor& exposure,
+                                           const Tensor& wb, const Tensor& vignette5, const Tensor& response, int64_t image_w,
+                                           int64_t image_h, double leak)
+    {
+        TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.scalar_type() == torch::kFloat32 && x.dim() == 4, "x: contiguous float32 CUDA [B,3,H,W]");
+        TORCH_CHECK(x.size(1) == 3, "the tonemapper works on RGB images");  // SAIGA_ASSERT(x.size(1) == 3), NeuralCamera.cpp:263
+        adop_tonemap_params p{};
+        p.batch = (int32_t)x.size(0); p.height = (int32_t)x.size(2); p.width = (int32_t)x.size(3);
+        p.vignette_image_w = (int32_t)image_w; p.vignette_image_h = (int32_t)image_h;
+        p.leak = (float)leak;
+        if (has(frame_index))
+        {
+            TORCH_CHECK(frame_index.is_cuda() && frame_index.scalar_type() == torch::kInt32 && frame_index.numel() == x.size(0), "frame_index: int32 CUDA [B]");
+            p.frame_index = frame_index.data_ptr<int32_t>();
+        }
+        if (has(exposure)) p.exposure = exposure.data_ptr<float>();
+        if (has(wb)) p.white_balance = wb.data_ptr<float>();
+        if (has(vignette5)) p.vignette = vignette5.data_ptr<float>();
+        if (has(uv))
+        {
+            TORCH_CHECK(uv.is_cuda() && uv.is_contiguous() && uv.scalar_type() == torch::kFloat32 && uv.numel() == x.size(0) * 2 * x.size(2) * x.size(3), "uv: contiguous float32 CUDA [B,2,H,W]");
+            p.uv = uv.data_ptr<float>();
+        }
+        if (has(response))
+        {
+            p.response = response.data_ptr<float>();
+            p.response_bins = (int32_t)response.size(response.dim() - 1);
+        }
+        return p;
+    }
+    static Variable forward(AutogradContext* ctx, Variable x, Variable exposures_values, Variable white_balance_values, Variable vignette_params,
+                            Variable vignette_center, Variable response, Tensor frame_index, Tensor uv, int64_t image_w, int64_t image_h, double leak)
+    {
+        c10::cuda::CUDAGuard guard(x.device());
+        cudaStream_t stream = c10::cuda::getCurrentCUDAStream().stream();
+        Tensor xc = x.contiguous();
+        Tensor e = exposures_values.contiguous(), wb = white_balance_values.contiguous(), r = response.contiguous();
+        Tensor vig = none_like(xc);
+        if (has(vignette_params))
+        {
+            Tensor c = has(vignette_center) ? vignette_center.reshape({2}) : torch::zeros({2}, vignette_params.options());
+            vig = torch::cat({vignette_params.reshape({3}), c}).contiguous();
+        }
+        if (has(wb)) TORCH_CHECK(wb.numel() % 3 == 0, "white_balance_values must be [n,3,1,1]");
+        if (has(r)) TORCH_CHECK(r.numel() == 3 * r.size(r.dim() - 1), "response must be [1,3,1,K]");
+        adop_tonemap_params p = make_params(xc, frame_index, uv, e, wb, vig, r, image_w, image_h, leak);
+        Tensor out = torch::empty_like(xc);
+        check_status(adop_tonemap_forward(&p, xc.data_ptr<float>(), out.data_ptr<float>(), stream), "adop_tonemap_forward");
+        ctx->save_for_backward({xc, e, wb, vig, r, frame_index, uv});
+        ctx->saved_data["image_w"] = image_w; ctx->saved_data["image_h"] = image_h; ctx->saved_data["leak"] = leak;
+        ctx->saved_data["has_center"] = has(vignette_center);
+        return out;
+    }
+    static variable_list backward(AutogradContext* ctx, variable_list grad_output)
+    {
+        auto saved = ctx->get_saved_variables();
+        Tensor x = saved[0], e = saved[1], wb = saved[2], vig = saved[3], r = saved[4], frame_index = saved[5], uv = saved[6];
+        c10::cuda::CUDAGuard guard(x.device());
+        cudaStream_t stream = c10::cuda::getCurrentCUDAStream().stream();
+        adop_tonemap_params p = make_params(x, frame_index, uv, e, wb, vig, r, ctx->saved_data["image_w"].toInt(), ctx->saved_data["image_h"].toInt(),
+                                            ctx->saved_data["leak"].toDouble());
+        Tensor go = grad_output[0].contiguous();
+        TORCH_CHECK(go.scalar_type() == torch::kFloat32, "the image gradient must be float32");
+        adop_tonemap_grads g{};
+        Tensor gx = torch::empty_like(x), ge, gwb, gvig, gr;
+        g.grad_x = gx.data_ptr<float>();
+        if (has(e)) { ge = torch::empty_like(e); g.grad_exposure = ge.data_ptr<float>(); }
+        if (has(wb)) { gwb = torch::empty_like(wb); g.grad_white_balance = gwb.data_ptr<float>(); }
+        if (has(vig)) { gvig = torch::empty_like(vig); g.grad_vignette = gvig.data_ptr<float>(); }
+        if (has(r)) { gr = torch::empty_like(r); g.grad_response = gr.data_ptr<float>(); }
+        g.num_frames = has(e) ? (int32_t)e.numel() : (has(wb) ? (int32_t)(wb.numel() / 3) : 0);
+        g.accumulate = 0;
+        check_status(adop_tonemap_backward(&p, x.data_ptr<float>(), go.data_ptr<float>(), &g, stream), "adop_tonemap_backward");
+        Tensor g_params, g_center;
+        if (has(gvig))
+        {
+            g_params = gvig.slice(0, 0, 3).clone();
+            if (ctx->saved_data["has_center"].toBool()) g_center = gvig.slice(0, 3, 5).reshape({1, 2, 1, 1}).clone();
+        }
+        return {gx, ge, gwb, g_params, g_center, gr, Variable(), Variable(), Variable(), Variable(), Variable()};
+    }
+};
+
+static Tensor tonemap(Tensor x, c10::optional<Tensor> frame_index, c10::optional<Tensor> uv, c10::optional<Tensor> exposures_values,
+                      c10::optional<Tensor> white_balance_values, c10::optional<Tensor> vignette_params, c10::optional<Tensor> vignette_center,
+                      c10::optional<Tensor> response, int64_t image_w, int64_t image_h, double leak)
+{
+    auto t = [&](const c10::optional<Tensor>& o) { return o ? *o : none_like(x); };
+    auto ti = [&](const c10::optional<Tensor>& o) { return o ? *o : torch::empty({0}, x.options().dtype(torch::kInt32)); };
+    return Tonemap::apply(x, t(exposures_values), t(white_balance_values), t(vignette_params), t(vignette_center), t(response), ti(frame_index), t(uv),
+                          image_w, image_h, leak);
+}
+
 }  // namespace adop
 
 TORCH_LIBRARY(adop, m)
@@ -281,5 +451,7 @@ TORCH_LIBRARY(adop, m)
         .def("set_param", &adop::RenderInfo::set_param)
         .def("set_num_layers", &adop::RenderInfo::set_num_layers);
     m.def("blend_point_cloud", &adop::blend_point_cloud);
+    m.def("blend_point_cloud_environment", &adop::blend_point_cloud_environment);
     m.def("apply_tangent_to_pose", &adop::apply_tangent_to_pose);
+    m.def("tonemap", &adop::tonemap);
 }
