@@ -90,7 +90,7 @@ adop_status validate_common(const adop_scene* s, const adop_view* views, int B, 
     if (rp->composite_environment_map && s->env_map && (s->env_h <= 0 || s->env_w <= 0)) return ADOP_ERR_INVALID_ARGUMENT;
     const int w = views[0].w, h = views[0].h;
     if (w <= 0 || h <= 0) return ADOP_ERR_INVALID_ARGUMENT;
-    if (w > 32767 || h > 32767) return ADOP_ERR_SIZE_LIMIT;  // splat-list entries keep a pixel as x | y << 16
+    if (w > 32767 || h > 32767) return ADOP_ERR_SIZE_LIMIT;  // the tile tables and region offsets of the backward pass are 16-bit pixel coordinates
     if ((w >> (L - 1)) <= 0 || (h >> (L - 1)) <= 0) return ADOP_ERR_INVALID_ARGUMENT;
     // pixel indices are 32-bit: a view's pyramid, and the layer-0 planes of a group of four views, must stay below 2^32
     unsigned long long total = 0;

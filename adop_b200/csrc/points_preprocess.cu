@@ -372,7 +372,14 @@ struct GridParams
     float cell;      // edge length of a cell
     float inv_cell;
     int dim[3];
+    int status;      // set by k_knn_distance when a query gave up (see kKnnVisitLimit)
 };
+// Most points one query of k_knn_distance looks at before it gives up. The grid is sized for a few points per cell, and a
+// query of an ordinary cloud looks at tens to a few hundred; a cloud with millions of coincident points, or with all its
+// points in a corner of a bounding box that one far outlier stretched, puts them into one cell, and every query would
+// walk them all: hours of one kernel. A query that reaches the limit writes the bound it has, raises the status word,
+// and every query that starts afterwards returns at once; the entry point then reports ADOP_ERR_SIZE_LIMIT.
+constexpr int kKnnVisitLimit = 1 << 16;
 
 __global__ void k_grid_params(const float* __restrict__ bbox, int n, float per_cell, GridParams* __restrict__ out)
 {
@@ -395,6 +402,7 @@ __global__ void k_grid_params(const float* __restrict__ bbox, int n, float per_c
         int d = (int)(ext[k] * g.inv_cell) + 1;
         g.dim[k] = d < 1 ? 1 : (d > kGridMax ? kGridMax : d);
     }
+    g.status = 0;
     *out = g;
 }
 
@@ -440,8 +448,11 @@ __global__ void __launch_bounds__(kBlock) k_knn_distance(const float4* __restric
     const int k = KT > 0 ? KT : k_runtime;
     const GridParams g = *gp;
     const float inf = __int_as_float(0x7f800000);
+    volatile int* status = const_cast<volatile int*>(&gp->status);
     for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < n; j += gridDim.x * blockDim.x)
     {
+        if (*status != 0) { out[__ldg(order + j)] = inf; continue; }  // another query gave up: drain
+        int visited = 0;
         const float4 p = __ldg(sorted_pos + j);
         const int cx = cell_coord(p.x, g.lo[0], g.inv_cell, g.dim[0]);
         const int cy = cell_coord(p.y, g.lo[1], g.inv_cell, g.dim[1]);
@@ -468,6 +479,8 @@ __global__ void __launch_bounds__(kBlock) k_knn_distance(const float4* __restric
                         if (a < 0) a = __ldg(start + row + x);
                         b = e;
                     }
+                    visited += b - a;
+                    if (visited > kKnnVisitLimit) { *status = 1; b = a; }  // give up: the rows left are skipped as well
                     for (int m = a; m < b; ++m)
                     {
                         const float4 o = __ldg(sorted_pos + m);
@@ -484,6 +497,7 @@ __global__ void __launch_bounds__(kBlock) k_knn_distance(const float4* __restric
                     }
                 }
             kth = best[k];
+            if (visited > kKnnVisitLimit) break;
             const bool whole = x0 == 0 && y0 == 0 && z0 == 0 && x1 == g.dim[0] - 1 && y1 == g.dim[1] - 1 && z1 == g.dim[2] - 1;
             if (whole) break;
             // nothing outside the cube is nearer than the nearest face that is not a face of the grid itself
@@ -740,6 +754,18 @@ extern "C" adop_status adop_points_knn_distance(const float* position, int32_t n
     else
         ADOP_LAUNCH("k_knn_distance", st, (k_knn_distance<0><<<grid, kBlock, 0, st>>>(sorted_pos, order, n, gp, start, end, k, distance)));
     ADOP_CUDA_TRY(cudaGetLastError());
+    // Scene preprocessing runs once: this call waits for its kernels and reports a cloud that it could not handle.
+    int status = 0;
+    ADOP_CUDA_TRY(cudaMemcpyAsync(&status, &gp->status, sizeof(int), cudaMemcpyDeviceToHost, st));
+    ADOP_CUDA_TRY(cudaStreamSynchronize(st));
+    if (status != 0)
+    {
+        snprintf(last_error_buffer(), 512,
+                 "adop_points_knn_distance: a query met more than %d points in the cells around it (coincident points, or a "
+                 "bounding box stretched by far outliers): distances are incomplete; remove duplicates / outliers first",
+                 kKnnVisitLimit);
+        return ADOP_ERR_SIZE_LIMIT;
+    }
     return ADOP_OK;
 }
 

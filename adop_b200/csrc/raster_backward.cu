@@ -1297,7 +1297,9 @@ extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view
             case 4: r = launch_view_backward<4>(pts, cam, kp, lt, tiles, bt, io->grad_background, ge, s->env_h, s->env_w, env_inter, st, vl, views[b].camera_model); break;
             case 8: r = launch_view_backward<8>(pts, cam, kp, lt, tiles, bt, io->grad_background, ge, s->env_h, s->env_w, env_inter, st, vl, views[b].camera_model); break;
             case 16: r = launch_view_backward<16>(pts, cam, kp, lt, tiles, bt, io->grad_background, ge, s->env_h, s->env_w, env_inter, st, vl, views[b].camera_model); break;
-            default: return ADOP_ERR_UNSUPPORTED;
+            default:
+                snprintf(last_error_buffer(), 512, "%d descriptor channels: the kernels are built for 3, 4, 8 and 16", C);
+                return ADOP_ERR_UNSUPPORTED;
         }
         if (r != ADOP_OK) return r;
     }

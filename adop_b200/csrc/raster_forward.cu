@@ -851,7 +851,9 @@ extern "C" adop_status adop_raster_forward(const adop_scene* s, const adop_view*
             case 4: r = dispatch_layers_forward<4>(L, pts, s, cam, kp, lt, plan, st, b, depth_views); break;
             case 8: r = dispatch_layers_forward<8>(L, pts, s, cam, kp, lt, plan, st, b, depth_views); break;
             case 16: r = dispatch_layers_forward<16>(L, pts, s, cam, kp, lt, plan, st, b, depth_views); break;
-            default: return ADOP_ERR_UNSUPPORTED;
+            default:
+                snprintf(last_error_buffer(), 512, "%d descriptor channels: the kernels are built for 3, 4, 8 and 16", C);
+                return ADOP_ERR_UNSUPPORTED;
         }
         if (r != ADOP_OK) return r;
     }

@@ -119,6 +119,44 @@ class ClockSampler:
                 "samples": len(sm), "window": "timed region" if inside else "warm-up and timed region"}
 
 
+def bind_to_gpu_numa_node(gpu_index):
+    """Pin this process to the CPU cores that `nvidia-smi topo -m` lists as the GPU's CPU affinity, BEFORE it allocates its
+    pinned host buffers (they are then placed on that socket's memory): with several ranks per node every rank otherwise
+    pulls its host->device copies through whatever socket it happened to start on. Read-only query; returns the core list
+    (or None when the table cannot be read)."""
+    try:
+        out = subprocess.run(["nvidia-smi", "topo", "-m"], capture_output=True, text=True, timeout=20).stdout
+    except (OSError, subprocess.SubprocessError):
+        return None
+    header = None
+    for ln in out.splitlines():
+        cols = [c.strip() for c in ln.split("\t") if c.strip()]
+        if not cols:
+            continue
+        if "CPU Affinity" in ln and header is None:
+            header = cols
+            continue
+        if header and cols[0] == f"GPU{gpu_index}":
+            # the header has no cell above the row labels: data column k sits under header[k - 1]
+            try:
+                spec = cols[header.index("CPU Affinity") + 1]
+            except (ValueError, IndexError):
+                return None
+            cores = set()
+            for part in spec.split(","):
+                part = part.strip()
+                if not part or not part[0].isdigit():
+                    return None
+                a, _, b = part.partition("-")
+                cores.update(range(int(a), int(b or a) + 1))
+            allowed = cores & os.sched_getaffinity(0)
+            if not allowed:
+                return None
+            os.sched_setaffinity(0, allowed)
+            return sorted(allowed)
+    return None
+
+
 def algorithmic_bytes(N, C, P, U_views, normals=False, point_grads=True, env_hw=None):
     """Bytes that one step has to move at the least. Per view: forward N*2*(16+n) + U*(4+4C) + P*(4C+8), backward
     N*(16+n) + U*(4+4C) + P*(8C+8); per step + 4CN for the descriptor gradient, + 20N with point gradients, + the
@@ -342,6 +380,7 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path in the product)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    numa_cores = bind_to_gpu_numa_node(local_rank) if world > 1 else None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
@@ -582,6 +621,7 @@ def main():
                                            "(reduce-scatter + all-reduce + normalise)" if parallelism_peer else
                                            f"view-sharded x{world}, gradients reduce-scattered by NCCL"),
                            "point_order": "Morton-sorted once (untimed), as the reference's scene preprocessing does",
+                           "host_binding": (f"rank 0 pinned to {len(numa_cores)} cores of its GPU's NUMA node" if numa_cores else "none"),
                            "e2e": "per step 705 MB host->device (the upstream gradient pyramid, pinned, double-buffered behind the kernels); "
                                   "device->host only the pose, intrinsics and background gradients (836 B): the descriptor and point "
                                   "gradients (320 MB) and the image pyramid stay on the device, where the optimiser and the U-Net use them"},

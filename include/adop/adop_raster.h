@@ -16,7 +16,8 @@ extern "C" {
 #endif
 
 #define ADOP_MAX_LAYERS 8
-#define ADOP_MAX_CHANNELS 32
+#define ADOP_MAX_CHANNELS 32 /* bound of the argument checks; the kernels are built for 3, 4, 8 and 16 channels and the
+                                entry points return ADOP_ERR_UNSUPPORTED (with a message) for other counts */
 #define ADOP_MAX_OCAM_POLY 16
 
 typedef enum adop_status
@@ -70,7 +71,7 @@ typedef struct adop_render_params
  *   position   [N,4] f32  xyz + drop-out radius            (NeuralPointCloudCuda.h:34)
  *   normal     [N]   i32  10-bit packed, may be NULL       (NeuralPointCloudCuda.h:36)
  *   index      [N]   i32  descriptor column, NULL=identity (NeuralPointCloudCuda.h:41)
- *   texture    [C,T] f32  descriptors                      (NeuralTexture.h:62)
+ *   texture    [C,T] f32  descriptors, C = 3, 4, 8 or 16   (NeuralTexture.h:62)
  *   background [C]   f32                                    (NeuralTexture.h:65)
  *   poses      [I,8] f64  world->camera, quaternion xyzw + translation + pad (NeuralStructure.cpp:13-27)
  *   intrinsics [K,cols] f32: pinhole cols=13 (fx fy cx cy s k1..k6 p1 p2), OCam cols=5+m (c d e cx cy a0..)
@@ -332,6 +333,9 @@ adop_status adop_points_sort_blocks_by_radius_order(const float* position, int32
  * k-th nearest OTHER point (the reference asks its KD-tree for k+1 neighbours, the point itself included, and takes the
  * last), exact: the square root of the (k+1)-th smallest float32 value ((dx*dx + dy*dy) + dz*dz) over all points.
  * 1 <= k <= 16 (the reference's default is 4); fewer than k+1 points in the cloud give +inf.
+ * The call waits for its kernels (scene preprocessing runs once). A cloud whose points pile up in single cells of the
+ * search grid (millions of coincident points; a bounding box stretched by a far outlier) would cost a full scan per
+ * query: a query gives up after 65536 visited points, the call returns ADOP_ERR_SIZE_LIMIT and `distance` is incomplete.
  * adop_points_radius_sample then forms the drop-out radius data(3) = distance * sqrt(1 / u) (SceneData.cpp:476-482) with
  * u in (0,1] from the counter hash of (seed, 1, point) instead of the reference's global random generator; the caller
  * stores it in position.w. */

@@ -166,3 +166,26 @@ def test_radius_sample(cuda_lib):
     got = preprocess.radius_sample(torch.from_numpy(dist).cuda(), seed=3).cpu().numpy()
     assert np.array_equal(got, want.astype(np.float32))
     assert np.all(got >= dist)
+
+
+def test_knn_gives_up_on_a_cloud_of_coincident_points(cuda_lib):
+    """A quarter of a million points in one place: every query would have to walk all of them. The kernel gives up after
+    a bounded number of visited points, the rest of the grid drains, and the call reports the size limit in seconds, not
+    hours."""
+    import time
+    from adop_b200 import capi
+    rng = np.random.default_rng(0)
+    n_same, n_other = 250_000, 2_000
+    pos = np.ones((n_same + n_other, 4), np.float32)
+    pos[:n_same, :3] = [0.25, -0.5, 1.0]
+    pos[n_same:, :3] = rng.uniform(-1, 1, (n_other, 3))
+    t0 = time.time()
+    with pytest.raises(capi.AdopError, match="size beyond the supported maximum"):
+        preprocess.knn_distance(torch.from_numpy(pos).cuda(), k=4)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 20.0
+    assert b"65536" in cuda_lib.adop_last_error()
+    # an ordinary cloud right afterwards: the status word does not stick
+    ok = rng.uniform(-1, 1, (5000, 4)).astype(np.float32)
+    d = preprocess.knn_distance(torch.from_numpy(ok).cuda(), k=4)
+    assert bool(torch.isfinite(d).all())

@@ -374,6 +374,10 @@ def test_argument_errors(cuda_lib):
     with pytest.raises(capi.AdopError):
         r.forward(Scene(**{k: (v.cpu() if v is not None else None) for k, v in scene.tensors().items()}),
                   cfg["views"], cfg["params"], 4)
+    # five descriptor channels: inside the header's bound, but no kernels are built for it
+    five = synth.make_config("c1", n_points=1000, size=(64, 64), channels=5)
+    with pytest.raises(capi.AdopError, match="built for 3, 4, 8 and 16"):
+        PointRasterizer("cuda:0").forward(to_scene(five["arrays"]), five["views"], five["params"], 4)
 
 
 def test_c2_full_size_one_view_against_checker(oracle, cuda_lib):
@@ -392,6 +396,40 @@ def test_c2_full_size_one_view_against_checker(oracle, cuda_lib):
     assert not bool(fwd.list_unusable().any())
     check_forward(ref, fwd, L, masks=True)
     check_backward(ref_b, bwd)
+
+
+def _full_size_case(oracle, cfg, want_env):
+    arrays, views, params, L = cfg["arrays"], cfg["views"], cfg["params"], cfg["num_layers"]
+    grads = synth.upstream_gradients(cfg["meta"], batch=len(views))
+    ref = oracle.forward(arrays, views, params, L, threads=16)
+    ref_b = oracle.backward(arrays, views, params, L, ref, grads, want_env=want_env, threads=16)
+    scene = to_scene(arrays)
+    r = PointRasterizer("cuda:0")
+    fwd = r.forward(scene, views, params, L)
+    bwd = r.backward(scene, params, fwd, [torch.from_numpy(g).cuda() for g in grads], want_env=want_env)
+    torch.cuda.synchronize()
+    assert not bool(fwd.list_unusable().any())
+    check_forward(ref, fwd, L, masks=bool(params.output_background_mask))
+    check_backward(ref_b, bwd)
+    return ref
+
+
+def test_c3_omnidirectional_10m_points_full_hd_against_checker(oracle, cuda_lib):
+    """The viewer configuration's camera and image size (omnidirectional model, 1920x1080, 4 layers) on 10 M of its points,
+    forward and backward."""
+    ref = _full_size_case(oracle, synth.make_config("c3", n_points=10_000_000), want_env=False)
+    assert ref["weights"][0].sum() > 100_000
+
+
+def test_c4_30m_points_one_view_against_checker(oracle, cuda_lib):
+    """The multi-GPU configuration's cloud (30 M points on surfaces) for one 1080p view."""
+    _full_size_case(oracle, synth.make_config("c4", n_views=1), want_env=True)
+
+
+def test_c5_one_4k_view_8_channels_6_layers_against_checker(oracle, cuda_lib):
+    """The HDR configuration's image size, channel and layer count (3840x2160, 8 channels, 6 layers, 2048x1024 environment
+    map) for one view on 6 M points."""
+    _full_size_case(oracle, synth.make_config("c5", n_points=6_000_000, n_views=1), want_env=True)
 
 
 def test_full_size_properties_16_views(cuda_lib):
