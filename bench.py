@@ -33,11 +33,8 @@ WORKLOAD = "c2: 10M points x 16 views/GPU, 1920x1080, L=4, C=4, pinhole k1=-0.1 
 
 # DRAM bytes (read + write) per launch of the kernels that can dominate, from ncu captures of a four-view run of this
 # workload (profiles/point_kernels_c2_ncu.md); one launch there = one launch here. Valid for the default workload only.
-NCU_TRAFFIC_BYTES = {}
-try:
-    NCU_TRAFFIC_BYTES = json.load(open(os.path.join(ROOT, "profiles", "c2_kernel_dram_bytes.json")))
-except (OSError, ValueError):
-    pass
+NCU_TRAFFIC_BYTES = {"k_depth_prepass": 220.0e6, "k_blend": 421.2e6, "k_resolve": 106.6e6, "k_backward_tiles": 313.9e6,
+                     "k_chain_and_holes": 222.1e6}
 
 
 def parse_args():
