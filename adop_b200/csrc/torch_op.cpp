@@ -119,8 +119,8 @@ static adop_scene make_scene(RenderInfo& info, const Tensor& texture, const Tens
 
 static void ensure_workspace(RenderInfo& info, const adop_scene& sc, const torch::TensorOptions& opt)
 {
-    const size_t need = adop_raster_workspace_bytes_full(sc.num_points, (int32_t)info.images.size(), info.images[0].w, info.images[0].h,
-                                                         (int32_t)info.num_layers, sc.channels);
+    // the small workspace: candidate streams (adop_raster_workspace_bytes_full) measured slower on training-sized views
+    const size_t need = adop_raster_workspace_bytes(info.images[0].w, info.images[0].h, (int32_t)info.num_layers, sc.channels);
     TORCH_CHECK(need > 0, "invalid view size / layer count");
     if (!info.workspace.defined() || (size_t)info.workspace.numel() < need)
         info.workspace = torch::empty({(int64_t)need}, opt.dtype(torch::kUInt8));

@@ -185,12 +185,11 @@ void adop_render_params_default(adop_render_params* p);
 /* Bytes of scratch that forward/backward need for views of w x h with `layers` layers and `channels`
  * descriptor channels. Replaces the size-keyed PointRendererCache (PointRenderer.h:96-157). */
 size_t adop_raster_workspace_bytes(int32_t w, int32_t h, int32_t layers, int32_t channels);
-/* The same plus room that grows with the cloud (16 bytes per point and view of a group of up to four views, about
- * 64 N bytes): with a workspace of at least this size the depth prepass hands the projected in-image points of each view to
- * the blend kernel (which then neither reads the cloud again nor projects a second time), and the backward pass over a
- * splat list keeps one image-space gradient sum per point, so that the projection chain runs once per visible point
- * instead of once per (point, layer). A smaller workspace (at least adop_raster_workspace_bytes) selects the kernels
- * that do without. Same results either way. */
+/* The same plus 16 bytes per point and view of a group of up to four views (about 64 N bytes): with a workspace of at
+ * least this size the depth prepass also hands the projected in-image points of each view to the blend kernel, which then
+ * neither reads the cloud again nor projects a second time. Same results either way. On the benchmark configuration the
+ * extra stream costs the prepass more than it saves the blend kernel (measured), so the host layers of this library ask
+ * for the small workspace; the option pays when few of the points land in the image. */
 size_t adop_raster_workspace_bytes_full(int32_t num_points, int32_t num_views, int32_t w, int32_t h, int32_t layers,
                                         int32_t channels);
 
