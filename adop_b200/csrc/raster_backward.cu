@@ -4,22 +4,23 @@
 // of the environment-map composite (RenderModule.cpp:121-125, grid_sample backward).
 //
 // Differences in how the same sums are formed (results agree within float-ordering tolerance):
-//  * the forward pass records which (point, layer) splats the backward pass will visit; the backward kernel then runs
-//    one thread per recorded splat in dense warps instead of one thread per point of the cloud (a fallback kernel
-//    with the reference's structure handles calls without such a list);
+//  * the forward pass lists, per 32 x 16 screen tile, the points that were accepted on some layer; the backward pass runs
+//    one block per tile over that list, with the tile's region of every layer (weight, forward image, upstream gradient)
+//    staged in shared memory, instead of one thread per point of the cloud reading scattered pixels (kernels with the
+//    reference's structure stay behind it for calls without a usable list);
+//  * a point's descriptor gradient is summed over its layers and leaves as one vector atomic; its image-space ghost
+//    gradient is summed over its layers too (scaled by 0.5^layer), so the projection chain runs once per visible point;
 //  * the point gradient and its counter leave as ONE 16-byte vector atomic (x, y, z, count);
 //  * pose and intrinsics gradients, which the reference adds with 7 + 14 same-address atomics per splat,
 //    are reduced warp -> block in shared memory and leave as one atomic per component and block;
-//  * the ghost-gradient stencil reads, per neighbour pixel, C values of the forward image and C of the upstream
-//    gradient. From NCHW planes that is 2C scattered 4-byte reads in 2C different sectors; a preparation pass
-//    (fused with the background / environment-map gradient) first interleaves both into one record per pixel
-//    [I_0..I_C-1, G_0..G_C-1], so a neighbour costs one or two 32-byte sectors.
+//  * the all-points kernels read the ghost stencil from one interleaved record per pixel [I_0..I_C-1, G_0..G_C-1] that a
+//    preparation pass builds (a neighbour then costs one or two 32-byte sectors instead of 2C).
 #include "common.cuh"
 
 namespace adop {
 
 // ------------------------------------------------------------------------------------------------------
-// K4: preparation pass over the pyramid pixels of one view.
+// K4: preparation pass over the pyramid pixels of one view (all-points path only; returns at once behind a usable list).
 //  * writes the interleaved record [I_0..I_C-1 | G_0..G_C-1] (I = the forward image before the environment-map
 //    composite: the background colour where nothing was blended, PointRenderer.cu:1523);
 //  * sums the gradient of the background colour over uncovered pixels (CombineAndFillBackward, :851-900);
@@ -450,9 +451,9 @@ __global__ void __launch_bounds__(kBlock) k_splat_backward_all(PointStreams pts,
 //                   ONE work item for the chain kernel: the point's image-space ghost gradient summed over its layers,
 //                   each scaled by 0.5^layer (the projection chain is linear in that gradient, and a layer's crop
 //                   transform is the full-resolution one times 0.5^layer, PointRenderer.cu:616).
-//   k_point_chain   per work item: chains the summed image-space gradient through the projection to the point, pose and
-//                   intrinsics gradients (block-reduced).
-//   k_hole_gradients  background-colour gradient and environment-map gradient of the uncovered pixels.
+//   k_chain_and_holes  one launch whose blocks split 3 : 1 between two independent parts: per work item, the summed
+//                   image-space gradient chained through the projection to the point, pose and intrinsics gradients
+//                   (block-reduced); and the background-colour and environment-map gradient of the uncovered pixels.
 // Nothing here waits on another block. These kernels are bound by memory latency, not by bandwidth or arithmetic: each
 // keeps several independent loads per thread in flight and as many blocks resident as registers and shared memory allow.
 constexpr int kTileThreads = 256;
