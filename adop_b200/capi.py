@@ -39,7 +39,9 @@ class AdopScene(C.Structure):
                 ("env_h", C.c_int32), ("env_w", C.c_int32),
                 ("position", C.c_void_p), ("normal", C.c_void_p), ("index", C.c_void_p), ("texture", C.c_void_p),
                 ("background", C.c_void_p), ("poses", C.c_void_p), ("intrinsics", C.c_void_p),
-                ("env_map", C.c_void_p), ("texture_interleaved", C.c_void_p)]
+                ("env_map", C.c_void_p), ("texture_interleaved", C.c_void_p),
+                ("outlier_position", C.c_void_p), ("outlier_normal", C.c_void_p), ("outlier_index", C.c_void_p),
+                ("num_outliers", C.c_int32), ("reserved_", C.c_int32)]
 
 
 class AdopLayerBuffers(C.Structure):

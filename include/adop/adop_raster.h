@@ -96,6 +96,16 @@ typedef struct adop_scene
     /* optional [T,C] copy of `texture` (adop_texture_interleave). The kernels then fetch a point's descriptor as one
      * contiguous vector instead of C values from C planes. The caller refreshes it whenever `texture` changes. */
     const float* texture_interleaved;
+    /* optional second cloud, rendered into the same depth and colour buffers before they are resolved (the reference's
+     * outlier cloud, PointRenderer.cu:1402-1441: random points around the scene whose descriptors the training drives
+     * towards the background). Same tensor layouts as the main cloud; its descriptor columns index the same `texture`.
+     * As in the reference it takes part in the forward pass only - the backward pass walks the main cloud - and a point
+     * i of it shares the drop-out decision of main point i, so num_outliers <= num_points. NULL / 0 = none. */
+    const float* outlier_position;   /* [M,4] */
+    const int32_t* outlier_normal;   /* [M], may be NULL */
+    const int32_t* outlier_index;    /* [M], NULL = identity */
+    int32_t num_outliers;
+    int32_t reserved_;
 } adop_scene;
 
 /* Per pyramid layer l (size w>>l, h>>l by integer halving, PointRenderer.cu:1015-1016), batch-major:
