@@ -87,6 +87,13 @@ adop_status validate_common(const adop_scene* s, const adop_view* views, int B, 
     if (s->num_texels <= 0 || s->num_images <= 0 || s->num_cameras <= 0) return ADOP_ERR_INVALID_ARGUMENT;
     if (!s->position || !s->texture || !s->background || !s->poses || !s->intrinsics) return ADOP_ERR_INVALID_ARGUMENT;
     if (!s->index && s->num_texels < s->num_points) return ADOP_ERR_INVALID_ARGUMENT;
+    if (s->outlier_position)
+    {
+        // the second cloud shares the main cloud's drop-out decisions (point i with point i), PointRenderer.cu:1437-1440
+        if (s->num_outliers < 0 || s->num_outliers > s->num_points) return ADOP_ERR_INVALID_ARGUMENT;
+        if (reinterpret_cast<uintptr_t>(s->outlier_position) & 15) return ADOP_ERR_INVALID_ARGUMENT;
+        if (!s->outlier_index && s->num_texels < s->num_outliers) return ADOP_ERR_INVALID_ARGUMENT;
+    }
     if (rp->composite_environment_map && s->env_map && (s->env_h <= 0 || s->env_w <= 0)) return ADOP_ERR_INVALID_ARGUMENT;
     const int w = views[0].w, h = views[0].h;
     if (w <= 0 || h <= 0) return ADOP_ERR_INVALID_ARGUMENT;

@@ -554,6 +554,7 @@ struct ForwardPlan
     LargeRegion lr;
     size_t cand_view_stride;  // records per candidate stream
     TileTable tiles;
+    PointStreams outliers;  // the optional second cloud (n = 0: none): forward only, never listed
 };
 
 template <int L, int C, bool PLAIN>
@@ -601,6 +602,24 @@ static adop_status launch_view_forward_impl(const PointStreams& pts, const adop_
             default: ADOP_PREPASS(4) break;
         }
 #undef ADOP_PREPASS
+        // the second cloud goes into the same depth planes (PointRenderer.cu:1421-1424); never through candidate streams
+        if (plan.outliers.n > 0)
+        {
+            const PointStreams& op = plan.outliers;
+            const int oneed = (op.n + kBlock - 1) / kBlock;
+            const int og = oneed < g_depth ? oneed : g_depth;
+            CandOut none;
+            none.rec = nullptr; none.count = nullptr; none.view_stride = 0; none.seg_cap = 0;
+#define ADOP_PREPASS_OUT(VV) ADOP_LAUNCH("k_depth_prepass", st, (k_depth_prepass<L, PLAIN, VV, false><<<og, kBlock, 0, st>>>(op, make_chunk_schedule(op.n, og), cam, kp, lt, none)))
+            switch (depth_views)
+            {
+                case 1: ADOP_PREPASS_OUT(1); break;
+                case 2: ADOP_PREPASS_OUT(2); break;
+                case 3: ADOP_PREPASS_OUT(3); break;
+                default: ADOP_PREPASS_OUT(4); break;
+            }
+#undef ADOP_PREPASS_OUT
+        }
     }
     VisibleList vl = make_visible_list(plan.list_base, pts.n, plan.w, plan.h, view);
     if (vl.header) ADOP_CUDA_TRY(cudaMemsetAsync(vl.header, 0, sizeof(int) * visible_list_clear_ints(plan.w, plan.h, pts.n), st));
@@ -619,6 +638,19 @@ static adop_status launch_view_forward_impl(const PointStreams& pts, const adop_
     {
         if (emit) ADOP_BLEND(false, true); else ADOP_BLEND(false, false);
     }
+    // the second cloud is blended into the same accumulator (PointRenderer.cu:1437-1440), from its positions, without a list
+    if (plan.outliers.n > 0)
+    {
+        const PointStreams& op = plan.outliers;
+        const int oneed = (op.n + kBlock - 1) / kBlock;
+        const int og = oneed < g_blend ? oneed : g_blend;
+        CandIn no_cand;
+        no_cand.rec = nullptr; no_cand.count = nullptr; no_cand.seg_cap = 0;
+        VisibleList no_list = make_visible_list(nullptr, op.n, plan.w, plan.h, view);
+        ADOP_LAUNCH("k_blend", st, (k_blend<L, C, PLAIN, false, false><<<og, kBlock, 0, st>>>(
+                                       op, make_chunk_schedule(op.n, og), no_cand, s->texture, s->texture_interleaved, s->num_texels, cam, kp, lt,
+                                       plan.tiles, plan.accum, no_list)));
+    }
 #undef ADOP_BLEND
     unsigned total = lt.rec_off[kMaxLayers];
     int grid_px = (int)((total + kBlock - 1) / kBlock);
@@ -634,7 +666,7 @@ static adop_status launch_view_forward(const PointStreams& pts, const adop_scene
                                        const LayerTable& lt, const ForwardPlan& plan, cudaStream_t st, int view, int depth_views)
 {
     // the common case - no normal test (or no normals) and no radius drop-out - gets kernels without that code
-    const bool plain = !(kp.check_normal && pts.normal) && !kp.drop_out_points_by_radius;
+    const bool plain = !(kp.check_normal && (pts.normal || plan.outliers.normal)) && !kp.drop_out_points_by_radius;
     return plain ? launch_view_forward_impl<L, C, true>(pts, s, cam, kp, lt, plan, st, view, depth_views)
                  : launch_view_forward_impl<L, C, false>(pts, s, cam, kp, lt, plan, st, view, depth_views);
 }
@@ -805,6 +837,10 @@ extern "C" adop_status adop_raster_forward(const adop_scene* s, const adop_view*
     plan.w = w0; plan.h = h0;
     plan.num_views = B;
     plan.tiles = make_tile_table(w0, h0, N);
+    plan.outliers.position = reinterpret_cast<const float4*>(s->outlier_position);
+    plan.outliers.normal = s->outlier_normal;
+    plan.outliers.index = s->outlier_index;
+    plan.outliers.n = s->outlier_position ? s->num_outliers : 0;
     plan.large = nullptr;
     plan.lr = large_region_layout(N, B);
     plan.cand_view_stride = entry_capacity(N);

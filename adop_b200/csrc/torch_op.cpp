@@ -31,6 +31,8 @@ struct RenderInfo : torch::CustomClassHolder
     // scene tensors that take no gradient (PointRenderer.cu:1146-1155, RenderModule.cpp:106-110)
     Tensor poses;    // [I,8] f64, world -> camera
     c10::optional<Tensor> normal, index, env_map;
+    // optional second cloud of the forward pass (scene.outlier_point_cloud_cuda, PointRenderer.cu:1402-1441)
+    c10::optional<Tensor> outlier_position, outlier_normal, outlier_index;
     // the batch: ReducedImageInfo per image (SceneData.h:37-47)
     std::vector<adop_view> images;
     adop_render_params params;
@@ -45,6 +47,15 @@ struct RenderInfo : torch::CustomClassHolder
         TORCH_CHECK(poses_.dim() == 2 && poses_.size(1) == 8 && poses_.scalar_type() == torch::kFloat64, "poses must be [I,8] float64");
         poses = poses_.contiguous();
         normal = normal_; index = index_; env_map = env_map_;
+    }
+    // render_outliers = true: positions [M,4] f32, packed normals [M] i32 or none, descriptor columns [M] i32 or none
+    void set_outlier_cloud(c10::optional<Tensor> position_, c10::optional<Tensor> normal_, c10::optional<Tensor> index_)
+    {
+        if (position_)
+            TORCH_CHECK(position_->is_cuda() && position_->is_contiguous() && position_->dim() == 2 && position_->size(1) == 4 &&
+                            position_->scalar_type() == torch::kFloat32,
+                        "outlier positions must be a contiguous CUDA [M,4] float32 tensor");
+        outlier_position = position_; outlier_normal = normal_; outlier_index = index_;
     }
     // views: [B,5] int64 on the CPU (w, h, image_index, camera_index, camera_model); crops: [B,5] float32 on the CPU
     void set_views(Tensor views, Tensor crops)
@@ -106,6 +117,13 @@ static adop_scene make_scene(RenderInfo& info, const Tensor& texture, const Tens
     sc.background = background.data_ptr<float>();
     sc.poses = info.poses.data_ptr<double>();
     sc.intrinsics = intrinsics.data_ptr<float>();
+    if (info.outlier_position)
+    {
+        sc.outlier_position = info.outlier_position->data_ptr<float>();
+        sc.num_outliers = (int32_t)info.outlier_position->size(0);
+        sc.outlier_normal = info.outlier_normal ? info.outlier_normal->data_ptr<int32_t>() : nullptr;
+        sc.outlier_index = info.outlier_index ? info.outlier_index->data_ptr<int32_t>() : nullptr;
+    }
     if (info.env_map)
     {
         Tensor e = *info.env_map;
@@ -447,6 +465,7 @@ TORCH_LIBRARY(adop, m)
     m.class_<adop::RenderInfo>("RenderInfo")
         .def(torch::init<>())
         .def("set_scene", &adop::RenderInfo::set_scene)
+        .def("set_outlier_cloud", &adop::RenderInfo::set_outlier_cloud)
         .def("set_views", &adop::RenderInfo::set_views)
         .def("set_param", &adop::RenderInfo::set_param)
         .def("set_num_layers", &adop::RenderInfo::set_num_layers);

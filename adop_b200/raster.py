@@ -18,23 +18,30 @@ class Scene:
 
     position [N,4] f32, normal [N] i32 or None, index [N] i32 or None (identity), texture [C,T] f32,
     background [C] f32, poses [I,8] f64, intrinsics [K,cols] f32, env_map [C,eh,ew] f32 or None.
+    Optional second cloud (the reference's outlier cloud, PointRenderer.cu:1402-1441; forward pass only):
+    outlier_position [M,4] f32, outlier_normal [M] i32 or None, outlier_index [M] i32 or None, M <= N.
     """
 
-    def __init__(self, position, texture, background, poses, intrinsics, normal=None, index=None, env_map=None):
+    def __init__(self, position, texture, background, poses, intrinsics, normal=None, index=None, env_map=None,
+                 outlier_position=None, outlier_normal=None, outlier_index=None):
         self.position, self.texture, self.background = position, texture, background
         self.poses, self.intrinsics = poses, intrinsics
         self.normal, self.index, self.env_map = normal, index, env_map
+        self.outlier_position, self.outlier_normal, self.outlier_index = outlier_position, outlier_normal, outlier_index
 
     def tensors(self):
         return dict(position=self.position, normal=self.normal, index=self.index, texture=self.texture,
-                    background=self.background, poses=self.poses, intrinsics=self.intrinsics, env_map=self.env_map)
+                    background=self.background, poses=self.poses, intrinsics=self.intrinsics, env_map=self.env_map,
+                    outlier_position=self.outlier_position, outlier_normal=self.outlier_normal,
+                    outlier_index=self.outlier_index)
 
     def to(self, device):
         return Scene(**{k: (v.to(device) if v is not None else None) for k, v in self.tensors().items()})
 
 
 _DTYPES = dict(position="float32", normal="int32", index="int32", texture="float32", background="float32",
-               poses="float64", intrinsics="float32", env_map="float32")
+               poses="float64", intrinsics="float32", env_map="float32", outlier_position="float32",
+               outlier_normal="int32", outlier_index="int32")
 
 
 def fill_scene_struct(tensors, ptr):
@@ -66,9 +73,15 @@ def fill_scene_struct(tensors, ptr):
         if env.shape[0] != s.channels:
             raise ValueError("env_map must be [C,eh,ew]")
         s.env_h, s.env_w = int(env.shape[1]), int(env.shape[2])
-    for name in ("position", "normal", "index", "texture", "background", "poses", "intrinsics", "env_map"):
+    for name in ("position", "normal", "index", "texture", "background", "poses", "intrinsics", "env_map",
+                 "outlier_position", "outlier_normal", "outlier_index"):
         a = tensors.get(name)
         setattr(s, name, ptr(a) if a is not None else None)
+    out = tensors.get("outlier_position")
+    if out is not None:
+        if out.ndim != 2 or out.shape[1] != 4:
+            raise ValueError("outlier_position must be [M,4]")
+        s.num_outliers = int(out.shape[0])
     return s
 
 

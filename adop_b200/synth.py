@@ -204,6 +204,32 @@ def make_config(name, n_points=None, n_views=None, size=None, seed=0, channels=N
     return dict(arrays=arrays, views=views, params=params, num_layers=L, meta=meta)
 
 
+def pack_normals(n):
+    """[M,3] unit vectors -> the library's 10-bit packing x | y<<10 | z<<20 (components mapped from [-1,1] to 0..1023)."""
+    q = np.round((np.asarray(n, np.float64) + 1) * 0.5 * 1023).astype(np.uint32)
+    return (q[:, 0] | (q[:, 1] << 10) | (q[:, 2] << 20)).astype(np.int32)
+
+
+def outlier_cloud(arrays, count, seed=0, distance=0.1, with_normals=True):
+    """The reference's outlier cloud for a scene (SceneData.cpp:419-439, NeuralScene.cpp:248-252): `count` points (at most
+    as many as the main cloud has) on the sphere around the cloud's bounding box, radius grown by `distance`, normals
+    towards the centre, descriptor columns drawn uniformly from the scene's texture. Returns the three outlier_* arrays."""
+    rng = np.random.default_rng(seed)
+    xyz = arrays["position"][:, :3]
+    count = min(int(count), len(xyz))
+    lo, hi = xyz.min(axis=0).astype(np.float64), xyz.max(axis=0).astype(np.float64)
+    centre = 0.5 * (lo + hi)
+    radius = 0.5 * np.linalg.norm(hi - lo) * (1.0 + distance)
+    d = rng.normal(size=(count, 3))
+    d /= np.linalg.norm(d, axis=1, keepdims=True)
+    pos = np.zeros((count, 4), np.float32)
+    pos[:, :3] = (centre + radius * d).astype(np.float32)
+    T = arrays["texture"].shape[1]
+    out = dict(outlier_position=pos, outlier_normal=pack_normals(-d) if with_normals else None,
+               outlier_index=rng.integers(0, max(T - 1, 1), count).astype(np.int32))
+    return out
+
+
 def upstream_gradients(meta, seed=1, batch=None):
     """N(0,1) upstream gradients, one [B,C,h_l,w_l] float32 array per layer."""
     rng = np.random.default_rng(seed)

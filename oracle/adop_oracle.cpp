@@ -85,6 +85,21 @@ inline PointFetch fetch_point(const adop_scene* s, int i)
 }
 inline int fetch_index(const adop_scene* s, int i) { return s->index ? s->index[i] : i; }
 
+// The main cloud, or the optional second one (the outlier cloud of PointRenderer.cu:1402-1441), as a scene of its own
+// that shares every other tensor: the forward loops below run over both.
+inline adop_scene cloud_of(const adop_scene* s, int which)
+{
+    adop_scene c = *s;
+    if (which == 1)
+    {
+        c.position = s->outlier_position;
+        c.normal = s->outlier_normal;
+        c.index = s->outlier_index;
+        c.num_points = s->outlier_position ? s->num_outliers : 0;
+    }
+    return c;
+}
+
 inline bool is_dropped(const adop_render_params* rp, const uint8_t* mask, int N, int b, int i)
 {
     if (mask) return mask[(size_t)b * N + i] == 1;
@@ -174,7 +189,13 @@ int adop_oracle_forward(const adop_scene* s, const adop_view* views, int B, cons
     for (int b = 0; b < B; ++b)
     {
         ViewCam cam = view_cam(s, &views[b]);
-        // DepthPrepassMulti, PointRenderer.cu:203-301 (drop-out is ignored here: dropped points still occlude)
+        // DepthPrepassMulti, PointRenderer.cu:203-301 (drop-out is ignored here: dropped points still occlude);
+        // main cloud, then the outlier cloud (:1417-1425)
+        for (int which = 0; which < 2; ++which)
+        {
+        const adop_scene cloud = cloud_of(s, which);
+        const adop_scene* s = &cloud;
+        const int N = cloud.num_points;
 #pragma omp parallel for schedule(static) if (par)
         for (int i = 0; i < N; ++i)
         {
@@ -192,11 +213,19 @@ int adop_oracle_forward(const adop_scene* s, const adop_view* views, int B, cons
                 else if (q.z < *d) *d = q.z;
             }
         }
-        // RenderForwardMulti, PointRenderer.cu:303-393
+        }
+        // RenderForwardMulti, PointRenderer.cu:303-393; main cloud, then the outlier cloud (:1433-1441), whose point i
+        // takes the drop-out decision of main point i (both index the same [B,N] tensor)
+        for (int which = 0; which < 2; ++which)
+        {
+        const adop_scene cloud = cloud_of(s, which);
+        const int N_main = N;
+        const adop_scene* s = &cloud;
+        const int N = cloud.num_points;
 #pragma omp parallel for schedule(static) if (par)
         for (int i = 0; i < N; ++i)
         {
-            if (is_dropped(rp, io->dropout_mask, N, b, i)) continue;
+            if (is_dropped(rp, io->dropout_mask, N_main, b, i)) continue;
             PointFetch f = fetch_point(s, i);
             RasterPoint q;
             if (!project_for_raster(cam, f.p, f.r, f.n, f.has_normal, rp->check_normal != 0, rp->dist_cutoff, &q)) continue;
@@ -220,6 +249,7 @@ int adop_oracle_forward(const adop_scene* s, const adop_view* views, int B, cons
                 float* wdst = io->layers[l].weight + (size_t)b * plane + pix;
                 if (par) atomic_add_float(wdst, 1.f); else *wdst += 1.f;
             }
+        }
         }
         // CombineAndFill + CreateMask (+ environment-map composite), PointRenderer.cu:726-754, 828-847,
         // EnvironmentMap.cu:62-156, RenderModule.cpp:106-127

@@ -578,3 +578,42 @@ def test_five_vector_projection_has_the_same_bits_as_the_general_one(oracle):
     assert oracle.project_hot(full, cfg["views"][0], cfg["params"]) is None
     c3 = synth.make_config("c3", n_points=1000, size=(64, 36))
     assert oracle.project_hot(c3["arrays"], c3["views"][0], c3["params"]) is None
+
+
+def test_outlier_cloud_takes_part_in_the_forward_pass_only(oracle):
+    """The second cloud of a scene (PointRenderer.cu:1402-1441) goes into the same depth, weight and colour buffers: the
+    depth of a pixel is the minimum over both clouds, the weights count both, and the result equals that of ONE cloud
+    that holds the points of both. The backward pass walks the main cloud only (:1588-1600): descriptor columns that only
+    outliers use get no gradient, and the main points' gradients are those of the merged render restricted to them."""
+    cfg = synth.make_config("c1", n_points=30_000, size=(96, 96))
+    a, views, params, L = cfg["arrays"], cfg["views"], cfg["params"], cfg["num_layers"]
+    n = len(a["position"])
+    # extra descriptor columns that only the outliers use
+    rng = np.random.default_rng(2)
+    a["texture"] = np.ascontiguousarray(np.concatenate([a["texture"], rng.uniform(0, 1, (4, 500)).astype(np.float32)], axis=1))
+    out = synth.outlier_cloud(a, 4000, seed=1, with_normals=False)
+    # pull the sphere in so that a good share of the outliers lies between the camera and the cloud
+    out["outlier_position"][:, :3] = (out["outlier_position"][:, :3] * 0.25 + np.array([0, 0, 2.5], np.float32)).astype(np.float32)
+    out["outlier_index"] = (n + rng.integers(0, 500, 4000)).astype(np.int32)
+    both = dict(a, **out)
+    plain = oracle.forward(a, views, params, L)
+    ref = oracle.forward(both, views, params, L)
+    merged = dict(a)
+    merged["position"] = np.ascontiguousarray(np.concatenate([a["position"], out["outlier_position"]]))
+    merged["index"] = np.concatenate([np.arange(n, dtype=np.int32), out["outlier_index"]])
+    one = oracle.forward(merged, views, params, L)
+    changed = 0
+    for l in range(L):
+        assert np.array_equal(ref["depths"][l], one["depths"][l]) and np.array_equal(ref["weights"][l], one["weights"][l])
+        assert np.allclose(ref["colors"][l], one["colors"][l], rtol=1e-6, atol=1e-7)
+        assert (ref["depths"][l] <= plain["depths"][l]).all()
+        changed += int((ref["depths"][l] < plain["depths"][l]).sum())
+    assert changed > 100
+    grads = synth.upstream_gradients(cfg["meta"], batch=len(views))
+    gb = oracle.backward(both, views, params, L, ref, grads)
+    gm = oracle.backward(merged, views, params, L, one, grads, normalize=False)
+    assert not gb["texture"][:, n:].any()
+    assert gm["texture"][:, n:].any()
+    g1 = oracle.backward(both, views, params, L, ref, grads, normalize=False)
+    assert np.allclose(g1["texture"][:, :n], gm["texture"][:, :n], rtol=1e-5, atol=1e-7)
+    assert np.allclose(g1["points"], gm["points"][:n], rtol=1e-5, atol=1e-7)

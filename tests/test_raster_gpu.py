@@ -219,6 +219,44 @@ def test_normals_radius_dropout_and_index(oracle, cuda_lib):
     assert 0 < ref["weights"][0].sum() < n
 
 
+@pytest.mark.parametrize("normals,listed", [(False, True), (True, True), (False, False)])
+def test_outlier_cloud(oracle, cuda_lib, normals, listed):
+    """The optional second cloud (the reference's outlier cloud, PointRenderer.cu:1402-1441): rendered into the same depth,
+    weight and colour buffers by the forward pass, ignored by the backward pass. Depth and weights bit-exact against the
+    checker, colours and the main cloud's gradients within tolerance, with and without a visible list; with normals on both
+    clouds the normal test applies to both; a drop-out mask is shared index by index."""
+    cfg = synth.make_config("c2", n_points=300_000, n_views=3, size=(320, 180), seed=6)
+    a, params = cfg["arrays"], cfg["params"]
+    n = len(a["position"])
+    rng = np.random.default_rng(8)
+    # a sphere INSIDE the scene's bounding sphere, so that outliers land in front of and between the surfaces
+    a.update(synth.outlier_cloud(a, 40_000, seed=2, distance=-0.55, with_normals=normals))
+    if normals:
+        nrm = rng.normal(size=(n, 3))
+        a["normal"] = synth.pack_normals(nrm / np.linalg.norm(nrm, axis=1, keepdims=True))
+        params.check_normal = 1
+    mask = (rng.uniform(size=(len(cfg["views"]), n)) < 0.2).astype(np.uint8)
+    plain = oracle.forward({k: v for k, v in a.items() if not k.startswith("outlier")}, cfg["views"], params, 4, dropout_mask=mask)
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg, want_env=True, dropout_mask=mask, record_visible=listed)
+    assert (ref["weights"][0] != plain["weights"][0]).sum() > 1000 and (ref["depths"][0] < plain["depths"][0]).sum() > 1000
+    check_forward(ref, fwd, 4)
+    check_backward(ref_b, bwd)
+
+
+def test_outlier_cloud_argument_checks(cuda_lib):
+    cfg = synth.make_config("c1", n_points=1000, size=(64, 64))
+    a = cfg["arrays"]
+    a.update(synth.outlier_cloud(a, 500, seed=1))
+    scene = to_scene(a)
+    r = PointRasterizer("cuda:0")
+    r.forward(scene, cfg["views"], cfg["params"], 4)
+    # more outliers than main points: they would index the drop-out decisions out of range
+    scene.outlier_position = torch.zeros((1001, 4), device="cuda:0")
+    scene.outlier_index, scene.outlier_normal = None, None
+    with pytest.raises(capi.AdopError, match="invalid argument"):
+        r.forward(scene, cfg["views"], cfg["params"], 4)
+
+
 def test_unusable_list_falls_back_to_all_points(oracle, cuda_lib):
     """A list whose header says that it is not usable: the backward pass finds the mark on the device (no host round
     trip), its tile kernels return at once and the all-points kernels behind them do the work, with the same result."""

@@ -21,6 +21,8 @@ def _info(cfg, dev):
     info = torch.classes.adop.RenderInfo()
     t = lambda v: torch.from_numpy(v).to(dev) if v is not None else None
     info.set_scene(t(a["poses"]), t(a["normal"]), t(a["index"]), t(a["env_map"]))
+    if a.get("outlier_position") is not None:
+        info.set_outlier_cloud(t(a["outlier_position"]), t(a.get("outlier_normal")), t(a.get("outlier_index")))
     v = cfg["views"]
     views = torch.tensor([[x["w"], x["h"], x["image_index"], x["camera_index"], x.get("camera_model", 0)] for x in v])
     crops = torch.tensor([list(x.get("crop", (1.0, 1.0, 0.0, 0.0, 0.0))) for x in v], dtype=torch.float32)
@@ -199,3 +201,31 @@ def test_tonemap_operator_through_autograd(cuda_lib, op):
     out2 = op.tonemap(x, fi, None, p["exposure"].detach(), None, None, None, None, W, H, 0.0)
     want2 = torch.clamp(x * (1.0 / torch.exp2(p["exposure"].detach().reshape(n)[fi.long()])).view(-1, 1, 1, 1), 0, 1)
     assert torch.allclose(out2, want2, rtol=1e-5, atol=1e-6)
+
+
+def test_outlier_cloud_through_the_operator(oracle, cuda_lib, op):
+    """RenderInfo.set_outlier_cloud: the second cloud of the forward pass (the reference's render_outliers,
+    PointRenderer.cu:1402-1441). Images and gradients against the checker; the outliers occlude and count, and get no
+    gradient of their own."""
+    cfg = synth.make_config("c2", n_points=200_000, n_views=2, size=(320, 180))
+    a, L = cfg["arrays"], cfg["num_layers"]
+    a.update(synth.outlier_cloud(a, 20_000, seed=3, distance=-0.5))
+    dev = torch.device("cuda:0")
+    grads_up = synth.upstream_gradients(cfg["meta"], batch=len(cfg["views"]))
+    ref = oracle.forward(a, cfg["views"], cfg["params"], L)
+    plain = oracle.forward({k: v for k, v in a.items() if not k.startswith("outlier")}, cfg["views"], cfg["params"], L)
+    assert (ref["weights"][0] != plain["weights"][0]).sum() > 500
+    ref_b = oracle.backward(a, cfg["views"], cfg["params"], L, ref, grads_up)
+    texture = torch.from_numpy(a["texture"]).to(dev).requires_grad_(True)
+    background = torch.from_numpy(a["background"]).to(dev).requires_grad_(True)
+    points = torch.from_numpy(a["position"]).to(dev).requires_grad_(True)
+    tangents = torch.zeros((a["poses"].shape[0], 6), dtype=torch.float64, device=dev, requires_grad=True)
+    intrinsics = torch.from_numpy(a["intrinsics"]).to(dev).requires_grad_(True)
+    out = op.blend_point_cloud(texture, background, points, tangents, intrinsics, _info(cfg, dev))
+    for l in range(L):
+        _close(out[l], ref["colors"][l], f"colour {l}")
+    sum((o * torch.from_numpy(g).to(dev)).sum() for o, g in zip(out[:L], grads_up)).backward()
+    _close(texture.grad, ref_b["texture"], "grad texture")
+    _close(points.grad, ref_b["points"], "grad points")
+    _close(tangents.grad, ref_b["pose"], "grad pose")
+    _close(intrinsics.grad, ref_b["intrinsics"], "grad intrinsics")
