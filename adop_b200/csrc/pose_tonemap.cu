@@ -136,48 +136,85 @@ struct ToneGradPtrs
 };
 
 // The response-curve gradient is a histogram-like scatter: two bins per pixel and channel. Shared-memory atomicAdd on
-// float is a compare-and-swap loop and cost more than the rest of the kernel together (185 us of 320 us per 4K image);
-// the integer one is a single instruction (22 us). So each chunk of 256 x VEC pixels is summed in block-scaled fixed point:
-//   1. the block finds M = max |upstream gradient| of the chunk and takes scale = 2^(18 - exponent(M)), an exact power
-//      of two, so that every term |g * weight * scale| < 2^19 and a bin can take all 2 x 256 x VEC terms of a chunk in 32 bits;
-//   2. terms are rounded to nearest and added with integer atomics into one of two integer histograms (ping-pong);
-//   3. after the chunk every thread converts the bins it owns back (exactly: a power-of-two factor) and adds them to the
-//      block's float histogram, which goes to global memory once at the end.
-// A term is off by at most 2^-19 of the chunk's largest gradient, unbiased; chunks whose M is not finite or is below
-// 2^-100 take the float atomics instead, so NaN / Inf gradients still show up in the result.
+// float is a compare-and-swap loop and cost more than the rest of the kernel together; the integer one is a single
+// instruction. So the terms are summed in scaled fixed point, and every WARP keeps a histogram pair of its own, so that no
+// step of the pixel loop needs a block-wide barrier:
+//   1. a warp takes 32 x VEC consecutive pixels at a time, finds M = max |upstream gradient| among them (one
+//      warp-wide reduction) and works with scale = 2^(18 - e), e = the exponent of the largest M since its last flush:
+//      every term |g * weight * scale| < 2^19;
+//   2. terms are rounded to nearest and added with integer atomics to the warp's integer histogram;
+//   3. a flush converts the warp's integer bins back (exactly: a power-of-two factor) into the warp's float histogram. It
+//      happens when a larger exponent turns up, and after kFlushEvery rounds (a bin takes at most 32 x VEC terms per round,
+//      so 2^19 x 128 x 16 < 2^31 never overflows);
+//   4. at the end the block adds its warps' float histograms up and sends one atomic per touched bin to global memory.
+// A term is off by at most 2^-19 of the largest gradient among the at most kFlushEvery x 32 x VEC neighbouring pixels
+// that share a scale, unbiased; rounds whose M is not finite or is below 2^-100 take float atomics on the warp's float
+// histogram instead, so NaN / Inf gradients still show up in the result.
+constexpr int kFlushEvery = 16;
 template <int VEC>
 __global__ void __launch_bounds__(256, 3) k_tonemap_backward(ToneArgs a, const float* __restrict__ x, const float* __restrict__ grad_out,
                                                            ToneGradPtrs g)
 {
-    extern __shared__ float smem[];  // lut [3,K], float histogram [3,K], two integer histograms [3,K]
-    const int K3 = 3 * a.K;
+    extern __shared__ float smem[];  // lut [3,K], slopes [3,K], per warp: float histogram [3,K], integer histogram [3,K]
+    const int K = a.K, K3 = 3 * a.K;
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* s_lut = smem;
-    float* s_acc = smem + K3;
-    int* s_int = reinterpret_cast<int*>(smem + 2 * K3);
+    float* s_slope = smem + K3;
+    float* s_acc_all = smem + 2 * K3;
+    float* s_acc = s_acc_all + warp * K3;
+    int* s_int = reinterpret_cast<int*>(s_acc_all + warps * K3) + warp * K3;
     __shared__ float s_small[9];  // exposure, wb[3], vignette[5]
-    __shared__ float s_max[2][8];
     const bool want_resp = g.grad_response && a.response;
+    const float Km1 = (float)(K - 1);
     for (int k = threadIdx.x; k < K3; k += blockDim.x) s_lut[k] = a.response[k];
-    if (want_resp)
-        for (int k = threadIdx.x; k < K3; k += blockDim.x) { s_acc[k] = 0.f; s_int[k] = 0; s_int[K3 + k] = 0; }
     if (threadIdx.x < 9) s_small[threadIdx.x] = 0.f;
+    __syncthreads();
+    // slope of the curve in bin i (0 in the last one, where both taps are the same entry)
+    for (int k = threadIdx.x; k < K3; k += blockDim.x)
+    {
+        const int i = k % K;
+        s_slope[k] = i + 1 < K ? (s_lut[k + 1] - s_lut[k]) * Km1 : 0.f;
+    }
+    if (want_resp)
+        for (int k = lane; k < K3; k += 32) { s_acc[k] = 0.f; s_int[k] = 0; }
     __syncthreads();
     const int b = blockIdx.y;
     const size_t plane = (size_t)a.H * a.W;
     const int fi = a.frame_index ? a.frame_index[b] : 0;
     const float ef = a.exposure ? 1.0f / exp2f(a.exposure[fi]) : 1.0f;
-    const float ln2 = 0.69314718056f;
-    float gE = 0.f, gWB[3] = {0.f, 0.f, 0.f}, gV[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
-    // a block walks over many pixel chunks of its image, so the parameter gradients leave it once, not once per chunk;
-    // every thread of the block makes the same number of rounds (the loop holds block-wide barriers)
-    const size_t per_chunk = (size_t)blockDim.x * VEC;
-    const size_t chunks = (plane + per_chunk - 1) / per_chunk;
-    int parity = 0;
-    for (size_t chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x, parity ^= 1)
+    float wb[3], wbef[3];
+#pragma unroll
+    for (int c = 0; c < 3; ++c) { wb[c] = a.white_balance ? a.white_balance[(size_t)fi * 3 + c] : 1.0f; wbef[c] = wb[c] * ef; }
+    float vg[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+    if (a.vignette)
+#pragma unroll
+        for (int k = 0; k < 5; ++k) vg[k] = a.vignette[k];
+    const float step_u = 2.0f / (float)(a.W - 1), step_v = 2.0f / (float)(a.H - 1);
+    const float* xb = x + (size_t)b * 3 * plane;
+    const float* gob = grad_out + (size_t)b * 3 * plane;
+    float* gxb = g.grad_x ? g.grad_x + (size_t)b * 3 * plane : nullptr;
+    float gPre = 0.f, gWB[3] = {0.f, 0.f, 0.f}, gV[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+    // a warp walks over many rounds of its image, so the parameter gradients leave it once; the trip count is the same
+    // for all lanes of a warp (the loop holds warp-wide votes)
+    const size_t per_round = (size_t)32 * VEC;
+    const size_t rounds = (plane + per_round - 1) / per_round;
+    int e_cur = 0, since = 0;  // exponent of the warp's current scale, rounds since its last flush (warp-uniform)
+    auto flush = [&]() {
+        __syncwarp();
+        const float inv = __int_as_float((127 - 18 + e_cur) << 23);  // 1 / scale, exact
+        for (int k = lane; k < K3; k += 32)
+        {
+            const int q = s_int[k];
+            if (q != 0) { s_acc[k] += (float)q * inv; s_int[k] = 0; }
+        }
+        __syncwarp();
+        since = 0;
+    };
+    for (size_t round = (size_t)blockIdx.x * warps + warp; round < rounds; round += (size_t)gridDim.x * warps)
     {
-        const size_t pix = chunk * per_chunk + (size_t)threadIdx.x * VEC;
+        const size_t pix = round * per_round + (size_t)lane * VEC;
         const bool live = pix < plane;
-        // all six loads of the chunk are requested before anything waits (the block-wide maximum needs a barrier)
+        // all six loads of the round are requested before anything waits
         float go[3][VEC], xall[3][VEC];
 #pragma unroll
         for (int c = 0; c < 3; ++c)
@@ -186,12 +223,42 @@ __global__ void __launch_bounds__(256, 3) k_tonemap_backward(ToneArgs a, const f
             for (int k = 0; k < VEC; ++k) { go[c][k] = 0.f; xall[c][k] = 0.f; }
             if (live)
             {
-                load_vec<VEC>(grad_out + ((size_t)b * 3 + c) * plane + pix, go[c]);
-                load_vec<VEC>(x + ((size_t)b * 3 + c) * plane + pix, xall[c]);
+                load_vec<VEC>(gob + c * plane + pix, go[c]);
+                load_vec<VEC>(xb + c * plane + pix, xall[c]);
             }
         }
-        float scale = 0.f;  // 0: this chunk adds to the float histogram directly
-        int* my_int = s_int + parity * K3;
+        float du[VEC], dv[VEC], r2[VEC], fac[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) { fac[k] = 1.f; du[k] = dv[k] = r2[k] = 0.f; }
+        if (a.vignette && live)
+        {
+            float u0[VEC], v0[VEC];
+            if (a.uv)
+            {
+                load_vec<VEC>(a.uv + ((size_t)b * 2 + 0) * plane + pix, u0);
+                load_vec<VEC>(a.uv + ((size_t)b * 2 + 1) * plane + pix, v0);
+            }
+            else
+            {
+                // 32-bit: the entry point rejects planes of 2^31 pixels or more
+                unsigned yy = (unsigned)pix / (unsigned)a.W, xx = (unsigned)pix - yy * (unsigned)a.W;
+#pragma unroll
+                for (int k = 0; k < VEC; ++k)
+                {
+                    u0[k] = fmaf((float)xx, step_u, -1.0f);
+                    v0[k] = fmaf((float)yy, step_v, -1.0f);
+                    if (++xx == (unsigned)a.W) { xx = 0; ++yy; }
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < VEC; ++k)
+            {
+                du[k] = (u0[k] - vg[3]) * a.aspect; dv[k] = v0[k] - vg[4];
+                r2[k] = fmaf(du[k], du[k], dv[k] * dv[k]);
+                fac[k] = fmaf(fmaf(fmaf(vg[2], r2[k], vg[1]), r2[k], vg[0]), r2[k], 1.0f);
+            }
+        }
+        float scale = 0.f;  // 0: this round adds to the float histogram directly
         if (want_resp)
         {
             float m = 0.f;
@@ -201,49 +268,51 @@ __global__ void __launch_bounds__(256, 3) k_tonemap_backward(ToneArgs a, const f
 #pragma unroll
                 for (int k = 0; k < VEC; ++k) { m = fmaxf(m, fabsf(go[c][k])); odd = odd || !(fabsf(go[c][k]) <= 3.0e38f); }
             if (odd) m = __int_as_float(0x7f800000);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-            if ((threadIdx.x & 31) == 0) s_max[parity][threadIdx.x >> 5] = m;
-            __syncthreads();
-            float M = 0.f;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) M = fmaxf(M, s_max[parity][k]);
+            // non-negative floats order like their bit patterns
+            const float M = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(m)));
             const int e = (int)((__float_as_uint(M) >> 23) & 0xffu) - 127;
-            if (M <= 3.0e38f && e >= -100) scale = __int_as_float((127 + 18 - e) << 23);
+            if (M <= 3.0e38f && e >= -100)
+            {
+                if (since > 0 && (e > e_cur || since >= kFlushEvery)) flush();
+                if (since == 0) e_cur = e;
+                scale = __int_as_float((127 + 18 - e_cur) << 23);
+                ++since;
+            }
         }
         if (live)
         {
-            float du[VEC], dv[VEC], r2[VEC], fac[VEC];
+            float gsum[VEC];  // sum over the channels of (gradient behind the vignette factor) x (value before it)
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) { fac[k] = 1.f; du[k] = dv[k] = r2[k] = 0.f; }
-            if (a.vignette) tone_geometry<VEC>(a, b, pix, plane, du, dv, r2, fac);
+            for (int k = 0; k < VEC; ++k) gsum[k] = 0.f;
 #pragma unroll
             for (int c = 0; c < 3; ++c)
             {
-                const float wb = a.white_balance ? a.white_balance[(size_t)fi * 3 + c] : 1.0f;
                 float gx[VEC];
                 const float* xin = xall[c];
                 // neighbouring pixels mostly fall into the same pair of bins: their two weights are added up in
                 // registers and reach shared memory once per run
-                int run_i0 = -1, run_i1 = 0;
+                int run_i0 = -1;
                 float run_w0 = 0.f, run_w1 = 0.f;
-                auto flush = [&]() {
+                auto put = [&]() {
+                    const int i1 = run_i0 + 1 < K ? run_i0 + 1 : K - 1;
                     if (scale != 0.f)
                     {
-                        atomicAdd(&my_int[c * a.K + run_i0], __float2int_rn(run_w0 * scale));
-                        atomicAdd(&my_int[c * a.K + run_i1], __float2int_rn(run_w1 * scale));
+                        atomicAdd(&s_int[c * K + run_i0], __float2int_rn(run_w0 * scale));
+                        atomicAdd(&s_int[c * K + i1], __float2int_rn(run_w1 * scale));
                     }
                     else
                     {
-                        atomicAdd(&s_acc[c * a.K + run_i0], run_w0);
-                        atomicAdd(&s_acc[c * a.K + run_i1], run_w1);
+                        atomicAdd(&s_acc[c * K + run_i0], run_w0);
+                        atomicAdd(&s_acc[c * K + i1], run_w1);
                     }
                 };
 #pragma unroll
                 for (int k = 0; k < VEC; ++k)
                 {
-                    const float pre = wb * (xin[k] * ef);
+                    const float xe = xin[k] * ef;
+                    const float pre = wb[c] * xe;
                     const float v = fac[k] * pre;
+                    const bool inside = v > 0.f && v < 1.f;
                     float dv_out;
                     if (a.response)
                     {
@@ -253,63 +322,52 @@ __global__ void __launch_bounds__(256, 3) k_tonemap_backward(ToneArgs a, const f
                             if (v < 0.f) dleak = a.leak;
                             if (v > 1.f) { float q = fabsf(v) + 1e-4f; dleak = 0.5f * a.leak / (q * sqrtf(q)); }
                         }
-                        float t = fminf(fmaxf(v, 0.f), 1.f) * (float)(a.K - 1);
-                        int i0 = (int)floorf(t);
-                        int i1 = i0 + 1 < a.K ? i0 + 1 : a.K - 1;
-                        float fr = t - (float)i0;
+                        const float t = fminf(fmaxf(v, 0.f), 1.f) * Km1;
+                        const int i0 = (int)t;  // t >= 0: truncation is the floor
+                        const float fr = t - (float)i0;
                         if (want_resp)
                         {
                             if (i0 != run_i0)
                             {
-                                if (run_i0 >= 0) flush();
-                                run_i0 = i0; run_i1 = i1; run_w0 = 0.f; run_w1 = 0.f;
+                                if (run_i0 >= 0) put();
+                                run_i0 = i0; run_w0 = 0.f; run_w1 = 0.f;
                             }
-                            run_w0 += go[c][k] * (1.0f - fr);
-                            run_w1 += go[c][k] * fr;
+                            run_w0 = fmaf(go[c][k], 1.0f - fr, run_w0);
+                            run_w1 = fmaf(go[c][k], fr, run_w1);
                         }
-                        float inside = (v > 0.f && v < 1.f) ? 1.f : 0.f;
-                        dv_out = inside * (s_lut[c * a.K + i1] - s_lut[c * a.K + i0]) * (float)(a.K - 1) + dleak;
+                        dv_out = (inside ? s_slope[c * K + i0] : 0.f) + dleak;
                     }
                     else
-                        dv_out = (v > 0.f && v < 1.f) ? 1.f : 0.f;
+                        dv_out = inside ? 1.f : 0.f;
                     const float gv = go[c][k] * dv_out;
-                    if (a.vignette)
-                    {
-                        float gfac = gv * pre;
-                        float r4 = r2[k] * r2[k];
-                        gV[0] += gfac * r2[k]; gV[1] += gfac * r4; gV[2] += gfac * (r4 * r2[k]);
-                        float gr2 = gfac * (a.vignette[0] + 2.f * a.vignette[1] * r2[k] + 3.f * a.vignette[2] * r4);
-                        gV[3] += gr2 * 2.f * du[k] * (-a.aspect);
-                        gV[4] += gr2 * 2.f * dv[k] * (-1.f);
-                    }
+                    gsum[k] = fmaf(gv, pre, gsum[k]);
                     const float gpre = gv * fac[k];
-                    gWB[c] += gpre * (xin[k] * ef);
-                    const float gxe = gpre * wb;
-                    gE += gxe * xin[k] * ef * (-ln2);
-                    gx[k] = gxe * ef;
+                    gWB[c] = fmaf(gpre, xe, gWB[c]);
+                    gPre = fmaf(gpre, pre, gPre);
+                    gx[k] = gpre * wbef[c];
                 }
-                if (run_i0 >= 0) flush();
-                if (g.grad_x) store_vec<VEC>(g.grad_x + ((size_t)b * 3 + c) * plane + pix, gx);
+                if (run_i0 >= 0) put();
+                if (gxb) store_vec<VEC>(gxb + c * plane + pix, gx);
             }
-        }
-        if (want_resp)
-        {
-            __syncthreads();  // the chunk's integer terms are all in
-            if (scale != 0.f)
+            if (a.vignette)
             {
-                const float inv = __int_as_float((254 - (int)(__float_as_uint(scale) >> 23)) << 23);  // 1 / scale, exact
-                for (int k = threadIdx.x; k < K3; k += blockDim.x)
+#pragma unroll
+                for (int k = 0; k < VEC; ++k)
                 {
-                    const int q = my_int[k];
-                    if (q != 0) { s_acc[k] += (float)q * inv; my_int[k] = 0; }
+                    const float r4 = r2[k] * r2[k];
+                    gV[0] = fmaf(gsum[k], r2[k], gV[0]); gV[1] = fmaf(gsum[k], r4, gV[1]); gV[2] = fmaf(gsum[k], r4 * r2[k], gV[2]);
+                    const float gr2 = gsum[k] * fmaf(3.f * vg[2], r4, fmaf(2.f * vg[1], r2[k], vg[0]));
+                    gV[3] = fmaf(gr2, -2.f * a.aspect * du[k], gV[3]);
+                    gV[4] = fmaf(gr2, -2.f * dv[k], gV[4]);
                 }
             }
-            // the other integer histogram takes the next chunk; this one is touched again only after that chunk's barrier
         }
     }
-    const bool lane0 = (threadIdx.x & 31) == 0;
+    if (want_resp && since > 0) flush();
+    const bool lane0 = lane == 0;
     float r;
-    r = warp_sum(gE); if (lane0) atomicAdd(&s_small[0], r);
+    // exposure: x * 2^-e, so d/de = -ln 2 times the sum of (gradient at the exposed value) x (exposed value)
+    r = warp_sum(gPre); if (lane0) atomicAdd(&s_small[0], r * -0.69314718056f);
 #pragma unroll
     for (int c = 0; c < 3; ++c) { r = warp_sum(gWB[c]); if (lane0) atomicAdd(&s_small[1 + c], r); }
 #pragma unroll
@@ -323,7 +381,8 @@ __global__ void __launch_bounds__(256, 3) k_tonemap_backward(ToneArgs a, const f
     if (want_resp)
         for (int k = threadIdx.x; k < K3; k += blockDim.x)
         {
-            const float sum = s_acc[k];
+            float sum = 0.f;
+            for (int w = 0; w < warps; ++w) sum += s_acc_all[w * K3 + k];
             if (sum != 0.f) atomicAdd(g.grad_response + k, sum);
         }
 }
@@ -334,7 +393,7 @@ static adop_status make_tone_args(const adop_tonemap_params* p, ToneArgs* a)
     if (p->response && (p->response_bins < 2)) return ADOP_ERR_INVALID_ARGUMENT;
     if (p->response && p->response_bins > kMaxResponseBins) return ADOP_ERR_SIZE_LIMIT;
     if (p->vignette && (p->vignette_image_w <= 0 || p->vignette_image_h <= 0)) return ADOP_ERR_INVALID_ARGUMENT;
-    if (p->batch > 65535) return ADOP_ERR_SIZE_LIMIT;
+    if (p->batch > 65535 || (size_t)p->height * (size_t)p->width >= ((size_t)1 << 31)) return ADOP_ERR_SIZE_LIMIT;
     a->B = p->batch; a->H = p->height; a->W = p->width;
     a->K = p->response ? p->response_bins : 0;
     a->aspect = p->vignette ? (float)p->vignette_image_w / (float)p->vignette_image_h : 1.f;
@@ -400,33 +459,27 @@ extern "C" adop_status adop_tonemap_backward(const adop_tonemap_params* p, const
     gp.grad_x = g->grad_x; gp.grad_exposure = g->grad_exposure; gp.grad_white_balance = g->grad_white_balance;
     gp.grad_vignette = g->grad_vignette; gp.grad_response = g->grad_response;
     size_t plane = (size_t)a.H * a.W;
-    // lut + float histogram + two integer histograms
-    const size_t smem_bytes = sizeof(float) * 3 * a.K * 4;
+    // fewer warps per block when the curve has many bins: every warp keeps two histograms of its own
+    const int threads = a.K <= 256 ? 256 : (a.K <= 512 ? 128 : 64);
+    // lut + slopes, and per warp a float and an integer histogram
+    const size_t smem_bytes = sizeof(float) * 3 * a.K * (2 + 2 * (threads / 32));
     if (smem_bytes > 40 * 1024)
     {
-        // beyond the default 48 KB with the static part: ask for it (1024 bins need 48 KB + 100 bytes)
         ADOP_CUDA_TRY(cudaFuncSetAttribute(k_tonemap_backward<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
         ADOP_CUDA_TRY(cudaFuncSetAttribute(k_tonemap_backward<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
     }
     int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_tonemap_backward<4>, 256, smem_bytes) != cudaSuccess || per_sm < 1)
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_tonemap_backward<4>, threads, smem_bytes) != cudaSuccess || per_sm < 1)
         per_sm = 1;
     // about as many blocks as stay resident at once, shared out over the images
     const size_t per_image = (size_t)((sm_count() * per_sm + a.B - 1) / a.B);
     const bool vec = plane % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(grad_out) |
                                          reinterpret_cast<uintptr_t>(g->grad_x) | reinterpret_cast<uintptr_t>(a.uv)) & 15) == 0;
-    if (vec)
-    {
-        size_t chunks = (plane / 4 + 255) / 256;
-        dim3 grid((unsigned)(chunks < per_image ? chunks : per_image), (unsigned)a.B);
-        ADOP_LAUNCH("k_tonemap_backward", st, (k_tonemap_backward<4><<<grid, 256, smem_bytes, st>>>(a, x, grad_out, gp)));
-    }
-    else
-    {
-        size_t chunks = (plane + 255) / 256;
-        dim3 grid((unsigned)(chunks < per_image ? chunks : per_image), (unsigned)a.B);
-        ADOP_LAUNCH("k_tonemap_backward", st, (k_tonemap_backward<1><<<grid, 256, smem_bytes, st>>>(a, x, grad_out, gp)));
-    }
+    const size_t rounds = vec ? (plane / 4 + 31) / 32 : (plane + 31) / 32;
+    const size_t blocks_needed = (rounds + threads / 32 - 1) / (threads / 32);
+    dim3 grid((unsigned)(blocks_needed < per_image ? blocks_needed : per_image), (unsigned)a.B);
+    if (vec) ADOP_LAUNCH("k_tonemap_backward", st, (k_tonemap_backward<4><<<grid, threads, smem_bytes, st>>>(a, x, grad_out, gp)));
+    else ADOP_LAUNCH("k_tonemap_backward", st, (k_tonemap_backward<1><<<grid, threads, smem_bytes, st>>>(a, x, grad_out, gp)));
     ADOP_CUDA_TRY(cudaGetLastError());
     return ADOP_OK;
 }
