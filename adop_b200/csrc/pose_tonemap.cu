@@ -45,9 +45,12 @@ __device__ __forceinline__ void store_vec(float* __restrict__ p, const float* v)
     if (VEC == 4) __stcs(reinterpret_cast<float4*>(p), make_float4(v[0], v[1], v[2], v[3]));
     else __stcs(p, v[0]);
 }
-// vignette geometry of VEC consecutive pixels starting at pix
+// vignette geometry of VEC consecutive pixels starting at pix; vg = the five vignette parameters (polynomial, centre).
+// Default coordinates: u = 2 x / (W - 1) - 1 as x times a precomputed step (32-bit pixel arithmetic: the entry points
+// reject planes of 2^31 pixels or more).
 template <int VEC>
-__device__ __forceinline__ void tone_geometry(const ToneArgs& a, int b, size_t pix, size_t plane, float* du, float* dv, float* r2, float* fac)
+__device__ __forceinline__ void tone_geometry(const ToneArgs& a, const float* vg, int b, size_t pix, size_t plane, float* du, float* dv, float* r2,
+                                              float* fac)
 {
     float u0[VEC], v0[VEC];
     if (a.uv)
@@ -57,72 +60,86 @@ __device__ __forceinline__ void tone_geometry(const ToneArgs& a, int b, size_t p
     }
     else
     {
-        int yy = (int)(pix / a.W), xx = (int)(pix - (size_t)yy * a.W);
+        const float step_u = 2.0f / (float)(a.W - 1), step_v = 2.0f / (float)(a.H - 1);
+        unsigned yy = (unsigned)pix / (unsigned)a.W, xx = (unsigned)pix - yy * (unsigned)a.W;
 #pragma unroll
         for (int k = 0; k < VEC; ++k)
         {
-            u0[k] = 2.0f * ((float)xx / (float)(a.W - 1)) - 1.0f;
-            v0[k] = 2.0f * ((float)yy / (float)(a.H - 1)) - 1.0f;
-            if (++xx == a.W) { xx = 0; ++yy; }
+            u0[k] = fmaf((float)xx, step_u, -1.0f);
+            v0[k] = fmaf((float)yy, step_v, -1.0f);
+            if (++xx == (unsigned)a.W) { xx = 0; ++yy; }
         }
     }
 #pragma unroll
     for (int k = 0; k < VEC; ++k)
     {
-        du[k] = (u0[k] - a.vignette[3]) * a.aspect; dv[k] = v0[k] - a.vignette[4];
-        r2[k] = du[k] * du[k] + dv[k] * dv[k];
-        float r4 = r2[k] * r2[k], r6 = r4 * r2[k];
-        fac[k] = 1.f + a.vignette[0] * r2[k] + a.vignette[1] * r4 + a.vignette[2] * r6;
+        du[k] = (u0[k] - vg[3]) * a.aspect; dv[k] = v0[k] - vg[4];
+        r2[k] = fmaf(du[k], du[k], dv[k] * dv[k]);
+        fac[k] = fmaf(fmaf(fmaf(vg[2], r2[k], vg[1]), r2[k], vg[0]), r2[k], 1.0f);
     }
 }
 
-// grid: (ceil(H*W / (block * VEC)), B)
+// grid: (blocks per image, B); a block walks over many chunks of 256 x VEC pixels, so the curve is staged once per block
 template <int VEC>
 __global__ void __launch_bounds__(256) k_tonemap_forward(ToneArgs a, const float* __restrict__ x, float* __restrict__ out)
 {
     extern __shared__ float s_lut[];  // [3,K]
-    for (int k = threadIdx.x; k < 3 * a.K; k += blockDim.x) s_lut[k] = a.response[k];
+    const int K = a.K;
+    for (int k = threadIdx.x; k < 3 * K; k += blockDim.x) s_lut[k] = a.response[k];
     __syncthreads();
     const int b = blockIdx.y;
     const size_t plane = (size_t)a.H * a.W;
-    const size_t pix = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
-    if (pix >= plane) return;
     const int fi = a.frame_index ? a.frame_index[b] : 0;
     const float ef = a.exposure ? 1.0f / exp2f(a.exposure[fi]) : 1.0f;
-    float du[VEC], dv[VEC], r2[VEC], fac[VEC];
+    const float Km1 = (float)(K - 1);
+    float wb[3];
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) fac[k] = 1.f;
-    if (a.vignette) tone_geometry<VEC>(a, b, pix, plane, du, dv, r2, fac);
+    for (int c = 0; c < 3; ++c) wb[c] = a.white_balance ? a.white_balance[(size_t)fi * 3 + c] : 1.0f;
+    float vg[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+    if (a.vignette)
 #pragma unroll
-    for (int c = 0; c < 3; ++c)
+        for (int k = 0; k < 5; ++k) vg[k] = a.vignette[k];
+    const float* xb = x + (size_t)b * 3 * plane;
+    float* ob = out + (size_t)b * 3 * plane;
+    const size_t per_chunk = (size_t)blockDim.x * VEC;
+    for (size_t pix = (size_t)blockIdx.x * per_chunk + (size_t)threadIdx.x * VEC; pix < plane; pix += (size_t)gridDim.x * per_chunk)
     {
-        const float wb = a.white_balance ? a.white_balance[(size_t)fi * 3 + c] : 1.0f;
-        float xin[VEC], o[VEC];
-        load_vec<VEC>(x + ((size_t)b * 3 + c) * plane + pix, xin);
+        float xin[3][VEC];
 #pragma unroll
-        for (int k = 0; k < VEC; ++k)
+        for (int c = 0; c < 3; ++c) load_vec<VEC>(xb + c * plane + pix, xin[c]);
+        float du[VEC], dv[VEC], r2[VEC], fac[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) fac[k] = 1.f;
+        if (a.vignette) tone_geometry<VEC>(a, vg, b, pix, plane, du, dv, r2, fac);
+#pragma unroll
+        for (int c = 0; c < 3; ++c)
         {
-            float v = xin[k] * ef;
-            v = wb * v;
-            v = fac[k] * v;
-            if (a.response)
+            float o[VEC];
+#pragma unroll
+            for (int k = 0; k < VEC; ++k)
             {
-                float leak_add = 0.f;
-                if (a.leak > 0.f)
+                float v = xin[c][k] * ef;
+                v = wb[c] * v;
+                v = fac[k] * v;
+                if (a.response)
                 {
-                    if (v < 0.f) leak_add = v * a.leak;
-                    if (v > 1.f) leak_add = -a.leak / sqrtf(fabsf(v) + 1e-4f) + a.leak;
+                    float leak_add = 0.f;
+                    if (a.leak > 0.f)
+                    {
+                        if (v < 0.f) leak_add = v * a.leak;
+                        if (v > 1.f) leak_add = -a.leak / sqrtf(fabsf(v) + 1e-4f) + a.leak;
+                    }
+                    const float t = fminf(fmaxf(v, 0.f), 1.f) * Km1;
+                    const int i0 = (int)t;  // t >= 0: truncation is the floor
+                    const int i1 = i0 + 1 < K ? i0 + 1 : K - 1;
+                    const float fr = t - (float)i0;
+                    o[k] = s_lut[c * K + i0] * (1.0f - fr) + s_lut[c * K + i1] * fr + leak_add;
                 }
-                float t = fminf(fmaxf(v, 0.f), 1.f) * (float)(a.K - 1);
-                int i0 = (int)floorf(t);
-                int i1 = i0 + 1 < a.K ? i0 + 1 : a.K - 1;
-                float fr = t - (float)i0;
-                o[k] = s_lut[c * a.K + i0] * (1.0f - fr) + s_lut[c * a.K + i1] * fr + leak_add;
+                else
+                    o[k] = fminf(fmaxf(v, 0.f), 1.f);
             }
-            else
-                o[k] = fminf(fmaxf(v, 0.f), 1.f);
+            store_vec<VEC>(ob + c * plane + pix, o);
         }
-        store_vec<VEC>(out + ((size_t)b * 3 + c) * plane + pix, o);
     }
 }
 
@@ -189,7 +206,6 @@ __global__ void __launch_bounds__(256, 3) k_tonemap_backward(ToneArgs a, const f
     if (a.vignette)
 #pragma unroll
         for (int k = 0; k < 5; ++k) vg[k] = a.vignette[k];
-    const float step_u = 2.0f / (float)(a.W - 1), step_v = 2.0f / (float)(a.H - 1);
     const float* xb = x + (size_t)b * 3 * plane;
     const float* gob = grad_out + (size_t)b * 3 * plane;
     float* gxb = g.grad_x ? g.grad_x + (size_t)b * 3 * plane : nullptr;
@@ -230,34 +246,7 @@ __global__ void __launch_bounds__(256, 3) k_tonemap_backward(ToneArgs a, const f
         float du[VEC], dv[VEC], r2[VEC], fac[VEC];
 #pragma unroll
         for (int k = 0; k < VEC; ++k) { fac[k] = 1.f; du[k] = dv[k] = r2[k] = 0.f; }
-        if (a.vignette && live)
-        {
-            float u0[VEC], v0[VEC];
-            if (a.uv)
-            {
-                load_vec<VEC>(a.uv + ((size_t)b * 2 + 0) * plane + pix, u0);
-                load_vec<VEC>(a.uv + ((size_t)b * 2 + 1) * plane + pix, v0);
-            }
-            else
-            {
-                // 32-bit: the entry point rejects planes of 2^31 pixels or more
-                unsigned yy = (unsigned)pix / (unsigned)a.W, xx = (unsigned)pix - yy * (unsigned)a.W;
-#pragma unroll
-                for (int k = 0; k < VEC; ++k)
-                {
-                    u0[k] = fmaf((float)xx, step_u, -1.0f);
-                    v0[k] = fmaf((float)yy, step_v, -1.0f);
-                    if (++xx == (unsigned)a.W) { xx = 0; ++yy; }
-                }
-            }
-#pragma unroll
-            for (int k = 0; k < VEC; ++k)
-            {
-                du[k] = (u0[k] - vg[3]) * a.aspect; dv[k] = v0[k] - vg[4];
-                r2[k] = fmaf(du[k], du[k], dv[k] * dv[k]);
-                fac[k] = fmaf(fmaf(fmaf(vg[2], r2[k], vg[1]), r2[k], vg[0]), r2[k], 1.0f);
-            }
-        }
+        if (a.vignette && live) tone_geometry<VEC>(a, vg, b, pix, plane, du, dv, r2, fac);
         float scale = 0.f;  // 0: this round adds to the float histogram directly
         if (want_resp)
         {
@@ -425,16 +414,15 @@ extern "C" adop_status adop_tonemap_forward(const adop_tonemap_params* p, const 
     size_t plane = (size_t)a.H * a.W;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool vec = plane % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(a.uv)) & 15) == 0;
-    if (vec)
-    {
-        dim3 grid((unsigned)((plane / 4 + 255) / 256), (unsigned)a.B);
-        ADOP_LAUNCH("k_tonemap_forward", st, (k_tonemap_forward<4><<<grid, 256, sizeof(float) * 3 * a.K, st>>>(a, x, out)));
-    }
-    else
-    {
-        dim3 grid((unsigned)((plane + 255) / 256), (unsigned)a.B);
-        ADOP_LAUNCH("k_tonemap_forward", st, (k_tonemap_forward<1><<<grid, 256, sizeof(float) * 3 * a.K, st>>>(a, x, out)));
-    }
+    // as many blocks as stay resident at once, shared out over the images
+    const size_t chunks = vec ? (plane / 4 + 255) / 256 : (plane + 255) / 256;
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_tonemap_forward<4>, 256, sizeof(float) * 3 * a.K) != cudaSuccess || per_sm < 1)
+        per_sm = 1;
+    const size_t per_image = (size_t)((sm_count() * per_sm + a.B - 1) / a.B);
+    dim3 grid((unsigned)(chunks < per_image ? chunks : per_image), (unsigned)a.B);
+    if (vec) ADOP_LAUNCH("k_tonemap_forward", st, (k_tonemap_forward<4><<<grid, 256, sizeof(float) * 3 * a.K, st>>>(a, x, out)));
+    else ADOP_LAUNCH("k_tonemap_forward", st, (k_tonemap_forward<1><<<grid, 256, sizeof(float) * 3 * a.K, st>>>(a, x, out)));
     ADOP_CUDA_TRY(cudaGetLastError());
     return ADOP_OK;
 }
