@@ -10,7 +10,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG_DIR)
 CSRC = os.path.join(PKG_DIR, "csrc")
 SOURCES = ["capi_common.cu", "raster_forward.cu", "raster_forward_static.cu", "raster_backward.cu", "pose_tonemap.cu",
-           "peer_reduce.cu", "points_preprocess.cu"]
+           "peer_reduce.cu", "peer_update.cu", "points_preprocess.cu"]
 CONTRACTION_ALLOWED = {"pose_tonemap.cu"}
 LIB = os.path.join(PKG_DIR, "libadop_raster.so")
 

@@ -96,6 +96,17 @@ class AdopPeerReduceOut(C.Structure):
                 ("grad_background", C.c_void_p), ("grad_env_map", C.c_void_p), ("normalize", C.c_int32)]
 
 
+class AdopPeerParamLayout(C.Structure):
+    _fields_ = [("channels", C.c_int32), ("num_texels", C.c_int32), ("num_points", C.c_int32), ("reserved", C.c_int32),
+                ("off_texture", C.c_size_t), ("off_points", C.c_size_t), ("total_bytes", C.c_size_t)]
+
+
+class AdopPeerUpdate(C.Structure):
+    _fields_ = [("grad_texture_shard", C.c_void_p), ("adam_m", C.c_void_p), ("adam_v", C.c_void_p),
+                ("grad_points_shard", C.c_void_p), ("lr_texture", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float),
+                ("eps", C.c_float), ("step", C.c_int32), ("lr_points", C.c_float)]
+
+
 class AdopKernelTime(C.Structure):
     _fields_ = [("name", C.c_char * 48), ("launches", C.c_int32), ("total_ms", C.c_float)]
 
@@ -109,7 +120,7 @@ EXPORTED_SYMBOLS = [
     "adop_raster_static_scratch_bytes", "adop_raster_forward_static", "adop_raster_visible_list_ints",
     "adop_texture_interleave", "adop_texture_deinterleave",
     "adop_peer_alloc", "adop_peer_free", "adop_peer_open", "adop_peer_close", "adop_peer_layout_fill",
-    "adop_peer_shard_range", "adop_peer_reduce_gradients",
+    "adop_peer_shard_range", "adop_peer_reduce_gradients", "adop_peer_param_layout_fill", "adop_peer_apply_update",
     "adop_points_morton_workspace_bytes", "adop_points_morton_order", "adop_points_permute",
     "adop_points_block_shuffle_order", "adop_points_sort_blocks_by_radius_order",
     "adop_points_knn_workspace_bytes", "adop_points_knn_distance", "adop_points_radius_sample",
@@ -171,8 +182,11 @@ def load_library():
     lib.adop_peer_shard_range.restype = None
     lib.adop_peer_reduce_gradients.argtypes = [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.POINTER(AdopPeerLayout),
                                                C.POINTER(AdopPeerReduceOut), C.c_void_p]
+    lib.adop_peer_param_layout_fill.argtypes = [C.POINTER(AdopPeerParamLayout)]
+    lib.adop_peer_apply_update.argtypes = [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.POINTER(AdopPeerParamLayout),
+                                           C.POINTER(AdopPeerUpdate), C.c_void_p]
     for name in ("adop_peer_alloc", "adop_peer_free", "adop_peer_open", "adop_peer_close", "adop_peer_layout_fill",
-                 "adop_peer_reduce_gradients"):
+                 "adop_peer_reduce_gradients", "adop_peer_param_layout_fill", "adop_peer_apply_update"):
         getattr(lib, name).restype = C.c_int
     lib.adop_points_morton_workspace_bytes.argtypes = [C.c_int32]
     lib.adop_points_morton_workspace_bytes.restype = C.c_size_t

@@ -107,37 +107,31 @@ def peer_shard_range(count, rank, world):
     return min(count, rank * per), min(count, (rank + 1) * per)
 
 
-class PeerGradientExchange:
-    """Gradient block of this rank + the mapped blocks of the other ranks of `group` (all on one node).
+class _MappedBlocks:
+    """One device block per rank of `group` (all on one node): this rank's own allocation plus the other ranks' blocks
+    mapped through CUDA IPC handles. Every rank runs the same collectives whether or not its own CUDA calls succeed, so a
+    failure on one rank (no peer access between two GPUs, IPC not permitted) ends in an exception on all of them, not in
+    a hang."""
 
-        ex = PeerGradientExchange(layout, device, group)
-        grads = ex.backward_outputs()            # pass as `out=` to PointRasterizer.backward(..., normalize=False)
-        ...backward...
-        result = ex.reduce()                      # dict of final gradients (owned shards + small tensors)
-
-    The barrier on either side of the kernel is a one-element all-reduce of the group's backend, in stream order."""
-
-    def __init__(self, layout, device, group=None):
+    def __init__(self, total_bytes, device, group):
         from . import capi
         import ctypes as C
         self.capi, self.C = capi, C
         self.lib = capi.load_library()
-        self.layout, self.device, self.group = layout, torch.device(device), group
+        self.device, self.group = torch.device(device), group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         if self.world > 8:
             raise ValueError("the peer exchange covers the GPUs of one node (at most 8 ranks)")
-        self._own = C.c_void_p()
+        self.own = C.c_void_p()
         self._opened = []
         handle = capi.AdopPeerHandle()
-        # Every rank runs the same collectives whether or not its own CUDA calls succeed, so a failure on one rank
-        # (no peer access between two GPUs, IPC not permitted) ends in an exception on all of them, not in a hang.
         problem = None
         with torch.cuda.device(self.device):
             try:
-                capi.check(self.lib.adop_peer_alloc(layout.total_bytes, C.byref(self._own), C.byref(handle)), "adop_peer_alloc")
+                capi.check(self.lib.adop_peer_alloc(total_bytes, C.byref(self.own), C.byref(handle)), "adop_peer_alloc")
             except capi.AdopError as e:
                 problem = e
-                self._own = C.c_void_p()
+                self.own = C.c_void_p()
             mine = torch.tensor(list(bytes(handle.bytes)), dtype=torch.uint8, device=self.device)
             everyone = [torch.empty_like(mine) for _ in range(self.world)]
             dist.all_gather(everyone, mine, group=group)
@@ -146,7 +140,7 @@ class PeerGradientExchange:
                 if problem is not None:
                     break
                 if r == self.rank:
-                    self.blocks[r] = self._own.value
+                    self.blocks[r] = self.own.value
                     continue
                 h = capi.AdopPeerHandle()
                 C.memmove(h.bytes, bytes(everyone[r].cpu().tolist()), 64)
@@ -158,7 +152,7 @@ class PeerGradientExchange:
                     break
                 self._opened.append(ptr)
                 self.blocks[r] = ptr.value
-            self._flag = torch.zeros(1, device=self.device)
+            self.flag = torch.zeros(1, device=self.device)
             ok = torch.tensor([0.0 if problem is not None else 1.0], device=self.device)
             # also: nobody may free its block before every rank has mapped it
             dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
@@ -166,24 +160,67 @@ class PeerGradientExchange:
                 for ptr in self._opened:
                     self.lib.adop_peer_close(ptr)
                 self._opened = []
-                dist.all_reduce(self._flag, group=group)
+                dist.all_reduce(self.flag, group=group)
                 torch.cuda.synchronize(self.device)
-                if self._own.value:
-                    self.lib.adop_peer_free(self._own)
-                self._own = None
+                if self.own.value:
+                    self.lib.adop_peer_free(self.own)
+                self.own = None
                 raise capi.AdopError(f"peer-memory exchange unavailable: {problem if problem is not None else 'another rank failed'}")
-            self._outputs = self._make_outputs()
-            self._results = self._make_results()
 
-    def _span(self, offset, shape, typestr, dtype):
+    def span(self, offset, shape, typestr, dtype, owner):
+        """Tensor view of a part of this rank's own block."""
         n = 1
         for d in shape:
             n *= d
         if n == 0:
             return None
-        t = torch.as_tensor(_DeviceSpan(self._own.value + offset, shape, typestr, self), device=self.device)
-        assert t.dtype == dtype and t.data_ptr() == self._own.value + offset
+        t = torch.as_tensor(_DeviceSpan(self.own.value + offset, shape, typestr, owner), device=self.device)
+        assert t.dtype == dtype and t.data_ptr() == self.own.value + offset
         return t
+
+    def barrier(self):
+        """Stream-ordered: everything the ranks launched before it is complete once it has run on every rank's stream."""
+        dist.all_reduce(self.flag, group=self.group)
+
+    def close(self):
+        if self.own is None:
+            return
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            dist.all_reduce(self.flag, group=self.group)
+            torch.cuda.synchronize(self.device)
+            for ptr in self._opened:
+                self.lib.adop_peer_close(ptr)
+            self._opened = []
+            # the other ranks have closed their mappings of this block only after the next collective
+            dist.all_reduce(self.flag, group=self.group)
+            torch.cuda.synchronize(self.device)
+            self.lib.adop_peer_free(self.own)
+            self.own = None
+
+
+class PeerGradientExchange:
+    """Gradient block of this rank + the mapped blocks of the other ranks of `group` (all on one node).
+
+        ex = PeerGradientExchange(layout, device, group)
+        grads = ex.backward_outputs()            # pass as `out=` to PointRasterizer.backward(..., normalize=False)
+        ...backward...
+        result = ex.reduce()                      # dict of final gradients (owned shards + small tensors)
+
+    The barrier on either side of the kernel is a one-element all-reduce of the group's backend, in stream order."""
+
+    def __init__(self, layout, device, group=None):
+        self._mapped = _MappedBlocks(layout.total_bytes, device, group)
+        m = self._mapped
+        self.capi, self.C, self.lib = m.capi, m.C, m.lib
+        self.layout, self.device, self.group = layout, m.device, group
+        self.world, self.rank, self.blocks = m.world, m.rank, m.blocks
+        self._own, self._flag = m.own, m.flag
+        self._outputs = self._make_outputs()
+        self._results = self._make_results()
+
+    def _span(self, offset, shape, typestr, dtype):
+        return self._mapped.span(offset, shape, typestr, dtype, self)
 
     def _make_outputs(self):
         lay = self.layout
@@ -246,16 +283,71 @@ class PeerGradientExchange:
     def close(self):
         if self._own is None:
             return
+        self._outputs = self._results = None
+        self._mapped.close()
+        self._own = None
+
+
+def peer_param_layout(channels, num_texels, num_points=0):
+    """adop_peer_param_layout for these tensor sizes; the same call on every rank."""
+    from . import capi
+    import ctypes as C
+    lay = capi.AdopPeerParamLayout()
+    lay.channels, lay.num_texels, lay.num_points = channels, num_texels, num_points
+    capi.check(capi.load_library().adop_peer_param_layout_fill(C.byref(lay)), "adop_peer_param_layout_fill")
+    return lay
+
+
+class PeerParameters:
+    """This rank's replica of the two large trainable tensors - descriptors [C,T] and point positions [N,4] - inside a
+    block that the other ranks map, and the optimiser state of the elements this rank owns.
+
+        params = PeerParameters(layout, device, group)
+        params.texture.copy_(...); params.points.copy_(...)      # same initial values on every rank
+        scene = Scene(position=params.points, texture=params.texture, ...)
+        ... forward, backward, result = exchange.reduce() ...
+        params.step(result, lr_texture=0.08, lr_points=0.005)     # Adam / SGD on the owned shard, written to all replicas
+
+    `step` is one kernel (adop_peer_apply_update) between two stream-ordered barriers: optimiser step and all-gather of
+    the updated parameters in one pass, Adam moments for 1 / world of the texels per rank. It follows the reference's
+    optimisers (torch Adam for the descriptors, SGD for the points: NeuralScene.cpp:76-107, 204-240)."""
+
+    def __init__(self, layout, device, group=None, beta1=0.9, beta2=0.999, eps=1e-8):
+        self._mapped = _MappedBlocks(layout.total_bytes, device, group)
+        m = self._mapped
+        self.layout, self.device, self.group = layout, m.device, group
+        self.world, self.rank = m.world, m.rank
+        self.texture = m.span(layout.off_texture, (layout.channels, layout.num_texels), "<f4", torch.float32, self)
+        self.points = m.span(layout.off_points, (layout.num_points, 4), "<f4", torch.float32, self)
+        t_lo, t_hi = peer_shard_range(layout.num_texels, self.rank, self.world)
+        self.texel_range = (t_lo, t_hi)
+        self.point_range = peer_shard_range(layout.num_points, self.rank, self.world)
+        self.adam_m = torch.zeros((layout.channels, t_hi - t_lo), device=self.device)
+        self.adam_v = torch.zeros_like(self.adam_m)
+        self.beta1, self.beta2, self.eps = beta1, beta2, eps
+        self.steps = 0
+
+    def step(self, reduced, lr_texture, lr_points=0.0):
+        """reduced: the dict PeerGradientExchange.reduce() returned (its texture_shard / points_shard are read)."""
+        m = self._mapped
+        C, capi = m.C, m.capi
+        self.steps += 1
+        u = capi.AdopPeerUpdate()
+        gt, gp = reduced.get("texture_shard"), reduced.get("points_shard")
+        u.grad_texture_shard = gt.data_ptr() if gt is not None else None
+        u.adam_m, u.adam_v = self.adam_m.data_ptr(), self.adam_v.data_ptr()
+        u.grad_points_shard = gp.data_ptr() if (gp is not None and lr_points != 0.0) else None
+        u.lr_texture, u.beta1, u.beta2, u.eps = lr_texture, self.beta1, self.beta2, self.eps
+        u.step, u.lr_points = self.steps, lr_points
         with torch.cuda.device(self.device):
-            torch.cuda.synchronize(self.device)
-            dist.all_reduce(self._flag, group=self.group)
-            torch.cuda.synchronize(self.device)
-            for ptr in self._opened:
-                self.lib.adop_peer_close(ptr)
-            self._opened = []
-            self._outputs = self._results = None
-            # the other ranks have closed their mappings of this block only after the next collective
-            dist.all_reduce(self._flag, group=self.group)
-            torch.cuda.synchronize(self.device)
-            self.lib.adop_peer_free(self._own)
-            self._own = None
+            # nobody still reads the parameters (every rank's backward pass is behind this collective) ...
+            m.barrier()
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            capi.check(m.lib.adop_peer_apply_update(m.blocks, self.world, self.rank, C.byref(self.layout), C.byref(u),
+                                                    C.c_void_p(stream)), "adop_peer_apply_update")
+            # ... and nobody reads them again (the next forward pass) before every rank's writes have landed
+            m.barrier()
+
+    def close(self):
+        self.texture = self.points = None
+        self._mapped.close()

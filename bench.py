@@ -256,6 +256,45 @@ def exchange_check(peer, dist, torch):
     return float(t.item())
 
 
+def measure_parameter_update(peer, scene, dev, dist, torch, adist, capi):
+    """The step that follows the exchange in a training step, outside any timed region: Adam on the owned descriptor shard,
+    SGD on the owned point shard, every new value written to all ranks' replicas (adop_peer_apply_update, one kernel
+    between two stream-ordered barriers). Returns the time of a whole step call and of the kernel alone (max over ranks),
+    and the largest difference between this rank's replica and rank 0's afterwards (must be 0)."""
+    import statistics
+    res = peer.reduce()
+    C_, T = scene.texture.shape
+    pp = adist.PeerParameters(adist.peer_param_layout(C_, T, scene.position.shape[0]), dev)
+    pp.texture.copy_(scene.texture)
+    pp.points.copy_(scene.position)
+    for _ in range(2):
+        pp.step(res, lr_texture=0.08, lr_points=0.005)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+    capi.profile_collect()
+    capi.profile_enable(True)
+    ev[0].record()
+    for i in range(5):
+        pp.step(res, lr_texture=0.08, lr_points=0.005)
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    kt = capi.profile_collect()
+    capi.profile_enable(False)
+    t = torch.tensor([statistics.median(ev[i].elapsed_time(ev[i + 1]) for i in range(5)),
+                      kt["k_peer_update"][1] / max(kt["k_peer_update"][0], 1) if "k_peer_update" in kt else 0.0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    same = pp.texture.clone()
+    dist.broadcast(same, src=0)
+    diff = torch.tensor([float((same - pp.texture).abs().max())], device=dev)
+    dist.all_reduce(diff, op=dist.ReduceOp.MAX)
+    world = dist.get_world_size()
+    own_bytes = (C_ * T * 4 * 4 + scene.position.shape[0] * 16 * 2) // world   # gradient, two moments, parameter; point gradient, point
+    pushed = (C_ * T * 4 + scene.position.shape[0] * 16) // world * (world - 1)    # to the other replicas over NVLink
+    pp.close()
+    return {"what": "Adam on the owned descriptor shard + SGD on the owned points, new values written to every rank's replica: "
+                    "one kernel between two stream-ordered barriers", "step_ms": float(t[0]), "kernel_ms": float(t[1]),
+            "local_bytes_per_rank": own_bytes, "nvlink_bytes_per_rank": pushed, "replica_difference": float(diff.item())}
+
+
 def measure_c4(rank, world, dev, steps, exchange):
     """The multi-GPU configuration (30 M points, 8 views per GPU, 1080p): forward + backward + gradient exchange, timed
     like the headline (barrier, CUDA events, maximum over ranks). Returns the record for the bench line."""
@@ -593,6 +632,7 @@ def main():
 
     # ---- records outside the headline: the exchange check and the 30 M point configuration (N > 1), two more kernels (N = 1)
     check = exchange_check(peer, dist, torch) if peer is not None else None
+    update = measure_parameter_update(peer, scene, dev, dist, torch, adist, capi) if peer is not None else None
     c4 = None
     extras = None
     if world > 1 and not args.no_c4:
@@ -632,6 +672,7 @@ def main():
         if world > 1:
             line["exchange_check"] = check  # peer-memory kernel against NCCL all-reduces of the same gradients: largest relative difference
             line["c4"] = c4
+            line["parameter_update"] = update  # optimiser step + all-gather of the updated parameters (outside the timed region)
         if extras is not None:
             line["extra"] = extras
         print(json.dumps(line), flush=True)

@@ -318,6 +318,42 @@ typedef struct adop_peer_reduce_out
 adop_status adop_peer_reduce_gradients(const void* const* blocks, int32_t world, int32_t rank,
                                        const adop_peer_layout* layout, const adop_peer_reduce_out* out, void* stream);
 
+/* ---- Optimiser step + parameter all-gather over peer memory ------------------------------------------------------
+ * The step after adop_peer_reduce_gradients in a view-sharded training step (the reference trains on one GPU: its
+ * optimisers are torch::optim::Adam for the descriptors, NeuralScene.cpp:76-107, and torch::optim::SGD for the point
+ * positions, NeuralScene.cpp:204-240, stepped at NeuralScene.cpp:384-411, adop_train.cpp:530-532). Every rank keeps its replica of the two large
+ * trainable tensors in one device block of its own, laid out by adop_peer_param_layout: descriptors [C,T], then points
+ * [N,4]; the other ranks map it like the gradient blocks. adop_peer_apply_update is one kernel that applies the
+ * optimiser to the texels and points this rank owns (the ranges of adop_peer_shard_range, i.e. exactly the gradient shards
+ * the reduce kernel produced) and writes every new value into ALL replicas with plain peer stores: optimiser step and
+ * all-gather in one pass, with the Adam moments kept for the owned shard only. Same arithmetic, in the same order of
+ * operations, as torch::optim::Adam::step (no weight decay, no amsgrad) and SGD without momentum. The kernel does not
+ * wait for other GPUs: the caller orders it after every rank's last read of the parameters and before anyone's next one. */
+typedef struct adop_peer_param_layout
+{
+    int32_t channels;    /* C */
+    int32_t num_texels;  /* T: descriptors [C,T] f32 */
+    int32_t num_points;  /* N: positions [N,4] f32 (0: not part of the block) */
+    int32_t reserved;
+    size_t off_texture, off_points;
+    size_t total_bytes;
+} adop_peer_param_layout;
+adop_status adop_peer_param_layout_fill(adop_peer_param_layout* layout);
+
+typedef struct adop_peer_update
+{
+    const float* grad_texture_shard; /* [C, t_hi - t_lo]: adop_peer_reduce_out.grad_texture_shard; NULL = descriptors stay */
+    float* adam_m;                   /* [C, t_hi - t_lo] first moments of the owned texels (zero before the first step) */
+    float* adam_v;                   /* [C, t_hi - t_lo] second moments */
+    const float* grad_points_shard;  /* [n_hi - n_lo, 4]: adop_peer_reduce_out.grad_points_shard; NULL = points stay */
+    float lr_texture, beta1, beta2, eps; /* Adam (torch defaults: 0.9, 0.999, 1e-8) */
+    int32_t step;                    /* 1 for the first step */
+    float lr_points;                 /* SGD */
+} adop_peer_update;
+/* param_blocks[r] = rank r's parameter block as mapped in THIS process, 1 <= world <= 8. */
+adop_status adop_peer_apply_update(void* const* param_blocks, int32_t world, int32_t rank, const adop_peer_param_layout* layout,
+                                   const adop_peer_update* update, void* stream);
+
 /* ---- Point-cloud preprocessing on the GPU ----------------------------------------------------------------------
  * point_cloud.ReorderMorton64(), called once per scene at src/lib/data/SceneData.cpp:100 (the function itself is saiga
  * code that is not in the reference tree; the key is this library's definition: each coordinate quantised in float32

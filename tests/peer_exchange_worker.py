@@ -84,6 +84,36 @@ def main():
     both = own.view(C_, T)[:, t_lo:t_hi]
     close(res["texture_shard"][both], nccl_ct[:, t_lo:t_hi][both], "texture shard against the NCCL exchange")
     close(nccl["pose"] / nccl["count_pose"].clamp(min=1)[:, None].double(), ref["pose"], "NCCL pose")
+    # optimiser step on the owned shard + all-gather of the updated parameters (one kernel), three training steps on
+    # parameter replicas in peer-mapped blocks, against torch.optim on the full tensors with the single-GPU gradients
+    play = adist.peer_param_layout(C_, T, scene.position.shape[0])
+    pp = adist.PeerParameters(play, dev)
+    pp.texture.copy_(scene.texture)
+    pp.points.copy_(scene.position)
+    live = Scene(**dict(scene.tensors(), texture=pp.texture, position=pp.points))
+    ref_scene = Scene(**dict(scene.tensors(), texture=scene.texture.clone(), position=scene.position.clone()))
+    ref_tex = ref_scene.texture.requires_grad_(True)
+    ref_xyz = ref_scene.position[:, :3].clone().requires_grad_(True)
+    adam, sgd = torch.optim.Adam([ref_tex], lr=0.02), torch.optim.SGD([ref_xyz], lr=1e-4)
+    for step in range(3):
+        fwd = ras.forward(live, views, params, L)
+        ras.backward(live, params, fwd, grads, want_env=True, normalize=False, out=ex.backward_outputs())
+        res = ex.reduce()
+        pp.step(res, lr_texture=0.02, lr_points=1e-4)
+        with torch.no_grad():
+            ref_scene.position[:, :3] = ref_xyz
+        f_all = ras.forward(ref_scene, cfg["views"], params, L)
+        g_all = ras.backward(ref_scene, params, f_all, grads_all, want_env=True, normalize=True)
+        ref_tex.grad, ref_xyz.grad = g_all["texture"].clone(), g_all["points"][:, :3].clone()
+        adam.step()
+        sgd.step()
+        torch.cuda.synchronize()
+        close(pp.texture, ref_tex.detach(), f"descriptors after step {step}", rtol=1e-4, atol=1e-5)
+        close(pp.points[:, :3], ref_xyz.detach(), f"points after step {step}", rtol=1e-5, atol=1e-6)
+    gathered = pp.texture.clone()
+    dist.broadcast(gathered, src=0)
+    assert torch.equal(gathered, pp.texture), "parameter replicas differ between ranks"
+    pp.close()
     ex.close()
     dist.barrier()
     with open(os.path.join(out_dir, f"ok_{rank}"), "w") as f:

@@ -499,15 +499,17 @@ def test_struct_sizes_match_the_header():
     """ctypes mirrors must have the C layout (compiled probe with the system compiler)."""
     import subprocess
     import tempfile
-    src = '#include <stdio.h>\n#include "adop/adop_raster.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n",' \
+    src = '#include <stdio.h>\n#include "adop/adop_raster.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n",' \
           'sizeof(adop_view),sizeof(adop_render_params),sizeof(adop_scene),sizeof(adop_layer_buffers),' \
-          'sizeof(adop_forward_io),sizeof(adop_backward_io),sizeof(adop_tonemap_params),sizeof(adop_tonemap_grads));return 0;}'
+          'sizeof(adop_forward_io),sizeof(adop_backward_io),sizeof(adop_tonemap_params),sizeof(adop_tonemap_grads),' \
+          'sizeof(adop_peer_layout),sizeof(adop_peer_reduce_out),sizeof(adop_peer_param_layout),sizeof(adop_peer_update));return 0;}'
     with tempfile.TemporaryDirectory() as d:
         open(os.path.join(d, "p.c"), "w").write(src)
         subprocess.run(["/usr/bin/gcc", "-I", os.path.join(ROOT, "include"), os.path.join(d, "p.c"), "-o", os.path.join(d, "p")], check=True)
         sizes = list(map(int, subprocess.run([os.path.join(d, "p")], capture_output=True, text=True).stdout.split()))
     mirrors = [capi.AdopView, capi.AdopRenderParams, capi.AdopScene, capi.AdopLayerBuffers, capi.AdopForwardIO,
-               capi.AdopBackwardIO, capi.AdopTonemapParams, capi.AdopTonemapGrads]
+               capi.AdopBackwardIO, capi.AdopTonemapParams, capi.AdopTonemapGrads, capi.AdopPeerLayout, capi.AdopPeerReduceOut,
+               capi.AdopPeerParamLayout, capi.AdopPeerUpdate]
     assert sizes == [ctypes.sizeof(m) for m in mirrors]
 
 

@@ -165,6 +165,83 @@ def test_backward_leaves_descriptor_gradients_interleaved(cuda_lib):
     assert torch.allclose(out["points"], ref["points"], rtol=1e-4, atol=1e-5)
 
 
+@pytest.mark.parametrize("channels,world,texels,points", [(4, 3, 1001, 777), (4, 4, 4096, 0), (8, 8, 40_000, 4099), (16, 1, 64, 64)])
+def test_update_kernel_with_all_replicas_on_one_gpu(cuda_lib, channels, world, texels, points):
+    """adop_peer_apply_update with `world` parameter blocks that all live on one GPU (the kernel only takes base pointers):
+    after every rank's launch of a step all replicas hold the same tensors, and after three steps those equal what
+    torch.optim.Adam (descriptors) and torch.optim.SGD (points) make of the full tensors and the full gradients. Covers
+    the vector path (shares that are multiples of four texels) and the element path (ragged shares)."""
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(channels + world)
+    lay = adist.peer_param_layout(channels, texels, points)
+    raws = [torch.zeros(lay.total_bytes, dtype=torch.uint8, device=dev) for _ in range(world)]
+    ptrs = (C.c_void_p * world)(*[r.data_ptr() for r in raws])
+
+    def views(raw):
+        tex = raw[lay.off_texture:lay.off_texture + channels * texels * 4].view(torch.float32).view(channels, texels)
+        pts = raw[lay.off_points:lay.off_points + points * 16].view(torch.float32).view(points, 4) if points else None
+        return tex, pts
+
+    tex0 = torch.randn((channels, texels), device=dev, generator=gen)
+    pts0 = torch.randn((points, 4), device=dev, generator=gen) if points else None
+    for raw in raws:
+        t, p = views(raw)
+        t.copy_(tex0)
+        if points:
+            p.copy_(pts0)
+    ref_tex = tex0.clone().requires_grad_(True)
+    adam = torch.optim.Adam([ref_tex], lr=0.08)
+    ref_pts = pts0[:, :3].clone().requires_grad_(True) if points else None
+    sgd = torch.optim.SGD([ref_pts], lr=0.005) if points else None
+    m = [torch.zeros((channels, adist.peer_shard_range(texels, r, world)[1] - adist.peer_shard_range(texels, r, world)[0]), device=dev)
+         for r in range(world)]
+    v = [torch.zeros_like(x) for x in m]
+    for step in range(1, 4):
+        g_tex = torch.randn((channels, texels), device=dev, generator=gen) * (10.0 ** (step - 2))
+        g_pts = torch.randn((points, 4), device=dev, generator=gen) if points else None
+        for rank in range(world):
+            t_lo, t_hi = adist.peer_shard_range(texels, rank, world)
+            p_lo, p_hi = adist.peer_shard_range(points, rank, world)
+            u = capi.AdopPeerUpdate()
+            shard = g_tex[:, t_lo:t_hi].contiguous()
+            pshard = g_pts[p_lo:p_hi].contiguous() if points and p_hi > p_lo else None
+            u.grad_texture_shard = shard.data_ptr() if t_hi > t_lo else None
+            u.adam_m, u.adam_v = m[rank].data_ptr(), v[rank].data_ptr()
+            u.grad_points_shard = pshard.data_ptr() if pshard is not None else None
+            u.lr_texture, u.beta1, u.beta2, u.eps, u.step, u.lr_points = 0.08, 0.9, 0.999, 1e-8, step, 0.005
+            capi.check(cuda_lib.adop_peer_apply_update(ptrs, world, rank, C.byref(lay), C.byref(u), None), "adop_peer_apply_update")
+        torch.cuda.synchronize()
+        ref_tex.grad = g_tex.clone()
+        adam.step()
+        if points:
+            ref_pts.grad = g_pts[:, :3].clone()
+            sgd.step()
+        t_first, p_first = views(raws[0])
+        for raw in raws[1:]:
+            t, p = views(raw)
+            assert torch.equal(t, t_first) and (not points or torch.equal(p, p_first))
+        assert torch.allclose(t_first, ref_tex.detach(), rtol=2e-6, atol=1e-7), float((t_first - ref_tex.detach()).abs().max())
+        if points:
+            assert torch.allclose(p_first[:, :3], ref_pts.detach(), rtol=1e-6, atol=1e-7)
+            assert torch.equal(p_first[:, 3], pts0[:, 3])  # the drop-out radius is not a parameter
+
+
+def test_update_kernel_argument_checks(cuda_lib):
+    dev = torch.device("cuda:0")
+    lay = adist.peer_param_layout(4, 64, 0)
+    raw = torch.zeros(lay.total_bytes, dtype=torch.uint8, device=dev)
+    ptrs = (C.c_void_p * 1)(raw.data_ptr())
+    g = torch.zeros((4, 64), device=dev)
+    u = capi.AdopPeerUpdate()
+    u.grad_texture_shard, u.adam_m, u.adam_v = g.data_ptr(), g.data_ptr(), g.data_ptr()
+    u.lr_texture, u.beta1, u.beta2, u.eps, u.step = 0.1, 0.9, 0.999, 1e-8, 0   # steps count from 1
+    assert cuda_lib.adop_peer_apply_update(ptrs, 1, 0, C.byref(lay), C.byref(u), None) == 1  # ADOP_ERR_INVALID_ARGUMENT
+    u.step, u.adam_v = 1, None
+    assert cuda_lib.adop_peer_apply_update(ptrs, 1, 0, C.byref(lay), C.byref(u), None) == 1  # ADOP_ERR_INVALID_ARGUMENT
+    assert cuda_lib.adop_peer_apply_update(ptrs, 9, 0, C.byref(lay), C.byref(u), None) == 1  # ADOP_ERR_INVALID_ARGUMENT
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_gpu_exchange_matches_single_gpu_and_nccl(cuda_lib, tmp_path):
     port = 29600 + (os.getpid() % 1000)
