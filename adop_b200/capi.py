@@ -61,7 +61,8 @@ class AdopBackwardIO(C.Structure):
                 ("grad_intrinsics", C.c_void_p), ("count_intrinsics", C.c_void_p), ("grad_env_map", C.c_void_p),
                 ("accumulate", C.c_int32), ("normalize", C.c_int32),
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("visible_list", C.c_void_p),
-                ("grad_texture_interleaved", C.c_void_p), ("grad_env_map_interleaved", C.c_void_p)]
+                ("grad_texture_interleaved", C.c_void_p), ("grad_env_map_interleaved", C.c_void_p),
+                ("touched_texels", C.c_void_p), ("touched_points", C.c_void_p)]
 
 
 class AdopTonemapParams(C.Structure):
@@ -84,10 +85,11 @@ class AdopPeerHandle(C.Structure):
 class AdopPeerLayout(C.Structure):
     _fields_ = [("channels", C.c_int32), ("num_texels", C.c_int32), ("num_points", C.c_int32), ("num_images", C.c_int32),
                 ("num_cameras", C.c_int32), ("intrinsics_cols", C.c_int32), ("env_h", C.c_int32), ("env_w", C.c_int32),
-                ("background", C.c_int32), ("reserved", C.c_int32),
+                ("background", C.c_int32), ("touched", C.c_int32),
                 ("off_texture", C.c_size_t), ("off_points", C.c_size_t), ("off_pose", C.c_size_t),
                 ("off_count_pose", C.c_size_t), ("off_intrinsics", C.c_size_t), ("off_count_intrinsics", C.c_size_t),
-                ("off_background", C.c_size_t), ("off_env_map", C.c_size_t), ("total_bytes", C.c_size_t)]
+                ("off_background", C.c_size_t), ("off_env_map", C.c_size_t), ("off_touched_texels", C.c_size_t),
+                ("off_touched_points", C.c_size_t), ("off_gathered", C.c_size_t), ("total_bytes", C.c_size_t)]
 
 
 class AdopPeerReduceOut(C.Structure):

@@ -196,6 +196,8 @@ inline void fill_cam_chunk(CamChunkSource* c, const adop_scene* s, const adop_vi
 //   entries                         T buckets of cap entries, 4 ints each
 constexpr int kVisibleSegments = 2048;    // most blocks the depth prepass writes candidate segments with
 constexpr int kVisibleHeaderInts = kVisibleSegments + 8;
+// granularity of the optional "a gradient was added here" flags of the backward pass (ADOP_TOUCHED_CHUNK in the header)
+constexpr int kTouchedShift = 8, kTouchedChunk = 1 << kTouchedShift;
 constexpr int kTileW = 32, kTileH = 16;   // screen tile, in layer-0 pixels (shifts 5 and 4 below)
 constexpr int kTileShiftX = 5, kTileShiftY = 4;
 constexpr unsigned kEntryDropped = 0x80000000u;

@@ -35,13 +35,39 @@ __device__ __forceinline__ float4 peer_load4(const float4* p) { return __ldcv(p)
 __device__ __forceinline__ float peer_load(const float* p) { return __ldcv(p); }
 __device__ __forceinline__ double peer_load(const double* p) { return __ldcv(p); }
 
+// With touched flags in the blocks: which ranks added anything to each chunk of the texels and points this rank owns.
+// One byte per chunk (bit r = rank r), written to this rank's own block ahead of the reduce kernel, so that the reduce
+// kernel decides with a local load which peers it has to read a vector from. A rank's view arc sees one side of the scene:
+// about half of the chunks of a Morton-sorted cloud get no gradient from it, and their zeros need not cross NVLink.
+__global__ void __launch_bounds__(kBlock) k_peer_gather_touched(PeerBlocks pb, int rank, adop_peer_layout lay, PeerWork w)
+{
+    unsigned char* dst = reinterpret_cast<unsigned char*>(const_cast<char*>(pb.base[rank]) + lay.off_gathered);
+    const int t_chunks = (lay.num_texels + kTouchedChunk - 1) / kTouchedChunk;
+    const int tc_lo = w.t_lo >> kTouchedShift, tc_hi = w.t_n > 0 ? ((w.t_lo + w.t_n - 1) >> kTouchedShift) + 1 : tc_lo;
+    const int pc_lo = w.p_lo >> kTouchedShift, pc_hi = w.p_n > 0 ? ((w.p_lo + w.p_n - 1) >> kTouchedShift) + 1 : pc_lo;
+    const int n_t = tc_hi - tc_lo, n_p = pc_hi - pc_lo;
+    for (int k = blockIdx.x * blockDim.x + threadIdx.x; k < n_t + n_p; k += gridDim.x * blockDim.x)
+    {
+        const bool tex = k < n_t;
+        const int c = tex ? tc_lo + k : pc_lo + (k - n_t);
+        const size_t off = tex ? lay.off_touched_texels : lay.off_touched_points;
+        unsigned mask = 0;
+        for (int r = 0; r < pb.world; ++r)
+            if (__ldcv(reinterpret_cast<const unsigned char*>(pb.base[r] + off) + c) != 0) mask |= 1u << r;
+        dst[tex ? c : t_chunks + c] = (unsigned char)mask;
+    }
+}
+
 // MAXR = upper bound of the rank count (2, 4 or 8), U = texels or points a thread has in flight at once: U * MAXR = 8
 // independent 16-byte loads per thread keep enough bytes in flight to fill NVLink whatever the rank count.
 template <int C, int MAXR, int U>
-__global__ void __launch_bounds__(kBlock) k_peer_reduce(PeerBlocks pb, adop_peer_layout lay, PeerWork w, adop_peer_reduce_out out)
+__global__ void __launch_bounds__(kBlock) k_peer_reduce(PeerBlocks pb, int rank, adop_peer_layout lay, PeerWork w, adop_peer_reduce_out out)
 {
     const long long stride = (long long)gridDim.x * blockDim.x;
     const long long first = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    // which ranks to read a texel's / point's vector from: all of them, or those that flagged its chunk (k_peer_gather_touched)
+    const unsigned char* gathered = lay.touched ? reinterpret_cast<const unsigned char*>(pb.base[rank] + lay.off_gathered) : nullptr;
+    const unsigned char* gathered_points = gathered ? gathered + (lay.num_texels + kTouchedChunk - 1) / kTouchedChunk : nullptr;
     // ---- owned texels: C floats from each rank, summed in rank order, written to the channel planes of the shard ----
     if (C % 4 == 0)
     {
@@ -55,13 +81,14 @@ __global__ void __launch_bounds__(kBlock) k_peer_reduce(PeerBlocks pb, adop_peer
                 const long long it = item + u * stride;
                 if (it < w.t_n)
                 {
+                    const unsigned mask = gathered ? gathered[(w.t_lo + it) >> kTouchedShift] : 0xffu;
 #pragma unroll
                     for (int r = 0; r < MAXR; ++r)
                         if (r < pb.world)
                         {
                             const float4* src = reinterpret_cast<const float4*>(pb.base[r] + lay.off_texture) + (size_t)(w.t_lo + it) * Q;
 #pragma unroll
-                            for (int k = 0; k < Q; ++k) v[u][r][k] = peer_load4(src + k);
+                            for (int k = 0; k < Q; ++k) v[u][r][k] = (mask >> r) & 1u ? peer_load4(src + k) : make_float4(0.f, 0.f, 0.f, 0.f);
                         }
                 }
             }
@@ -98,8 +125,10 @@ __global__ void __launch_bounds__(kBlock) k_peer_reduce(PeerBlocks pb, adop_peer
             float acc[C];
 #pragma unroll
             for (int c = 0; c < C; ++c) acc[c] = 0.f;
+            const unsigned mask = gathered ? gathered[(w.t_lo + item) >> kTouchedShift] : 0xffu;
             for (int r = 0; r < pb.world; ++r)
             {
+                if (!((mask >> r) & 1u)) continue;
                 const float* src = reinterpret_cast<const float*>(pb.base[r] + lay.off_texture) + (size_t)(w.t_lo + item) * C;
 #pragma unroll
                 for (int c = 0; c < C; ++c) acc[c] += peer_load(src + c);
@@ -118,10 +147,12 @@ __global__ void __launch_bounds__(kBlock) k_peer_reduce(PeerBlocks pb, adop_peer
             const long long it = item + u * stride;
             if (it < w.p_n)
             {
+                const unsigned mask = gathered_points ? gathered_points[(w.p_lo + it) >> kTouchedShift] : 0xffu;
 #pragma unroll
                 for (int r = 0; r < MAXR; ++r)
                     if (r < pb.world)
-                        v[u][r] = peer_load4(reinterpret_cast<const float4*>(pb.base[r] + lay.off_points) + (size_t)w.p_lo + (size_t)it);
+                        v[u][r] = (mask >> r) & 1u ? peer_load4(reinterpret_cast<const float4*>(pb.base[r] + lay.off_points) + (size_t)w.p_lo + (size_t)it)
+                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
 #pragma unroll
@@ -303,6 +334,11 @@ extern "C" adop_status adop_peer_layout_fill(adop_peer_layout* l)
     l->off_count_intrinsics = take(sizeof(float) * (size_t)l->num_cameras);
     l->off_background = take(l->background ? sizeof(float) * l->channels : 0);
     l->off_env_map = take(sizeof(float) * (size_t)l->channels * l->env_h * l->env_w);
+    const size_t t_chunks = l->touched ? ((size_t)l->num_texels + kTouchedChunk - 1) / kTouchedChunk : 0;
+    const size_t p_chunks = l->touched ? ((size_t)l->num_points + kTouchedChunk - 1) / kTouchedChunk : 0;
+    l->off_touched_texels = take(t_chunks);
+    l->off_touched_points = take(p_chunks);
+    l->off_gathered = take(t_chunks + p_chunks);
     l->total_bytes = at ? at : 256;
     return ADOP_OK;
 }
@@ -364,13 +400,19 @@ extern "C" adop_status adop_peer_reduce_gradients(const void* const* blocks, int
     if (total == 0) return ADOP_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int C = layout->channels;
+    if (layout->touched && (w.t_n > 0 || w.p_n > 0))
+    {
+        const int chunks = (w.t_n + w.p_n) / kTouchedChunk + 4;
+        const int grid = (chunks + kBlock - 1) / kBlock;
+        ADOP_LAUNCH("k_peer_gather_touched", st, (k_peer_gather_touched<<<grid, kBlock, 0, st>>>(pb, rank, *layout, w)));
+    }
 #define ADOP_PEER_LAUNCH(CC, MAXR)                                                                                      \
     {                                                                                                                   \
         constexpr int Q = CC % 4 == 0 ? CC / 4 : 1;                                                                     \
         constexpr int U = 8 / (MAXR * Q) > 0 ? 8 / (MAXR * Q) : 1;                                                      \
         static const int per_sm_grid = resident_grid(k_peer_reduce<CC, MAXR, U>, 1ll << 40);                            \
         int grid = need < per_sm_grid ? (int)need : per_sm_grid;                                                        \
-        ADOP_LAUNCH("k_peer_reduce", st, (k_peer_reduce<CC, MAXR, U><<<grid, kBlock, 0, st>>>(pb, *layout, w, *out)));  \
+        ADOP_LAUNCH("k_peer_reduce", st, (k_peer_reduce<CC, MAXR, U><<<grid, kBlock, 0, st>>>(pb, rank, *layout, w, *out)));  \
     }
 #define ADOP_PEER_CASE(CC)                                                                                              \
     case CC:                                                                                                            \

@@ -135,10 +135,18 @@ static adop_scene make_scene(RenderInfo& info, const Tensor& texture, const Tens
     return sc;
 }
 
-static void ensure_workspace(RenderInfo& info, const adop_scene& sc, const torch::TensorOptions& opt)
+// Returns the size the library is told (it picks its kernels by it), which may be less than what an earlier call left behind.
+static size_t ensure_workspace(RenderInfo& info, const std::vector<adop_view>& views, int64_t num_layers, const adop_scene& sc,
+                               const torch::TensorOptions& opt, bool forward)
 {
-    // the small workspace: candidate streams (adop_raster_workspace_bytes_full) measured slower on training-sized views
-    const size_t need = adop_raster_workspace_bytes(info.images[0].w, info.images[0].h, (int32_t)info.num_layers, sc.channels);
+    // Candidate streams (adop_raster_workspace_bytes_full) pay for views of the omnidirectional model, whose projection is
+    // expensive and whose image holds a small part of the cloud; on pinhole training views they measured slower.
+    bool ocam = false;
+    for (const adop_view& v : views) ocam = ocam || v.camera_model == ADOP_CAMERA_OCAM;
+    const size_t need = (forward && ocam)
+                            ? adop_raster_workspace_bytes_full(sc.num_points, (int32_t)views.size(), views[0].w, views[0].h, (int32_t)num_layers,
+                                                               sc.channels)
+                            : adop_raster_workspace_bytes(views[0].w, views[0].h, (int32_t)num_layers, sc.channels);
     TORCH_CHECK(need > 0, "invalid view size / layer count");
     if (!info.workspace.defined() || (size_t)info.workspace.numel() < need)
         info.workspace = torch::empty({(int64_t)need}, opt.dtype(torch::kUInt8));
@@ -147,6 +155,7 @@ static void ensure_workspace(RenderInfo& info, const adop_scene& sc, const torch
         info.texture_interleaved = torch::empty({sc.num_texels, sc.channels}, opt);
         info.grad_texture_interleaved = torch::empty({sc.num_texels, sc.channels}, opt);
     }
+    return need;
 }
 
 // What a forward call used and its backward call must use again, whatever happens to the RenderInfo in between (a second
@@ -186,7 +195,7 @@ struct PointRender : public torch::autograd::Function<PointRender>
         }
         const int B = (int)info->images.size(), L = (int)info->num_layers, C = sc.channels;
         auto opt = texture.options();
-        ensure_workspace(*info, sc, opt);
+        const size_t workspace_bytes = ensure_workspace(*info, info->images, info->num_layers, sc, opt, true);
         check_status(adop_texture_interleave(sc.texture, info->texture_interleaved.data_ptr<float>(), C, sc.num_texels, stream),
                      "adop_texture_interleave");
         sc.texture_interleaved = info->texture_interleaved.data_ptr<float>();
@@ -210,7 +219,7 @@ struct PointRender : public torch::autograd::Function<PointRender>
         Tensor visible = torch::empty({B, (int64_t)adop_raster_visible_list_ints(sc.num_points, info->images[0].w, info->images[0].h, L)}, opt.dtype(torch::kInt32));
         io.visible_list = visible.data_ptr<int32_t>();
         io.workspace = info->workspace.data_ptr();
-        io.workspace_bytes = (size_t)info->workspace.numel();
+        io.workspace_bytes = workspace_bytes;
         check_status(adop_raster_forward(&sc, info->images.data(), B, &info->params, L, &io, stream), "adop_raster_forward");
 
         // saved for backward: depth, weight per layer, then the colours (PointRenderer.cu:1514-1527); the visible list
@@ -265,7 +274,7 @@ struct PointRender : public torch::autograd::Function<PointRender>
         if (has(env_map)) call.env_map = env_map;
         adop_scene sc = make_scene(call, texture, background, points, intrinsics);
         // the shared [T,C] working copy may belong to a later forward call by now: rebuild it from this call's descriptors
-        ensure_workspace(*info, sc, texture.options());
+        const size_t workspace_bytes = ensure_workspace(*info, views, L, sc, texture.options(), false);
         check_status(adop_texture_interleave(sc.texture, info->texture_interleaved.data_ptr<float>(), sc.channels, sc.num_texels, stream),
                      "adop_texture_interleave");
         sc.texture_interleaved = info->texture_interleaved.data_ptr<float>();
@@ -322,7 +331,7 @@ struct PointRender : public torch::autograd::Function<PointRender>
         io.accumulate = 0;
         io.normalize = 1;
         io.workspace = info->workspace.data_ptr();
-        io.workspace_bytes = (size_t)info->workspace.numel();
+        io.workspace_bytes = workspace_bytes;
         check_status(adop_raster_backward(&sc, views.data(), B, &params, L, &io, stream), "adop_raster_backward");
         // {texture, background, points, pose tangents, intrinsics}, the environment map, and nothing for the info object
         // (PointRenderer.cu:1641-1643, RenderInfo.cpp:56)

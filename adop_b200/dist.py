@@ -88,8 +88,11 @@ class _DeviceSpan:
 
 
 def peer_layout(channels, num_texels, num_points=0, num_images=0, num_cameras=0, intrinsics_cols=0, env_hw=(0, 0),
-                background=True):
-    """adop_peer_layout for these tensor sizes (0 = tensor not exchanged); the same call on every rank."""
+                background=True, touched=False):
+    """adop_peer_layout for these tensor sizes (0 = tensor not exchanged); the same call on every rank.
+    touched: the blocks also carry the backward pass's flags "a gradient was added in this chunk of 256 texels / points",
+    and the reduce kernel reads a peer's descriptor / point gradients only where that peer set them (the flags are part of
+    PeerGradientExchange.backward_outputs(), so the backward pass fills them)."""
     from . import capi
     import ctypes as C
     lay = capi.AdopPeerLayout()
@@ -97,6 +100,7 @@ def peer_layout(channels, num_texels, num_points=0, num_images=0, num_cameras=0,
     lay.num_images, lay.num_cameras, lay.intrinsics_cols = num_images, num_cameras, intrinsics_cols
     lay.env_h, lay.env_w = env_hw
     lay.background = 1 if background else 0
+    lay.touched = 1 if touched else 0
     capi.check(capi.load_library().adop_peer_layout_fill(C.byref(lay)), "adop_peer_layout_fill")
     return lay
 
@@ -234,6 +238,10 @@ class PeerGradientExchange:
         o["count_intrinsics"] = self._span(lay.off_count_intrinsics, (lay.num_cameras,), "<f4", f32)
         o["background"] = self._span(lay.off_background, (lay.channels if lay.background else 0,), "<f4", f32)
         o["env_map"] = self._span(lay.off_env_map, (lay.channels, lay.env_h, lay.env_w), "<f4", f32)
+        if lay.touched:
+            chunk = 256
+            o["touched_texels"] = self._span(lay.off_touched_texels, ((lay.num_texels + chunk - 1) // chunk,), "|u1", torch.uint8)
+            o["touched_points"] = self._span(lay.off_touched_points, ((lay.num_points + chunk - 1) // chunk,), "|u1", torch.uint8)
         return o
 
     def _make_results(self):

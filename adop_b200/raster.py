@@ -121,10 +121,13 @@ class ForwardResult:
 class PointRasterizer:
     """Owns the reusable scratch (the role of PointRendererCache, PointRenderer.h:96-157)."""
 
-    def __init__(self, device="cuda:0", interleave_descriptors=True, full_workspace=False):
-        """full_workspace: size the scratch with adop_raster_workspace_bytes_full (about 64 bytes per point more), which lets
-        the depth prepass hand projected points to the blend kernel instead of the blend kernel projecting again; False keeps
-        the small workspace."""
+    def __init__(self, device="cuda:0", interleave_descriptors=True, full_workspace=None):
+        """full_workspace: True sizes the forward scratch with adop_raster_workspace_bytes_full (16 bytes per point and view
+        of a group more), which lets the depth prepass hand the projected in-image points to the blend kernel instead of the
+        blend kernel reading the cloud and projecting again; False keeps the small workspace. None (default) decides per
+        call: on for views of the omnidirectional model, whose projection is expensive and whose image holds a small part
+        of the cloud (forward pass of the 100 M point viewer configuration: a third faster), off for pinhole views, where the
+        extra stream costs more than it saves (measured on the training configuration)."""
         self.lib = capi.load_library()
         self.device = torch.device(device)
         self._ws = None
@@ -148,8 +151,8 @@ class PointRasterizer:
             sc.texture_interleaved = self._tex_i.data_ptr()
         return sc
 
-    def _workspace(self, w, h, layers, channels, num_points=0, num_views=1):
-        if self.full_workspace:
+    def _workspace(self, w, h, layers, channels, num_points=0, num_views=1, full=False):
+        if full:
             need = self.lib.adop_raster_workspace_bytes_full(num_points, num_views, w, h, layers, channels)
         else:
             need = self.lib.adop_raster_workspace_bytes(w, h, layers, channels)
@@ -157,6 +160,9 @@ class PointRasterizer:
             raise ValueError("invalid size")
         if self._ws is None or self._ws.numel() < need:
             self._ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+        # the library picks its kernels by the size it is told: it is told the size asked for, not what an earlier, larger
+        # call left behind
+        self._ws_bytes = need
         return self._ws
 
     def forward(self, scene, views, params, num_layers, dropout_mask=None, out=None, record_visible=True,
@@ -173,7 +179,10 @@ class PointRasterizer:
             # rendering frame after frame), so the [T,C] working copy is reused as it is
             sc = self._scene_struct(scene, refresh=refresh_descriptors)
             ch = sc.channels
-            ws = self._workspace(w, h, num_layers, ch, sc.num_points, B)
+            full = self.full_workspace
+            if full is None:
+                full = any(v.camera_model == capi.CAMERA_OCAM for v in va)
+            ws = self._workspace(w, h, num_layers, ch, sc.num_points, B, full=bool(full))
             sizes = capi.layer_sizes(w, h, num_layers)
             if out is None:
                 f32 = dict(dtype=torch.float32, device=self.device)
@@ -198,7 +207,7 @@ class PointRasterizer:
                 io.layers[l].mask = out.masks[l].data_ptr() if out.masks else None
             io.dropout_mask = _tptr(dropout_mask) if dropout_mask is not None else None
             io.workspace = ws.data_ptr()
-            io.workspace_bytes = ws.numel()
+            io.workspace_bytes = self._ws_bytes
             io.visible_list = out.visible.data_ptr() if out.visible is not None else None
             if out.packed is not None:
                 for l in range(num_layers):
@@ -253,11 +262,13 @@ class PointRasterizer:
             io.grad_pose, io.count_pose = p("pose"), p("count_pose")
             io.grad_intrinsics, io.count_intrinsics = p("intrinsics"), p("count_intrinsics")
             io.grad_env_map = p("env_map")
+            # optional byte flags "a gradient was added in this chunk of 256 texels / points" (the multi-GPU exchange reads them)
+            io.touched_texels, io.touched_points = p("touched_texels"), p("touched_points")
             io.accumulate = 0
             io.normalize = 1 if normalize else 0
             ws = self._workspace(va[0].w, va[0].h, L, sc.channels, sc.num_points, B)
             io.workspace = ws.data_ptr()
-            io.workspace_bytes = ws.numel()
+            io.workspace_bytes = self._ws_bytes
             io.visible_list = fwd.visible.data_ptr() if fwd.visible is not None else None
             if out.get("texture_interleaved") is not None:
                 # the caller keeps the descriptor gradients in [T,C] layout (the block the GPUs exchange, dist.py)

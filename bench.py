@@ -40,7 +40,7 @@ NCU_TRAFFIC_BYTES = {"k_depth_prepass": 220.0e6, "k_blend": 421.2e6, "k_resolve"
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--points", type=int, default=10_000_000)
@@ -51,6 +51,8 @@ def parse_args():
     ap.add_argument("--candidates", action="store_true",
                     help="size the scratch with room for candidate streams (the depth prepass then hands projected points to "
                          "the blend kernel; measured slightly slower overall than projecting twice)")
+    ap.add_argument("--no-touched", action="store_true",
+                    help="N > 1: the exchange kernel reads every rank's whole gradient block instead of only the chunks a rank flagged")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: gradient exchange by the peer-memory kernel (default) or by NCCL reduce-scatter / all-reduce")
     return ap.parse_args()
@@ -295,7 +297,7 @@ def measure_parameter_update(peer, scene, dev, dist, torch, adist, capi):
             "local_bytes_per_rank": own_bytes, "nvlink_bytes_per_rank": pushed, "replica_difference": float(diff.item())}
 
 
-def measure_c4(rank, world, dev, steps, exchange):
+def measure_c4(rank, world, dev, steps, exchange, touched=True):
     """The multi-GPU configuration (30 M points, 8 views per GPU, 1080p): forward + backward + gradient exchange, timed
     like the headline (barrier, CUDA events, maximum over ranks). Returns the record for the bench line."""
     import torch
@@ -320,7 +322,7 @@ def measure_c4(rank, world, dev, steps, exchange):
         try:
             layout = adist.peer_layout(C, bwd["texture"].shape[1], n_points, num_images=bwd["pose"].shape[0],
                                        num_cameras=bwd["intrinsics"].shape[0], intrinsics_cols=bwd["intrinsics"].shape[1],
-                                       env_hw=tuple(arrays["env_map"].shape[1:]))
+                                       env_hw=tuple(arrays["env_map"].shape[1:]), touched=touched)
             peer = adist.PeerGradientExchange(layout, dev)
             bwd = peer.backward_outputs()
         except capi.AdopError:
@@ -432,7 +434,7 @@ def main():
     w, h = cfg["meta"]["w"], cfg["meta"]["h"]
     P = sum(a * b for a, b in capi.layer_sizes(w, h, L))
     scene = Scene(**{k: (torch.from_numpy(v).to(dev) if v is not None else None) for k, v in arrays.items()})
-    ras = PointRasterizer(dev, full_workspace=args.candidates)
+    ras = PointRasterizer(dev, full_workspace=True if args.candidates else None)
     gen = torch.Generator(device=dev)
     gen.manual_seed(1234 + rank)
     grads_dev = [torch.randn((V, C, hh, ww), device=dev, generator=gen) for ww, hh in capi.layer_sizes(w, h, L)]
@@ -449,7 +451,7 @@ def main():
         try:
             layout = adist.peer_layout(C, bwd["texture"].shape[1], N, num_images=bwd["pose"].shape[0],
                                        num_cameras=bwd["intrinsics"].shape[0], intrinsics_cols=bwd["intrinsics"].shape[1],
-                                       env_hw=tuple(arrays["env_map"].shape[1:]))
+                                       env_hw=tuple(arrays["env_map"].shape[1:]), touched=not args.no_touched)
             peer = adist.PeerGradientExchange(layout, dev)
             bwd = peer.backward_outputs()
         except capi.AdopError as e:
@@ -643,7 +645,7 @@ def main():
         del fwd, bwd, scene, grads_dev, staged
         ras = None
         torch.cuda.empty_cache()
-        c4 = measure_c4(rank, world, dev, max(3, min(args.steps, 10)), args.exchange)
+        c4 = measure_c4(rank, world, dev, max(3, min(args.steps, 10)), args.exchange, not args.no_touched)
     elif world == 1 and not args.no_extras:
         extras = single_gpu_extras(dev)
     parallelism_peer = check is not None

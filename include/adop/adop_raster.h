@@ -19,6 +19,7 @@ extern "C" {
 #define ADOP_MAX_CHANNELS 32 /* bound of the argument checks; the kernels are built for 3, 4, 8 and 16 channels and the
                                 entry points return ADOP_ERR_UNSUPPORTED (with a message) for other counts */
 #define ADOP_MAX_OCAM_POLY 16
+#define ADOP_TOUCHED_CHUNK 256
 
 typedef enum adop_status
 {
@@ -183,6 +184,11 @@ typedef struct adop_backward_io
     /* optional [env_h,env_w,C] scratch (C a multiple of 4): the environment-map gradient is summed there with one
      * vector atomic per bilinear tap and added to grad_env_map [C,env_h,env_w] at the end of the call. */
     float* grad_env_map_interleaved;
+    /* optional, [ceil(T / ADOP_TOUCHED_CHUNK)] and [ceil(N / ADOP_TOUCHED_CHUNK)] bytes: set to 1 for every chunk of
+     * ADOP_TOUCHED_CHUNK consecutive texels / points that this call adds a descriptor / point gradient to (zeroed first
+     * unless accumulate). adop_peer_reduce_gradients uses them to skip what a rank did not touch. */
+    uint8_t* touched_texels;
+    uint8_t* touched_points;
 } adop_backward_io;
 
 const char* adop_status_string(adop_status s);
@@ -197,9 +203,11 @@ void adop_render_params_default(adop_render_params* p);
 size_t adop_raster_workspace_bytes(int32_t w, int32_t h, int32_t layers, int32_t channels);
 /* The same plus 16 bytes per point and view of a group of up to four views (about 64 N bytes): with a workspace of at
  * least this size the depth prepass also hands the projected in-image points of each view to the blend kernel, which then
- * neither reads the cloud again nor projects a second time. Same results either way. On the benchmark configuration the
- * extra stream costs the prepass more than it saves the blend kernel (measured), so the host layers of this library ask
- * for the small workspace; the option pays when few of the points land in the image. */
+ * neither reads the cloud again nor projects a second time. Same results either way. Whether it pays depends on the view:
+ * measured, the forward pass of a 100 M point cloud through the omnidirectional model gets a third faster (expensive
+ * projection, a small part of the cloud in the image), while on 1080p pinhole training views with 70 % of a 10 M point cloud
+ * in the image the extra stream costs the prepass more than it saves the blend kernel. The host layers of this library
+ * ask for it when a batch has omnidirectional views. */
 size_t adop_raster_workspace_bytes_full(int32_t num_points, int32_t num_views, int32_t w, int32_t h, int32_t layers,
                                         int32_t channels);
 
@@ -291,9 +299,12 @@ typedef struct adop_peer_layout
     int32_t intrinsics_cols;
     int32_t env_h, env_w;    /* environment-map gradient [C,env_h,env_w] f32 */
     int32_t background;      /* 1: background gradient [C] f32 */
-    int32_t reserved;
+    int32_t touched;         /* 1: the block also holds adop_backward_io's touched_texels / touched_points flags, and the
+                                reduce kernel reads a peer's descriptor / point gradients only where that peer set them */
     size_t off_texture, off_points, off_pose, off_count_pose, off_intrinsics, off_count_intrinsics, off_background,
         off_env_map;
+    size_t off_touched_texels, off_touched_points; /* one byte per ADOP_TOUCHED_CHUNK texels / points */
+    size_t off_gathered;     /* scratch of the reduce call: which ranks touched each chunk of the owned ranges */
     size_t total_bytes;
 } adop_peer_layout;
 /* Fills the offsets (256-byte aligned) and total_bytes from the counts. */

@@ -47,7 +47,7 @@ def main():
     C_, T = scene.texture.shape
     lay = adist.peer_layout(C_, T, scene.position.shape[0], num_images=ref["pose"].shape[0],
                             num_cameras=ref["intrinsics"].shape[0], intrinsics_cols=ref["intrinsics"].shape[1],
-                            env_hw=tuple(scene.env_map.shape[1:]))
+                            env_hw=tuple(scene.env_map.shape[1:]), touched=True)
     ex = adist.PeerGradientExchange(lay, dev)
     for step in range(2):  # the second pass re-uses the blocks: covers the barrier after the kernel
         fwd = ras.forward(scene, views, params, L)

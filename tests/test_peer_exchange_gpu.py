@@ -112,6 +112,63 @@ def test_reduce_kernel_with_all_blocks_on_one_gpu(cuda_lib, channels, world, tex
         assert torch.equal(res_env, total("env_map"))
 
 
+@pytest.mark.parametrize("channels,world,texels,points", [(4, 3, 5000, 3333), (3, 2, 1000, 0), (8, 8, 40_000, 20_001)])
+def test_reduce_kernel_skips_what_a_rank_did_not_touch(cuda_lib, channels, world, texels, points):
+    """Blocks with touched flags: every rank has gradients only in some chunks of 256 texels / points (zeros elsewhere, as
+    the backward pass leaves them) and flags exactly those chunks. The sums must equal the plain sums of all blocks. To
+    show that unflagged chunks are really not read, a second run poisons them with NaN: the result must not change."""
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(channels * 7 + world)
+    lay = adist.peer_layout(channels, texels, points, num_images=2, num_cameras=1, intrinsics_cols=13, touched=True)
+    chunk = 256
+    blocks = [_fill_block(lay, dev, gen) for _ in range(world)]
+    flags = []
+    for raw, t in blocks:
+        tc, pc = (texels + chunk - 1) // chunk, (points + chunk - 1) // chunk
+        ft = torch.rand(tc, device=dev, generator=gen) < 0.5
+        fp = torch.rand(max(pc, 1), device=dev, generator=gen)[:pc] < 0.4
+        t["texture"][~ft.repeat_interleave(chunk)[:texels]] = 0
+        if points:
+            t["points"][~fp.repeat_interleave(chunk)[:points]] = 0
+        raw[lay.off_touched_texels:lay.off_touched_texels + tc] = ft.to(torch.uint8)
+        if points:
+            raw[lay.off_touched_points:lay.off_touched_points + pc] = fp.to(torch.uint8)
+        flags.append((ft, fp))
+    ptrs = (C.c_void_p * world)(*[b[0].data_ptr() for b in blocks])
+    tex_sum = sum(t["texture"] for _, t in blocks).t().contiguous()
+    pts_sum = sum(t["points"] for _, t in blocks) if points else None
+
+    def run_all():
+        res = []
+        for rank in range(world):
+            t_lo, t_hi = adist.peer_shard_range(texels, rank, world)
+            p_lo, p_hi = adist.peer_shard_range(points, rank, world)
+            out = capi.AdopPeerReduceOut()
+            r_tex = torch.full((channels, t_hi - t_lo), float("nan"), device=dev)
+            r_pts = torch.full((max(p_hi - p_lo, 1), 4), float("nan"), device=dev)
+            out.grad_texture_shard = r_tex.data_ptr()
+            out.grad_points_shard = r_pts.data_ptr() if p_hi > p_lo else None
+            out.normalize = 0
+            capi.check(cuda_lib.adop_peer_reduce_gradients(ptrs, world, rank, C.byref(lay), C.byref(out), None), "reduce")
+            torch.cuda.synchronize()
+            res.append((r_tex, r_pts[:p_hi - p_lo], (t_lo, t_hi), (p_lo, p_hi)))
+        return res
+
+    first = run_all()
+    for r_tex, r_pts, (t_lo, t_hi), (p_lo, p_hi) in first:
+        assert torch.allclose(r_tex, tex_sum[:, t_lo:t_hi], rtol=1e-6, atol=1e-6)
+        if points:
+            assert torch.allclose(r_pts, pts_sum[p_lo:p_hi], rtol=1e-6, atol=1e-6)
+    for (raw, t), (ft, fp) in zip(blocks, flags):
+        t["texture"][~ft.repeat_interleave(chunk)[:texels]] = float("nan")
+        if points:
+            t["points"][~fp.repeat_interleave(chunk)[:points]] = float("nan")
+    second = run_all()
+    for a, b in zip(first, second):
+        assert torch.equal(a[0], b[0]) and (not points or torch.equal(a[1], b[1]))
+
+
 @pytest.mark.parametrize("channels,env_hw", [(3, (1, 1)), (3, (1, 2)), (4, (1, 1))])
 def test_reduce_kernel_with_only_a_tiny_environment_map(cuda_lib, channels, env_hw):
     """The only work is an environment-map gradient of one to three floats (fewer than one 16-byte vector): the launch
