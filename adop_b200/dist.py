@@ -68,6 +68,51 @@ def exchange_gradients(grads, group=None):
     return out
 
 
+class ShardedParameterUpdate:
+    """The optimiser step of the NCCL path (what PeerParameters.step does in one kernel over peer memory, here as library
+    collectives; also what runs under gloo in the CPU tests): every rank applies the reference's optimisers to the shard
+    of the flattened tensors it owns after exchange_gradients - torch Adam for the descriptors, SGD for the point positions
+    (NeuralScene.cpp:76-107, 204-240) - and the updated shards are all-gathered into every rank's replica. Adam moments
+    exist for the owned shard only.
+
+        upd = ShardedParameterUpdate(texture, points)     # this rank's replicas, updated in place
+        ex = exchange_gradients(backward_outputs)
+        upd.step(ex, lr_texture=0.08, lr_points=0.005)"""
+
+    def __init__(self, texture, points=None, group=None, betas=(0.9, 0.999), eps=1e-8):
+        self.texture, self.points, self.group = texture, points, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        lo, hi = shard_range(texture.numel(), self.rank, self.world)
+        self._tex_shard = texture.detach().reshape(-1)[lo:hi].clone().requires_grad_(True)
+        self._adam = torch.optim.Adam([self._tex_shard], lr=1.0, betas=betas, eps=eps)
+        if points is not None and not points_shard_is_aligned(points.shape[0], self.world):
+            raise ValueError("the point shards of this rank count do not start on point boundaries")
+
+    def _all_gather_into(self, full, shard):
+        flat = full.reshape(-1)
+        per = (flat.numel() + self.world - 1) // self.world
+        mine = flat.new_zeros(per)
+        mine[:shard.numel()] = shard
+        parts = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(parts, mine, group=self.group)
+        flat.copy_(torch.cat(parts)[:flat.numel()])
+
+    def step(self, exchanged, lr_texture, lr_points=0.0):
+        for g in self._adam.param_groups:
+            g["lr"] = lr_texture
+        self._tex_shard.grad = exchanged["texture_shard"].reshape(-1).to(self._tex_shard.dtype)
+        self._adam.step()
+        with torch.no_grad():
+            self._all_gather_into(self.texture, self._tex_shard.detach())
+            if self.points is not None and lr_points != 0.0 and exchanged.get("points_shard") is not None:
+                g = exchanged["points_shard"].reshape(-1, 4)   # sums of x, y, z and the contribution count
+                lo, hi = shard_range(self.points.numel(), self.rank, self.world)
+                p = self.points.reshape(-1)[lo:hi].reshape(-1, 4).clone()
+                cnt = g[:, 3:4]
+                p[:, :3] -= lr_points * torch.where(cnt > 0, g[:, :3] / cnt.clamp(min=1e-30), g[:, :3])  # NormalizeGradient, then SGD
+                self._all_gather_into(self.points, p.reshape(-1))
+
+
 def points_shard_is_aligned(num_points, world):
     """True when every rank's share of the flattened [N,4] tensor starts on a point boundary."""
     per = (num_points * 4 + world - 1) // world

@@ -69,6 +69,54 @@ def test_view_sharded_gradient_exchange_world_size_2(oracle, tmp_path):
     assert np.allclose(np.load(tmp_path / "env.npy"), ref["env_map"], rtol=1e-4, atol=1e-5)
 
 
+def _update_worker(rank, world, port, result_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    g = torch.Generator().manual_seed(3)
+    C_, T, N = 4, 1001, 600
+    texture = torch.randn((C_, T), generator=g)
+    points = torch.randn((N, 4), generator=g)
+    upd = adist.ShardedParameterUpdate(texture, points)
+    for step in range(3):
+        gr = torch.Generator().manual_seed(100 * step + rank)   # every rank has gradients of its own views
+        grads = {"texture": torch.randn((C_, T), generator=gr), "points": torch.randn((N, 4), generator=gr)}
+        grads["points"][:, 3] = torch.randint(0, 3, (N,), generator=gr).float()
+        upd.step(adist.exchange_gradients(grads), lr_texture=0.05, lr_points=0.01)
+    np.save(os.path.join(result_dir, f"texture_{rank}.npy"), texture.numpy())
+    np.save(os.path.join(result_dir, f"points_{rank}.npy"), points.numpy())
+    dist.destroy_process_group()
+
+
+def test_sharded_optimiser_step_and_all_gather_world_size_2(tmp_path):
+    """ShardedParameterUpdate under gloo: after three steps every rank's replicas equal what torch.optim.Adam (descriptors)
+    and SGD on the normalised point gradients make of the full tensors with the gradients summed over the ranks."""
+    world = 2
+    port = 29500 + ((os.getpid() + 7) % 2000)
+    mp.spawn(_update_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    g = torch.Generator().manual_seed(3)
+    C_, T, N = 4, 1001, 600
+    texture = torch.randn((C_, T), generator=g).requires_grad_(True)
+    points = torch.randn((N, 4), generator=g)
+    adam = torch.optim.Adam([texture], lr=0.05)
+    for step in range(3):
+        tg, pg = torch.zeros((C_, T)), torch.zeros((N, 4))
+        for rank in range(world):
+            gr = torch.Generator().manual_seed(100 * step + rank)
+            tg += torch.randn((C_, T), generator=gr)
+            p = torch.randn((N, 4), generator=gr)
+            p[:, 3] = torch.randint(0, 3, (N,), generator=gr).float()
+            pg += p
+        texture.grad = tg
+        adam.step()
+        cnt = pg[:, 3:4]
+        points[:, :3] -= 0.01 * torch.where(cnt > 0, pg[:, :3] / cnt.clamp(min=1e-30), pg[:, :3])
+    for rank in range(world):
+        assert np.allclose(np.load(tmp_path / f"texture_{rank}.npy"), texture.detach().numpy(), rtol=1e-5, atol=1e-6)
+        assert np.allclose(np.load(tmp_path / f"points_{rank}.npy"), points.numpy(), rtol=1e-5, atol=1e-6)
+    assert np.array_equal(np.load(tmp_path / "texture_0.npy"), np.load(tmp_path / "texture_1.npy"))
+
+
 def test_shard_helpers():
     assert adist.shard_views(list(range(10)), 0, 4) == [0, 1, 2]
     assert adist.shard_views(list(range(10)), 3, 4) == [8, 9]
