@@ -352,13 +352,17 @@ class Tonemapper:
                        "adop_tonemap_forward")
         return out
 
-    def backward(self, x, grad_out, frame_index=None, uv=None):
+    def backward(self, x, grad_out, frame_index=None, uv=None, want_response=True):
+        """Gradients for x and for every parameter tensor the tonemapper has; want_response=False leaves the response curve's
+        out (a fixed curve: the backward pass then has no histogram to build)."""
         p = self._params(x, frame_index, uv)
         g = capi.AdopTonemapGrads()
         res = dict(x=torch.empty_like(x))
         g.grad_x = res["x"].data_ptr()
         for name in ("exposure", "white_balance", "vignette", "response"):
             t = getattr(self, name)
+            if name == "response" and not want_response:
+                t = None
             res[name] = torch.empty_like(t) if t is not None else None
             setattr(g, "grad_" + name, res[name].data_ptr() if t is not None else None)
         g.num_frames = self.exposure.shape[0] if self.exposure is not None else (

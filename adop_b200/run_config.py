@@ -1,6 +1,6 @@
 """Run one of the benchmark configurations end to end on one GPU and print its timings as one JSON line.
 
-    python -m adop_b200.run_config c1|c2|c3|c4|c5 [--points N] [--views V] [--reps R]
+    python -m adop_b200.run_config c1|c2|c3|c4|c5|reorder|tonemap [--points N] [--views V] [--reps R]
 
 bench.py measures the headline configuration (c2) under the driver's contract; this runner covers the others:
 c1 (small cloud, 512x512), c3 (100 M points, omnidirectional camera, forward only, ms per frame), c4 (30 M points, 8 views),
@@ -74,9 +74,48 @@ def reorder(dev, args):
     return 0
 
 
+def tonemap(dev, args):
+    """The fused tonemapper on one 4K frame of uniformly random values (the worst case for the response-curve histogram of
+    the backward pass) and on a smooth frame: time per image and fraction of the HBM roofline (24 bytes per pixel forward,
+    36 backward), with and without the response-curve gradient."""
+    w, h = 3840, 2160
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+    exposure = torch.rand(1, device=dev, generator=g) * 4 - 2
+    wb = (1 + 0.05 * torch.randn((1, 3), device=dev, generator=g)).contiguous()
+    vig = torch.tensor([0.1, -0.05, 0.01, 0.0, 0.0], device=dev)
+    response = (torch.linspace(0, 1, 256, device=dev) ** (1 / 2.2)).repeat(3, 1).contiguous()
+    fi = torch.zeros(1, device=dev, dtype=torch.int32)
+    peak = 6542.7
+    out = {"config": "tonemap", "image": [w, h], "response_bins": 256}
+    yy, xx = torch.meshgrid(torch.linspace(0, 1, h, device=dev), torch.linspace(0, 1, w, device=dev), indexing="ij")
+    smooth = torch.stack([0.5 + 0.4 * torch.sin(6 * xx + 3 * yy), 0.5 + 0.4 * torch.cos(5 * yy), xx * yy]).unsqueeze(0)
+    frames = {"random": torch.rand((1, 3, h, w), device=dev, generator=g),
+              "smooth": (smooth + 0.01 * torch.rand((1, 3, h, w), device=dev, generator=g)).contiguous()}
+    go = torch.randn((1, 3, h, w), device=dev, generator=g)
+    for name, x in frames.items():
+        for label, resp in (("", response), ("_no_response_gradient", None)):
+            tm = Tonemapper((w, h), exposure=exposure, white_balance=wb, vignette=vig, response=response, leak=0.01)
+            if resp is None:
+                # same forward arithmetic, no histogram in the backward pass: the curve is not a trainable tensor here
+                bw = lambda: tm.backward(x, go, fi, want_response=False)
+            else:
+                bw = lambda: tm.backward(x, go, fi)
+            for _ in range(3):
+                bw()
+            t_b = statistics.median(timed(bw, args.reps))
+            out[f"{name}{label}_bwd_us"] = t_b * 1e3
+            out[f"{name}{label}_bwd_frac"] = 36 * w * h / (t_b * 1e-3) / 1e9 / peak
+        t_f = statistics.median(timed(lambda: tm.forward(x, fi), args.reps))
+        out[f"{name}_fwd_us"] = t_f * 1e3
+        out[f"{name}_fwd_frac"] = 24 * w * h / (t_f * 1e-3) / 1e9 / peak
+    print(json.dumps(out), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("config", choices=["c1", "c2", "c3", "c4", "c5", "reorder"])
+    ap.add_argument("config", choices=["c1", "c2", "c3", "c4", "c5", "reorder", "tonemap"])
     ap.add_argument("--points", type=int, default=None)
     ap.add_argument("--views", type=int, default=None)
     ap.add_argument("--reps", type=int, default=5)
@@ -86,6 +125,8 @@ def main():
     dev = torch.device("cuda:0")
     if args.config == "reorder":
         return reorder(dev, args)
+    if args.config == "tonemap":
+        return tonemap(dev, args)
     cfg = synth.make_config(args.config, n_points=args.points, n_views=args.views)
     meta, params, L = cfg["meta"], cfg["params"], cfg["num_layers"]
     forward_only = args.config == "c3"
