@@ -51,7 +51,7 @@ class AdopLayerBuffers(C.Structure):
 class AdopForwardIO(C.Structure):
     _fields_ = [("layers", AdopLayerBuffers * MAX_LAYERS), ("dropout_mask", C.c_void_p),
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("visible_list", C.c_void_p),
-                ("packed_depth", C.c_void_p * MAX_LAYERS)]
+                ("packed_depth", C.c_void_p * MAX_LAYERS), ("touched_points", C.c_void_p), ("touched_texels", C.c_void_p)]
 
 
 class AdopBackwardIO(C.Structure):
@@ -61,8 +61,7 @@ class AdopBackwardIO(C.Structure):
                 ("grad_intrinsics", C.c_void_p), ("count_intrinsics", C.c_void_p), ("grad_env_map", C.c_void_p),
                 ("accumulate", C.c_int32), ("normalize", C.c_int32),
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("visible_list", C.c_void_p),
-                ("grad_texture_interleaved", C.c_void_p), ("grad_env_map_interleaved", C.c_void_p),
-                ("touched_texels", C.c_void_p), ("touched_points", C.c_void_p)]
+                ("grad_texture_interleaved", C.c_void_p), ("grad_env_map_interleaved", C.c_void_p)]
 
 
 class AdopTonemapParams(C.Structure):

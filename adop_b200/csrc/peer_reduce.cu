@@ -3,7 +3,11 @@
 // and NormalizeGradient (PointRenderer.cu:1609-1637), as ONE kernel that reads every rank's gradient block with plain
 // peer loads over NVLink. The reference is single-GPU and has nothing of this.
 //
-// The kernel never waits for another GPU: the caller orders it between two stream-ordered collectives of its
+// With touched flags in the blocks (set by the forward pass where it listed points for the backward pass) a small kernel
+// first gathers, per chunk of the owned ranges, which ranks have anything there, and the reduce kernel reads a peer's
+// descriptor and point gradients only in those chunks: zeros do not cross NVLink.
+//
+// The kernels never wait for another GPU: the caller orders them between two stream-ordered collectives of its
 // communication library, so there is no spin loop here that could hang.
 #include <cstdio>
 #include <cstring>

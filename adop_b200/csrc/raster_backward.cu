@@ -180,19 +180,7 @@ struct BackwardTargets
     float* grad_intrinsics;   // row of this view's camera
     float* count_intrinsics;  // element of this view's camera
     const float* records;     // interleaved [I | G] per pyramid pixel, written by k_prepare_backward
-    // optional: one byte per kTouchedChunk texels / points, set where this call adds a gradient (the multi-GPU exchange
-    // skips the chunks that a rank left alone)
-    unsigned char* touched_texels;
-    unsigned char* touched_points;
 };
-
-// Sets the flag of element i's chunk. Thousands of threads mark the same few chunks: the flag is read first (a cached,
-// possibly stale value is fine: a stale 0 only repeats the store) so that the stores to one byte do not queue up.
-__device__ __forceinline__ void mark_touched(unsigned char* flags, int i)
-{
-    unsigned char* f = flags + (i >> kTouchedShift);
-    if (*f == 0) *f = 1;
-}
 
 template <int C>
 __device__ __forceinline__ void load_record(const float* records, size_t r, float* out)
@@ -446,13 +434,8 @@ __global__ void __launch_bounds__(kBlock) k_splat_backward_all(PointStreams pts,
         {
             if (ti < 0) ti = pts.index ? __ldg(pts.index + i) : i;
             add_descriptor_gradient<C>(bt.grad_texture, bt.grad_texture_interleaved, bt.num_texels, ti, dg);
-            if (bt.touched_texels) mark_touched(bt.touched_texels, ti);
         }
-        if (gp[3] > 0.f && bt.grad_points)
-        {
-            atomicAdd(bt.grad_points + i, make_float4(gp[0], gp[1], gp[2], gp[3]));
-            if (bt.touched_points) mark_touched(bt.touched_points, i);
-        }
+        if (gp[3] > 0.f && bt.grad_points) atomicAdd(bt.grad_points + i, make_float4(gp[0], gp[1], gp[2], gp[3]));
     }
     geo_block_reduce<MODEL>(&s_geo, acc, bt);
 }
@@ -748,11 +731,7 @@ __global__ void __launch_bounds__(kTileThreads, C <= 4 ? (DEEP ? 3 : 4) : (C <= 
                 pv.have_dg = false;
                 pv.gx = pv.gy = pv.cnt = 0.f;
                 visit_layers<C, 0, STRIDE, LMAX>(lt, s_tile, x0, y0, __int_as_float(e.z), __int_as_float(e.w), 1.f, pv);
-                if (pv.have_dg)
-                {
-                    add_descriptor_gradient<C>(bt.grad_texture, bt.grad_texture_interleaved, bt.num_texels, ti, pv.dg);
-                    if (bt.touched_texels) mark_touched(bt.touched_texels, ti);
-                }
+                if (pv.have_dg) add_descriptor_gradient<C>(bt.grad_texture, bt.grad_texture_interleaved, bt.num_texels, ti, pv.dg);
                 // the entry becomes the chain kernel's work item (every entry of this pass has been read into shared memory)
                 if (want_geo)
                     reinterpret_cast<float4*>(ent)[pass0 + sidx] = pv.cnt > 0.f ? make_float4(__int_as_float(i), pv.gx, pv.gy, pv.cnt) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -878,7 +857,7 @@ struct PinholeSums
     float cnt;
 };
 __device__ __forceinline__ void chain_pinhole_fast(const ViewCam& cam, bool check_normal, const ChainItem& it, float4* __restrict__ grad_points,
-                                                   unsigned char* __restrict__ touched_points, PinholeSums& a)
+                                                   PinholeSums& a)
 {
     const Rigid32& V = cam.V;
     V3 view;
@@ -933,11 +912,7 @@ __device__ __forceinline__ void chain_pinhole_fast(const ViewCam& cam, bool chec
     a.pose[4] += fmaf(view.z, gv.x, -view.x * gv.z);
     a.pose[5] += fmaf(view.x, gv.y, -view.y * gv.x);
     a.cnt += it.count;
-    if (grad_points)
-    {
-        atomicAdd(grad_points + it.id, make_float4(gp.x, gp.y, gp.z, it.count));
-        if (touched_points) mark_touched(touched_points, it.id);
-    }
+    if (grad_points) atomicAdd(grad_points + it.id, make_float4(gp.x, gp.y, gp.z, it.count));
 }
 
 // General form (used for the omnidirectional model): chain of one point's summed image-space gradient (already scaled
@@ -989,7 +964,7 @@ __device__ __forceinline__ void point_chain_part(const PointStreams& pts, const 
     auto chain_one = [&](const ChainItem& it)
     {
         if (MODEL == kPinholeDistortion)
-            chain_pinhole_fast(cam, check_normal, it, bt.grad_points, bt.touched_points, ps);
+            chain_pinhole_fast(cam, check_normal, it, bt.grad_points, ps);
         else
         {
             FetchedPoint f;
@@ -999,10 +974,7 @@ __device__ __forceinline__ void point_chain_part(const PointStreams& pts, const 
             V2 g; g.x = it.gx; g.y = it.gy;
             float gp[4];
             if (chain_gradient_sum<kOcam>(cam, kp, f, g, it.count, gp, reinterpret_cast<GeoAccum<kOcam>&>(acc)) && bt.grad_points)
-            {
                 atomicAdd(bt.grad_points + it.id, make_float4(gp[0], gp[1], gp[2], gp[3]));
-                if (bt.touched_points) mark_touched(bt.touched_points, it.id);
-            }
         }
     };
     constexpr int U = 2;  // items per thread and round: their dependent loads (item -> position) are in flight together
@@ -1263,8 +1235,6 @@ extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view
         if (io->count_intrinsics) ADOP_CUDA_TRY(cudaMemsetAsync(io->count_intrinsics, 0, sizeof(float) * s->num_cameras, st));
         if (io->grad_env_map && s->env_h > 0 && s->env_w > 0)
             ADOP_CUDA_TRY(cudaMemsetAsync(io->grad_env_map, 0, sizeof(float) * (size_t)C * s->env_h * s->env_w, st));
-        if (io->touched_texels) ADOP_CUDA_TRY(cudaMemsetAsync(io->touched_texels, 0, ((size_t)T + kTouchedChunk - 1) / kTouchedChunk, st));
-        if (io->touched_points) ADOP_CUDA_TRY(cudaMemsetAsync(io->touched_points, 0, ((size_t)N + kTouchedChunk - 1) / kTouchedChunk, st));
     }
 
     // environment-map gradient: summed in an [eh,ew,C] scratch with vector atomics when the caller gave one
@@ -1318,8 +1288,6 @@ extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view
         bt.grad_intrinsics = io->grad_intrinsics ? io->grad_intrinsics + (size_t)views[b].camera_index * cols : nullptr;
         bt.count_intrinsics = io->grad_intrinsics ? io->count_intrinsics + views[b].camera_index : nullptr;
         bt.records = reinterpret_cast<const float*>(static_cast<const char*>(io->workspace) + kCamRegionBytes);
-        bt.touched_texels = io->touched_texels;
-        bt.touched_points = io->touched_points;
         float* ge = env ? (env_inter ? io->grad_env_map_interleaved : io->grad_env_map) : nullptr;
         // the list's geometry (segments in use, entries per segment) sits in its header, written by the forward pass
         VisibleList vl = make_visible_list(const_cast<int32_t*>(io->visible_list), N, views[0].w, views[0].h, b);

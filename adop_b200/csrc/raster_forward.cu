@@ -270,7 +270,8 @@ template <int L, int C, bool PLAIN, bool CAND, bool EMIT>
 __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, ChunkSchedule sched, CandIn cs, const float* __restrict__ texture,
                                                    const float* __restrict__ texture_interleaved, int num_texels,
                                                    const ViewCam* __restrict__ camp, KernelParams kp, LayerTable lt, TileTable tt,
-                                                   float* __restrict__ accum, VisibleList vl)
+                                                   float* __restrict__ accum, VisibleList vl, unsigned char* __restrict__ touched_points,
+                                                   unsigned char* __restrict__ touched_texels)
 {
     static_assert(!CAND || PLAIN, "candidate records carry no drop-out radius");
     const ViewCam& cam = *camp;
@@ -383,12 +384,26 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, ChunkSche
             }
         }
     };
-    auto park_and_finish = [&](int4 e)
+    // chunk >= 0: all 32 points belong to that chunk of kBlock consecutive points; -1: they are candidates from anywhere
+    auto park_and_finish = [&](int4 e, int chunk)
     {
         const bool keep = e.y != 0;
         const unsigned vote = __ballot_sync(0xffffffffu, keep);
         if (vote)
         {
+            // the backward pass can add gradients only where a point was kept: one mark per warp and chunk
+            if (touched_points)
+            {
+                if (chunk >= 0)
+                {
+                    if (lane == 0) { touched_points[chunk] = 1; touched_texels[chunk] = 1; }
+                }
+                else if (keep)
+                {
+                    const int c = (int)(((unsigned)e.x & ~kEntryDropped) >> kTouchedShift);
+                    if (touched_points[c] == 0) { touched_points[c] = 1; touched_texels[c] = 1; }
+                }
+            }
             if (keep) park[n_parked + __popc(vote & ((1u << lane) - 1u))] = e;
             n_parked += __popc(vote);
             __syncwarp();
@@ -414,7 +429,7 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, ChunkSche
                 const float4 c = __ldcs(rec + k);
                 e = make_entry(__float_as_int(c.w), c);
             }
-            park_and_finish(e);
+            park_and_finish(e, -1);
         }
     }
     else
@@ -426,7 +441,7 @@ __global__ void __launch_bounds__(kBlock, 8) k_blend(PointStreams pts, ChunkSche
             const int i = chunk * kBlock + threadIdx.x;
             int4 e = make_int4(0, 0, 0, 0);
             if (i < pts.n) e = make_entry(i, __ldg(pts.position + i));
-            park_and_finish(e);
+            park_and_finish(e, chunk);
         }
     }
     if (n_parked > 0) finish(lane < n_parked, lane < n_parked ? park[lane] : make_int4(0, 0, 0, 0));
@@ -555,6 +570,8 @@ struct ForwardPlan
     size_t cand_view_stride;  // records per candidate stream
     TileTable tiles;
     PointStreams outliers;  // the optional second cloud (n = 0: none): forward only, never listed
+    unsigned char* touched_points;  // optional flags per chunk of kTouchedChunk points / texels (null: none)
+    unsigned char* touched_texels;
 };
 
 template <int L, int C, bool PLAIN>
@@ -629,7 +646,7 @@ static adop_status launch_view_forward_impl(const PointStreams& pts, const adop_
     ci.seg_cap = seg_cap;
 #define ADOP_BLEND(CAND_, EMIT_)                                                                                                 \
     ADOP_LAUNCH("k_blend", st, (k_blend<L, C, PLAIN, CAND_, EMIT_><<<grid_blend, kBlock, 0, st>>>(                               \
-                                   pts, make_chunk_schedule(pts.n, grid_blend), ci, s->texture, s->texture_interleaved, s->num_texels, cam, kp, lt, plan.tiles, plan.accum, vl)))
+                                   pts, make_chunk_schedule(pts.n, grid_blend), ci, s->texture, s->texture_interleaved, s->num_texels, cam, kp, lt, plan.tiles, plan.accum, vl, emit ? plan.touched_points : nullptr, emit ? plan.touched_texels : nullptr)))
     if (cand)
     {
         if (emit) ADOP_BLEND(kCand, true); else ADOP_BLEND(kCand, false);
@@ -649,7 +666,7 @@ static adop_status launch_view_forward_impl(const PointStreams& pts, const adop_
         VisibleList no_list = make_visible_list(nullptr, op.n, plan.w, plan.h, view);
         ADOP_LAUNCH("k_blend", st, (k_blend<L, C, PLAIN, false, false><<<og, kBlock, 0, st>>>(
                                        op, make_chunk_schedule(op.n, og), no_cand, s->texture, s->texture_interleaved, s->num_texels, cam, kp, lt,
-                                       plan.tiles, plan.accum, no_list)));
+                                       plan.tiles, plan.accum, no_list, nullptr, nullptr)));
     }
 #undef ADOP_BLEND
     unsigned total = lt.rec_off[kMaxLayers];
@@ -837,6 +854,20 @@ extern "C" adop_status adop_raster_forward(const adop_scene* s, const adop_view*
     plan.w = w0; plan.h = h0;
     plan.num_views = B;
     plan.tiles = make_tile_table(w0, h0, N);
+    // flags "the backward pass of these views can touch this chunk": zeroed here, set by the blend kernel where it lists a
+    // point; descriptor columns follow the point numbers only without an index array, else every texel chunk counts as touched
+    static_assert(kTouchedChunk == kBlock, "the blend kernel marks one flag per chunk of kBlock points");
+    if ((io->touched_points != nullptr) != (io->touched_texels != nullptr) || (io->touched_points && !io->visible_list))
+        return ADOP_ERR_INVALID_ARGUMENT;
+    plan.touched_points = io->touched_points;
+    plan.touched_texels = io->touched_texels;
+    if (io->touched_points)
+    {
+        const size_t t_chunks = ((size_t)s->num_texels + kTouchedChunk - 1) / kTouchedChunk;
+        ADOP_CUDA_TRY(cudaMemsetAsync(io->touched_points, 0, ((size_t)N + kTouchedChunk - 1) / kTouchedChunk, st));
+        ADOP_CUDA_TRY(cudaMemsetAsync(io->touched_texels, s->index ? 1 : 0, t_chunks, st));
+        if (s->index) plan.touched_texels = io->touched_points;  // the kernel's second store then repeats the first
+    }
     plan.outliers.position = reinterpret_cast<const float4*>(s->outlier_position);
     plan.outliers.normal = s->outlier_normal;
     plan.outliers.index = s->outlier_index;

@@ -135,9 +135,9 @@ class _DeviceSpan:
 def peer_layout(channels, num_texels, num_points=0, num_images=0, num_cameras=0, intrinsics_cols=0, env_hw=(0, 0),
                 background=True, touched=False):
     """adop_peer_layout for these tensor sizes (0 = tensor not exchanged); the same call on every rank.
-    touched: the blocks also carry the backward pass's flags "a gradient was added in this chunk of 256 texels / points",
-    and the reduce kernel reads a peer's descriptor / point gradients only where that peer set them (the flags are part of
-    PeerGradientExchange.backward_outputs(), so the backward pass fills them)."""
+    touched: the blocks also carry the forward pass's flags "the backward pass of this rank's views can add a gradient in
+    this chunk of 256 points / texels", and the reduce kernel reads a peer's descriptor / point gradients only where that
+    peer set them (PeerGradientExchange.touched_flags() are the tensors to hand to PointRasterizer.forward)."""
     from . import capi
     import ctypes as C
     lay = capi.AdopPeerLayout()
@@ -283,10 +283,11 @@ class PeerGradientExchange:
         o["count_intrinsics"] = self._span(lay.off_count_intrinsics, (lay.num_cameras,), "<f4", f32)
         o["background"] = self._span(lay.off_background, (lay.channels if lay.background else 0,), "<f4", f32)
         o["env_map"] = self._span(lay.off_env_map, (lay.channels, lay.env_h, lay.env_w), "<f4", f32)
+        self._touched = None
         if lay.touched:
             chunk = 256
-            o["touched_texels"] = self._span(lay.off_touched_texels, ((lay.num_texels + chunk - 1) // chunk,), "|u1", torch.uint8)
-            o["touched_points"] = self._span(lay.off_touched_points, ((lay.num_points + chunk - 1) // chunk,), "|u1", torch.uint8)
+            self._touched = (self._span(lay.off_touched_points, ((lay.num_points + chunk - 1) // chunk,), "|u1", torch.uint8),
+                             self._span(lay.off_touched_texels, ((lay.num_texels + chunk - 1) // chunk,), "|u1", torch.uint8))
         return o
 
     def _make_results(self):
@@ -304,6 +305,12 @@ class PeerGradientExchange:
         r["background"] = torch.empty((lay.channels,), device=dev) if lay.background else None
         r["env_map"] = torch.empty((lay.channels, lay.env_h, lay.env_w), device=dev) if lay.env_h * lay.env_w > 0 else None
         return r
+
+    def touched_flags(self):
+        """(points, texels) byte flags inside this rank's block, or None when the layout has none: pass them as `touched=` to
+        the step's PointRasterizer.forward call, which marks the chunks its views can give gradients to; reduce() on every
+        rank then reads this rank's descriptor and point gradients only there."""
+        return self._touched
 
     def backward_outputs(self):
         """The `out=` dict for PointRasterizer.backward: tensors inside this rank's block (texture stays [T,C])."""

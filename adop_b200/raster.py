@@ -166,11 +166,13 @@ class PointRasterizer:
         return self._ws
 
     def forward(self, scene, views, params, num_layers, dropout_mask=None, out=None, record_visible=True,
-                refresh_descriptors=True, packed_depth=False):
+                refresh_descriptors=True, packed_depth=False, touched=None):
         """BlendPointCloudForward (PointRenderer.cu:1389-1531). `views`: list of dicts or an AdopView array.
 
         Returns a ForwardResult; result.colors + result.masks is the reference's return list.
-        `out`: a previous ForwardResult whose tensors are reused (no allocation in steady state)."""
+        `out`: a previous ForwardResult whose tensors are reused (no allocation in steady state).
+        `touched`: optional (points, texels) uint8 tensors of ceil(N / 256) and ceil(T / 256) flags that the call fills: 1
+        where the backward pass of these views can add a gradient (dist.PeerGradientExchange.touched_flags())."""
         va = views if isinstance(views, C.Array) else capi.make_views(views)
         B = len(va)
         w, h = va[0].w, va[0].h
@@ -209,6 +211,8 @@ class PointRasterizer:
             io.workspace = ws.data_ptr()
             io.workspace_bytes = self._ws_bytes
             io.visible_list = out.visible.data_ptr() if out.visible is not None else None
+            if touched is not None:
+                io.touched_points, io.touched_texels = _tptr(touched[0]), _tptr(touched[1])
             if out.packed is not None:
                 for l in range(num_layers):
                     io.packed_depth[l] = out.packed[l].data_ptr()
@@ -262,8 +266,6 @@ class PointRasterizer:
             io.grad_pose, io.count_pose = p("pose"), p("count_pose")
             io.grad_intrinsics, io.count_intrinsics = p("intrinsics"), p("count_intrinsics")
             io.grad_env_map = p("env_map")
-            # optional byte flags "a gradient was added in this chunk of 256 texels / points" (the multi-GPU exchange reads them)
-            io.touched_texels, io.touched_points = p("touched_texels"), p("touched_points")
             io.accumulate = 0
             io.normalize = 1 if normalize else 0
             ws = self._workspace(va[0].w, va[0].h, L, sc.channels, sc.num_points, B)

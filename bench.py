@@ -327,9 +327,10 @@ def measure_c4(rank, world, dev, steps, exchange, touched=True):
             bwd = peer.backward_outputs()
         except capi.AdopError:
             peer = None
+    touched_flags = peer.touched_flags() if peer is not None else None
 
     def step():
-        ras.forward(scene, views, params, L, out=fwd)
+        ras.forward(scene, views, params, L, out=fwd, touched=touched_flags)
         ras.backward(scene, params, fwd, grads, want_env=True, normalize=False, out=bwd)
         if peer is not None:
             peer.reduce()
@@ -457,6 +458,7 @@ def main():
         except capi.AdopError as e:
             if rank == 0:
                 print(f"bench: {e}; using the NCCL exchange", file=sys.stderr, flush=True)
+    touched_flags = peer.touched_flags() if peer is not None else None
     final = {}  # the step's final small gradients (what the end-to-end loop reads back)
 
     def exchange():
@@ -475,7 +477,7 @@ def main():
             final.update(bwd)
 
     def step():
-        ras.forward(scene, views, params, L, out=fwd)
+        ras.forward(scene, views, params, L, out=fwd, touched=touched_flags)
         ras.backward(scene, params, fwd, grads_dev, want_env=True, normalize=normalize_local, out=bwd)
         exchange()
 
@@ -543,7 +545,7 @@ def main():
             slot = k & 1
             if k + 1 < n_steps:
                 start_copy(slot ^ 1)
-            ras.forward(scene, views, params, L, out=fwd)
+            ras.forward(scene, views, params, L, out=fwd, touched=touched_flags)
             main_stream.wait_event(copied[slot])
             ras.backward(scene, params, fwd, staged[slot], want_env=True, normalize=normalize_local, out=bwd)
             consumed[slot].record(main_stream)
@@ -566,14 +568,14 @@ def main():
     # ---- per-kernel times (CUDA events around every launch, on the launching stream) and the roofline -----------------
     capi.profile_enable(True)
     for _ in range(max(1, min(args.steps, 5))):
-        ras.forward(scene, views, params, L, out=fwd)
+        ras.forward(scene, views, params, L, out=fwd, touched=touched_flags)
         ras.backward(scene, params, fwd, grads_dev, want_env=True, normalize=normalize_local, out=bwd)
         if peer is not None:
             peer.reduce()
     torch.cuda.synchronize()
     ktimes = capi.profile_collect()
     capi.profile_enable(False)
-    ras.forward(scene, views, params, L, out=fwd)
+    ras.forward(scene, views, params, L, out=fwd, touched=touched_flags)
     torch.cuda.synchronize()
     # U_v: points of the view with at least one accepted layer. The forward pass records (point, layer) splats; the
     # points accepted on the finest layer are a lower bound of U_v, the splat count an upper bound; the lower bound is used.

@@ -403,6 +403,15 @@ ADOP_HD V2 ocam_project(V3 v, const Ocam& o, float cutoff, float* depth, float* 
     float l = fmaxf(sqrtf(l2), 1.0e-12f);
     float il = reciprocal(l);
     float t = -v.z * il;
+    if (!J_p && !J_aff && t > cutoff)
+    {
+        // rejected (see below) and nobody wants the Jacobians: the angle and the polynomial need not be evaluated. On the
+        // 100 M point viewer configuration this is more than half of the cloud.
+        *depth = 0.f;
+        V2 none;
+        none.x = none.y = 0.f;
+        return none;
+    }
     float theta = atan_f(t);
     float rho = 0.f, drho = 0.f;
     for (int i = o.npoly - 1; i >= 0; --i)

@@ -141,6 +141,13 @@ typedef struct adop_forward_io
      * the 32-bit depth buffer cannot tell and which does not depend on the order the GPU visits the points in.
      * Empty pixels hold (bits of 100000.0f << 32 | 0xFFFFFFFF). One extra pass over the points per view. */
     uint64_t* packed_depth[ADOP_MAX_LAYERS];
+    /* optional, [ceil(N / ADOP_TOUCHED_CHUNK)] and [ceil(T / ADOP_TOUCHED_CHUNK)] bytes (both or none; needs visible_list):
+     * zeroed, then set to 1 for every chunk of ADOP_TOUCHED_CHUNK consecutive points in which a view of this call listed a
+     * point for the backward pass, i.e. the only chunks in which the backward pass of these views can add a point or
+     * descriptor gradient. The texel flags are the same flags when the scene has no index array (descriptor column =
+     * point number) and all 1 otherwise. adop_peer_reduce_gradients uses them to skip what a rank did not touch. */
+    uint8_t* touched_points;
+    uint8_t* touched_texels;
 } adop_forward_io;
 
 /* Gradients (outputs) follow the reference's order {texture, background, points, pose tangents, intrinsics}
@@ -184,11 +191,6 @@ typedef struct adop_backward_io
     /* optional [env_h,env_w,C] scratch (C a multiple of 4): the environment-map gradient is summed there with one
      * vector atomic per bilinear tap and added to grad_env_map [C,env_h,env_w] at the end of the call. */
     float* grad_env_map_interleaved;
-    /* optional, [ceil(T / ADOP_TOUCHED_CHUNK)] and [ceil(N / ADOP_TOUCHED_CHUNK)] bytes: set to 1 for every chunk of
-     * ADOP_TOUCHED_CHUNK consecutive texels / points that this call adds a descriptor / point gradient to (zeroed first
-     * unless accumulate). adop_peer_reduce_gradients uses them to skip what a rank did not touch. */
-    uint8_t* touched_texels;
-    uint8_t* touched_points;
 } adop_backward_io;
 
 const char* adop_status_string(adop_status s);
@@ -299,8 +301,8 @@ typedef struct adop_peer_layout
     int32_t intrinsics_cols;
     int32_t env_h, env_w;    /* environment-map gradient [C,env_h,env_w] f32 */
     int32_t background;      /* 1: background gradient [C] f32 */
-    int32_t touched;         /* 1: the block also holds adop_backward_io's touched_texels / touched_points flags, and the
-                                reduce kernel reads a peer's descriptor / point gradients only where that peer set them */
+    int32_t touched;         /* 1: the block also holds adop_forward_io's touched_points / touched_texels flags of the step, and
+                                the reduce kernel reads a peer's descriptor / point gradients only where that peer set them */
     size_t off_texture, off_points, off_pose, off_count_pose, off_intrinsics, off_count_intrinsics, off_background,
         off_env_map;
     size_t off_touched_texels, off_touched_points; /* one byte per ADOP_TOUCHED_CHUNK texels / points */

@@ -50,7 +50,7 @@ def main():
                             env_hw=tuple(scene.env_map.shape[1:]), touched=True)
     ex = adist.PeerGradientExchange(lay, dev)
     for step in range(2):  # the second pass re-uses the blocks: covers the barrier after the kernel
-        fwd = ras.forward(scene, views, params, L)
+        fwd = ras.forward(scene, views, params, L, touched=ex.touched_flags())
         ras.backward(scene, params, fwd, grads, want_env=True, normalize=False, out=ex.backward_outputs())
         res = ex.reduce()
         torch.cuda.synchronize()
@@ -96,7 +96,7 @@ def main():
     ref_xyz = ref_scene.position[:, :3].clone().requires_grad_(True)
     adam, sgd = torch.optim.Adam([ref_tex], lr=0.02), torch.optim.SGD([ref_xyz], lr=1e-4)
     for step in range(3):
-        fwd = ras.forward(live, views, params, L)
+        fwd = ras.forward(live, views, params, L, touched=ex.touched_flags())
         ras.backward(live, params, fwd, grads, want_env=True, normalize=False, out=ex.backward_outputs())
         res = ex.reduce()
         pp.step(res, lr_texture=0.02, lr_points=1e-4)

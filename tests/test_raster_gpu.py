@@ -257,6 +257,40 @@ def test_outlier_cloud_argument_checks(cuda_lib):
         r.forward(scene, cfg["views"], cfg["params"], 4)
 
 
+@pytest.mark.parametrize("with_index", [False, True])
+def test_touched_flags_cover_every_chunk_that_gets_a_gradient(cuda_lib, with_index):
+    """The forward pass can flag the chunks of 256 consecutive points in which it listed a point for the backward pass. Every
+    chunk in which the backward pass of the same views then adds a point or descriptor gradient must carry its flag (the
+    multi-GPU exchange does not read unflagged chunks), chunks the views cannot see stay unflagged, and with an index
+    array (descriptor columns in another order than the points) every texel chunk counts as touched."""
+    cfg = synth.make_config("c2", n_points=400_000, n_views=2, size=(320, 180), seed=12)
+    a = cfg["arrays"]
+    n = len(a["position"])
+    if with_index:
+        a["index"] = np.random.default_rng(0).permutation(n).astype(np.int32)
+    scene = to_scene(a)
+    chunks = (n + 255) // 256
+    flags_p = torch.full((chunks,), 7, dtype=torch.uint8, device="cuda:0")
+    flags_t = torch.full((chunks,), 7, dtype=torch.uint8, device="cuda:0")
+    r = PointRasterizer("cuda:0")
+    fwd = r.forward(scene, cfg["views"], cfg["params"], 4, touched=(flags_p, flags_t))
+    grads = [torch.from_numpy(g).cuda() for g in synth.upstream_gradients(cfg["meta"])]
+    bwd = r.backward(scene, cfg["params"], fwd, grads, normalize=False)
+    torch.cuda.synchronize()
+    assert set(flags_p.unique().tolist()) <= {0, 1}
+    pad = chunks * 256 - n
+    got_p = torch.nn.functional.pad(bwd["points"][:, 3] > 0, (0, pad)).view(chunks, 256).any(dim=1)
+    got_t = torch.nn.functional.pad((bwd["texture"] != 0).any(dim=0), (0, pad)).view(chunks, 256).any(dim=1)
+    assert int(got_p.sum()) > 100 and int(got_t.sum()) > 100
+    assert not bool((got_p & (flags_p == 0)).any()), "a chunk with point gradients is not flagged"
+    assert not bool((got_t & (flags_t == 0)).any()), "a chunk with descriptor gradients is not flagged"
+    assert 0.05 < float((flags_p != 0).float().mean()) < 0.95     # two views of an orbit do not see everything
+    if with_index:
+        assert bool((flags_t == 1).all())
+    else:
+        assert torch.equal(flags_t, flags_p)
+
+
 def test_unusable_list_falls_back_to_all_points(oracle, cuda_lib):
     """A list whose header says that it is not usable: the backward pass finds the mark on the device (no host round
     trip), its tile kernels return at once and the all-points kernels behind them do the work, with the same result."""
