@@ -127,7 +127,8 @@ __global__ void __launch_bounds__(256) k_tonemap_forward(ToneArgs a, const float
                     if (a.leak > 0.f)
                     {
                         if (v < 0.f) leak_add = v * a.leak;
-                        if (v > 1.f) leak_add = -a.leak / sqrtf(fabsf(v) + 1e-4f) + a.leak;
+                        // reciprocal square root of the hardware (2 ulp): the soft knee above 1 needs no correctly rounded division
+                        if (v > 1.f) leak_add = fmaf(-a.leak, rsqrtf(fabsf(v) + 1e-4f), a.leak);
                     }
                     const float t = fminf(fmaxf(v, 0.f), 1.f) * Km1;
                     const int i0 = (int)t;  // t >= 0: truncation is the floor
@@ -250,15 +251,14 @@ __global__ void __launch_bounds__(256, 3) k_tonemap_backward(ToneArgs a, const f
         float scale = 0.f;  // 0: this round adds to the float histogram directly
         if (want_resp)
         {
-            float m = 0.f;
-            bool odd = false;  // a NaN anywhere: fmaxf would drop it
+            // the bit patterns of non-negative floats order like the floats, with the NaNs above infinity: an integer
+            // maximum keeps a NaN anywhere in the round visible (fmaxf would drop it)
+            unsigned mi = 0u;
 #pragma unroll
             for (int c = 0; c < 3; ++c)
 #pragma unroll
-                for (int k = 0; k < VEC; ++k) { m = fmaxf(m, fabsf(go[c][k])); odd = odd || !(fabsf(go[c][k]) <= 3.0e38f); }
-            if (odd) m = __int_as_float(0x7f800000);
-            // non-negative floats order like their bit patterns
-            const float M = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(m)));
+                for (int k = 0; k < VEC; ++k) mi = max(mi, __float_as_uint(go[c][k]) & 0x7fffffffu);
+            const float M = __uint_as_float(__reduce_max_sync(0xffffffffu, mi));
             const int e = (int)((__float_as_uint(M) >> 23) & 0xffu) - 127;
             if (M <= 3.0e38f && e >= -100)
             {
@@ -309,7 +309,7 @@ __global__ void __launch_bounds__(256, 3) k_tonemap_backward(ToneArgs a, const f
                         if (a.leak > 0.f)
                         {
                             if (v < 0.f) dleak = a.leak;
-                            if (v > 1.f) { float q = fabsf(v) + 1e-4f; dleak = 0.5f * a.leak / (q * sqrtf(q)); }
+                            if (v > 1.f) { const float r = rsqrtf(fabsf(v) + 1e-4f); dleak = 0.5f * a.leak * (r * r * r); }
                         }
                         const float t = fminf(fmaxf(v, 0.f), 1.f) * Km1;
                         const int i0 = (int)t;  // t >= 0: truncation is the floor
