@@ -217,8 +217,8 @@ __global__ void __launch_bounds__(kBlock) k_radix_scan(unsigned* __restrict__ da
 //   1. every warp counts its digits (match.any per round, the lowest lane of each group adds the group size);
 //   2. thread d turns the per-warp counts of digit d into places inside the tile sorted by digit (tile prefix of the
 //      digit + warps before), and remembers where the tile's run of digit d starts in the output;
-//   3. every warp walks its rounds again: place = its digit's place + keys of that digit in earlier rounds + rank in the
-//      round (per-warp running counts in the same shared array, __syncwarp only); keys and indices go to that place of
+//   3. every warp walks its rounds again (with the groups it found in step 1): place = its digit's place + keys of that
+//      digit in earlier rounds + rank in the round (per-warp running counts in the same shared array, __syncwarp only); keys and indices go to that place of
 //      a shared-memory copy of the tile;
 //   4. the tile leaves in sorted order: neighbouring threads write neighbouring addresses of a digit's run (8 keys per
 //      digit and tile on average), instead of every lane writing a sector of its own.
@@ -270,10 +270,12 @@ __global__ void __launch_bounds__(kBlock) k_radix_scatter(const unsigned long lo
         digit[j] = live ? (unsigned)(key[j] >> shift) & (kRadixBins - 1) : kRadixBins;
     }
     unsigned* cnt = s_count[warp];
+    unsigned peers_of[kRadixItems];  // lanes of the round with the same digit: found once, used by both walks (match.any is slow)
 #pragma unroll
     for (int j = 0; j < kRadixItems; ++j)
     {
         const unsigned peers = __match_any_sync(0xffffffffu, digit[j]);
+        peers_of[j] = peers;
         if (digit[j] < kRadixBins && (peers & ((1u << lane) - 1u)) == 0) cnt[digit[j]] += __popc(peers);
         __syncwarp();
     }
@@ -310,7 +312,7 @@ __global__ void __launch_bounds__(kBlock) k_radix_scatter(const unsigned long lo
 #pragma unroll
     for (int j = 0; j < kRadixItems; ++j)
     {
-        const unsigned peers = __match_any_sync(0xffffffffu, digit[j]);
+        const unsigned peers = peers_of[j];
         const unsigned rank = __popc(peers & ((1u << lane) - 1u));
         unsigned at = 0;
         if (digit[j] < kRadixBins) at = cnt[digit[j]] + rank;
