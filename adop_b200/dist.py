@@ -316,8 +316,20 @@ class PeerGradientExchange:
         """The `out=` dict for PointRasterizer.backward: tensors inside this rank's block (texture stays [T,C])."""
         return self._outputs
 
-    def reduce(self, normalize=True):
+    def release(self):
+        """The barrier that reduce(defer_release=True) left out: call it before this rank writes its block again (before the
+        next backward pass). By then the other ranks finished reading long ago, so it costs no waiting."""
+        if getattr(self, "_pending_release", False):
+            with torch.cuda.device(self.device):
+                dist.all_reduce(self._flag, group=self.group)
+            self._pending_release = False
+
+    def reduce(self, normalize=True, defer_release=False):
+        """defer_release: leave out the barrier behind the kernel ("every rank has read my block"); the caller then calls
+        release() before its next backward pass, typically after the next forward pass, where the barrier finds every rank
+        long done instead of making all of them wait for the slowest reader right away."""
         C, capi = self.C, self.capi
+        self.release()
         res = self._results
         o = capi.AdopPeerReduceOut()
 
@@ -337,12 +349,16 @@ class PeerGradientExchange:
             capi.check(self.lib.adop_peer_reduce_gradients(self.blocks, self.world, self.rank, C.byref(self.layout),
                                                            C.byref(o), C.c_void_p(stream)), "adop_peer_reduce_gradients")
             # ... and nobody overwrites its block (the next backward pass) before every rank has read it
-            dist.all_reduce(self._flag, group=self.group)
+            if defer_release:
+                self._pending_release = True
+            else:
+                dist.all_reduce(self._flag, group=self.group)
         return res
 
     def close(self):
         if self._own is None:
             return
+        self.release()
         self._outputs = self._results = None
         self._mapped.close()
         self._own = None

@@ -331,9 +331,11 @@ def measure_c4(rank, world, dev, steps, exchange, touched=True):
 
     def step():
         ras.forward(scene, views, params, L, out=fwd, touched=touched_flags)
+        if peer is not None:
+            peer.release()  # the barrier deferred by the last reduce: everyone has read this rank's block
         ras.backward(scene, params, fwd, grads, want_env=True, normalize=False, out=bwd)
         if peer is not None:
-            peer.reduce()
+            peer.reduce(defer_release=True)
         else:
             adist.exchange_gradients(bwd)
 
@@ -463,7 +465,7 @@ def main():
 
     def exchange():
         if peer is not None:
-            final.update(peer.reduce())
+            final.update(peer.reduce(defer_release=True))
         elif world > 1:
             ex = adist.exchange_gradients(bwd)
             # normalise the owned shard of the point gradients (sum / count), PointRenderer.cu:1620-1627
@@ -478,6 +480,8 @@ def main():
 
     def step():
         ras.forward(scene, views, params, L, out=fwd, touched=touched_flags)
+        if peer is not None:
+            peer.release()  # the barrier deferred by the last reduce: everyone has read this rank's block
         ras.backward(scene, params, fwd, grads_dev, want_env=True, normalize=normalize_local, out=bwd)
         exchange()
 
@@ -547,6 +551,8 @@ def main():
                 start_copy(slot ^ 1)
             ras.forward(scene, views, params, L, out=fwd, touched=touched_flags)
             main_stream.wait_event(copied[slot])
+            if peer is not None:
+                peer.release()
             ras.backward(scene, params, fwd, staged[slot], want_env=True, normalize=normalize_local, out=bwd)
             consumed[slot].record(main_stream)
             exchange()
@@ -569,9 +575,11 @@ def main():
     capi.profile_enable(True)
     for _ in range(max(1, min(args.steps, 5))):
         ras.forward(scene, views, params, L, out=fwd, touched=touched_flags)
+        if peer is not None:
+            peer.release()
         ras.backward(scene, params, fwd, grads_dev, want_env=True, normalize=normalize_local, out=bwd)
         if peer is not None:
-            peer.reduce()
+            peer.reduce(defer_release=True)
     torch.cuda.synchronize()
     ktimes = capi.profile_collect()
     capi.profile_enable(False)

@@ -51,8 +51,9 @@ def main():
     ex = adist.PeerGradientExchange(lay, dev)
     for step in range(2):  # the second pass re-uses the blocks: covers the barrier after the kernel
         fwd = ras.forward(scene, views, params, L, touched=ex.touched_flags())
+        ex.release()  # the barrier that the first pass deferred
         ras.backward(scene, params, fwd, grads, want_env=True, normalize=False, out=ex.backward_outputs())
-        res = ex.reduce()
+        res = ex.reduce(defer_release=(step == 0))
         torch.cuda.synchronize()
         t_lo, t_hi = res["texel_range"]
         p_lo, p_hi = res["point_range"]
