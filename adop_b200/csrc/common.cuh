@@ -413,21 +413,6 @@ __device__ __forceinline__ bool point_dropped(const KernelParams& kp, int i)
     if (kp.dropout_mask) return kp.dropout_mask[i] == 1;
     return dropout_decision(kp.dropout, kp.dropout_seed, (uint32_t)kp.batch_slot, (uint32_t)i);
 }
-// Lanes whose key equals their lower neighbour's form a run (keys of neighbouring points mostly do). Returns the lane
-// that starts this lane's run and the run's length: the first lane of a run can then speak for all of it (one atomic
-// per run instead of one per lane). Cheaper than __match_any_sync, which was measured to dominate the kernels that
-// used it (MIO-pipe bound); equal keys that are not adjacent simply form separate runs.
-__device__ __forceinline__ void warp_runs(int key, int lane, int* start_lane, int* length)
-{
-    const int prev = __shfl_up_sync(0xffffffffu, key, 1);
-    const unsigned starts = __ballot_sync(0xffffffffu, lane == 0 || key != prev);
-    const unsigned at_or_below = starts & (0xffffffffu >> (31 - lane));
-    const int s = 31 - __clz(at_or_below);
-    const unsigned above = lane == 31 ? 0u : (starts & (0xfffffffeu << lane));
-    const int e = above ? __ffs(above) - 1 : 32;
-    *start_lane = s;
-    *length = e - s;
-}
 // chunk of round k of this block, or -1 when the round has none (the last superblocks can be short)
 __device__ __forceinline__ int scheduled_chunk(const ChunkSchedule& cs, int k)
 {
