@@ -560,6 +560,21 @@ def main():
                 hdst.copy_(final[kk], non_blocking=True)
         main_stream.synchronize()
 
+    # the host limit of the end-to-end figure, measured: all ranks copy their step's pinned gradients to the device at the
+    # same time, nothing else running (GB/s per rank, slowest rank)
+    barrier()
+    hc0, hc1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    hc0.record()
+    for _ in range(3):
+        for s_, hsrc in zip(staged[0], grads_host):
+            s_.copy_(hsrc, non_blocking=True)
+    hc1.record()
+    torch.cuda.synchronize()
+    t_copy = torch.tensor([hc0.elapsed_time(hc1) / 3], device=dev)
+    if world > 1:
+        dist.all_reduce(t_copy, op=dist.ReduceOp.MAX)
+    h2d_gbs_per_rank = sum(g.numel() * 4 for g in grads_host) / (float(t_copy.item()) * 1e-3) / 1e9
+
     run_e2e(3)
     barrier()
     e0.record()
@@ -671,6 +686,7 @@ def main():
                                            f"view-sharded x{world}, gradients reduce-scattered by NCCL"),
                            "point_order": "Morton-sorted once (untimed), as the reference's scene preprocessing does",
                            "host_binding": (f"rank 0 pinned to {len(numa_cores)} cores of its GPU's NUMA node" if numa_cores else "none"),
+                           "h2d_copy_gbs_per_rank": round(h2d_gbs_per_rank, 1),  # all ranks copying at once, nothing else running
                            "e2e": "per step 705 MB host->device (the upstream gradient pyramid, pinned, double-buffered behind the kernels); "
                                   "device->host only the pose, intrinsics and background gradients (836 B): the descriptor and point "
                                   "gradients (320 MB) and the image pyramid stay on the device, where the optimiser and the U-Net use them"},
