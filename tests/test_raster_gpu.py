@@ -161,6 +161,17 @@ def test_other_channel_counts(oracle, cuda_lib, channels, interleave):
     check_backward(ref_b, bwd)
 
 
+@pytest.mark.parametrize("layers,size", [(8, (512, 384)), (5, (200, 120)), (7, (320, 192))])
+def test_deep_pyramids(oracle, cuda_lib, layers, size):
+    """The largest layer count the header allows (8: the coarsest layer of a 512 x 384 view is 4 x 3 pixels) and two counts
+    in between: the backward pass's staged-tile kernel has a variant of its own for more than four layers."""
+    cfg = synth.make_config("c2", n_points=120_000, n_views=2, size=size, layers=layers)
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg, want_env=True)
+    check_forward(ref, fwd, layers)
+    check_backward(ref_b, bwd)
+    assert not bool(fwd.list_unusable().any())
+
+
 def test_odd_sizes_and_ragged_point_count(oracle, cuda_lib):
     # 135 -> 67 -> 33 by integer halving; N not a multiple of 32
     cfg = synth.make_config("c1", n_points=10_007, size=(135, 77), layers=3)
