@@ -85,7 +85,8 @@ adop_status validate_common(const adop_scene* s, const adop_view* views, int B, 
     if (s->num_points > 0x7F000000) return ADOP_ERR_SIZE_LIMIT;  // grid-stride loops index points with 32-bit ints
     if (s->num_points < 0 || s->channels <= 0 || s->channels > ADOP_MAX_CHANNELS) return ADOP_ERR_INVALID_ARGUMENT;
     if (s->num_texels <= 0 || s->num_images <= 0 || s->num_cameras <= 0) return ADOP_ERR_INVALID_ARGUMENT;
-    if (!s->position || !s->texture || !s->background || !s->poses || !s->intrinsics) return ADOP_ERR_INVALID_ARGUMENT;
+    // an empty cloud (no points, no position tensor) is a valid scene: every pixel takes the background
+    if ((!s->position && s->num_points > 0) || !s->texture || !s->background || !s->poses || !s->intrinsics) return ADOP_ERR_INVALID_ARGUMENT;
     if (!s->index && s->num_texels < s->num_points) return ADOP_ERR_INVALID_ARGUMENT;
     if (s->outlier_position)
     {

@@ -393,6 +393,46 @@ def test_no_visible_points(oracle, cuda_lib):
     close(bwd["background"], ref_b["background"], name="background gradient")
 
 
+def test_empty_cloud(oracle, cuda_lib):
+    """No points at all: every pixel takes the background (and the environment map), the descriptor gradient is zero and the
+    background gradient is the sum of the upstream gradient over all pixels."""
+    cfg = synth.make_config("c2", n_points=1000, n_views=2, size=(96, 54))
+    a = cfg["arrays"]
+    a["position"] = np.zeros((0, 4), np.float32)
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg, want_env=True)
+    check_forward(ref, fwd, 4)
+    check_backward(ref_b, bwd)
+    assert float(fwd.weights[0].sum()) == 0 and not bool(bwd["texture"].any())
+
+
+def test_thousands_of_points_on_one_pixel(oracle, cuda_lib):
+    """Collisions: 60 000 points at one position (one pixel per layer holds them all, its tile's bucket of the visible list
+    overflows and the backward pass takes the all-points kernels) among a normal cloud. Depth and the counts stay exact."""
+    cfg = synth.make_config("c1", n_points=100_000, size=(128, 128))
+    a = cfg["arrays"]
+    a["position"][:60_000, :3] = np.array([0.1, -0.05, 3.0], np.float32)
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg)
+    check_forward(ref, fwd, 4)
+    check_backward(ref_b, bwd)
+    assert float(ref["weights"][0].max()) >= 60_000 and bool(fwd.list_unusable().all())
+
+
+def test_points_that_are_not_finite(oracle, cuda_lib):
+    """NaN, infinite and absurdly distant coordinates: such points take part in nothing, on either side, and their
+    neighbours in memory are not disturbed."""
+    cfg = synth.make_config("c2", n_points=80_000, n_views=2, size=(160, 90))
+    a = cfg["arrays"]
+    rng = np.random.default_rng(5)
+    idx = rng.choice(80_000, 900, replace=False)
+    a["position"][idx[:300], 0] = np.nan
+    a["position"][idx[300:600], 1] = np.inf
+    a["position"][idx[600:], 2] = -3e38
+    ref, ref_b, fwd, bwd = run_both(oracle, cfg, want_env=True)
+    check_forward(ref, fwd, 4)
+    check_backward(ref_b, bwd)
+    assert not bool(torch.isnan(bwd["points"]).any()) and not bool(bwd["points"][torch.from_numpy(idx).cuda()].any())
+
+
 def test_unnormalized_then_normalize_matches(oracle, cuda_lib):
     cfg = synth.make_config("c1", n_points=50_000, size=(128, 128))
     ref, ref_b, fwd, bwd = run_both(oracle, cfg, normalize=False)
