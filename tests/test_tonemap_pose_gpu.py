@@ -94,3 +94,53 @@ def test_apply_tangent_to_pose(oracle, cuda_lib):
     assert np.abs(p.cpu().numpy() - p_ref).max() < 1e-12
     with pytest.raises(TypeError):
         apply_tangent_to_pose(t.float(), p)
+
+
+@pytest.mark.parametrize("K", [300, 512, 1024])
+def test_tonemapper_long_response_curves(oracle, cuda_lib, K):
+    """Curves with more than 256 bins: the backward kernel runs with fewer warps per block (every warp keeps two histograms
+    of its own in shared memory), up to the 1024 bins the entry point accepts."""
+    c, go = _case(3, B=2, H=48, W=64, K=K, n=3, with_uv=False)
+    kw = dict(image_size=(64, 48), frame_index=c["frame_index"], exposure=c["exposure"], white_balance=c["white_balance"],
+              vignette=c["vignette"], uv=None, response=c["response"], leak=0.01)
+    ref = oracle.tonemap_forward(c["x"], **kw)
+    ref_g = oracle.tonemap_backward(c["x"], go, **kw)
+    d = {k: (torch.from_numpy(v).cuda() if v is not None else None) for k, v in c.items()}
+    tm = Tonemapper((64, 48), exposure=d["exposure"], white_balance=d["white_balance"], vignette=d["vignette"],
+                    response=d["response"], leak=0.01)
+    _close(tm.forward(d["x"], d["frame_index"]), ref, rtol=1e-5)
+    g = tm.backward(d["x"], torch.from_numpy(go).cuda(), d["frame_index"])
+    for k in ("x", "exposure", "white_balance", "vignette", "response"):
+        _close(g[k], ref_g[k], name="grad " + k)
+
+
+def test_tonemapper_gradient_that_is_not_finite_shows_up(cuda_lib):
+    """The response-curve histogram is summed in scaled fixed point; rounds whose upstream gradient holds an infinity or a NaN
+    take float atomics instead, so the non-finite value reaches the curve's gradient (and only the bins that pixel touches),
+    and huge and tiny finite gradients next to each other keep their sums."""
+    c, go = _case(4, B=1, H=64, W=64, K=256, n=1, with_uv=False)
+    d = {k: (torch.from_numpy(v).cuda() if v is not None else None) for k, v in c.items()}
+    tm = Tonemapper((64, 64), exposure=d["exposure"], white_balance=d["white_balance"], vignette=d["vignette"],
+                    response=d["response"])
+    g0 = torch.from_numpy(go).cuda()
+    clean = tm.backward(d["x"], g0, d["frame_index"])["response"]
+    assert bool(torch.isfinite(clean).all())
+    g1 = g0.clone()
+    g1[0, 1, 10, 7] = float("inf")
+    bad = tm.backward(d["x"], g1, d["frame_index"])["response"]
+    assert not bool(torch.isfinite(bad[1]).all())                      # the green curve got the infinity
+    assert int((~torch.isfinite(bad)).sum()) <= 2                      # in the two bins of that pixel only
+    ok = torch.isfinite(bad)
+    assert torch.allclose(bad[ok], clean[ok], rtol=1e-4, atol=1e-4 * float(clean.abs().max()))
+    # a wide dynamic range inside one image: rows of gradients scaled by 1e+12 and 1e-12
+    g2 = g0.clone()
+    g2[:, :, :8] *= 1e12
+    g2[:, :, 8:16] *= 1e-12
+    wide = tm.backward(d["x"], g2, d["frame_index"])["response"]
+    assert bool(torch.isfinite(wide).all())
+    gl, gh = g0.clone(), g0.clone()
+    gl[:, :, :16] = 0
+    gh[:, :, 16:] = 0
+    gh[:, :, 8:16] = 0
+    part = tm.backward(d["x"], gl, d["frame_index"])["response"] + 1e12 * tm.backward(d["x"], gh, d["frame_index"])["response"]
+    assert torch.allclose(wide, part, rtol=2e-4, atol=2e-4 * float(part.abs().max()))
