@@ -128,11 +128,13 @@ typedef struct adop_forward_io
     const uint8_t* dropout_mask; /* optional [B,N]: 1 = dropped; NULL = hash of dropout_seed */
     void* workspace;
     size_t workspace_bytes;
-    /* optional, [B, adop_raster_visible_list_ints(N, w, h, layers)] i32: the forward pass records which (point, layer) splats of
-     * each view the backward pass has to visit, so that it runs over those instead of over the whole cloud. It takes
-     * the place of the [B,N] drop-out tensor the reference saves for backward (PointRenderer.cu:1524). If a view has
-     * more such splats than the list holds (about one per point of the cloud), the list marks itself unusable and
-     * the backward pass walks all points. NULL = not recorded. */
+    /* optional, [B, adop_raster_visible_list_ints(N, w, h, layers)] i32: per view, the forward pass lists the points that were
+     * accepted on at least one layer, grouped by 32 x 16 screen tile (one bucket of max(2048, 2N / tiles) entries of 16 bytes
+     * per tile), so that the backward pass runs per tile over those points, with the tile's pixels in shared memory, instead
+     * of over the whole cloud. It takes the place of the [B,N] drop-out tensor the reference saves for backward
+     * (PointRenderer.cu:1524). A view with more visible points in one tile than its bucket holds marks its list unusable and
+     * the backward pass of that view walks all points (decided on the device). The backward pass overwrites the entries:
+     * a list serves one backward call, a second one walks all points. NULL = not recorded. */
     int32_t* visible_list;
     /* optional, per layer [B,1,h_l,w_l] u64 (all of the first num_layers entries or none): for every pixel the minimum
      * over the points landing there of (bits of the depth << 32 | point index), the packed depth|index word of
