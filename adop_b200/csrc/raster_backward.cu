@@ -353,7 +353,7 @@ __device__ __forceinline__ void geo_block_reduce(GeoShared<MODEL>* s, const GeoA
 }
 
 // K5 (all points): the reference's structure, one thread per point walking its layers (RenderBackward, :396-724). Used
-// when the forward pass recorded no splat list (or the list overflowed).
+// when the forward pass recorded no visible list (or a tile's bucket overflowed, or the list was used before).
 template <int C, int MODEL>
 __global__ void __launch_bounds__(kBlock) k_splat_backward_all(PointStreams pts, const ViewCam* __restrict__ camp, KernelParams kp, LayerTable lt,
                                                                 BackwardTargets bt, int* __restrict__ list_header, int mark_consumed)
@@ -1289,7 +1289,7 @@ extern "C" adop_status adop_raster_backward(const adop_scene* s, const adop_view
         bt.count_intrinsics = io->grad_intrinsics ? io->count_intrinsics + views[b].camera_index : nullptr;
         bt.records = reinterpret_cast<const float*>(static_cast<const char*>(io->workspace) + kCamRegionBytes);
         float* ge = env ? (env_inter ? io->grad_env_map_interleaved : io->grad_env_map) : nullptr;
-        // the list's geometry (segments in use, entries per segment) sits in its header, written by the forward pass
+        // the list's layout (tiles, bucket size) follows from the view size and the point count, as in the forward pass
         VisibleList vl = make_visible_list(const_cast<int32_t*>(io->visible_list), N, views[0].w, views[0].h, b);
         adop_status r;
         switch (C)
