@@ -185,7 +185,7 @@ typedef struct adop_backward_io
      * the forward pass wrote untouched: a list can serve several backward calls.
      * NULL = the backward pass walks all points again, as the reference does. */
     int32_t* visible_list;
-    /* optional [T,C] scratch: descriptor gradients are then summed there with one vector atomic per splat and moved
+    /* optional [T,C] scratch: descriptor gradients are then summed there with one vector atomic per visible point and moved
      * into grad_texture [C,T] at the end of the call. Contents on entry are ignored.
      * With grad_texture == NULL the descriptor gradients STAY here, in [T,C] layout (zeroed first unless accumulate):
      * the form adop_peer_reduce_gradients reads from every GPU. */
