@@ -23,6 +23,83 @@ def close(a, b, what, rtol=1e-4, atol=1e-5):
         raise AssertionError(f"{what}: max abs diff {float((a - b).abs().max())} at scale {scale}")
 
 
+def train_steps(ras, scene, cfg, views, mine, ex, dev, rank, world):
+    """Four training steps of the whole scene through train.ViewShardedSceneOptimizer (descriptors and points sharded over
+    the ranks, the small tensors stepped on every rank), fitting the pyramid to that of a scene with other descriptors,
+    against the same steps in one process over all views with torch's optimisers on every tensor."""
+    from adop_b200.train import SceneLearningRates, ViewShardedSceneOptimizer
+    from adop_b200.raster import apply_tangent_to_pose
+    params, L = cfg["params"], cfg["num_layers"]
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(11)
+    target_scene = Scene(**dict(scene.tensors(), texture=scene.texture + 0.3 * torch.randn(scene.texture.shape, device=dev, generator=gen)))
+    targets = [c.clone() for c in ras.forward(target_scene, cfg["views"], params, L).colors]
+    rates = SceneLearningRates(lr_texture=0.02, lr_background_color=0.004, lr_environment_map=0.02, lr_points=1e-4,
+                               lr_poses=1e-5, lr_intrinsics=1e-4, lock_structure_params_epochs=0)
+    C_, T = scene.texture.shape
+    n_img = scene.poses.shape[0]
+
+    def copies():
+        t = {k: (v.clone() if v is not None else None) for k, v in scene.tensors().items()}
+        return t, torch.zeros((n_img, 6), dtype=torch.float64, device=dev)
+
+    # the sharded job
+    t_a, tan_a = copies()
+    pp = adist.PeerParameters(adist.peer_param_layout(C_, T, scene.position.shape[0]), dev)
+    pp.texture.copy_(scene.texture)
+    pp.points.copy_(scene.position)
+    t_a["texture"], t_a["position"] = pp.texture, pp.points
+    live = Scene(**t_a)
+    opt = ViewShardedSceneOptimizer(pp, live.background, live.env_map, tan_a, live.poses, live.intrinsics, rates)
+    # one process, all views, torch's optimisers
+    t_b, tan_b = copies()
+    ref = Scene(**t_b)
+    xyz = ref.position[:, :3].clone().requires_grad_(True)
+    for p in (ref.texture, ref.background, ref.env_map, tan_b, ref.intrinsics):
+        p.requires_grad_(True)
+    adam = torch.optim.Adam([{"params": [ref.texture], "lr": rates.lr_texture}, {"params": [ref.background], "lr": rates.lr_background_color},
+                             {"params": [ref.env_map], "lr": rates.lr_environment_map}], lr=1.0)
+    sgd = torch.optim.SGD([{"params": [xyz], "lr": rates.lr_points}, {"params": [tan_b], "lr": rates.lr_poses},
+                           {"params": [ref.intrinsics], "lr": rates.lr_intrinsics}], lr=1e-10)
+    losses = []
+    for step in range(4):
+        fwd = ras.forward(live, views, params, L, touched=ex.touched_flags())
+        g = [(c - t[mine[0]:mine[-1] + 1]).contiguous() for c, t in zip(fwd.colors, targets)]
+        loss = torch.stack([0.5 * (x * x).sum() for x in g]).sum()
+        dist.all_reduce(loss)
+        losses.append(float(loss))
+        ex.release()
+        ras.backward(live, params, fwd, g, want_env=True, normalize=False, out=ex.backward_outputs())
+        opt.step(ex.reduce(), epoch_id=1)
+        with torch.no_grad():
+            ref.position[:, :3] = xyz
+            f_all = ras.forward(ref, cfg["views"], params, L)
+            g_all = [(c - t).contiguous() for c, t in zip(f_all.colors, targets)]
+            b_all = ras.backward(ref, params, f_all, g_all, want_env=True, normalize=True)
+        ref.texture.grad, ref.background.grad, ref.env_map.grad = b_all["texture"], b_all["background"], b_all["env_map"]
+        xyz.grad, tan_b.grad, ref.intrinsics.grad = b_all["points"][:, :3].contiguous(), b_all["pose"], b_all["intrinsics"]
+        adam.step()
+        sgd.step()
+        with torch.no_grad():
+            apply_tangent_to_pose(tan_b.detach(), ref.poses)
+        torch.cuda.synchronize()
+        close(pp.texture, ref.texture.detach(), f"descriptors after training step {step}", rtol=1e-3, atol=1e-4)
+        close(pp.points[:, :3], xyz.detach(), f"points after training step {step}", rtol=1e-5, atol=1e-6)
+        close(live.background.detach(), ref.background.detach(), "background colour", rtol=1e-3, atol=1e-4)
+        close(live.env_map.detach(), ref.env_map.detach(), "environment map", rtol=1e-3, atol=1e-4)
+        close(live.poses, ref.poses, "poses", rtol=1e-9, atol=1e-9)
+        close(live.intrinsics.detach(), ref.intrinsics.detach(), "intrinsics", rtol=1e-4, atol=1e-5)
+    assert losses[-1] < 0.8 * losses[0], losses
+    same = pp.texture.clone()
+    dist.broadcast(same, src=0)
+    assert torch.equal(same, pp.texture), "descriptor replicas differ between ranks after training"
+    small = torch.cat([live.background.detach().double().flatten(), live.poses.flatten(), live.intrinsics.detach().double().flatten()])
+    other = small.clone()
+    dist.broadcast(other, src=0)
+    assert torch.equal(other, small), "small-tensor replicas differ between ranks after training"
+    pp.close()
+
+
 def main():
     out_dir = sys.argv[1]
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -115,6 +192,7 @@ def main():
     dist.broadcast(gathered, src=0)
     assert torch.equal(gathered, pp.texture), "parameter replicas differ between ranks"
     pp.close()
+    train_steps(ras, scene, cfg, views, mine, ex, dev, rank, world)
     ex.close()
     dist.barrier()
     with open(os.path.join(out_dir, f"ok_{rank}"), "w") as f:

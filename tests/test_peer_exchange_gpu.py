@@ -308,3 +308,16 @@ def test_two_gpu_exchange_matches_single_gpu_and_nccl(cuda_lib, tmp_path):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert (tmp_path / "ok_0").exists() and (tmp_path / "ok_1").exists(), r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_one_rank_runs_the_whole_sharded_step(cuda_lib, tmp_path):
+    """The worker of the two-GPU test with a single rank on one GPU: gradient blocks, touched flags, reduce kernel, optimiser
+    kernel and the scene optimiser's training steps all run (a world of one shards nothing, but every code path between the
+    backward pass and the next forward pass is the one the multi-GPU job takes), against the plain single-GPU results."""
+    port = 29700 + (os.getpid() % 1000)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "1", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(ROOT, "tests", "peer_exchange_worker.py"), str(tmp_path)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert (tmp_path / "ok_0").exists(), r.stdout[-3000:] + r.stderr[-3000:]
