@@ -189,3 +189,42 @@ def test_knn_gives_up_on_a_cloud_of_coincident_points(cuda_lib):
     ok = rng.uniform(-1, 1, (5000, 4)).astype(np.float32)
     d = preprocess.knn_distance(torch.from_numpy(ok).cuda(), k=4)
     assert bool(torch.isfinite(d).all())
+
+
+def test_scene_directory_preprocessed_and_rendered(cuda_lib, tmp_path):
+    """A scene written in ADOP's directory layout, read back (scene_io), preprocessed on the GPU as the reference does once per
+    scene (Morton reorder, drop-out radius from the 4 nearest neighbours: SceneData.cpp:100-103) and rendered: the images
+    agree with those of the arrays the directory was written from (the poses went through text and two inversions, so
+    depth agrees to rounding, not bit for bit)."""
+    from adop_b200 import scene_io
+    from adop_b200.raster import PointRasterizer, Scene
+    dev = torch.device("cuda:0")
+    cfg = synth.make_config("c2", n_points=60_000, n_views=3, size=(160, 90), sort=False)
+    a = cfg["arrays"]
+    q_cw, t_cw = scene_io.invert_poses(a["poses"][:, :4], a["poses"][:, 4:7])
+    cams = [dict(w=160, h=90, K=a["intrinsics"][0, :5], distortion=a["intrinsics"][0, 5:13])]
+    scene_io.save_scene_directory(str(tmp_path), a["position"][:, :3], np.concatenate([q_cw, t_cw], axis=1), cams)
+    sc = scene_io.load_scene_directory(str(tmp_path))
+    pos = torch.from_numpy(sc["arrays"]["position"]).to(dev)
+    order = preprocess.morton_order(pos)
+    pos = preprocess.permute_rows(pos, order)
+    dist = preprocess.knn_distance(pos, k=4)
+    assert bool(torch.isfinite(dist).all()) and float(dist.min()) > 0
+    pos[:, 3] = dist
+    tex = torch.from_numpy(a["texture"]).to(dev)
+    tex_sorted = tex[:, order.long()].contiguous()      # descriptor i belongs to point i of the file's order
+    common = dict(background=torch.from_numpy(a["background"]).to(dev), env_map=torch.from_numpy(a["env_map"]).to(dev))
+    loaded = Scene(position=pos, texture=tex_sorted, poses=torch.from_numpy(sc["arrays"]["poses"]).to(dev),
+                   intrinsics=torch.from_numpy(sc["arrays"]["intrinsics"]).to(dev), **common)
+    source = Scene(position=torch.from_numpy(a["position"]).to(dev), texture=tex, poses=torch.from_numpy(a["poses"]).to(dev),
+                   intrinsics=torch.from_numpy(a["intrinsics"]).to(dev), **common)
+    ras = PointRasterizer(dev)
+    f1 = ras.forward(loaded, sc["views"], cfg["params"], 4)
+    f2 = PointRasterizer(dev).forward(source, cfg["views"], cfg["params"], 4)
+    torch.cuda.synchronize()
+    for l in range(4):
+        same_depth = torch.isclose(f1.depths[l], f2.depths[l], rtol=1e-5, atol=1e-5)
+        assert float(same_depth.float().mean()) > 0.999
+        assert float((f1.weights[l] == f2.weights[l]).float().mean()) > 0.995
+        ok = same_depth.expand_as(f1.colors[l]) & (f1.weights[l] == f2.weights[l]).expand_as(f1.colors[l])
+        assert torch.allclose(f1.colors[l][ok], f2.colors[l][ok], rtol=1e-3, atol=1e-4)
