@@ -535,8 +535,11 @@ __global__ void __launch_bounds__(kBlock) k_resolve(LayerTable lt, const ViewCam
             }
             else
             {
+                // one division per pixel instead of one per channel: sum * (1 / count) is within an ulp of sum / count, far
+                // inside what the order of the atomic sums already leaves open; a single splat (count 1) stays exact
+                const float inv = 1.0f / cou;
 #pragma unroll
-                for (int c = 0; c < C; ++c) color[c * plane] = v[c] / cou;
+                for (int c = 0; c < C; ++c) color[c * plane] = v[c] * inv;
                 // leave the record clean for the next view
 #pragma unroll
                 for (int k = 0; k < RS / 4; ++k) rec[k] = make_float4(0.f, 0.f, 0.f, 0.f);
