@@ -552,7 +552,7 @@ __device__ __forceinline__ void visit_layer(PIX at, bool drop_out, bool want_dg,
         if (wgt == 0.f) return;  // :473
         if (want_dg)
         {
-            const float iw = 1.f / wgt;
+            const float iw = reciprocal(wgt);
 #pragma unroll
             for (int c = 0; c < C; ++c) dg[c] += iw * at(1 + C + c, 0, 0);
             *have_dg = true;
@@ -870,13 +870,13 @@ __device__ __forceinline__ void chain_pinhole_fast(const ViewCam& cam, bool chec
         V3 vn = rotate(V, unpack_normal_10bit(it.normal));
         if (fmaf(view.z, vn.z, fmaf(view.y, vn.y, view.x * vn.x)) > 0.f) return;
     }
-    const float iz = 1.0f / view.z;
+    const float iz = reciprocal(view.z);
     const float x = view.x * iz, y = view.y * iz;
     const float x2 = x * x, y2 = y * y, r2 = x2 + y2, r4 = r2 * r2, r6 = r4 * r2, xy2 = 2.f * x * y;
     const Dist8& d = cam.dist;
     const float num = fmaf(fmaf(fmaf(d.k3, r2, d.k2), r2, d.k1), r2, 1.0f);
     const float den = fmaf(fmaf(fmaf(d.k6, r2, d.k5), r2, d.k4), r2, 1.0f);
-    const float iden = 1.0f / den;
+    const float iden = reciprocal(den);
     const float rad = num * iden;
     const float dnum = fmaf(fmaf(3.f * d.k3, r2, 2.f * d.k2), r2, d.k1);
     const float dden = fmaf(fmaf(3.f * d.k6, r2, 2.f * d.k5), r2, d.k4);

@@ -537,7 +537,7 @@ __global__ void __launch_bounds__(kBlock) k_resolve(LayerTable lt, const ViewCam
             {
                 // one division per pixel instead of one per channel: sum * (1 / count) is within an ulp of sum / count, far
                 // inside what the order of the atomic sums already leaves open; a single splat (count 1) stays exact
-                const float inv = 1.0f / cou;
+                const float inv = reciprocal(cou);
 #pragma unroll
                 for (int c = 0; c < C; ++c) color[c * plane] = v[c] * inv;
                 // leave the record clean for the next view
