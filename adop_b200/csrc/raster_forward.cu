@@ -486,7 +486,7 @@ __device__ __forceinline__ void resolve_environment_pixel(const LayerTable& lt, 
 }
 
 template <int C>
-__global__ void __launch_bounds__(kBlock) k_resolve(LayerTable lt, const ViewCam* __restrict__ camp, KernelParams kp, float* __restrict__ accum,
+__global__ void __launch_bounds__(kBlock, 6) k_resolve(LayerTable lt, const ViewCam* __restrict__ camp, KernelParams kp, float* __restrict__ accum,
                                                      const float* __restrict__ background, const float* __restrict__ env,
                                                      int env_h, int env_w)
 {
