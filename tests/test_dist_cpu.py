@@ -152,3 +152,28 @@ def test_peer_layout_and_shard_ranges():
     bad = capi.AdopPeerLayout()
     bad.channels = 0
     assert lib.adop_peer_layout_fill(C.byref(bad)) != capi.ADOP_OK
+
+
+def test_touched_and_parameter_layouts():
+    """Host-side layouts of the flags inside a gradient block and of a parameter block (no GPU needed)."""
+    import ctypes as C
+    from adop_b200 import capi
+    lib = capi.load_library()
+    plain = adist.peer_layout(4, 100_000, 70_001, num_images=3, num_cameras=1, intrinsics_cols=13, env_hw=(4, 8))
+    flagged = adist.peer_layout(4, 100_000, 70_001, num_images=3, num_cameras=1, intrinsics_cols=13, env_hw=(4, 8), touched=True)
+    # the gradient tensors sit where they sit without flags; the flags and the gather scratch follow them
+    for name in ("off_texture", "off_points", "off_pose", "off_count_pose", "off_intrinsics", "off_count_intrinsics", "off_background", "off_env_map"):
+        assert getattr(plain, name) == getattr(flagged, name)
+    t_chunks, p_chunks = (100_000 + 255) // 256, (70_001 + 255) // 256
+    assert plain.off_touched_texels == plain.off_touched_points == plain.off_gathered
+    assert flagged.off_touched_texels >= flagged.off_env_map + 4 * 4 * 8 * 4
+    assert flagged.off_touched_points - flagged.off_touched_texels >= t_chunks
+    assert flagged.off_gathered - flagged.off_touched_points >= p_chunks
+    assert flagged.total_bytes - flagged.off_gathered >= t_chunks + p_chunks and flagged.total_bytes > plain.total_bytes
+    assert all(getattr(flagged, n) % 256 == 0 for n in ("off_touched_texels", "off_touched_points", "off_gathered", "total_bytes"))
+    pl = adist.peer_param_layout(8, 1001, 77)
+    assert pl.off_texture == 0 and pl.off_points >= 8 * 1001 * 4 and pl.off_points % 256 == 0
+    assert pl.total_bytes >= pl.off_points + 77 * 16 and pl.total_bytes % 256 == 0
+    bad = capi.AdopPeerParamLayout()
+    bad.channels, bad.num_texels = 4, 0
+    assert lib.adop_peer_param_layout_fill(C.byref(bad)) != capi.ADOP_OK
